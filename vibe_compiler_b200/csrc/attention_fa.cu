@@ -1,0 +1,492 @@
+// Flash-attention prefill for sm_100a on tcgen05 tensor cores (bf16 / f16 storage, head_dim 128).
+//
+// Arithmetic is the reference's online-attention update per KV tile
+// (lib/Wafer/Transforms/Linalg/OnlineAttentionDecomposition.cpp:568-594):
+//   S = Q K^T (f32), s = S*scale (+mask), m' = max(m, rowmax s), m_e = (m' == -inf ? 0 : m'),
+//   alpha = exp(m - m_e), l' = l*alpha + sum exp(s - m_e), acc' = acc*alpha + round(P) V,
+// with P rounded to the storage type at the PV input, and finalize out = acc * (1/l)
+// (lib/Wafer/Transforms/Linalg/OnlineAttentionMaterialization.cpp:196-262). The KV axis is never
+// split across workers. Scores are kept in the log2 domain (scale*log2e folded into one f32
+// constant) so exp is one ex2 per element.
+//
+// One CTA owns 256 query rows of one (batch, head): two 128-row Q tiles, each with its own S and O
+// accumulators in TMEM (S0 S1 O0 O1 = 4 x 128 columns) and its own softmax warpgroup, so the tensor
+// pipe works on one tile while the other tile's softmax runs. Warp 0 = TMA producer (Q once, then
+// K0 V0 K1 V1 ... through a ring of 32 KiB slots), warp 1 = MMA issuer and TMEM owner, warps 2-5 /
+// 6-9 = softmax + rescale + epilogue for Q tile 0 / 1 (thread = query row, so row max and row sum
+// need no shuffles). kPInTmem selects where the rounded P lives: in TMEM, aliasing the first 64
+// columns of S (A operand read from TMEM, 5 ring slots), or in shared memory (3 ring slots).
+// Roofline: tensor pipe; algorithmic work is 4 * head_dim flop per visible (query, key) pair.
+#include "kernels.h"
+#include "ptx_sm100.cuh"
+
+namespace wb200 {
+namespace {
+
+constexpr int kHd = 128;          // head dimension
+constexpr int kTileM = 128;       // query rows per Q tile (TMEM lanes)
+constexpr int kTileN = 128;       // keys per KV tile
+constexpr int kTileBytesFa = kTileN * kHd * 2;  // 32 KiB: two 64-element column blocks of 128 rows
+constexpr int kBlockBytes = 128 * 128;          // one [128 rows][128 B] swizzled block
+constexpr int kFaThreads = 320;
+constexpr uint32_t kColS0 = 0, kColO0 = 256;    // S_t at t*128, O_t at 256 + t*128
+
+template <bool kPInTmem>
+struct FaSmem {
+  static constexpr int kSlots = kPInTmem ? 5 : 3;
+  static constexpr int kQOff = 0;
+  static constexpr int kRingOff = 2 * kTileBytesFa;
+  static constexpr int kPOff = kRingOff + kSlots * kTileBytesFa;
+  static constexpr int kBarOff = kPOff + (kPInTmem ? 0 : 2 * kTileBytesFa);
+  static constexpr size_t kBytes = kBarOff + 256 + 1024;
+};
+
+struct FaParams {
+  int batch, q_heads, kv_heads, group;
+  int q_len, kv_len;
+  int kv_visible;          // keys >= kv_visible are masked
+  int causal;
+  long long causal_offset; // key j visible to query row q iff j <= causal_offset + q
+  int zero_fully_masked;
+  int out_format;
+  int bf16;
+  int num_pairs;           // ceil(q_len / 256)
+  float scale_log2;        // scale * log2(e)
+  void *out;
+  float *lse, *row_max, *row_sum;
+  int *status;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "setp.ne.b32 P, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, P;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+
+// Number of KV tiles a Q tile starting at query row `row0` has to visit.
+__device__ __forceinline__ int kv_tiles_for(const FaParams &p, int row0) {
+  long long last = static_cast<long long>(p.kv_visible) - 1;
+  if (p.causal) {
+    const long long causal_last = p.causal_offset + row0 + (kTileM - 1);
+    if (causal_last < last) last = causal_last;
+  }
+  if (row0 >= p.q_len || last < 0) return 0;
+  return static_cast<int>(last / kTileN) + 1;
+}
+
+template <bool kPInTmem, bool kBf16>
+__global__ void __launch_bounds__(kFaThreads, 1)
+fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+               const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
+  using L = FaSmem<kPInTmem>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t *smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  const uint32_t smem_base = smem_u32(smem);
+
+  const uint32_t bar_base = smem_base + L::kBarOff;
+  auto kv_full = [&](int s) { return bar_base + 8u * s; };
+  auto kv_empty = [&](int s) { return bar_base + 8u * (L::kSlots + s); };
+  const uint32_t q_full = bar_base + 8u * (2 * L::kSlots);
+  auto s_full = [&](int t) { return bar_base + 8u * (2 * L::kSlots + 1 + t); };
+  auto p_full = [&](int t) { return bar_base + 8u * (2 * L::kSlots + 3 + t); };
+  auto o_done = [&](int t) { return bar_base + 8u * (2 * L::kSlots + 5 + t); };
+  uint8_t *bar_ptr = smem + L::kBarOff;
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bar_ptr + 8 * (2 * L::kSlots + 7));
+  volatile int *abort_word = reinterpret_cast<volatile int *>(bar_ptr + 8 * (2 * L::kSlots + 8));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh_count = p.batch * p.q_heads;
+  const int pair = p.num_pairs - 1 - static_cast<int>(blockIdx.x) / bh_count;  // heaviest pairs first
+  const int bh = static_cast<int>(blockIdx.x) % bh_count;
+  const int b = bh / p.q_heads, h = bh % p.q_heads;
+  const int bh_kv = b * p.kv_heads + h / p.group;
+  const int row_base = pair * 2 * kTileM;
+  const int n_tiles[2] = {kv_tiles_for(p, row_base), kv_tiles_for(p, row_base + kTileM)};
+  const int n_max = n_tiles[0] > n_tiles[1] ? n_tiles[0] : n_tiles[1];
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < L::kSlots; ++s) {
+      mbar_init(kv_full(s), 1);
+      mbar_init(kv_empty(s), 1);
+    }
+    mbar_init(q_full, 1);
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(s_full(t), 1);
+      mbar_init(p_full(t), kTileM);
+      mbar_init(o_done(t), 1);
+    }
+    *abort_word = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0 && n_max > 0) {
+      mbar_arrive_expect_tx(q_full, 2 * kTileBytesFa);
+      for (int t = 0; t < 2; ++t)
+        for (int c = 0; c < 2; ++c)
+          tma_load_3d(smem_base + L::kQOff + t * kTileBytesFa + c * kBlockBytes, &tmap_q, q_full, c * 64,
+                      row_base + t * kTileM, bh);
+      int slot = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int i = 0; ok && i < 2 * n_max; ++i) {  // ring position 2j = K_j, 2j+1 = V_j
+        if (!mbar_wait(kv_empty(slot), phase ^ 1u, abort_word)) { ok = false; break; }
+        mbar_arrive_expect_tx(kv_full(slot), kTileBytesFa);
+        const CUtensorMap *map = (i & 1) ? &tmap_v : &tmap_k;
+        const uint32_t dst = smem_base + L::kRingOff + slot * kTileBytesFa;
+        tma_load_3d(dst, map, kv_full(slot), 0, (i >> 1) * kTileN, bh_kv);
+        tma_load_3d(dst + kBlockBytes, map, kv_full(slot), 64, (i >> 1) * kTileN, bh_kv);
+        if (++slot == L::kSlots) { slot = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0 && n_max > 0) {
+      const uint32_t idesc_s = umma_idesc_f16(kTileM, kTileN, kBf16, false, false);
+      const uint32_t idesc_o = umma_idesc_f16(kTileM, kHd, kBf16, false, true);
+      int slot = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      auto advance = [&]() { if (++slot == L::kSlots) { slot = 0; phase ^= 1u; } };
+      auto issue_s = [&](int t, uint32_t k_addr) {
+        const uint32_t q_addr = smem_base + L::kQOff + t * kTileBytesFa;
+#pragma unroll
+        for (int ks = 0; ks < kHd / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * kBlockBytes + (ks & 3) * 32;
+          umma_f16_ss(tmem_base + kColS0 + t * 128, umma_desc_kmajor(q_addr + off),
+                      umma_desc_kmajor(k_addr + off), idesc_s, ks != 0 ? 1u : 0u);
+        }
+        umma_commit(s_full(t));
+      };
+      auto issue_pv = [&](int t, uint32_t v_addr, bool accumulate) {
+#pragma unroll
+        for (int ks = 0; ks < kTileN / 16; ++ks) {
+          const uint64_t bdesc = umma_desc_mnmajor(v_addr + ks * 2048, kBlockBytes);
+          const uint32_t acc = (accumulate || ks != 0) ? 1u : 0u;
+          if constexpr (kPInTmem) {
+            umma_f16_ts(tmem_base + kColO0 + t * 128, tmem_base + kColS0 + t * 128 + ks * 8, bdesc, idesc_o, acc);
+          } else {
+            const uint32_t p_addr = smem_base + L::kPOff + t * kTileBytesFa + (ks >> 2) * kBlockBytes + (ks & 3) * 32;
+            umma_f16_ss(tmem_base + kColO0 + t * 128, umma_desc_kmajor(p_addr), bdesc, idesc_o, acc);
+          }
+        }
+        umma_commit(o_done(t));
+      };
+
+      ok = mbar_wait(q_full, 0, abort_word);
+      // K_0: first scores of both tiles.
+      if (ok) ok = mbar_wait(kv_full(slot), phase, abort_word);
+      if (ok) {
+        tc_fence_after();
+        const uint32_t k_addr = smem_base + L::kRingOff + slot * kTileBytesFa;
+        for (int t = 0; t < 2; ++t)
+          if (n_tiles[t] > 0) issue_s(t, k_addr);
+        umma_commit(kv_empty(slot));
+        advance();
+      }
+      for (int j = 0; ok && j < n_max; ++j) {
+        // ring now points at V_j; K_{j+1} follows it.
+        const int v_slot = slot;
+        const uint32_t v_phase = phase;
+        advance();
+        const int k_slot = slot;
+        const uint32_t k_phase = phase;
+        const bool has_next = j + 1 < n_max;
+        if (has_next) advance();
+        if (!mbar_wait(kv_full(v_slot), v_phase, abort_word)) { ok = false; break; }
+        const uint32_t v_addr = smem_base + L::kRingOff + v_slot * kTileBytesFa;
+        const uint32_t k_addr = smem_base + L::kRingOff + k_slot * kTileBytesFa;
+        bool k_ready = false;
+        for (int t = 0; ok && t < 2; ++t) {
+          if (j < n_tiles[t]) {
+            if (!mbar_wait(p_full(t), j & 1, abort_word)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv(t, v_addr, j > 0);
+          }
+          if (j + 1 < n_tiles[t]) {
+            if (!k_ready) {
+              if (!mbar_wait(kv_full(k_slot), k_phase, abort_word)) { ok = false; break; }
+              tc_fence_after();
+              k_ready = true;
+            }
+            issue_s(t, k_addr);
+          }
+        }
+        if (!ok) break;
+        umma_commit(kv_empty(v_slot));
+        if (has_next) umma_commit(kv_empty(k_slot));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ softmax / rescale / epilogue
+    const int t = (warp - 2) >> 2;          // Q tile of this warpgroup
+    const int quarter = warp & 3;           // TMEM lane quarter this warp may access
+    const int row_in_tile = quarter * 32 + lane;
+    const int row = row_base + t * kTileM + row_in_tile;   // query row inside the head
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_sel + kColS0 + t * 128;
+    const uint32_t o_addr = tmem_base + lane_sel + kColO0 + t * 128;
+    const int my_tiles = n_tiles[t];
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    const long long causal_limit = p.causal ? p.causal_offset + row : 0x7fffffffffffLL;
+
+    for (int j = 0; ok && j < my_tiles; ++j) {
+      if (!mbar_wait(s_full(t), j & 1, abort_word)) { ok = false; break; }
+      tc_fence_after();
+      const int key0 = j * kTileN;
+      // Masking is needed only when the tile sticks out of the visible region of some row.
+      const bool need_mask = (key0 + kTileN > p.kv_visible) ||
+                             (p.causal && key0 + kTileN - 1 > p.causal_offset + row_base + t * kTileM);
+      float tile_max = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_addr + c * 32, r);
+        tmem_wait_ld();
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int key = key0 + c * 32 + i;
+            const float s = __uint_as_float(r[i]) * p.scale_log2;
+            const bool visible = key < p.kv_visible && key <= causal_limit;
+            tile_max = fmaxf(tile_max, visible ? s : -INFINITY);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, __uint_as_float(r[i]) * p.scale_log2);
+        }
+      }
+      const float m_new = fmaxf(m_run, tile_max);
+      const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = exp2f(m_run - m_exp);
+      float row_sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_addr + c * 32, r);
+        tmem_wait_ld();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float e0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_exp));
+          float e1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_exp));
+          if (need_mask) {
+            const int key = key0 + c * 32 + i;
+            if (!(key < p.kv_visible && key <= causal_limit)) e0 = 0.f;
+            if (!(key + 1 < p.kv_visible && key + 1 <= causal_limit)) e1 = 0.f;
+          }
+          row_sum += e0 + e1;
+          if constexpr (kBf16) {
+            __nv_bfloat162 v = __floats2bfloat162_rn(e0, e1);
+            packed[i >> 1] = *reinterpret_cast<uint32_t *>(&v);
+          } else {
+            __half2 v = __floats2half2_rn(e0, e1);
+            packed[i >> 1] = *reinterpret_cast<uint32_t *>(&v);
+          }
+        }
+        if constexpr (kPInTmem) {
+          tmem_st_32x16(s_addr + c * 16, packed);   // P aliases the first 64 columns of S
+        } else {
+          uint8_t *p_row = smem + L::kPOff + t * kTileBytesFa + (c >> 1) * kBlockBytes + row_in_tile * 128;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int chunk = ((c & 1) * 4 + i) ^ (row_in_tile & 7);
+            *reinterpret_cast<uint4 *>(p_row + chunk * 16) =
+                make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+          }
+        }
+      }
+      l_run = l_run * alpha + row_sum;
+      m_run = m_new;
+      // acc' = acc * alpha: needs PV of the previous tile to have landed in TMEM.
+      if (j > 0) {
+        if (!mbar_wait(o_done(t), (j - 1) & 1, abort_word)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(o_addr + c * 32, r);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(o_addr + c * 32, r);
+          }
+        }
+      }
+      tmem_wait_st();
+      if constexpr (!kPInTmem) fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_full(t));
+    }
+
+    // Finalize: out = acc * (1 / l), rounded once to the storage type.
+    if (ok && my_tiles > 0) ok = mbar_wait(o_done(t), (my_tiles - 1) & 1, abort_word);
+    if (ok && row_base + t * kTileM < p.q_len) {
+      tc_fence_after();
+      float coefficient = 1.0f / l_run;
+      if (p.zero_fully_masked && l_run == 0.f) coefficient = 0.f;
+      const size_t out_row = (static_cast<size_t>(bh) * p.q_len + row) * kHd;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        if (my_tiles > 0) {
+          tmem_ld_32x32(o_addr + c * 32, r);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        if (row < p.q_len) {
+          uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + out_row + c * 32;
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t lo = narrow_bits(__uint_as_float(r[i + 2 * k]) * coefficient, p.out_format);
+              const uint32_t hi = narrow_bits(__uint_as_float(r[i + 2 * k + 1]) * coefficient, p.out_format);
+              w[k] = lo | (hi << 16);
+            }
+            *reinterpret_cast<uint4 *>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+      if (row < p.q_len) {
+        const size_t stat = static_cast<size_t>(bh) * p.q_len + row;
+        const float m_nat = m_run * 0.69314718055994530942f;  // back from the log2 domain
+        if (p.lse) p.lse[stat] = (l_run == 0.f) ? -INFINITY : m_nat + logf(l_run);
+        if (p.row_max) p.row_max[stat] = m_nat;
+        if (p.row_sum) p.row_sum[stat] = l_run;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+    if (threadIdx.x == 0) atomicExch(p.status, *abort_word);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <bool kPInTmem>
+wb200_status launch_variant(const AttentionArgs &a, const FaParams &p, const CUtensorMap &tq,
+                            const CUtensorMap &tk, const CUtensorMap &tv, cudaStream_t stream) {
+  using L = FaSmem<kPInTmem>;
+  auto kernel_bf16 = fa_umma_kernel<kPInTmem, true>;
+  auto kernel_f16 = fa_umma_kernel<kPInTmem, false>;
+  static bool attribute_set = false;
+  if (!attribute_set) {
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(kernel_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(L::kBytes)));
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(kernel_f16, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(L::kBytes)));
+    attribute_set = true;
+  }
+  const int grid = p.num_pairs * a.batch * a.q_heads;
+  if (a.format == WB200_BF16)
+    kernel_bf16<<<grid, kFaThreads, L::kBytes, stream>>>(tq, tk, tv, p);
+  else
+    kernel_f16<<<grid, kFaThreads, L::kBytes, stream>>>(tq, tk, tv, p);
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
+}
+
+// 0 = P in shared memory, 1 = P in TMEM. Chosen once per process from WB200_FA_P_IN_TMEM (default 1).
+int p_in_tmem_mode() {
+  static int mode = -1;
+  if (mode < 0) {
+    const char *env = getenv("WB200_FA_P_IN_TMEM");
+    mode = (env && env[0] == '0') ? 0 : 1;
+  }
+  return mode;
+}
+
+}  // namespace
+
+bool attention_fa_umma_supports(const AttentionArgs &a) {
+  if (a.format != WB200_BF16 && a.format != WB200_F16) return false;
+  if (a.head_dim != kHd || a.q_len <= 0 || a.kv_len <= 0 || a.batch <= 0) return false;
+  if (a.kv_heads <= 0 || a.q_heads % a.kv_heads != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v) |
+       reinterpret_cast<uintptr_t>(a.out)) & 15u)
+    return false;
+  return true;
+}
+
+wb200_status launch_attention_fa_umma(const AttentionArgs &a, int sm_count, int *device_status,
+                                      cudaStream_t stream) {
+  (void)sm_count;
+  if (!attention_fa_umma_supports(a))
+    return fail(WB200_ERR_UNSUPPORTED, "attention request outside the tcgen05 prefill kernel's domain");
+  CUtensorMap tq, tk, tv;
+  const uint64_t row_pitch = kHd * 2;
+  wb200_status st = encode_tmap_3d(&tq, a.q, a.format, kHd, a.q_len, static_cast<uint64_t>(a.batch) * a.q_heads,
+                                   row_pitch, row_pitch * a.q_len, 64, kTileM);
+  if (st != WB200_OK) return st;
+  st = encode_tmap_3d(&tk, a.k, a.format, kHd, a.kv_len, static_cast<uint64_t>(a.batch) * a.kv_heads, row_pitch,
+                      row_pitch * a.kv_len, 64, kTileN);
+  if (st != WB200_OK) return st;
+  st = encode_tmap_3d(&tv, a.v, a.format, kHd, a.kv_len, static_cast<uint64_t>(a.batch) * a.kv_heads, row_pitch,
+                      row_pitch * a.kv_len, 64, kTileN);
+  if (st != WB200_OK) return st;
+
+  FaParams p;
+  p.batch = a.batch; p.q_heads = a.q_heads; p.kv_heads = a.kv_heads; p.group = a.q_heads / a.kv_heads;
+  p.q_len = a.q_len; p.kv_len = a.kv_len;
+  int64_t visible = a.kv_valid < a.kv_len ? a.kv_valid : a.kv_len;
+  if (visible < 0) visible = 0;
+  p.kv_visible = static_cast<int>(visible);
+  p.causal = a.causal;
+  p.causal_offset = a.causal_offset;
+  p.zero_fully_masked = a.zero_fully_masked;
+  p.out_format = a.format;
+  p.bf16 = a.format == WB200_BF16;
+  p.num_pairs = (a.q_len + 2 * kTileM - 1) / (2 * kTileM);
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.out = a.out; p.lse = a.lse; p.row_max = a.row_max; p.row_sum = a.row_sum;
+  p.status = device_status;
+  if (p_in_tmem_mode()) return launch_variant<true>(a, p, tq, tk, tv, stream);
+  return launch_variant<false>(a, p, tq, tk, tv, stream);
+}
+
+}  // namespace wb200

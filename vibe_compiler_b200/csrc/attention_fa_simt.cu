@@ -1,0 +1,126 @@
+// Flash-attention prefill on CUDA cores, f32 arithmetic throughout: the path for f32 storage (where
+// the 1e-5 parity bound rules out tensor-core inputs narrower than f32) and for shapes the tcgen05
+// kernel does not take. One warp owns one query row and walks the keys in tiles of 32, applying the
+// reference's online update literally
+// (lib/Wafer/Transforms/Linalg/OnlineAttentionDecomposition.cpp:568-594):
+//   s = (q.k)*scale (+mask); m' = max(m, max s); m_e = (m' == -inf ? 0 : m'); alpha = ExpLp(m - m_e);
+//   l = l*alpha + sum ExpLp(s - m_e); acc = acc*alpha + round_to_storage(P) V
+// and the finalize acc * (1/l) of OnlineAttentionMaterialization.cpp:196-262. ExpLp is
+// exp2(x * log2e) in f32 (lib/Wafer/Simulator/Reference/ManagedReferenceTargetModel.cpp:265-270).
+#include "kernels.h"
+
+namespace wb200 {
+namespace {
+
+constexpr int kWarpsPerBlock = 4;
+constexpr int kMaxDPerLane = 8;  // head_dim <= 256
+
+struct SimtParams {
+  AttentionArgs a;
+  int group;
+  int kv_visible;
+};
+
+__device__ __forceinline__ float exp_lp(float x) { return exp2f(__fmul_rn(x, 0x1.715476p+0f)); }
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32) fa_simt_kernel(const SimtParams p) {
+  const AttentionArgs &a = p.a;
+  extern __shared__ float q_smem[];  // [kWarpsPerBlock][head_dim]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * kWarpsPerBlock + warp;
+  const int bh = blockIdx.y;
+  const int b = bh / a.q_heads, h = bh % a.q_heads;
+  const int D = a.head_dim;
+  const int per_lane = D / 32;
+  if (row >= a.q_len) return;
+
+  const size_t q_off = (static_cast<size_t>(bh) * a.q_len + row) * D;
+  const size_t kv_off = (static_cast<size_t>(b) * a.kv_heads + h / p.group) * static_cast<size_t>(a.kv_len) * D;
+  const uint8_t *q = static_cast<const uint8_t *>(a.q);
+  const uint8_t *k = static_cast<const uint8_t *>(a.k);
+  const uint8_t *v = static_cast<const uint8_t *>(a.v);
+  float *my_q = q_smem + warp * D;
+  for (int d = lane; d < D; d += 32) my_q[d] = widen_bits(load_element_bits(q, q_off + d, a.format), a.format);
+  __syncwarp();
+
+  long long last = static_cast<long long>(p.kv_visible) - 1;
+  if (a.causal && a.causal_offset + row < last) last = a.causal_offset + row;
+  const int visible = last < 0 ? 0 : static_cast<int>(last + 1);
+
+  float m_run = -INFINITY, l_run = 0.0f;
+  float acc[kMaxDPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxDPerLane; ++i) acc[i] = 0.0f;
+
+  for (int key0 = 0; key0 < visible; key0 += 32) {
+    const int key = key0 + lane;
+    float s = -INFINITY;
+    if (key < visible) {
+      float dot = 0.0f;
+      const size_t k_row = kv_off + static_cast<size_t>(key) * D;
+      for (int d = 0; d < D; ++d)
+        dot = __fmaf_rn(my_q[d], widen_bits(load_element_bits(k, k_row + d, a.format), a.format), dot);
+      s = __fmul_rn(dot, a.scale);
+    }
+    float tile_max = s;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, off));
+    const float m_new = fmaxf(tile_max, m_run);
+    const float m_exp = (m_new == -INFINITY) ? 0.0f : m_new;
+    const float alpha = exp_lp(__fsub_rn(m_run, m_exp));
+    const float prob = exp_lp(__fsub_rn(s, m_exp));
+    float tile_sum = prob;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) tile_sum += __shfl_xor_sync(0xffffffffu, tile_sum, off);
+    l_run = __fadd_rn(__fmul_rn(l_run, alpha), tile_sum);
+    m_run = m_new;
+    // P is rounded to the storage type of V before the PV contraction.
+    const float prob_rounded = widen_bits(narrow_bits(prob, a.format), a.format);
+#pragma unroll
+    for (int i = 0; i < kMaxDPerLane; ++i) acc[i] = __fmul_rn(acc[i], alpha);
+    const int count = min(32, visible - key0);
+    for (int j = 0; j < count; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, prob_rounded, j);
+      const size_t v_row = kv_off + static_cast<size_t>(key0 + j) * D;
+#pragma unroll
+      for (int i = 0; i < kMaxDPerLane; ++i)
+        if (i < per_lane)
+          acc[i] = __fmaf_rn(pj, widen_bits(load_element_bits(v, v_row + i * 32 + lane, a.format), a.format), acc[i]);
+    }
+  }
+
+  float coefficient = __fdiv_rn(1.0f, l_run);
+  if (a.zero_fully_masked && l_run == 0.0f) coefficient = 0.0f;
+  uint8_t *out = static_cast<uint8_t *>(a.out);
+#pragma unroll
+  for (int i = 0; i < kMaxDPerLane; ++i)
+    if (i < per_lane)
+      store_element_bits(out, q_off + i * 32 + lane, a.format, narrow_bits(__fmul_rn(acc[i], coefficient), a.format));
+  if (lane == 0) {
+    const size_t stat = static_cast<size_t>(bh) * a.q_len + row;
+    if (a.lse) a.lse[stat] = (l_run == 0.0f) ? -INFINITY : m_run + logf(l_run);
+    if (a.row_max) a.row_max[stat] = m_run;
+    if (a.row_sum) a.row_sum[stat] = l_run;
+  }
+}
+
+}  // namespace
+
+wb200_status launch_attention_fa_simt(const AttentionArgs &a, cudaStream_t stream) {
+  if (!is_float_format(a.format)) return fail(WB200_ERR_UNSUPPORTED, "attention admits f16, bf16 and f32 storage");
+  if (a.head_dim <= 0 || a.head_dim % 32 != 0 || a.head_dim > 32 * kMaxDPerLane)
+    return fail(WB200_ERR_UNSUPPORTED, "head_dim must be a multiple of 32 up to 256");
+  if (a.kv_heads <= 0 || a.q_heads % a.kv_heads != 0 || a.q_len <= 0 || a.kv_len <= 0 || a.batch <= 0)
+    return fail(WB200_ERR_INVALID_ARGUMENT, "invalid attention extents");
+  SimtParams p;
+  p.a = a;
+  p.group = a.q_heads / a.kv_heads;
+  int64_t visible = a.kv_valid < a.kv_len ? a.kv_valid : a.kv_len;
+  p.kv_visible = visible < 0 ? 0 : static_cast<int>(visible);
+  dim3 grid((a.q_len + kWarpsPerBlock - 1) / kWarpsPerBlock, a.batch * a.q_heads);
+  fa_simt_kernel<<<grid, kWarpsPerBlock * 32, kWarpsPerBlock * a.head_dim * sizeof(float), stream>>>(p);
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
+}
+
+}  // namespace wb200

@@ -1,0 +1,442 @@
+// Flash-decoding (split-KV attention for query length 1, grouped queries) for sm_100a.
+//
+// Arithmetic follows the reference's online-attention materialisation:
+//   per KV tile   lib/Wafer/Transforms/Linalg/OnlineAttentionDecomposition.cpp:568-594
+//   state merge   lib/Wafer/Transforms/Linalg/OnlineAttentionMaterialization.cpp:264-373
+//   finalize      lib/Wafer/Transforms/Linalg/OnlineAttentionMaterialization.cpp:196-262
+//   fold order    lib/Wafer/Transforms/Linalg/SpatialRegionMaterialization.cpp:2420-2433 (ascending)
+// exp is the target's ExpLp, exp2(x * log2e) in f32
+// (lib/Wafer/Simulator/Reference/ManagedReferenceTargetModel.cpp:265-270).
+//
+// Stage 1 (fd_partial_kernel): one CTA per (split, kv head, batch). Each of the 4 warps streams its
+// own contiguous quarter of the CTA's KV interval through a private 3-deep cp.async ring of 16-row
+// tiles (128-bit coalesced copies, XOR-swizzled rows), computes S = Q K^T and acc += P V with
+// mma.sync m16n8k16 on the group's query heads (rows padded to 16) and carries (m, l, acc) in
+// registers. Warps then left-fold their states in ascending KV order through shared memory and the
+// CTA writes one (acc[D], m, l) record. Stage 2 (fd_combine_kernel) left-folds the records of all
+// splits in ascending order and finalizes. The kernel is HBM-bound: algorithmic bytes per launch
+// are the K and V bytes of the visible keys, read exactly once.
+#include "kernels.h"
+
+namespace wb200 {
+namespace {
+
+constexpr int kD = 128;            // head dimension
+constexpr int kTileRows = 16;      // KV rows per warp tile
+constexpr int kWarps = 4;
+constexpr int kStagesFd = 3;
+constexpr int kTileBytes = kTileRows * kD * 2;  // 4 KiB for K, same for V
+constexpr int kRecord = kD + 2;    // acc[D], m, l
+constexpr int kQBytes = 16 * kD * 2;
+constexpr int kFdSmemBytes = kWarps * kStagesFd * 2 * kTileBytes + kQBytes;
+
+__device__ __forceinline__ float exp_lp(float x) { return exp2f(x * 0x1.715476p+0f); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+template <bool kBf16>
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (kBf16) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+        "{%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+        "{%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+template <bool kBf16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if constexpr (kBf16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&v);
+  }
+}
+
+struct FdParams {
+  int batch, q_heads, kv_heads, group;
+  int kv_len;         // rows physically present per (batch, kv head)
+  int kv_visible;     // keys [0, kv_visible) are visible
+  int splits, rows_per_split, rows_per_warp;
+  float scale;
+  const uint16_t *q, *k, *v;
+  float *partials;    // [batch, q_heads, splits, kRecord]
+};
+
+// Swizzled byte offset of 16-byte chunk `c` of row `r` inside a 16 x 256-byte tile.
+__device__ __forceinline__ uint32_t tile_offset(int r, int c) {
+  return static_cast<uint32_t>(r * 256 + ((c ^ (r & 7)) << 4));
+}
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kWarps * 32, 2) fd_partial_kernel(const FdParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  uint8_t *q_smem = smem + kWarps * kStagesFd * 2 * kTileBytes;
+  // Stage the group's query rows, zero-padded to 16 rows.
+  {
+    const uint16_t *q_src = p.q + (static_cast<size_t>(b) * p.q_heads + static_cast<size_t>(hk) * p.group) * kD;
+    for (int i = threadIdx.x; i < 16 * kD / 8; i += blockDim.x) {
+      const int row = i / (kD / 8), chunk = i % (kD / 8);
+      uint4 value = make_uint4(0, 0, 0, 0);
+      if (row < p.group) value = *reinterpret_cast<const uint4 *>(q_src + row * kD + chunk * 8);
+      *reinterpret_cast<uint4 *>(q_smem + row * (kD * 2) + chunk * 16) = value;
+    }
+  }
+  __syncthreads();
+  uint32_t q_frag[kD / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < kD / 16; ++ks) {
+    const uint32_t *row_lo = reinterpret_cast<const uint32_t *>(q_smem + g * (kD * 2));
+    const uint32_t *row_hi = reinterpret_cast<const uint32_t *>(q_smem + (g + 8) * (kD * 2));
+    q_frag[ks][0] = row_lo[ks * 8 + t];
+    q_frag[ks][1] = row_hi[ks * 8 + t];
+    q_frag[ks][2] = row_lo[ks * 8 + 4 + t];
+    q_frag[ks][3] = row_hi[ks * 8 + 4 + t];
+  }
+
+  // This warp's KV interval.
+  const int split_begin = split * p.rows_per_split;
+  const int warp_begin = split_begin + warp * p.rows_per_warp;
+  int warp_end = warp_begin + p.rows_per_warp;
+  if (warp_end > p.kv_visible) warp_end = p.kv_visible;
+  const int tiles = warp_end > warp_begin ? (warp_end - warp_begin + kTileRows - 1) / kTileRows : 0;
+
+  const size_t head_offset = (static_cast<size_t>(b) * p.kv_heads + hk) * static_cast<size_t>(p.kv_len) * kD;
+  const uint16_t *k_base = p.k + head_offset;
+  const uint16_t *v_base = p.v + head_offset;
+  uint8_t *ring = smem + warp * (kStagesFd * 2 * kTileBytes);
+  const uint32_t ring_addr = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
+
+  auto issue_tile = [&](int tile, int slot) {
+    if (tile < tiles) {
+      const int row0 = warp_begin + tile * kTileRows;
+      const uint32_t k_dst = ring_addr + slot * (2 * kTileBytes);
+      const uint32_t v_dst = k_dst + kTileBytes;
+#pragma unroll
+      for (int i = 0; i < (kTileRows * 16) / 32; ++i) {
+        const int idx = i * 32 + lane;
+        const int r = idx >> 4, c = idx & 15;
+        const int row = row0 + r;
+        const bool in_range = row < p.kv_len;
+        const size_t src = static_cast<size_t>(in_range ? row : 0) * kD + c * 8;
+        cp_async16(k_dst + tile_offset(r, c), k_base + src, in_range ? 16u : 0u);
+        cp_async16(v_dst + tile_offset(r, c), v_base + src, in_range ? 16u : 0u);
+      }
+    }
+    cp_async_commit();
+  };
+
+  float m_run[2] = {-INFINITY, -INFINITY};  // rows g and g + 8
+  float l_run[2] = {0.f, 0.f};              // this lane's share of the row sum
+  float acc[kD / 8][4];
+#pragma unroll
+  for (int j = 0; j < kD / 8; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+#pragma unroll
+  for (int s = 0; s < kStagesFd - 1; ++s) issue_tile(s, s);
+
+  for (int tile = 0; tile < tiles; ++tile) {
+    cp_async_wait<kStagesFd - 2>();
+    __syncwarp();
+    issue_tile(tile + kStagesFd - 1, (tile + kStagesFd - 1) % kStagesFd);
+
+    const uint32_t k_src = ring_addr + (tile % kStagesFd) * (2 * kTileBytes);
+    const uint32_t v_src = k_src + kTileBytes;
+    const int row0 = warp_begin + tile * kTileRows;
+
+    // S = Q K^T for 16 keys: two n-tiles of 8 keys.
+    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int ks = 0; ks < kD / 16; ++ks) {
+      const int mi = lane >> 3;
+      const int r = (mi >> 1) * 8 + (lane & 7);
+      const int c = 2 * ks + (mi & 1);
+      uint32_t bfrag[4];
+      ldmatrix_x4(k_src + tile_offset(r, c), bfrag);
+      mma_16816<kBf16>(s0, q_frag[ks], bfrag[0], bfrag[1]);
+      mma_16816<kBf16>(s1, q_frag[ks], bfrag[2], bfrag[3]);
+    }
+    // score region: scale, then mask keys outside the visible interval.
+    const int key0 = row0 + 2 * t;
+    float sc[2][4];  // [row half][key 2t, 2t+1, 8+2t, 8+2t+1]
+    sc[0][0] = s0[0] * p.scale; sc[0][1] = s0[1] * p.scale; sc[0][2] = s1[0] * p.scale; sc[0][3] = s1[1] * p.scale;
+    sc[1][0] = s0[2] * p.scale; sc[1][1] = s0[3] * p.scale; sc[1][2] = s1[2] * p.scale; sc[1][3] = s1[3] * p.scale;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (key0 >= warp_end) sc[h][0] = -INFINITY;
+      if (key0 + 1 >= warp_end) sc[h][1] = -INFINITY;
+      if (key0 + 8 >= warp_end) sc[h][2] = -INFINITY;
+      if (key0 + 9 >= warp_end) sc[h][3] = -INFINITY;
+    }
+    uint32_t p_frag[4];
+    float alpha[2];
+    float pr[2][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float tile_max = fmaxf(fmaxf(sc[h][0], sc[h][1]), fmaxf(sc[h][2], sc[h][3]));
+      tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 1));
+      tile_max = fmaxf(tile_max, __shfl_xor_sync(0xffffffffu, tile_max, 2));
+      const float m_new = fmaxf(tile_max, m_run[h]);
+      const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;
+      alpha[h] = exp_lp(m_run[h] - m_exp);
+      float row_sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        pr[h][i] = exp_lp(sc[h][i] - m_exp);
+        row_sum += pr[h][i];
+      }
+      l_run[h] = l_run[h] * alpha[h] + row_sum;
+      m_run[h] = m_new;
+    }
+    // Probabilities are rounded to the storage type of V at the PV input.
+    p_frag[0] = pack2<kBf16>(pr[0][0], pr[0][1]);
+    p_frag[1] = pack2<kBf16>(pr[1][0], pr[1][1]);
+    p_frag[2] = pack2<kBf16>(pr[0][2], pr[0][3]);
+    p_frag[3] = pack2<kBf16>(pr[1][2], pr[1][3]);
+#pragma unroll
+    for (int j = 0; j < kD / 8; ++j) {
+      acc[j][0] *= alpha[0]; acc[j][1] *= alpha[0];
+      acc[j][2] *= alpha[1]; acc[j][3] *= alpha[1];
+    }
+#pragma unroll
+    for (int j = 0; j < kD / 8; j += 2) {
+      const int mi = lane >> 3;
+      const int r = (mi & 1) * 8 + (lane & 7);
+      const int c = j + (mi >> 1);
+      uint32_t vfrag[4];
+      ldmatrix_x4_trans(v_src + tile_offset(r, c), vfrag);
+      mma_16816<kBf16>(acc[j], p_frag, vfrag[0], vfrag[1]);
+      mma_16816<kBf16>(acc[j + 1], p_frag, vfrag[2], vfrag[3]);
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+    l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+  }
+  __syncthreads();  // every warp is done with its ring; reuse it for the merge records
+
+  float *records = reinterpret_cast<float *>(smem);  // [warp][16][kRecord]
+  {
+    float *mine = records + static_cast<size_t>(warp) * 16 * kRecord;
+#pragma unroll
+    for (int j = 0; j < kD / 8; ++j) {
+      mine[g * kRecord + j * 8 + 2 * t] = acc[j][0];
+      mine[g * kRecord + j * 8 + 2 * t + 1] = acc[j][1];
+      mine[(g + 8) * kRecord + j * 8 + 2 * t] = acc[j][2];
+      mine[(g + 8) * kRecord + j * 8 + 2 * t + 1] = acc[j][3];
+    }
+    if (t == 0) {
+      mine[g * kRecord + kD] = m_run[0];
+      mine[g * kRecord + kD + 1] = l_run[0];
+      mine[(g + 8) * kRecord + kD] = m_run[1];
+      mine[(g + 8) * kRecord + kD + 1] = l_run[1];
+    }
+  }
+  __syncthreads();
+  // Left fold over the warps (ascending KV order), one thread per (head, d).
+  for (int idx = threadIdx.x; idx < p.group * kD; idx += blockDim.x) {
+    const int head = idx / kD, d = idx % kD;
+    const float *rec = records + head * kRecord;
+    float m = rec[kD], l = rec[kD + 1], a = rec[d];
+    for (int w = 1; w < kWarps; ++w) {
+      const float *right = records + static_cast<size_t>(w) * 16 * kRecord + head * kRecord;
+      const float m_right = right[kD], l_right = right[kD + 1], a_right = right[d];
+      const float m_new = fmaxf(m, m_right);
+      const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;
+      const float scale_left = exp_lp(m - m_exp), scale_right = exp_lp(m_right - m_exp);
+      l = l * scale_left + l_right * scale_right;
+      a = a * scale_left + a_right * scale_right;
+      m = m_new;
+    }
+    float *out = p.partials +
+                 ((static_cast<size_t>(b) * p.q_heads + hk * p.group + head) * p.splits + split) * kRecord;
+    out[d] = a;
+    if (d == 0) {
+      out[kD] = m;
+      out[kD + 1] = l;
+    }
+  }
+}
+
+struct FdCombineParams {
+  int rows;            // batch * q_heads
+  int records;         // number of records folded per row
+  size_t row_stride;   // floats between consecutive rows of one record index
+  size_t record_stride;// floats between consecutive records of one row
+  const float *records_ptr;
+  int out_format;
+  int zero_fully_masked;
+  int finalize;
+  void *out;
+  float *lse, *row_max, *row_sum, *state_out;
+};
+
+__global__ void __launch_bounds__(kD) fd_combine_kernel(const FdCombineParams p) {
+  const int row = blockIdx.x, d = threadIdx.x;
+  const float *rec = p.records_ptr + row * p.row_stride;
+  float m = rec[kD], l = rec[kD + 1], a = rec[d];
+  for (int i = 1; i < p.records; ++i) {
+    const float *right = rec + i * p.record_stride;
+    const float m_right = right[kD], l_right = right[kD + 1], a_right = right[d];
+    const float m_new = fmaxf(m, m_right);
+    const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;
+    const float scale_left = exp_lp(m - m_exp), scale_right = exp_lp(m_right - m_exp);
+    l = l * scale_left + l_right * scale_right;
+    a = a * scale_left + a_right * scale_right;
+    m = m_new;
+  }
+  if (!p.finalize) {
+    float *state = p.state_out + static_cast<size_t>(row) * kRecord;
+    state[d] = a;
+    if (d == 0) {
+      state[kD] = m;
+      state[kD + 1] = l;
+    }
+    return;
+  }
+  float coefficient = 1.0f / l;
+  if (p.zero_fully_masked && l == 0.f) coefficient = 0.f;
+  const float value = a * coefficient;
+  if (p.out_format == WB200_F32)
+    reinterpret_cast<float *>(p.out)[static_cast<size_t>(row) * kD + d] = value;
+  else
+    reinterpret_cast<uint16_t *>(p.out)[static_cast<size_t>(row) * kD + d] =
+        static_cast<uint16_t>(narrow_bits(value, p.out_format));
+  if (d == 0) {
+    if (p.lse) p.lse[row] = (l == 0.f) ? -INFINITY : m + logf(l);
+    if (p.row_max) p.row_max[row] = m;
+    if (p.row_sum) p.row_sum[row] = l;
+  }
+}
+
+int visible_keys(const AttentionArgs &a) {
+  int64_t visible = a.kv_valid < a.kv_len ? a.kv_valid : a.kv_len;
+  if (a.causal && a.causal_offset + 1 < visible) visible = a.causal_offset + 1;
+  return visible < 0 ? 0 : static_cast<int>(visible);
+}
+
+}  // namespace
+
+bool attention_fd_supports(const AttentionArgs &a) {
+  if (a.q_len != 1 || a.head_dim != kD) return false;
+  if (a.format != WB200_BF16 && a.format != WB200_F16) return false;
+  if (a.kv_heads <= 0 || a.q_heads % a.kv_heads != 0 || a.q_heads / a.kv_heads > 16) return false;
+  if ((reinterpret_cast<uintptr_t>(a.q) | reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15u)
+    return false;
+  return a.kv_len > 0 && a.batch > 0;
+}
+
+uint32_t fd_choose_splits(const AttentionArgs &a, int sm_count) {
+  const int64_t visible = visible_keys(a);
+  int64_t splits = (visible + 2047) / 2048;
+  const int64_t units = static_cast<int64_t>(a.batch) * a.kv_heads;
+  // Enough CTAs for four resident waves when the KV axis allows it (>= 256 rows per split).
+  while (units * splits < 4LL * sm_count && (visible + splits * 2 - 1) / (splits * 2) >= 256) splits *= 2;
+  if (splits < 2) splits = 2;  // flash-decoding splits K2 into at least two intervals
+  if (splits > 4096) splits = 4096;
+  return static_cast<uint32_t>(splits);
+}
+
+size_t fd_partial_floats(const AttentionArgs &a, uint32_t splits) {
+  return static_cast<size_t>(a.batch) * a.q_heads * splits * kRecord;
+}
+
+wb200_status launch_attention_fd(const AttentionArgs &a, uint32_t splits, float *partials, int finalize,
+                                 float *state_out, cudaStream_t stream) {
+  if (!attention_fd_supports(a)) return fail(WB200_ERR_UNSUPPORTED, "flash-decoding request outside the kernel's domain");
+  if (splits < 1) return fail(WB200_ERR_INVALID_ARGUMENT, "kv_splits must be positive");
+  FdParams p;
+  p.batch = a.batch; p.q_heads = a.q_heads; p.kv_heads = a.kv_heads; p.group = a.q_heads / a.kv_heads;
+  p.kv_len = a.kv_len;
+  p.kv_visible = visible_keys(a);
+  p.splits = static_cast<int>(splits);
+  const int64_t per_split = (static_cast<int64_t>(p.kv_visible) + splits - 1) / splits;
+  const int64_t granule = kWarps * kTileRows;
+  p.rows_per_split = static_cast<int>(((per_split + granule - 1) / granule) * granule);
+  if (p.rows_per_split == 0) p.rows_per_split = static_cast<int>(granule);
+  p.rows_per_warp = p.rows_per_split / kWarps;
+  p.scale = a.scale;
+  p.q = static_cast<const uint16_t *>(a.q);
+  p.k = static_cast<const uint16_t *>(a.k);
+  p.v = static_cast<const uint16_t *>(a.v);
+  p.partials = partials;
+
+  static bool attribute_set = false;
+  if (!attribute_set) {
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(fd_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmemBytes));
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(fd_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmemBytes));
+    attribute_set = true;
+  }
+  dim3 grid(splits, a.kv_heads, a.batch);
+  if (a.format == WB200_BF16)
+    fd_partial_kernel<true><<<grid, kWarps * 32, kFdSmemBytes, stream>>>(p);
+  else
+    fd_partial_kernel<false><<<grid, kWarps * 32, kFdSmemBytes, stream>>>(p);
+  WB200_CUDA_CHECK(cudaGetLastError());
+
+  FdCombineParams c;
+  c.rows = a.batch * a.q_heads;
+  c.records = static_cast<int>(splits);
+  c.row_stride = static_cast<size_t>(splits) * kRecord;
+  c.record_stride = kRecord;
+  c.records_ptr = partials;
+  c.out_format = a.format;
+  c.zero_fully_masked = a.zero_fully_masked;
+  c.finalize = finalize;
+  c.out = a.out; c.lse = a.lse; c.row_max = a.row_max; c.row_sum = a.row_sum; c.state_out = state_out;
+  fd_combine_kernel<<<c.rows, kD, 0, stream>>>(c);
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
+}
+
+wb200_status launch_attention_fd_merge(const AttentionArgs &a, const float *states, uint32_t shard_count,
+                                       cudaStream_t stream) {
+  if (a.head_dim != kD) return fail(WB200_ERR_UNSUPPORTED, "merge supports head_dim 128");
+  if (shard_count < 1) return fail(WB200_ERR_INVALID_ARGUMENT, "shard_count must be positive");
+  FdCombineParams c;
+  c.rows = a.batch * a.q_heads;
+  c.records = static_cast<int>(shard_count);
+  c.row_stride = kRecord;
+  c.record_stride = static_cast<size_t>(c.rows) * kRecord;
+  c.records_ptr = states;
+  c.out_format = a.format;
+  c.zero_fully_masked = a.zero_fully_masked;
+  c.finalize = 1;
+  c.out = a.out; c.lse = a.lse; c.row_max = a.row_max; c.row_sum = a.row_sum; c.state_out = nullptr;
+  fd_combine_kernel<<<c.rows, kD, 0, stream>>>(c);
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
+}
+
+}  // namespace wb200

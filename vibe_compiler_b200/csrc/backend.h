@@ -1,0 +1,107 @@
+// Internal definition of the backend object and request-validation helpers shared by the C-ABI
+// translation units.
+#pragma once
+
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "kernels.h"
+
+namespace wb200 {
+const char *last_error_cstr();
+}
+
+struct wb200_backend {
+  int device = 0;
+  int sm_count = 0;
+  cudaStream_t stream = nullptr;  // used by WB200_MEM_HOST calls
+  int *d_status = nullptr;        // [0] bounded-wait status, [1] NaN flag
+  uint64_t launches = 0;
+  uint64_t max_total_bytes = 0, max_scratch_bytes = 0;
+  char digest[96] = {0};
+  struct Slot { void *ptr = nullptr; size_t bytes = 0; };
+  std::vector<Slot> slots;
+
+  // Grow-only staging buffer number `index`.
+  wb200_status buffer(size_t index, size_t bytes, void **out) {
+    if (slots.size() <= index) slots.resize(index + 1);
+    Slot &slot = slots[index];
+    if (slot.bytes < bytes) {
+      if (slot.ptr) cudaFree(slot.ptr);
+      slot.ptr = nullptr;
+      slot.bytes = 0;
+      const size_t rounded = ((bytes + 255) / 256) * 256;
+      WB200_CUDA_CHECK(cudaMalloc(&slot.ptr, rounded));
+      slot.bytes = rounded;
+    }
+    *out = slot.ptr;
+    return WB200_OK;
+  }
+};
+
+namespace wb200 {
+
+struct DeviceGuard {
+  int previous = -1;
+  explicit DeviceGuard(int device) {
+    cudaGetDevice(&previous);
+    if (previous != device) cudaSetDevice(device);
+    else previous = -1;
+  }
+  ~DeviceGuard() { if (previous >= 0) cudaSetDevice(previous); }
+};
+
+inline void fill_evidence(const wb200_backend *backend, wb200_evidence *evidence, const char *implementation) {
+  if (!evidence) return;
+  memset(evidence, 0, sizeof(*evidence));
+  evidence->evidence_kind = 2;
+  strncpy(evidence->digest, backend->digest, sizeof(evidence->digest) - 1);
+  strncpy(evidence->implementation, implementation, sizeof(evidence->implementation) - 1);
+}
+
+// Reads and clears the device status words. status[0] != 0 -> a bounded wait gave up.
+inline wb200_status read_device_status(wb200_backend *backend, cudaStream_t stream, int *nan_flag) {
+  int host[2] = {0, 0};
+  WB200_CUDA_CHECK(cudaMemcpyAsync(host, backend->d_status, sizeof(host), cudaMemcpyDeviceToHost, stream));
+  WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
+  if (host[0] != 0 || host[1] != 0) {
+    WB200_CUDA_CHECK(cudaMemsetAsync(backend->d_status, 0, sizeof(host), stream));
+    WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
+  }
+  if (nan_flag) *nan_flag = host[1];
+  if (host[0] != 0) return fail(WB200_ERR_DEVICE_TIMEOUT, "a device-side bounded wait gave up (status " + std::to_string(host[0]) + ")");
+  return WB200_OK;
+}
+
+inline wb200_status check_storage(const wb200_tensor_desc &desc, uint64_t bytes, const void *ptr, const char *what,
+                           LayoutMap *map, wb200_geometry *geometry) {
+  wb200_status st = make_layout_map(desc, map, geometry);
+  if (st != WB200_OK) return st;
+  if (!ptr) return fail(WB200_ERR_INVALID_ARGUMENT, std::string(what) + " storage pointer is null");
+  if (bytes != static_cast<uint64_t>(geometry->physical_bytes))
+    return fail(WB200_ERR_INVALID_ARGUMENT, std::string(what) + " storage size does not match its physical geometry");
+  return WB200_OK;
+}
+
+inline bool same_shape(const wb200_tensor_desc &a, const wb200_tensor_desc &b) {
+  if (a.rank != b.rank) return false;
+  for (int d = 0; d < a.rank; ++d)
+    if (a.shape[d] != b.shape[d]) return false;
+  return true;
+}
+
+inline wb200_status check_budget(const wb200_backend *backend, uint64_t scalar_evaluations, uint64_t max_scalar,
+                          uint64_t total_bytes, uint64_t logical_values) {
+  if (scalar_evaluations > max_scalar) return fail(WB200_ERR_BUDGET, "scalar evaluation budget exceeded");
+  if (backend->max_total_bytes && total_bytes > backend->max_total_bytes)
+    return fail(WB200_ERR_BUDGET, "physical byte budget exceeded");
+  // The reference accounts 16 bytes of scratch per logical value (sizeof(RawLogicalValue)).
+  if (backend->max_scratch_bytes && logical_values * 16 > backend->max_scratch_bytes)
+    return fail(WB200_ERR_BUDGET, "logical scratch budget exceeded");
+  return WB200_OK;
+}
+
+}  // namespace wb200
+

@@ -1,0 +1,96 @@
+// Internal launcher interface between the C-ABI layer (api.cu) and the kernel translation units.
+// All pointers are device pointers. Launchers enqueue on `stream` and never synchronise.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace wb200 {
+
+// ---- TMA descriptor encoding (driver entry point fetched at run time; libcuda is not linked)
+// `inner`/`outer`(/`batch`) are extents in elements, innermost first; the box is {box_inner,
+// box_outer(,1)} with 128-byte swizzle; 16-bit elements only.
+wb200_status encode_tmap_2d(CUtensorMap *map, const void *base, int format, uint64_t inner,
+                            uint64_t outer, uint64_t row_pitch_bytes, uint32_t box_inner,
+                            uint32_t box_outer);
+wb200_status encode_tmap_3d(CUtensorMap *map, const void *base, int format, uint64_t inner,
+                            uint64_t outer, uint64_t batch, uint64_t row_pitch_bytes,
+                            uint64_t batch_pitch_bytes, uint32_t box_inner, uint32_t box_outer);
+
+// ---- tcgen05 GEMM with fused epilogue (gemm_umma.cu)
+struct GemmUmmaArgs {
+  int m, n, k;
+  int in_format, out_format;   // wb200_format
+  int lhs_transposed;          // 0: A[m,k] row-major, 1: A[k,m] row-major
+  int rhs_transposed;          // 0: B[k,n] row-major, 1: B[n,k] row-major
+  int epilogue;                // wb200_epilogue
+  const void *a, *b;
+  const float *bias;
+  void *out;
+};
+bool gemm_umma_supports(const GemmUmmaArgs &args);
+wb200_status launch_gemm_umma(const GemmUmmaArgs &args, int sm_count, int *device_status,
+                              cudaStream_t stream);
+
+// ---- bit-exact sequential-k GEMM on physical or compact storage (gemm_formal.cu)
+struct GemmFormalArgs {
+  int m, k, n, batch;
+  int in_format, out_format;
+  int lhs_transposed, rhs_transposed;
+  int has_psum;
+  const uint8_t *lhs, *rhs, *psum;
+  uint8_t *dst;
+  LayoutMap lhs_map, rhs_map, psum_map, dst_map;  // physical placement of every operand
+};
+wb200_status launch_gemm_formal(const GemmFormalArgs &args, cudaStream_t stream);
+
+// ---- managed-reference tensor commands (tensor_ops.cu)
+// `nan_flag` is set to 1 by the kernel if any input or result is NaN (the contract rejects those).
+wb200_status launch_elementwise(int op, int format, int input_count, const uint8_t *in0,
+                                const uint8_t *in1, uint8_t *dst, const LayoutMap &map, int *nan_flag,
+                                cudaStream_t stream);
+wb200_status launch_convert(int src_format, int dst_format, const uint8_t *src, uint8_t *dst,
+                            const LayoutMap &src_map, const LayoutMap &dst_map, int *nan_flag,
+                            cudaStream_t stream);
+wb200_status launch_reduce(int op, int format, const uint8_t *src, uint8_t *dst,
+                           const LayoutMap &src_map, const LayoutMap &dst_map, uint32_t reduced_mask,
+                           int *nan_flag, cudaStream_t stream);
+// Device codec: compact <-> physical.
+wb200_status launch_unpack(const uint8_t *storage, uint8_t *compact, const LayoutMap &map,
+                           int element_bytes, cudaStream_t stream);
+wb200_status launch_pack(const uint8_t *compact, uint8_t *storage, const LayoutMap &map,
+                         int element_bytes, cudaStream_t stream);
+
+// ---- attention (attention_fa.cu, attention_fa_f32.cu, attention_fd.cu)
+struct AttentionArgs {
+  int batch, q_heads, kv_heads, q_len, kv_len, head_dim;
+  int format;
+  int causal, zero_fully_masked;
+  float scale;
+  int64_t causal_offset;  // query_start - key_start
+  int64_t kv_valid;       // keys with index >= kv_valid are masked (key_end - key_start)
+  const void *q, *k, *v;
+  void *out;
+  float *lse, *row_max, *row_sum;
+};
+bool attention_fa_umma_supports(const AttentionArgs &args);
+wb200_status launch_attention_fa_umma(const AttentionArgs &args, int sm_count, int *device_status,
+                                      cudaStream_t stream);
+wb200_status launch_attention_fa_simt(const AttentionArgs &args, cudaStream_t stream);
+
+// Flash-decoding. `partials` is scratch of fd_partial_floats(args, splits) floats.
+// Stage 1 writes one (acc[D], m, l) record per (batch, q_head, split); stage 2 left-folds records in
+// ascending split order. With `finalize` == 0 stage 2 writes the merged state to `state_out`
+// instead of out / lse.
+bool attention_fd_supports(const AttentionArgs &args);
+uint32_t fd_choose_splits(const AttentionArgs &args, int sm_count);
+size_t fd_partial_floats(const AttentionArgs &args, uint32_t splits);
+wb200_status launch_attention_fd(const AttentionArgs &args, uint32_t splits, float *partials,
+                                 int finalize, float *state_out, cudaStream_t stream);
+wb200_status launch_attention_fd_merge(const AttentionArgs &args, const float *states,
+                                       uint32_t shard_count, cudaStream_t stream);
+
+}  // namespace wb200
