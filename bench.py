@@ -1,0 +1,345 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: flash-attention prefill (tensor-pipe bound) as the headline line, with
+flash-decoding (HBM bound) and the GEMM + bias + GELU region reported beside it in the same JSON line.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (N = 1): FA prefill bf16, batch 4, 32 heads, seq 4096, head_dim 128, causal, synthetic
+N(0,1) inputs from a seed. One step = one pass of the kernel over that batch. At N > 1 every rank
+runs the same-size batch of independent (batch, head) units (weak scaling, no data-path collective).
+`value` is device-timed with inputs resident in HBM; `e2e` goes through the public host-buffer call
+(pinned host memory, copies inside the timed region). `--impl reference` times the CPU restatement
+of the reference's numeric path (the reference itself needs LLVM/MLIR/SystemC and cannot be built
+here) on all host threads on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FA = dict(batch=4, heads=32, kv_heads=32, seq=4096, head_dim=128)
+FD = dict(batch=64, q_heads=32, kv_heads=8, kv_len=32768, head_dim=128)
+GEMM = dict(m=8192, n=8192, k=8192)
+SEED = 20260803
+
+
+def fa_flops(batch, heads, seq, d):
+    """Visible (query, key) pairs only: 4 * B * H * D * S (S + 1) / 2."""
+    return 4 * batch * heads * d * seq * (seq + 1) // 2
+
+
+def peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        data = json.loads(path.read_text())
+        return {"hbm_gbs": data["hbm_gbs"], "bf16_tflops": data["bf16_tflops"],
+                "bf16_tflops_sustained": data.get("bf16_tflops_sustained", data["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.proc:
+            return
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, reasons, max_clock = [], set(), None
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                clocks.append(float(parts[1]))
+                max_clock = float(parts[2])
+            except ValueError:
+                continue
+            for name, value in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[3:7]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        if clocks:
+            self.result = {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max_clock, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def timed_steps(fn, steps, warmup, torch, dist=None):
+    """Warm-up, then `steps` launches bracketed by barrier + synchronize; per-launch CUDA events on the
+    launching stream. Returns (total ms over the bracket, mean per-launch ms)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for begin, end in events:
+        begin.record()
+        fn()
+        end.record()
+    stop.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    total = start.elapsed_time(stop)
+    per_launch = sum(b.elapsed_time(e) for b, e in events) / steps
+    return total, per_launch
+
+
+CPU_SAMPLE_UNITS = 4
+
+
+def cpu_sample(threads: int, units: int = CPU_SAMPLE_UNITS):
+    """`units` (batch, head) units of the FA workload through the CPU oracle. Returns (seconds, flops, description)."""
+    import numpy as np
+    from oracle import binding
+    binding.build()
+    rng = np.random.default_rng(SEED)
+    s, d = FA["seq"], FA["head_dim"]
+
+    def bf16(shape):
+        x = rng.standard_normal(shape, dtype=np.float32)
+        return binding.convert("f32", "bf16", x.view(np.uint32).reshape(-1))[1].reshape(shape)
+    q, k, v = bf16((1, units, s, d)), bf16((1, units, s, d)), bf16((1, units, s, d))
+    t0 = time.perf_counter()
+    binding.attention("bf16", q, k, v, d ** -0.5, True, tile_n=128, threads=threads)
+    seconds = time.perf_counter() - t0
+    return seconds, fa_flops(1, units, s, d), (f"{units} of {FA['batch'] * FA['heads']} (batch, head) units: seq {s}, head_dim {d}, causal, "
+                                               f"{threads} threads")
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    threads = os.cpu_count() or 1
+    for _ in range(min(args.warmup, 1)):
+        cpu_sample(threads)
+    seconds, flops, sample = 0.0, 0, ""
+    t_all = []
+    for _ in range(args.steps):
+        sec, fl, sample = cpu_sample(threads)
+        t_all.append(sec)
+        flops = fl
+    seconds = sum(t_all) / len(t_all)
+    value = flops / seconds / 1e12
+    line = {"impl": "reference", "metric": "fa_prefill_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "FA prefill bf16 B4 H32 S4096 D128 causal", "sample": sample},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "CPU restatement of the reference's numeric path (reference sources need LLVM/MLIR/SystemC: not buildable here)"}
+    print(json.dumps(line))
+    return 0
+
+
+def run_profile_case(name: str):
+    """Three launches of one kernel on a case a few hundred MB large (above the 126 MB L2, far below a full-size
+    workload) so that a multi-pass ncu capture ends within a minute or two. Prints nothing to parse."""
+    import torch
+    from vibe_compiler_b200 import _abi as abi
+    from vibe_compiler_b200.backend import B200TargetModelBackend
+    backend = B200TargetModelBackend(0)
+    device = torch.device("cuda", 0)
+    gen = torch.Generator(device=device).manual_seed(SEED)
+    if name == "fa":       # batch 2 of the benchmark's 4: Q + K + V = 201 MB
+        shape = (2, FA["heads"], FA["seq"], FA["head_dim"])
+        q, k, v = (torch.randn(shape, device=device, generator=gen).bfloat16() for _ in range(3))
+        fn = lambda: backend.attention_fa(q, k, v, FA["head_dim"] ** -0.5, True)
+    elif name == "fd":     # batch 8 of the benchmark's 64: K + V = 1.07 GB
+        q = torch.randn(8, FD["q_heads"], 1, FD["head_dim"], device=device, generator=gen).bfloat16()
+        k = torch.randn(8, FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
+        v = torch.randn(8, FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
+        fn = lambda: backend.attention_fd(q, k, v, FD["head_dim"] ** -0.5)
+    else:                  # 4096^3 of the benchmark's 8192^3: A + B + out = 100 MB
+        a = (torch.rand(4096, 4096, device=device, generator=gen) * 2 - 1).bfloat16()
+        b = (torch.rand(4096, 4096, device=device, generator=gen) * 2 - 1).bfloat16()
+        bias = torch.randn(4096, device=device, generator=gen) * 0.02
+        fn = lambda: backend.gemm_epilogue(a, b, bias, epilogue=abi.EPI_BIAS_GELU)
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    backend.poll()
+    print(f"profile case {name}: 3 launches done")
+    return 0
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--skip-extras", action="store_true", help="only the headline FA workload")
+    parser.add_argument("--profile-case", choices=["fa", "fd", "gemm"],
+                        help="run three launches of a reduced-size case of one kernel and exit (for ncu captures)")
+    args = parser.parse_args()
+    if args.profile_case:
+        return run_profile_case(args.profile_case)
+    if args.impl == "reference":
+        return run_reference(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    from vibe_compiler_b200 import _abi as abi
+    from vibe_compiler_b200.backend import B200TargetModelBackend
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    backend = B200TargetModelBackend(local_rank)
+    peak = peaks()
+
+    # ---------------------------------------------------------------- FA prefill (headline)
+    gen = torch.Generator(device=device).manual_seed(SEED + rank)
+    shape = (FA["batch"], FA["heads"], FA["seq"], FA["head_dim"])
+    q = torch.randn(shape, device=device, generator=gen).bfloat16()
+    k = torch.randn(shape, device=device, generator=gen).bfloat16()
+    v = torch.randn(shape, device=device, generator=gen).bfloat16()
+    out = torch.empty_like(q)
+    lse = torch.empty(shape[:3], device=device)
+    scale = FA["head_dim"] ** -0.5
+    flops = fa_flops(FA["batch"], FA["heads"], FA["seq"], FA["head_dim"])
+
+    def fa_step():
+        backend.attention_fa(q, k, v, scale, True, out=out, lse=lse)
+
+    launches_before = backend.launch_count
+    with ClockSampler(local_rank) as sampler:
+        total_ms, launch_ms = timed_steps(fa_step, args.steps, args.warmup, torch, dist)
+    backend.poll()
+    launches = backend.launch_count - launches_before - args.warmup
+    times = torch.tensor([total_ms, launch_ms], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, launch_ms = times.tolist()
+    ms_per_step = total_ms / args.steps
+    value = world * flops / (ms_per_step * 1e-3) / 1e12
+    achieved = flops / (launch_ms * 1e-3) / 1e12
+
+    # ---------------------------------------------------------------- e2e through host buffers
+    e2e_steps = max(1, min(args.steps, 5))
+    hq, hk, hv = (torch.empty(shape, dtype=torch.bfloat16).pin_memory() for _ in range(3))
+    hq.copy_(q); hk.copy_(k); hv.copy_(v)
+    hout = torch.empty(shape, dtype=torch.bfloat16).pin_memory()
+    hlse = torch.empty(shape[:3], dtype=torch.float32).pin_memory()
+    backend.attention_fa(hq, hk, hv, scale, True, out=hout, lse=hlse)   # warm-up (allocates staging)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        backend.attention_fa(hq, hk, hv, scale, True, out=hout, lse=hlse)   # synchronous: returns after D2H
+    e2e_seconds = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device=device, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(e2e_seconds, op=dist.ReduceOp.MAX)
+    e2e_value = world * flops / e2e_seconds.item() / 1e12
+    h2d = 3 * q.numel() * 2
+    d2h = out.numel() * 2 + lse.numel() * 4
+    assert torch.equal(hout.view(torch.int16), out.cpu().view(torch.int16)), "host-buffer path disagrees with device path"
+    del hq, hk, hv, hout, hlse
+
+    extras = {}
+    if not args.skip_extras and world == 1:
+        del q, k, v, out
+        torch.cuda.empty_cache()
+        # ------------------------------------------------------------ FD decode (HBM bound)
+        fq = torch.randn(FD["batch"], FD["q_heads"], 1, FD["head_dim"], device=device, generator=gen).bfloat16()
+        fk = torch.randn(FD["batch"], FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
+        fv = torch.randn(FD["batch"], FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
+        fout = torch.empty_like(fq)
+        flse = torch.empty(FD["batch"], FD["q_heads"], 1, device=device)
+        fd_bytes = 2 * fk.numel() * 2
+        _, fd_ms = timed_steps(lambda: backend.attention_fd(fq, fk, fv, scale, out=fout, lse=flse), args.steps, args.warmup, torch)
+        backend.poll()
+        fd_gbs = fd_bytes / (fd_ms * 1e-3) / 1e9
+        extras["fd_decode"] = {"workload": "FD decode bf16 B64 Hq32 Hkv8 KV32768 D128, inputs (8.6 GB) larger than L2", "value": fd_gbs,
+                               "unit": "GB/s", "ms_per_step": fd_ms,
+                               "roofline": {"bound": "hbm", "achieved": fd_gbs, "peak": peak["hbm_gbs"], "unit": "GB/s",
+                                            "frac": fd_gbs / peak["hbm_gbs"], "traffic": None, "peak_source": peak["source"]}}
+        del fq, fk, fv
+        torch.cuda.empty_cache()
+        # ------------------------------------------------------------ GEMM + bias + GELU (tensor bound)
+        ga = (torch.rand(GEMM["m"], GEMM["k"], device=device, generator=gen) * 2 - 1).bfloat16()
+        gb = (torch.rand(GEMM["k"], GEMM["n"], device=device, generator=gen) * 2 - 1).bfloat16()
+        gbias = torch.randn(GEMM["n"], device=device, generator=gen) * 0.02
+        gout = torch.empty(GEMM["m"], GEMM["n"], device=device, dtype=torch.bfloat16)
+        _, g_ms = timed_steps(lambda: backend.gemm_epilogue(ga, gb, gbias, epilogue=abi.EPI_BIAS_GELU, out=gout), args.steps, args.warmup, torch)
+        backend.poll()
+        g_tflops = 2 * GEMM["m"] * GEMM["n"] * GEMM["k"] / (g_ms * 1e-3) / 1e12
+        extras["gemm_bias_gelu"] = {"workload": "GEMM 8192^3 bf16 + f32 bias + GELU(erf) -> bf16", "value": g_tflops, "unit": "TFLOP/s",
+                                    "ms_per_step": g_ms,
+                                    "roofline": {"bound": "tensor", "achieved": g_tflops, "peak": peak["bf16_tflops"], "unit": "TFLOP/s",
+                                                 "frac": g_tflops / peak["bf16_tflops"], "traffic": None, "peak_source": peak["source"]}}
+
+    if rank == 0:
+        cpu_threads = os.cpu_count() or 1
+        cpu_seconds, cpu_flops, cpu_desc = cpu_sample(cpu_threads) if world == 1 else (None, None, None)
+        line = {
+            "metric": "fa_prefill_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "FA prefill bf16 B4 H32 S4096 D128 causal (+f32 LSE), per GPU", "batch": FA["batch"], "heads": FA["heads"],
+                       "seq_len": FA["seq"], "head_dim": FA["head_dim"], "causal": True,
+                       "flops_per_step_per_gpu": flops, "flops_counting": "visible (query,key) pairs only",
+                       "l2": "inputs (Q+K+V 403 MB) larger than the 126 MB L2",
+                       "parallelism": f"independent (batch, head) units, {world} rank(s), no collective"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / peak["bf16_tflops"], "traffic": None, "peak_source": peak["source"],
+                         "frac_of_sustained": achieved / peak["bf16_tflops_sustained"], "launch_ms": launch_ms},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": launches,
+            "clocks": sampler.result,
+        }
+        if cpu_seconds is not None:
+            line["cpu_baseline"] = {"value": cpu_flops / cpu_seconds / 1e12, "unit": "TFLOP/s", "cores": cpu_threads, "kind": "port",
+                                    "sample": cpu_desc, "seconds": cpu_seconds}
+        line.update(extras)
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
