@@ -57,6 +57,11 @@ struct FaParams {
   int *status;
 };
 
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -259,7 +264,12 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     const uint32_t s_addr = tmem_base + lane_sel + kColS0 + t * 128;
     const uint32_t o_addr = tmem_base + lane_sel + kColO0 + t * 128;
     const int my_tiles = n_tiles[t];
-    float m_run = -INFINITY, l_run = 0.f;
+    // m_ref is the exponent reference the stored P, l and acc are scaled by; m_true is the running row
+    // maximum. The reference moves to the new maximum only when the maximum has grown by more than
+    // kRescaleThreshold (log2 units), so P stays below 2^8 and the rescale of acc is rare. acc / l and
+    // m_ref + log2(l) do not depend on the reference chosen, and every rounding keeps its relative error.
+    constexpr float kRescaleThreshold = 8.0f;
+    float m_ref = -INFINITY, m_true = -INFINITY, l_run = 0.f;
     bool ok = true;
     const long long causal_limit = p.causal ? p.causal_offset + row : 0x7fffffffffffLL;
 
@@ -267,47 +277,39 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       if (!mbar_wait(s_full(t), j & 1, abort_word)) { ok = false; break; }
       tc_fence_after();
       const int key0 = j * kTileN;
-      // Masking is needed only when the tile sticks out of the visible region of some row.
+      uint32_t r[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tmem_ld_32x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
+      tmem_wait_ld();
+      // Masking is needed only when the tile sticks out of the visible region of some row of the tile.
       const bool need_mask = (key0 + kTileN > p.kv_visible) ||
                              (p.causal && key0 + kTileN - 1 > p.causal_offset + row_base + t * kTileM);
-      float tile_max = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
-        tmem_wait_ld();
-        if (need_mask) {
+      if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = key0 + c * 32 + i;
-            const float s = __uint_as_float(r[i]) * p.scale_log2;
-            const bool visible = key < p.kv_visible && key <= causal_limit;
-            tile_max = fmaxf(tile_max, visible ? s : -INFINITY);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) tile_max = fmaxf(tile_max, __uint_as_float(r[i]) * p.scale_log2);
+        for (int i = 0; i < 128; ++i) {
+          const int key = key0 + i;
+          if (!(key < p.kv_visible && key <= causal_limit)) r[i] = 0xff800000u;   // -inf
         }
       }
-      const float m_new = fmaxf(m_run, tile_max);
-      const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_exp);
+      float raw_max = fmax3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+#pragma unroll
+      for (int i = 3; i + 1 < 128; i += 2) raw_max = fmax3(raw_max, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+      raw_max = fmaxf(raw_max, __uint_as_float(r[127]));
+      m_true = fmaxf(m_true, raw_max * p.scale_log2);     // scale > 0, so max commutes with the scaling
+      float alpha = 1.0f;
+      if (m_true - m_ref > kRescaleThreshold) {           // also taken when m_ref is still -inf
+        alpha = exp2f(m_ref - m_true);
+        m_ref = m_true;
+      }
+      const float m_exp = (m_ref == -INFINITY) ? 0.f : m_ref;
       float row_sum = 0.f;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(s_addr + c * 32, r);
-        tmem_wait_ld();
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float e0 = ex2_approx(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_exp));
-          float e1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_exp));
-          if (need_mask) {
-            const int key = key0 + c * 32 + i;
-            if (!(key < p.kv_visible && key <= causal_limit)) e0 = 0.f;
-            if (!(key + 1 < p.kv_visible && key + 1 <= causal_limit)) e1 = 0.f;
-          }
+          const float e0 = ex2_approx(fmaf(__uint_as_float(r[32 * c + i]), p.scale_log2, -m_exp));
+          const float e1 = ex2_approx(fmaf(__uint_as_float(r[32 * c + i + 1]), p.scale_log2, -m_exp));
           row_sum += e0 + e1;
           if constexpr (kBf16) {
             __nv_bfloat162 v = __floats2bfloat162_rn(e0, e1);
@@ -330,21 +332,18 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
       }
       l_run = l_run * alpha + row_sum;
-      m_run = m_new;
       // acc' = acc * alpha: needs PV of the previous tile to have landed in TMEM.
       if (j > 0) {
         if (!mbar_wait(o_done(t), (j - 1) & 1, abort_word)) { ok = false; break; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(o_addr + c * 32, r);
-            tmem_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(o_addr + c * 32, r);
-          }
+          for (int c = 0; c < 4; ++c) tmem_ld_32x32(o_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 128; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) tmem_st_32x32(o_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
         }
       }
       tmem_wait_st();
@@ -387,10 +386,11 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       }
       if (row < p.q_len) {
         const size_t stat = static_cast<size_t>(bh) * p.q_len + row;
-        const float m_nat = m_run * 0.69314718055994530942f;  // back from the log2 domain
-        if (p.lse) p.lse[stat] = (l_run == 0.f) ? -INFINITY : m_nat + logf(l_run);
-        if (p.row_max) p.row_max[stat] = m_nat;
-        if (p.row_sum) p.row_sum[stat] = l_run;
+        const float ln2 = 0.69314718055994530942f;  // back from the log2 domain
+        if (p.lse) p.lse[stat] = (l_run == 0.f) ? -INFINITY : m_ref * ln2 + logf(l_run);
+        if (p.row_max) p.row_max[stat] = m_true * ln2;
+        // the carried sum is reported relative to the true maximum, as the reference carries it
+        if (p.row_sum) p.row_sum[stat] = (l_run == 0.f) ? 0.f : l_run * exp2f(m_ref - m_true);
       }
     }
   }
