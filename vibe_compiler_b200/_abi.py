@@ -147,10 +147,12 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not LIBRARY_PATH.exists():
-        raise RuntimeError(f"{LIBRARY_PATH} is missing: run `python -m vibe_compiler_b200.build`. "
+    import os
+    path = Path(os.environ.get("WB200_LIBRARY", LIBRARY_PATH))   # override: load another build of the same ABI
+    if not path.exists():
+        raise RuntimeError(f"{path} is missing: run `python -m vibe_compiler_b200.build`. "
                            "There is no fallback implementation.")
-    lib = C.CDLL(str(LIBRARY_PATH))
+    lib = C.CDLL(str(path))
     for name, (restype, argtypes) in SIGNATURES.items():
         fn = getattr(lib, name)
         fn.restype = restype

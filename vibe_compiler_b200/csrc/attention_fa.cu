@@ -12,11 +12,13 @@
 // One CTA owns 256 query rows of one (batch, head): two 128-row Q tiles, each with its own S and O
 // accumulators in TMEM (S0 S1 O0 O1 = 4 x 128 columns) and its own softmax warpgroup, so the tensor
 // pipe works on one tile while the other tile's softmax runs. Warp 0 = TMA producer (Q once, then
-// K0 V0 K1 V1 ... through a ring of 32 KiB slots), warp 1 = MMA issuer and TMEM owner, warps 2-5 /
-// 6-9 = softmax + rescale + epilogue for Q tile 0 / 1 (thread = query row, so row max and row sum
-// need no shuffles). kPInTmem selects where the rounded P lives: in TMEM, aliasing the first 64
+// K0 V0 K1 V1 ... through a ring of 32 KiB slots), warp 1 = MMA issuer and TMEM owner, warps 4-7 /
+// 8-11 = softmax + rescale + epilogue for Q tile 0 / 1 (thread = query row, so row max and row sum
+// need no shuffles; setmaxnreg moves registers from warpgroup 0 to the softmax warpgroups). kPInTmem selects where the rounded P lives: in TMEM, aliasing the first 64
 // columns of S (A operand read from TMEM, 5 ring slots), or in shared memory (3 ring slots).
 // Roofline: tensor pipe; algorithmic work is 4 * head_dim flop per visible (query, key) pair.
+#include <type_traits>
+
 #include "kernels.h"
 #include "ptx_sm100.cuh"
 
@@ -28,7 +30,15 @@ constexpr int kTileM = 128;       // query rows per Q tile (TMEM lanes)
 constexpr int kTileN = 128;       // keys per KV tile
 constexpr int kTileBytesFa = kTileN * kHd * 2;  // 32 KiB: two 64-element column blocks of 128 rows
 constexpr int kBlockBytes = 128 * 128;          // one [128 rows][128 B] swizzled block
-constexpr int kFaThreads = 320;
+constexpr int kFaThreads = 384;          // warpgroup 0: TMA + MMA warps; warpgroups 1, 2: softmax of Q tile 0, 1
+#ifndef WB200_FA_POLY_EVERY
+#define WB200_FA_POLY_EVERY 0
+#endif
+#ifndef WB200_FA_SPLIT_P
+#define WB200_FA_SPLIT_P 1
+#endif
+constexpr int kPolyEvery = WB200_FA_POLY_EVERY;  // every kPolyEvery-th pair of exponentials runs on the FMA pipe (0: none)
+constexpr bool kSplitP = WB200_FA_SPLIT_P != 0;  // publish P in two halves so PV starts on the first
 constexpr uint32_t kColS0 = 0, kColO0 = 256;    // S_t at t*128, O_t at 256 + t*128
 
 template <bool kPInTmem>
@@ -61,6 +71,26 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+// 2^x on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-4 polynomial
+// (max relative error 2.7e-6), 2^n by adding n to the exponent field. x is clamped at -126.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.0f);
+  const float shifted = x + 12582912.0f;                 // 1.5 * 2^23: the low mantissa bits now hold n
+  const float f = x - (shifted - 12582912.0f);
+  float p = fmaf(0.00957008171826601f, f, 0.05591784045100212f);
+  p = fmaf(p, f, 0.240247443318367f);
+  p = fmaf(p, f, 0.6931217908859253f);
+  p = fmaf(p, f, 0.9999992847442627f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(shifted) << 23));
 }
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -113,11 +143,12 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   auto kv_empty = [&](int s) { return bar_base + 8u * (L::kSlots + s); };
   const uint32_t q_full = bar_base + 8u * (2 * L::kSlots);
   auto s_full = [&](int t) { return bar_base + 8u * (2 * L::kSlots + 1 + t); };
-  auto p_full = [&](int t) { return bar_base + 8u * (2 * L::kSlots + 3 + t); };
-  auto o_done = [&](int t) { return bar_base + 8u * (2 * L::kSlots + 5 + t); };
+  // P of one tile is published in two halves (keys 0-63, 64-127) so PV can start on the first half.
+  auto p_half = [&](int t, int half) { return bar_base + 8u * (2 * L::kSlots + 3 + 2 * t + half); };
+  auto o_done = [&](int t) { return bar_base + 8u * (2 * L::kSlots + 7 + t); };
   uint8_t *bar_ptr = smem + L::kBarOff;
-  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bar_ptr + 8 * (2 * L::kSlots + 7));
-  volatile int *abort_word = reinterpret_cast<volatile int *>(bar_ptr + 8 * (2 * L::kSlots + 8));
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bar_ptr + 8 * (2 * L::kSlots + 9));
+  volatile int *abort_word = reinterpret_cast<volatile int *>(bar_ptr + 8 * (2 * L::kSlots + 10));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh_count = p.batch * p.q_heads;
@@ -137,7 +168,8 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     mbar_init(q_full, 1);
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1);
-      mbar_init(p_full(t), kTileM);
+      mbar_init(p_half(t, 0), kTileM);
+      mbar_init(p_half(t, 1), kTileM);
       mbar_init(o_done(t), 1);
     }
     *abort_word = 0;
@@ -155,6 +187,8 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  if (warp < 4) {
+  setmaxnreg_dec<72>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0 && n_max > 0) {
@@ -195,9 +229,9 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         }
         umma_commit(s_full(t));
       };
-      auto issue_pv = [&](int t, uint32_t v_addr, bool accumulate) {
+      auto issue_pv_half = [&](int t, int half, uint32_t v_addr, bool accumulate) {
 #pragma unroll
-        for (int ks = 0; ks < kTileN / 16; ++ks) {
+        for (int ks = 4 * half; ks < 4 * half + 4; ++ks) {
           const uint64_t bdesc = umma_desc_mnmajor(v_addr + ks * 2048, kBlockBytes);
           const uint32_t acc = (accumulate || ks != 0) ? 1u : 0u;
           if constexpr (kPInTmem) {
@@ -207,7 +241,7 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             umma_f16_ss(tmem_base + kColO0 + t * 128, umma_desc_kmajor(p_addr), bdesc, idesc_o, acc);
           }
         }
-        umma_commit(o_done(t));
+        if (half == 1) umma_commit(o_done(t));
       };
 
       ok = mbar_wait(q_full, 0, abort_word);
@@ -236,9 +270,12 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         bool k_ready = false;
         for (int t = 0; ok && t < 2; ++t) {
           if (j < n_tiles[t]) {
-            if (!mbar_wait(p_full(t), j & 1, abort_word)) { ok = false; break; }
+            if (!mbar_wait(p_half(t, 0), j & 1, abort_word)) { ok = false; break; }
             tc_fence_after();
-            issue_pv(t, v_addr, j > 0);
+            issue_pv_half(t, 0, v_addr, j > 0);
+            if (!mbar_wait(p_half(t, 1), j & 1, abort_word)) { ok = false; break; }
+            tc_fence_after();
+            issue_pv_half(t, 1, v_addr, j > 0);
           }
           if (j + 1 < n_tiles[t]) {
             if (!k_ready) {
@@ -254,9 +291,11 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (has_next) umma_commit(kv_empty(k_slot));
       }
     }
+  }
   } else {
+    setmaxnreg_inc<216>();
     // ------------------------------------------------------------ softmax / rescale / epilogue
-    const int t = (warp - 2) >> 2;          // Q tile of this warpgroup
+    const int t = (warp - 4) >> 2;          // Q tile of this warpgroup
     const int quarter = warp & 3;           // TMEM lane quarter this warp may access
     const int row_in_tile = quarter * 32 + lane;
     const int row = row_base + t * kTileM + row_in_tile;   // query row inside the head
@@ -291,10 +330,18 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           if (!(key < p.kv_visible && key <= causal_limit)) r[i] = 0xff800000u;   // -inf
         }
       }
-      float raw_max = fmax3(__uint_as_float(r[0]), __uint_as_float(r[1]), __uint_as_float(r[2]));
+      // Row maximum: four independent chains of 3-input max.
+      float mx[4];
 #pragma unroll
-      for (int i = 3; i + 1 < 128; i += 2) raw_max = fmax3(raw_max, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-      raw_max = fmaxf(raw_max, __uint_as_float(r[127]));
+      for (int a = 0; a < 4; ++a) mx[a] = fmax3(__uint_as_float(r[32 * a]), __uint_as_float(r[32 * a + 1]), __uint_as_float(r[32 * a + 2]));
+#pragma unroll
+      for (int i = 3; i + 1 < 32; i += 2) {
+#pragma unroll
+        for (int a = 0; a < 4; ++a) mx[a] = fmax3(mx[a], __uint_as_float(r[32 * a + i]), __uint_as_float(r[32 * a + i + 1]));
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a) mx[a] = fmaxf(mx[a], __uint_as_float(r[32 * a + 31]));
+      const float raw_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       m_true = fmaxf(m_true, raw_max * p.scale_log2);     // scale > 0, so max commutes with the scaling
       float alpha = 1.0f;
       if (m_true - m_ref > kRescaleThreshold) {           // also taken when m_ref is still -inf
@@ -302,15 +349,39 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         m_ref = m_true;
       }
       const float m_exp = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float row_sum = 0.f;
+      // acc' = acc * alpha (rare): needs PV of the previous tile to have landed in TMEM, and must be done
+      // before any PV of this tile is issued, i.e. before the first half of P is published.
+      if (j > 0) {
+        if (!mbar_wait(o_done(t), (j - 1) & 1, abort_word)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            uint32_t o[32];
+            tmem_ld_32x32(o_addr + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32(o_addr + c * 32, o);
+          }
+        }
+      }
+      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      auto exp_phase = [&](auto masked_tag) {
+      constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float e0 = ex2_approx(fmaf(__uint_as_float(r[32 * c + i]), p.scale_log2, -m_exp));
-          const float e1 = ex2_approx(fmaf(__uint_as_float(r[32 * c + i + 1]), p.scale_log2, -m_exp));
-          row_sum += e0 + e1;
+          const float x0 = fmaf(__uint_as_float(r[32 * c + i]), p.scale_log2, -m_exp);
+          const float x1 = fmaf(__uint_as_float(r[32 * c + i + 1]), p.scale_log2, -m_exp);
+          // Masked tiles keep the hardware ex2 for every element: exp2(-inf) must be exactly 0 there.
+          constexpr int kEvery = kPolyEvery > 0 ? kPolyEvery : 1;
+          const bool poly = !kMasked && kPolyEvery > 0 && ((i >> 1) % kEvery) == 0;
+          const float e0 = poly ? ex2_poly(x0) : ex2_approx(x0);
+          const float e1 = poly ? ex2_poly(x1) : ex2_approx(x1);
+          sum[(i >> 1) & 3] += e0 + e1;
           if constexpr (kBf16) {
             __nv_bfloat162 v = __floats2bfloat162_rn(e0, e1);
             packed[i >> 1] = *reinterpret_cast<uint32_t *>(&v);
@@ -330,26 +401,18 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
           }
         }
-      }
-      l_run = l_run * alpha + row_sum;
-      // acc' = acc * alpha: needs PV of the previous tile to have landed in TMEM.
-      if (j > 0) {
-        if (!mbar_wait(o_done(t), (j - 1) & 1, abort_word)) { ok = false; break; }
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) tmem_ld_32x32(o_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
-          tmem_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 128; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-#pragma unroll
-          for (int c = 0; c < 4; ++c) tmem_st_32x32(o_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
+        if (kSplitP ? (c & 1) : (c == 3)) {   // publish the completed half (or everything at the end)
+          tmem_wait_st();
+          if constexpr (!kPInTmem) fence_proxy_async_smem();
+          tc_fence_before();
+          if (kSplitP) mbar_arrive(p_half(t, c >> 1));
+          else { mbar_arrive(p_half(t, 0)); mbar_arrive(p_half(t, 1)); }
         }
       }
-      tmem_wait_st();
-      if constexpr (!kPInTmem) fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(p_full(t));
+      };
+      if (need_mask) exp_phase(std::true_type{});
+      else exp_phase(std::false_type{});
+      l_run = l_run * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
     }
 
     // Finalize: out = acc * (1 / l), rounded once to the storage type.
