@@ -91,11 +91,15 @@ class ClockSampler:
             self.result = {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max_clock, "reasons": sorted(reasons), "samples": len(clocks)}
 
 
-def timed_steps(fn, steps, warmup, torch, dist=None):
+def timed_steps(fn, steps, warmup, torch, dist=None, check=None):
     """Warm-up, then `steps` launches bracketed by barrier + synchronize; per-launch CUDA events on the
-    launching stream. Returns (total ms over the bracket, mean per-launch ms)."""
-    for _ in range(warmup):
+    launching stream. Returns (total ms over the bracket, mean per-launch ms). `check` runs after the
+    first warm-up launch and raises if the device reported a failure, before any time is spent."""
+    for i in range(warmup):
         fn()
+        if i == 0 and check is not None:
+            torch.cuda.synchronize()
+            check()
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
@@ -246,7 +250,7 @@ def main():
 
     launches_before = backend.launch_count
     with ClockSampler(local_rank) as sampler:
-        total_ms, launch_ms = timed_steps(fa_step, args.steps, args.warmup, torch, dist)
+        total_ms, launch_ms = timed_steps(fa_step, args.steps, args.warmup, torch, dist, check=backend.poll)
     backend.poll()
     launches = backend.launch_count - launches_before - args.warmup
     times = torch.tensor([total_ms, launch_ms], device=device, dtype=torch.float64)
@@ -290,7 +294,7 @@ def main():
         fout = torch.empty_like(fq)
         flse = torch.empty(FD["batch"], FD["q_heads"], 1, device=device)
         fd_bytes = 2 * fk.numel() * 2
-        _, fd_ms = timed_steps(lambda: backend.attention_fd(fq, fk, fv, scale, out=fout, lse=flse), args.steps, args.warmup, torch)
+        _, fd_ms = timed_steps(lambda: backend.attention_fd(fq, fk, fv, scale, out=fout, lse=flse), args.steps, args.warmup, torch, check=backend.poll)
         backend.poll()
         fd_gbs = fd_bytes / (fd_ms * 1e-3) / 1e9
         extras["fd_decode"] = {"workload": "FD decode bf16 B64 Hq32 Hkv8 KV32768 D128, inputs (8.6 GB) larger than L2", "value": fd_gbs,
@@ -304,7 +308,7 @@ def main():
         gb = (torch.rand(GEMM["k"], GEMM["n"], device=device, generator=gen) * 2 - 1).bfloat16()
         gbias = torch.randn(GEMM["n"], device=device, generator=gen) * 0.02
         gout = torch.empty(GEMM["m"], GEMM["n"], device=device, dtype=torch.bfloat16)
-        _, g_ms = timed_steps(lambda: backend.gemm_epilogue(ga, gb, gbias, epilogue=abi.EPI_BIAS_GELU, out=gout), args.steps, args.warmup, torch)
+        _, g_ms = timed_steps(lambda: backend.gemm_epilogue(ga, gb, gbias, epilogue=abi.EPI_BIAS_GELU, out=gout), args.steps, args.warmup, torch, check=backend.poll)
         backend.poll()
         g_tflops = 2 * GEMM["m"] * GEMM["n"] * GEMM["k"] / (g_ms * 1e-3) / 1e12
         extras["gemm_bias_gelu"] = {"workload": "GEMM 8192^3 bf16 + f32 bias + GELU(erf) -> bf16", "value": g_tflops, "unit": "TFLOP/s",

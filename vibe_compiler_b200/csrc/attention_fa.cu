@@ -38,7 +38,15 @@ constexpr int kFaThreads = 384;          // warpgroup 0: TMA + MMA warps; warpgr
 #define WB200_FA_SPLIT_P 1
 #endif
 constexpr int kPolyEvery = WB200_FA_POLY_EVERY;  // every kPolyEvery-th pair of exponentials runs on the FMA pipe (0: none)
-constexpr bool kSplitP = WB200_FA_SPLIT_P != 0;  // publish P in two halves so PV starts on the first
+constexpr bool kSplitP = WB200_FA_SPLIT_P != 0;  // publish P in four 32-key parts so PV starts while exp still runs
+#ifndef WB200_FA_P_PARTS
+#define WB200_FA_P_PARTS 2
+#endif
+#ifndef WB200_FA_FENCE_EVERY_PART
+#define WB200_FA_FENCE_EVERY_PART 1
+#endif
+constexpr int kPParts = WB200_FA_P_PARTS;        // 1, 2 or 4 publications of P per tile
+constexpr int kChunksPerPart = 4 / kPParts;
 constexpr uint32_t kColS0 = 0, kColO0 = 256;    // S_t at t*128, O_t at 256 + t*128
 
 template <bool kPInTmem>
@@ -50,6 +58,14 @@ struct FaSmem {
   static constexpr int kBarOff = kPOff + (kPInTmem ? 0 : 2 * kTileBytesFa);
   static constexpr size_t kBytes = kBarOff + 256 + 1024;
 };
+
+#ifdef WB200_FA_TRACE
+// Debug build only: clock64 time stamps of one CTA, read back through wb200_debug_fa_trace.
+__device__ long long g_fa_trace[8192];
+#define FA_TRACE(slot, index) do { if (blockIdx.x == 0) g_fa_trace[(slot) * 64 + ((index) & 63)] = clock64(); } while (0)
+#else
+#define FA_TRACE(slot, index) do { } while (0)
+#endif
 
 struct FaParams {
   int batch, q_heads, kv_heads, group;
@@ -144,11 +160,11 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   const uint32_t q_full = bar_base + 8u * (2 * L::kSlots);
   auto s_full = [&](int t) { return bar_base + 8u * (2 * L::kSlots + 1 + t); };
   // P of one tile is published in two halves (keys 0-63, 64-127) so PV can start on the first half.
-  auto p_half = [&](int t, int half) { return bar_base + 8u * (2 * L::kSlots + 3 + 2 * t + half); };
-  auto o_done = [&](int t) { return bar_base + 8u * (2 * L::kSlots + 7 + t); };
+  auto p_part = [&](int t, int part) { return bar_base + 8u * (2 * L::kSlots + 3 + kPParts * t + part); };
+  auto o_done = [&](int t) { return bar_base + 8u * (2 * L::kSlots + 3 + 2 * kPParts + t); };
   uint8_t *bar_ptr = smem + L::kBarOff;
-  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bar_ptr + 8 * (2 * L::kSlots + 9));
-  volatile int *abort_word = reinterpret_cast<volatile int *>(bar_ptr + 8 * (2 * L::kSlots + 10));
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bar_ptr + 8 * (2 * L::kSlots + 5 + 2 * kPParts));
+  volatile int *abort_word = reinterpret_cast<volatile int *>(bar_ptr + 8 * (2 * L::kSlots + 6 + 2 * kPParts));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh_count = p.batch * p.q_heads;
@@ -168,8 +184,7 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     mbar_init(q_full, 1);
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1);
-      mbar_init(p_half(t, 0), kTileM);
-      mbar_init(p_half(t, 1), kTileM);
+      for (int part = 0; part < kPParts; ++part) mbar_init(p_part(t, part), kTileM);
       mbar_init(o_done(t), 1);
     }
     *abort_word = 0;
@@ -187,8 +202,11 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // setmaxnreg.inc blocks until the CTA's own register pool can supply the request, so the totals after
+  // reallocation (128 * 88 + 256 * 208) must not exceed what the CTA was launched with (384 * 168).
+  static_assert(128 * 88 + 256 * 208 <= kFaThreads * 168, "setmaxnreg totals exceed the launch allocation");
   if (warp < 4) {
-  setmaxnreg_dec<72>();
+  setmaxnreg_dec<88>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0 && n_max > 0) {
@@ -219,29 +237,41 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       uint32_t phase = 0;
       bool ok = true;
       auto advance = [&]() { if (++slot == L::kSlots) { slot = 0; phase ^= 1u; } };
+      // Descriptors differ only in the 14-bit start-address field, so a tile's descriptor is built once
+      // and each k-step adds a compile-time constant to it.
+      const uint64_t q_desc[2] = {umma_desc_kmajor(smem_base + L::kQOff), umma_desc_kmajor(smem_base + L::kQOff + kTileBytesFa)};
+#ifdef WB200_FA_TRACE
+      int s_count[2] = {0, 0};
+#endif
       auto issue_s = [&](int t, uint32_t k_addr) {
-        const uint32_t q_addr = smem_base + L::kQOff + t * kTileBytesFa;
+        const uint64_t k_desc = umma_desc_kmajor(k_addr);
+        const uint32_t d_tmem = tmem_base + kColS0 + t * 128;
 #pragma unroll
         for (int ks = 0; ks < kHd / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * kBlockBytes + (ks & 3) * 32;
-          umma_f16_ss(tmem_base + kColS0 + t * 128, umma_desc_kmajor(q_addr + off),
-                      umma_desc_kmajor(k_addr + off), idesc_s, ks != 0 ? 1u : 0u);
+          const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kBlockBytes + (ks & 3) * 32) >> 4);
+          umma_f16_ss(d_tmem, q_desc[t] + off, k_desc + off, idesc_s, ks != 0 ? 1u : 0u);
         }
         umma_commit(s_full(t));
+#ifdef WB200_FA_TRACE
+        FA_TRACE(0 + t, s_count[t]++);
+#endif
       };
-      auto issue_pv_half = [&](int t, int half, uint32_t v_addr, bool accumulate) {
+      // PV over the keys of one published part of P.
+      auto issue_pv_part = [&](int t, int part, uint32_t v_addr, bool accumulate) {
+        const uint64_t v_desc = umma_desc_mnmajor(v_addr, kBlockBytes);
+        const uint32_t d_tmem = tmem_base + kColO0 + t * 128;
 #pragma unroll
-        for (int ks = 4 * half; ks < 4 * half + 4; ++ks) {
-          const uint64_t bdesc = umma_desc_mnmajor(v_addr + ks * 2048, kBlockBytes);
+        for (int ks = (8 / kPParts) * part; ks < (8 / kPParts) * (part + 1); ++ks) {
+          const uint64_t bdesc = v_desc + static_cast<uint64_t>((ks * 2048) >> 4);
           const uint32_t acc = (accumulate || ks != 0) ? 1u : 0u;
           if constexpr (kPInTmem) {
-            umma_f16_ts(tmem_base + kColO0 + t * 128, tmem_base + kColS0 + t * 128 + ks * 8, bdesc, idesc_o, acc);
+            umma_f16_ts(d_tmem, tmem_base + kColS0 + t * 128 + ks * 8, bdesc, idesc_o, acc);
           } else {
             const uint32_t p_addr = smem_base + L::kPOff + t * kTileBytesFa + (ks >> 2) * kBlockBytes + (ks & 3) * 32;
-            umma_f16_ss(tmem_base + kColO0 + t * 128, umma_desc_kmajor(p_addr), bdesc, idesc_o, acc);
+            umma_f16_ss(d_tmem, umma_desc_kmajor(p_addr), bdesc, idesc_o, acc);
           }
         }
-        if (half == 1) umma_commit(o_done(t));
+        if (part == kPParts - 1) umma_commit(o_done(t));
       };
 
       ok = mbar_wait(q_full, 0, abort_word);
@@ -270,12 +300,15 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         bool k_ready = false;
         for (int t = 0; ok && t < 2; ++t) {
           if (j < n_tiles[t]) {
-            if (!mbar_wait(p_half(t, 0), j & 1, abort_word)) { ok = false; break; }
-            tc_fence_after();
-            issue_pv_half(t, 0, v_addr, j > 0);
-            if (!mbar_wait(p_half(t, 1), j & 1, abort_word)) { ok = false; break; }
-            tc_fence_after();
-            issue_pv_half(t, 1, v_addr, j > 0);
+#pragma unroll
+            for (int part = 0; part < kPParts; ++part) {
+              if (!mbar_wait_spin(p_part(t, part), j & 1, abort_word)) { ok = false; break; }
+              if (WB200_FA_FENCE_EVERY_PART || part == 0) tc_fence_after();
+              if (part == 0) FA_TRACE(2 + t, j);
+              issue_pv_part(t, part, v_addr, j > 0);
+            }
+            if (!ok) break;
+            FA_TRACE(4 + t, j);
           }
           if (j + 1 < n_tiles[t]) {
             if (!k_ready) {
@@ -293,7 +326,7 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     }
   }
   } else {
-    setmaxnreg_inc<216>();
+    setmaxnreg_inc<208>();
     // ------------------------------------------------------------ softmax / rescale / epilogue
     const int t = (warp - 4) >> 2;          // Q tile of this warpgroup
     const int quarter = warp & 3;           // TMEM lane quarter this warp may access
@@ -315,6 +348,8 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     for (int j = 0; ok && j < my_tiles; ++j) {
       if (!mbar_wait(s_full(t), j & 1, abort_word)) { ok = false; break; }
       tc_fence_after();
+      const bool tracer = lane == 0;
+      if (tracer) FA_TRACE(8 + 16 * t + quarter, j);
       const int key0 = j * kTileN;
       uint32_t r[128];
 #pragma unroll
@@ -342,6 +377,7 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 #pragma unroll
       for (int a = 0; a < 4; ++a) mx[a] = fmaxf(mx[a], __uint_as_float(r[32 * a + 31]));
       const float raw_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      if (tracer) FA_TRACE(12 + 16 * t + quarter, j);
       m_true = fmaxf(m_true, raw_max * p.scale_log2);     // scale > 0, so max commutes with the scaling
       float alpha = 1.0f;
       if (m_true - m_ref > kRescaleThreshold) {           // also taken when m_ref is still -inf
@@ -401,12 +437,13 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
           }
         }
-        if (kSplitP ? (c & 1) : (c == 3)) {   // publish the completed half (or everything at the end)
+        if ((c + 1) % kChunksPerPart == 0) {   // a part of P is complete: publish it
           tmem_wait_st();
           if constexpr (!kPInTmem) fence_proxy_async_smem();
           tc_fence_before();
-          if (kSplitP) mbar_arrive(p_half(t, c >> 1));
-          else { mbar_arrive(p_half(t, 0)); mbar_arrive(p_half(t, 1)); }
+          mbar_arrive(p_part(t, c / kChunksPerPart));
+          if (tracer && c == 3) FA_TRACE(16 + 16 * t + quarter, j);
+          if (tracer && c == kChunksPerPart - 1) FA_TRACE(20 + 16 * t + quarter, j);
         }
       }
       };
@@ -505,6 +542,12 @@ int p_in_tmem_mode() {
 }
 
 }  // namespace
+
+#ifdef WB200_FA_TRACE
+extern "C" int wb200_debug_fa_trace(long long *out, int count) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_fa_trace, sizeof(long long) * count));
+}
+#endif
 
 bool attention_fa_umma_supports(const AttentionArgs &a) {
   if (a.format != WB200_BF16 && a.format != WB200_F16) return false;

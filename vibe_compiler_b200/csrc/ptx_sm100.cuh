@@ -77,6 +77,26 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Low-latency variant for a single issuing thread: polls without suspending for a short while (the
+// expected case is a wait of well under a microsecond), then falls back to the bounded wait above.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int *abort_word) {
+#pragma unroll 1
+  for (int i = 0; i < 4096; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
+  return mbar_wait(bar, parity, abort_word);
+}
+
 // Generic-proxy writes to shared memory must be fenced before the async proxy (TMA, UMMA) reads them.
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
