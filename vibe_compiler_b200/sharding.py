@@ -1,0 +1,55 @@
+"""Host-side partitioning for multi-GPU runs of the hot path (one process per GPU).
+
+Independent units (FA: batch x head; FD with many sequences: batch x kv-head; GEMM: row blocks) are
+dealt out in contiguous blocks with no data-path collective. The long-context decode shards the KV
+sequence instead: every rank computes the un-finalized (acc, m, l) state of its contiguous KV range,
+the states are all-gathered and left-folded in ascending shard order - the fold order of the
+reference's spatial flash-decoding materialisation
+(lib/Wafer/Transforms/Linalg/SpatialRegionMaterialization.cpp:2420-2433).
+"""
+from __future__ import annotations
+
+from typing import Callable, Tuple
+
+import torch
+
+
+def unit_range(units: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Contiguous block [begin, end) of `units` independent work items owned by `rank`.
+    The first `units % world_size` ranks own one extra unit."""
+    if world_size < 1 or not 0 <= rank < world_size:
+        raise ValueError("rank must lie in [0, world_size)")
+    base, extra = divmod(units, world_size)
+    begin = rank * base + min(rank, extra)
+    return begin, begin + base + (1 if rank < extra else 0)
+
+
+def sequence_range(kv_len: int, world_size: int, rank: int, granule: int = 64) -> Tuple[int, int]:
+    """Contiguous KV interval of `rank`, boundaries rounded to `granule` keys (the decode kernel's
+    per-CTA granule) so every shard but the last is a whole number of tiles."""
+    per = -(-kv_len // world_size)
+    per = -(-per // granule) * granule
+    begin = min(rank * per, kv_len)
+    return begin, min(begin + per, kv_len)
+
+
+def sharded_decode(state_fn: Callable[[int, int], torch.Tensor], merge_fn: Callable[[torch.Tensor], torch.Tensor],
+                   kv_len: int, group=None) -> torch.Tensor:
+    """Sequence-sharded flash-decoding step.
+
+    state_fn(begin, end) -> this rank's [batch, q_heads, D + 2] float32 state for keys [begin, end)
+                            (B200TargetModelBackend.attention_fd_partial on the GPU);
+    merge_fn(states)     -> finalized output from [world, batch, q_heads, D + 2] states in shard order
+                            (B200TargetModelBackend.attention_fd_merge).
+    The only exchange is one all-gather of the states (D + 2 floats per query head and rank).
+    """
+    import torch.distributed as dist
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    begin, end = sequence_range(kv_len, world, rank)
+    state = state_fn(begin, end).contiguous()
+    if world == 1:
+        return merge_fn(state.unsqueeze(0))
+    gathered = [torch.empty_like(state) for _ in range(world)]
+    dist.all_gather(gathered, state, group=group)
+    return merge_fn(torch.stack(gathered))   # index = rank = ascending KV order
