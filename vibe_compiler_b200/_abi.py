@@ -129,6 +129,7 @@ SIGNATURES = {
     "wb200_reduce": (C.c_int, [C.c_void_p, C.POINTER(ReduceRequest), C.POINTER(Evidence)]),
     "wb200_attention_fa": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams)]),
     "wb200_attention_fd": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams), C.c_uint32]),
+    "wb200_attention_fd_static": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams), C.c_uint32]),
     "wb200_attention_fd_partial": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams), C.c_uint32, C.c_void_p]),
     "wb200_attention_fd_merge": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams), C.c_void_p, C.c_uint32]),
     "wb200_gemm_epilogue": (C.c_int, [C.c_void_p, C.POINTER(GemmEpilogueParams)]),

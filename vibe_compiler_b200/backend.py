@@ -307,6 +307,22 @@ class B200TargetModelBackend:
         self._check(self._lib.wb200_attention_fd(self._handle, C.byref(p), kv_splits))
         return out
 
+    def attention_fd_static(self, q, k, v, scale: float, *, kv_splits: int = 0, out=None, lse=None,
+                            zero_fully_masked: bool = False, stream: Optional[int] = None):
+        """Flash-decoding without any allocation inside the call (CUDA tensors only; `out` should be
+        passed by callers that must not allocate either). The split-KV partial records use a fixed
+        16 MiB array inside the library, shared by all calls: do not overlap two such calls on the GPU.
+        Raises WB200Error (limit) when batch * q_heads * kv_splits * (head_dim + 2) exceeds 4 Mi floats."""
+        if not q.is_cuda:
+            raise ValueError("attention_fd_static takes CUDA tensors")
+        if out is None:
+            out = torch.empty_like(q)
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream
+        p = self._attention_params(q, k, v, out, scale, False, zero_fully_masked, 0, 0, 0, lse, None, None, stream)
+        self._check(self._lib.wb200_attention_fd_static(self._handle, C.byref(p), kv_splits))
+        return out
+
     def attention_fd_partial(self, q, k, v, scale: float, *, kv_splits: int = 0, state=None, key_start: int = 0,
                              key_end: int = 0, stream: Optional[int] = None):
         """One sequence shard's un-finalized (acc[D], m, l) state, [batch, q_heads, D + 2] float32."""

@@ -440,3 +440,83 @@ wb200_status launch_attention_fd_merge(const AttentionArgs &a, const float *stat
 }
 
 }  // namespace wb200
+
+// ------------------------------------------------------------------ allocation-free entry point
+// Some callers may not allocate device memory when they reach this library: code running while a
+// CUDA stream is being captured, or inside a latency-critical serving loop whose memory was carved up
+// at start-up and where a cudaMalloc (an implicit device synchronisation) is not acceptable, or a
+// host that shares the GPU under a fixed memory budget. For them the split-KV partial records live in
+// a fixed array inside the library image instead of in a buffer the backend allocates on demand.
+#include <mutex>
+
+#include "backend.h"
+
+namespace wb200 {
+namespace {
+
+constexpr size_t kStaticScratchFloats = size_t(4) << 20;   // 16 MiB, held by every GPU that loads the library
+static __device__ __align__(256) float g_fd_static_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+float *g_fd_static_scratch_address[kMaxDevices] = {nullptr};
+std::mutex g_fd_static_scratch_mutex;
+
+// In host code `g_fd_static_scratch` names a host-side handle, not device memory; the address a kernel
+// can use has to be asked for, once per device, with that device current.
+wb200_status static_scratch_for_device(int device, float **out) {
+  if (device < 0 || device >= kMaxDevices) return fail(WB200_ERR_LIMIT, "device index beyond the static scratch table");
+  std::lock_guard<std::mutex> lock(g_fd_static_scratch_mutex);
+  if (!g_fd_static_scratch_address[device]) {
+    void *address = nullptr;
+    WB200_CUDA_CHECK(cudaGetSymbolAddress(&address, g_fd_static_scratch));
+    g_fd_static_scratch_address[device] = static_cast<float *>(address);
+  }
+  *out = g_fd_static_scratch_address[device];
+  return WB200_OK;
+}
+
+}  // namespace
+}  // namespace wb200
+
+extern "C" wb200_status wb200_attention_fd_static(wb200_backend *backend, const wb200_attention_params *p,
+                                                  uint32_t kv_splits) {
+  using namespace wb200;
+  if (!backend || !p) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  if (p->memory != WB200_MEM_DEVICE)
+    return fail(WB200_ERR_UNSUPPORTED, "the allocation-free decode takes device buffers only (staging host buffers would allocate)");
+  if (!p->q || !p->k || !p->v || !p->out) return fail(WB200_ERR_INVALID_ARGUMENT, "q, k, v and out must not be null");
+  if (p->q_len != 1) return fail(WB200_ERR_INVALID_ARGUMENT, "flash-decoding takes query length 1");
+  if (p->batch == 0 || p->q_heads == 0 || p->kv_heads == 0 || p->kv_len == 0 || p->q_heads % p->kv_heads != 0 ||
+      p->kv_len > 0x7fffffffu)
+    return fail(WB200_ERR_INVALID_ARGUMENT, "invalid attention extents");
+  AttentionArgs a{};
+  a.batch = p->batch; a.q_heads = p->q_heads; a.kv_heads = p->kv_heads;
+  a.q_len = 1; a.kv_len = p->kv_len; a.head_dim = p->head_dim;
+  a.format = p->format;
+  a.causal = p->causal ? 1 : 0;
+  a.zero_fully_masked = p->zero_fully_masked ? 1 : 0;
+  a.scale = p->scale;
+  a.causal_offset = p->query_start - p->key_start;
+  a.kv_valid = p->key_end > 0 ? p->key_end - p->key_start : static_cast<int64_t>(p->kv_len);
+  a.q = p->q; a.k = p->k; a.v = p->v; a.out = p->out;
+  a.lse = p->lse; a.row_max = p->row_max; a.row_sum = p->row_sum;
+  if (!attention_fd_supports(a))
+    return fail(WB200_ERR_UNSUPPORTED, "flash-decoding kernel takes f16/bf16 storage, head_dim 128, group size <= 16");
+  DeviceGuard guard(backend->device);
+  uint32_t splits = kv_splits;
+  if (splits == 0) {
+    splits = fd_choose_splits(a, backend->sm_count);
+    while (splits > 2 && fd_partial_floats(a, splits) > kStaticScratchFloats) splits = (splits + 1) / 2;
+  }
+  const size_t needed = fd_partial_floats(a, splits);
+  if (needed > kStaticScratchFloats)
+    return fail(WB200_ERR_LIMIT, "allocation-free decode: batch * q_heads * kv_splits * (head_dim + 2) = " + std::to_string(needed) +
+                                     " floats exceeds the fixed scratch of " + std::to_string(kStaticScratchFloats) + " floats (16 MiB)");
+  float *scratch = nullptr;
+  wb200_status st = static_scratch_for_device(backend->device, &scratch);
+  if (st != WB200_OK) return st;
+  // Stage 1 writes every record stage 2 reads, so nothing left by an earlier call needs clearing.
+  st = launch_attention_fd(a, splits, scratch, 1, nullptr, static_cast<cudaStream_t>(p->stream));
+  if (st == WB200_OK) backend->launches += 2;
+  return st;
+}
