@@ -459,29 +459,36 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       float coefficient = 1.0f / l_run;
       if (p.zero_fully_masked && l_run == 0.f) coefficient = 0.f;
       const size_t out_row = (static_cast<size_t>(bh) * p.q_len + row) * kHd;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        if (my_tiles > 0) {
-          tmem_ld_32x32(o_addr + c * 32, r);
-          tmem_wait_ld();
-        } else {
+      uint32_t r[128];
+      if (my_tiles > 0) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
-        }
-        if (row < p.q_len) {
-          uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + out_row + c * 32;
+        for (int c = 0; c < 4; ++c) tmem_ld_32x32(o_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32 * c]));
+        tmem_wait_ld();
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; i += 8) {
-            uint32_t w[4];
+        for (int i = 0; i < 128; ++i) r[i] = 0u;
+      }
+      if (row < p.q_len) {
+        uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + out_row;
+        // 0 * (1/0): a row that saw no key and is not zero-filled is the canonical quiet NaN of the format.
+        const bool nan_row = !(coefficient == coefficient) || (l_run == 0.f && !p.zero_fully_masked);
+        const uint32_t nan_pair = kBf16 ? 0x7fc07fc0u : 0x7e007e00u;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const uint32_t lo = narrow_bits(__uint_as_float(r[i + 2 * k]) * coefficient, p.out_format);
-              const uint32_t hi = narrow_bits(__uint_as_float(r[i + 2 * k + 1]) * coefficient, p.out_format);
-              w[k] = lo | (hi << 16);
+        for (int i = 0; i < 128; i += 8) {
+          uint32_t w[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float lo = __uint_as_float(r[i + 2 * k]) * coefficient, hi = __uint_as_float(r[i + 2 * k + 1]) * coefficient;
+            if constexpr (kBf16) {
+              __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+              w[k] = *reinterpret_cast<uint32_t *>(&v);
+            } else {
+              __half2 v = __floats2half2_rn(lo, hi);
+              w[k] = *reinterpret_cast<uint32_t *>(&v);
             }
-            *reinterpret_cast<uint4 *>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
+            if (nan_row) w[k] = nan_pair;
           }
+          *reinterpret_cast<uint4 *>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
       if (row < p.q_len) {

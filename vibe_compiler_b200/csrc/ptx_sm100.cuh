@@ -61,7 +61,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait. `abort_word` lives in shared memory; any role that gives up sets it and every other
 // spinning role sees it within a few hundred polls and gives up too.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_word) {
+// `site` identifies the wait in the status word when it gives up (1 if not given).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_word, int site = kDeviceWaitTimeout) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   uint32_t polls = 0;
@@ -70,7 +71,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if ((++polls & 255u) == 0u) {
       if (*abort_word != 0) return false;
       if (clock64() - start > kSpinCycleLimit) {
-        *abort_word = kDeviceWaitTimeout;
+        *abort_word = site;
         return false;
       }
     }
@@ -90,11 +91,11 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 }
 // Low-latency variant for a single issuing thread: polls without suspending for a short while (the
 // expected case is a wait of well under a microsecond), then falls back to the bounded wait above.
-__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int *abort_word) {
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int *abort_word, int site = kDeviceWaitTimeout) {
 #pragma unroll 1
   for (int i = 0; i < 4096; ++i)
     if (mbar_test_wait(bar, parity)) return true;
-  return mbar_wait(bar, parity, abort_word);
+  return mbar_wait(bar, parity, abort_word, site);
 }
 
 // Generic-proxy writes to shared memory must be fenced before the async proxy (TMA, UMMA) reads them.
