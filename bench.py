@@ -29,6 +29,7 @@ sys.path.insert(0, str(ROOT))
 FA = dict(batch=4, heads=32, kv_heads=32, seq=4096, head_dim=128)
 FD = dict(batch=64, q_heads=32, kv_heads=8, kv_len=32768, head_dim=128)
 GEMM = dict(m=8192, n=8192, k=8192)
+LAYER = dict(batch=8, seq=2048)   # Llama-style decoder layer: d_model 4096, 32/8 heads, head_dim 128, FFN 14336
 SEED = 20260803
 
 
@@ -140,6 +141,29 @@ def cpu_sample(threads: int, units: int = CPU_SAMPLE_UNITS):
     seconds = time.perf_counter() - t0
     return seconds, fa_flops(1, units, s, d), (f"{units} of {FA['batch'] * FA['heads']} (batch, head) units: seq {s}, head_dim {d}, causal, "
                                                f"{threads} threads")
+
+
+def layer_extra(backend, args, torch, dist, rank, world, device, peak):
+    """Llama-style decoder layer forward (batch 8 x seq 2048), tensor-parallel over the ranks: heads and FFN columns are
+    sharded, the two partial sums are NCCL all-reduces. Strong scaling: total work is fixed as the world grows."""
+    from vibe_compiler_b200.decoder_layer import LayerConfig, ShardedDecoderLayer, layer_flops, random_weights
+    cfg = LayerConfig()
+    layer = ShardedDecoderLayer(backend, cfg, random_weights(cfg, seed=SEED), rank=rank, world_size=world, device=device)
+    gen = torch.Generator(device="cpu").manual_seed(SEED + 5)
+    x = torch.randn(LAYER["batch"], LAYER["seq"], cfg.d_model, generator=gen).bfloat16().to(device)
+    total_ms, _ = timed_steps(lambda: layer.forward(x), args.steps, args.warmup, torch, dist=dist, check=backend.poll)
+    backend.poll()
+    elapsed = torch.tensor([total_ms], device=device)
+    if dist is not None:
+        dist.all_reduce(elapsed, op=dist.ReduceOp.MAX)
+    ms = elapsed.item() / args.steps
+    flops = layer_flops(cfg, LAYER["batch"], LAYER["seq"])
+    tflops = flops / (ms * 1e-3) / 1e12
+    return {"workload": f"decoder layer forward bf16 d4096 32/8 heads hd128 FFN14336, batch 8 x seq 2048, TP{world} (NCCL all-reduce after o-proj and down-proj)",
+            "value": tflops, "unit": "TFLOP/s", "ms_per_step": ms, "scaling": "strong", "tokens_per_s": LAYER["batch"] * LAYER["seq"] / (ms * 1e-3),
+            "kernels_per_step": 10, "collectives_per_step": 0 if world == 1 else 2,
+            "roofline": {"bound": "tensor", "achieved": tflops / world, "peak": peak["bf16_tflops_sustained"], "unit": "TFLOP/s per GPU",
+                         "frac": tflops / world / peak["bf16_tflops_sustained"], "traffic": None, "peak_source": peak["source"] + " (sustained)"}}
 
 
 def run_reference(args):
@@ -284,9 +308,10 @@ def main():
     del hq, hk, hv, hout, hlse
 
     extras = {}
-    if not args.skip_extras and world == 1:
-        del q, k, v, out
+    if not args.skip_extras:
+        q = k = v = out = None
         torch.cuda.empty_cache()
+    if not args.skip_extras and world == 1:
         # ------------------------------------------------------------ FD decode (HBM bound)
         fq = torch.randn(FD["batch"], FD["q_heads"], 1, FD["head_dim"], device=device, generator=gen).bfloat16()
         fk = torch.randn(FD["batch"], FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
@@ -315,6 +340,11 @@ def main():
                                     "ms_per_step": g_ms,
                                     "roofline": {"bound": "tensor", "achieved": g_tflops, "peak": peak["bf16_tflops"], "unit": "TFLOP/s",
                                                  "frac": g_tflops / peak["bf16_tflops"], "traffic": None, "peak_source": peak["source"]}}
+
+    if not args.skip_extras:
+        ga = gb = gout = fk = fv = None
+        torch.cuda.empty_cache()
+        extras["decoder_layer"] = layer_extra(backend, args, torch, dist, rank, world, device, peak)
 
     if rank == 0:
         cpu_threads = os.cpu_count() or 1

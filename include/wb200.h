@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define WB200_ABI_VERSION 1
+#define WB200_ABI_VERSION 2
 #define WB200_MAX_RANK 8
 
 typedef struct wb200_backend wb200_backend;
@@ -236,6 +236,10 @@ wb200_status wb200_reduce(wb200_backend *backend, const wb200_reduce_request *re
  * returns without synchronising; device status is then read by wb200_backend_poll(). */
 typedef enum wb200_memory { WB200_MEM_HOST = 0, WB200_MEM_DEVICE = 1 } wb200_memory;
 
+/* Where wb200_attention_fa writes `out`: head-major like q, or token-major [batch, q_len, q_heads, head_dim]
+ * (the row layout a following output-projection GEMM reads). */
+typedef enum wb200_out_layout { WB200_OUT_HEAD_MAJOR = 0, WB200_OUT_TOKEN_MAJOR = 1 } wb200_out_layout;
+
 typedef struct wb200_attention_params {
   uint32_t batch, q_heads, kv_heads; /* q_heads % kv_heads == 0 (grouped queries) */
   uint32_t q_len, kv_len, head_dim;
@@ -255,6 +259,8 @@ typedef struct wb200_attention_params {
   float *row_max;  /* optional: carried state m */
   float *row_sum;  /* optional: carried state l */
   void *stream;
+  uint32_t out_layout; /* wb200_out_layout; flash-attention prefill only */
+  uint32_t reserved;
 } wb200_attention_params;
 
 /* Flash-attention prefill: online (m, l, acc) update over KV tiles, K2 never split across workers.
@@ -298,7 +304,9 @@ wb200_status wb200_attention_fd_merge(wb200_backend *backend, const wb200_attent
 typedef enum wb200_epilogue {
   WB200_EPI_NONE = 0,      /* out = round(acc)                                   */
   WB200_EPI_BIAS = 1,      /* out = round(acc + bias[n])                         */
-  WB200_EPI_BIAS_GELU = 2  /* out = round(gelu_erf(acc + bias[n])), f32 math     */
+  WB200_EPI_BIAS_GELU = 2, /* out = round(gelu_erf(acc + bias[n])), f32 math     */
+  WB200_EPI_SWIGLU = 3     /* out[m, j] = round(silu(acc[m, 2j]) * acc[m, 2j+1]): gate and up columns
+                              interleaved in B; out is [m, n / 2]                 */
 } wb200_epilogue;
 
 typedef struct wb200_gemm_epilogue_params {
@@ -318,6 +326,22 @@ typedef struct wb200_gemm_epilogue_params {
 /* Tiled GEMM region with fused producer/epilogue chain (dot_general -> +bias -> GELU -> narrow):
  * fp32 accumulation and a single final rounding (ContractionAccumulation.cpp:147-218). */
 wb200_status wb200_gemm_epilogue(wb200_backend *backend, const wb200_gemm_epilogue_params *params);
+
+/* Pieces of a Llama-style decoder layer between the GEMM and attention regions (device buffers, bf16 / f16,
+ * enqueued on `stream`). They are the fused producer / epilogue chains of config "decoder layer": the reference
+ * lowers them to elementwise / reduce command runs (lib/Wafer/Simulator/Reference/ManagedReferenceTargetModel.cpp:
+ * 230-458); here each chain is one kernel with f32 arithmetic and one rounding per produced element.
+ *   rmsnorm:      y = round(round(x * rsqrt(mean(x^2) + eps)) * gamma), rows x dim
+ *   rope_split:   token-major qkv rows [q heads | k heads | v heads] -> head-major Q, K (rotary, pairs (i, i + D/2),
+ *                 angle = (position_offset + s) * theta^(-2i/D)) and V
+ *   residual_add: out = round(a + b) */
+wb200_status wb200_rmsnorm(wb200_backend *backend, uint32_t format, const void *x, const void *gamma, void *y,
+                           uint32_t rows, uint32_t dim, float eps, void *stream);
+wb200_status wb200_rope_split(wb200_backend *backend, uint32_t format, const void *qkv, void *q, void *k, void *v,
+                              uint32_t batch, uint32_t seq, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
+                              float theta, uint32_t position_offset, void *stream);
+wb200_status wb200_residual_add(wb200_backend *backend, uint32_t format, const void *a, const void *b, void *out,
+                                uint64_t elements, void *stream);
 
 /* Reads and clears the device status word of asynchronous (WB200_MEM_DEVICE) calls after
  * synchronising `stream`. Returns WB200_ERR_DEVICE_TIMEOUT if a kernel gave up a bounded wait. */

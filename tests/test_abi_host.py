@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in include/wb200.h but not exported"
         assert name in abi.SIGNATURES, f"{name} has no ctypes signature"
-    assert lib.wb200_abi_version() == 1
+    assert lib.wb200_abi_version() == 2
 
 
 def test_struct_layouts_match_the_header():
@@ -33,7 +33,7 @@ def test_struct_layouts_match_the_header():
     assert C.sizeof(abi.TensorDesc) == 8 + 8 * abi.MAX_RANK
     assert C.sizeof(abi.Geometry) == 12 * 8
     assert C.sizeof(abi.Evidence) == 4 * 8 + 4 * 4 + 96 + 64
-    assert C.sizeof(abi.AttentionParams) == 6 * 4 + 4 + 4 + 3 * 8 + 8 * 8
+    assert C.sizeof(abi.AttentionParams) == 6 * 4 + 4 + 4 + 3 * 8 + 8 * 8 + 8
     assert C.sizeof(abi.GemmEpilogueParams) == 3 * 4 + 8 + 4 + 5 * 8
 
 

@@ -26,7 +26,9 @@ MEM_HOST, MEM_DEVICE = 0, 1
 # wb200_gemm_policy
 GEMM_FORMAL, GEMM_TENSOR = 0, 1
 # wb200_epilogue
-EPI_NONE, EPI_BIAS, EPI_BIAS_GELU = 0, 1, 2
+EPI_NONE, EPI_BIAS, EPI_BIAS_GELU, EPI_SWIGLU = 0, 1, 2, 3
+# wb200_out_layout
+OUT_HEAD_MAJOR, OUT_TOKEN_MAJOR = 0, 1
 # wb200_orientation
 NORMAL, TRANSPOSE = 0, 1
 
@@ -99,7 +101,8 @@ class AttentionParams(C.Structure):
                 ("scale", C.c_float),
                 ("query_start", C.c_int64), ("key_start", C.c_int64), ("key_end", C.c_int64),
                 ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p),
-                ("lse", C.c_void_p), ("row_max", C.c_void_p), ("row_sum", C.c_void_p), ("stream", C.c_void_p)]
+                ("lse", C.c_void_p), ("row_max", C.c_void_p), ("row_sum", C.c_void_p), ("stream", C.c_void_p),
+                ("out_layout", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 class GemmEpilogueParams(C.Structure):
@@ -133,6 +136,9 @@ SIGNATURES = {
     "wb200_attention_fd_partial": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams), C.c_uint32, C.c_void_p]),
     "wb200_attention_fd_merge": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams), C.c_void_p, C.c_uint32]),
     "wb200_gemm_epilogue": (C.c_int, [C.c_void_p, C.POINTER(GemmEpilogueParams)]),
+    "wb200_rmsnorm": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p]),
+    "wb200_rope_split": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_uint32] * 5 + [C.c_float, C.c_uint32, C.c_void_p]),
+    "wb200_residual_add": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
     "wb200_spm_create": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(C.c_void_p)]),
     "wb200_spm_destroy": (None, [C.c_void_p]),
     "wb200_spm_write": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]),

@@ -283,15 +283,17 @@ class B200TargetModelBackend:
 
     def attention_fa(self, q, k, v, scale: float, causal: bool = False, *, out=None, lse=None, row_max=None,
                      row_sum=None, zero_fully_masked: bool = False, query_start: int = 0, key_start: int = 0,
-                     key_end: int = 0, stream: Optional[int] = None):
+                     key_end: int = 0, stream: Optional[int] = None, token_major_out: bool = False):
         """Flash-attention prefill. CPU tensors are staged by the library (copies inside the call);
         CUDA tensors are used in place and the kernel is enqueued on `stream` (default: current)."""
         if out is None:
-            out = torch.empty_like(q)
+            out = torch.empty(q.shape[0], q.shape[2], q.shape[1], q.shape[3], dtype=q.dtype, device=q.device) if token_major_out \
+                else torch.empty_like(q)
         if stream is None:
             stream = torch.cuda.current_stream().cuda_stream if q.is_cuda else 0
         p = self._attention_params(q, k, v, out, scale, causal, zero_fully_masked, query_start, key_start, key_end,
                                    lse, row_max, row_sum, stream)
+        p.out_layout = abi.OUT_TOKEN_MAJOR if token_major_out else abi.OUT_HEAD_MAJOR
         self._check(self._lib.wb200_attention_fa(self._handle, C.byref(p)))
         return out
 
@@ -364,7 +366,7 @@ class B200TargetModelBackend:
         n = b.shape[0] if rhs_transposed else b.shape[1]
         out_dtype = out_dtype or a.dtype
         if out is None:
-            out = torch.empty(m, n, dtype=out_dtype, device=a.device)
+            out = torch.empty(m, n // 2 if epilogue == abi.EPI_SWIGLU else n, dtype=out_dtype, device=a.device)
         if stream is None:
             stream = torch.cuda.current_stream().cuda_stream if a.is_cuda else 0
         p = abi.GemmEpilogueParams()
@@ -377,4 +379,37 @@ class B200TargetModelBackend:
         p.bias = bias.data_ptr() if bias is not None else None
         p.stream = stream
         self._check(self._lib.wb200_gemm_epilogue(self._handle, C.byref(p)))
+        return out
+
+    # ------------------------------------------------------------------ decoder-layer pieces (CUDA tensors)
+    def rmsnorm(self, x, gamma, eps: float, *, out=None, stream: Optional[int] = None):
+        """y = round(round(x * rsqrt(mean(x^2) + eps)) * gamma) over the last dimension."""
+        if out is None:
+            out = torch.empty_like(x)
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream
+        rows = x.numel() // x.shape[-1]
+        self._check(self._lib.wb200_rmsnorm(self._handle, _TORCH_FORMATS[x.dtype], x.data_ptr(), gamma.data_ptr(), out.data_ptr(),
+                                            rows, x.shape[-1], float(eps), stream))
+        return out
+
+    def rope_split(self, qkv, batch: int, seq: int, q_heads: int, kv_heads: int, head_dim: int, theta: float,
+                   position_offset: int = 0, stream: Optional[int] = None):
+        """Token-major projection rows [q heads | k heads | v heads] -> head-major Q, K (rotary applied) and V."""
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream
+        q = torch.empty(batch, q_heads, seq, head_dim, dtype=qkv.dtype, device=qkv.device)
+        k = torch.empty(batch, kv_heads, seq, head_dim, dtype=qkv.dtype, device=qkv.device)
+        v = torch.empty_like(k)
+        self._check(self._lib.wb200_rope_split(self._handle, _TORCH_FORMATS[qkv.dtype], qkv.data_ptr(), q.data_ptr(), k.data_ptr(),
+                                               v.data_ptr(), batch, seq, q_heads, kv_heads, head_dim, float(theta), position_offset, stream))
+        return q, k, v
+
+    def residual_add(self, a, b, *, out=None, stream: Optional[int] = None):
+        if out is None:
+            out = torch.empty_like(a)
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream
+        self._check(self._lib.wb200_residual_add(self._handle, _TORCH_FORMATS[a.dtype], a.data_ptr(), b.data_ptr(), out.data_ptr(),
+                                                 a.numel(), stream))
         return out

@@ -26,6 +26,8 @@ wb200_status make_attention_args(const wb200_attention_params *p, AttentionArgs 
   a->kv_valid = p->key_end > 0 ? p->key_end - p->key_start : static_cast<int64_t>(p->kv_len);
   a->q = p->q; a->k = p->k; a->v = p->v; a->out = p->out;
   a->lse = p->lse; a->row_max = p->row_max; a->row_sum = p->row_sum;
+  a->out_token_major = p->out_layout == WB200_OUT_TOKEN_MAJOR ? 1 : 0;
+  if (p->out_layout > WB200_OUT_TOKEN_MAJOR) return fail(WB200_ERR_INVALID_ARGUMENT, "unknown attention output layout");
   return WB200_OK;
 }
 
@@ -196,8 +198,8 @@ wb200_status wb200_attention_fd_merge(wb200_backend *backend, const wb200_attent
 wb200_status wb200_gemm_epilogue(wb200_backend *backend, const wb200_gemm_epilogue_params *p) {
   if (!backend || !p) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
   if (!p->a || !p->b || !p->out) return fail(WB200_ERR_INVALID_ARGUMENT, "a, b and out must not be null");
-  if (p->epilogue > WB200_EPI_BIAS_GELU) return fail(WB200_ERR_INVALID_ARGUMENT, "unknown epilogue");
-  if (p->epilogue != WB200_EPI_NONE && !p->bias) return fail(WB200_ERR_INVALID_ARGUMENT, "bias must not be null for this epilogue");
+  if (p->epilogue > WB200_EPI_SWIGLU) return fail(WB200_ERR_INVALID_ARGUMENT, "unknown epilogue");
+  if ((p->epilogue == WB200_EPI_BIAS || p->epilogue == WB200_EPI_BIAS_GELU) && !p->bias) return fail(WB200_ERR_INVALID_ARGUMENT, "bias must not be null for this epilogue");
   GemmUmmaArgs g{};
   g.m = p->m; g.n = p->n; g.k = p->k;
   g.in_format = p->in_format; g.out_format = p->out_format;
@@ -212,7 +214,8 @@ wb200_status wb200_gemm_epilogue(wb200_backend *backend, const wb200_gemm_epilog
     return st;
   }
   const size_t a_bytes = static_cast<size_t>(p->m) * p->k * 2, b_bytes = static_cast<size_t>(p->k) * p->n * 2;
-  const size_t out_bytes = static_cast<size_t>(p->m) * p->n * element_bytes_of(p->out_format);
+  const size_t out_cols = p->epilogue == WB200_EPI_SWIGLU ? p->n / 2 : p->n;
+  const size_t out_bytes = static_cast<size_t>(p->m) * out_cols * element_bytes_of(p->out_format);
   void *da, *db, *dout, *dbias = nullptr;
   if ((st = backend->buffer(0, a_bytes, &da)) != WB200_OK) return st;
   if ((st = backend->buffer(1, b_bytes, &db)) != WB200_OK) return st;
@@ -229,6 +232,40 @@ wb200_status wb200_gemm_epilogue(wb200_backend *backend, const wb200_gemm_epilog
   backend->launches += 1;
   WB200_CUDA_CHECK(cudaMemcpyAsync(p->out, dout, out_bytes, cudaMemcpyDeviceToHost, stream));
   return read_device_status(backend, stream, nullptr);
+}
+
+}  // extern "C"
+
+// ------------------------------------------------------------------ decoder-layer pieces (device buffers)
+extern "C" {
+
+wb200_status wb200_rmsnorm(wb200_backend *backend, uint32_t format, const void *x, const void *gamma, void *y,
+                           uint32_t rows, uint32_t dim, float eps, void *stream) {
+  if (!backend || !x || !gamma || !y) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard guard(backend->device);
+  wb200_status st = launch_rmsnorm(format, x, gamma, y, rows, dim, eps, static_cast<cudaStream_t>(stream));
+  if (st == WB200_OK) backend->launches += 1;
+  return st;
+}
+
+wb200_status wb200_rope_split(wb200_backend *backend, uint32_t format, const void *qkv, void *q, void *k, void *v,
+                              uint32_t batch, uint32_t seq, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
+                              float theta, uint32_t position_offset, void *stream) {
+  if (!backend || !qkv || !q || !k || !v) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard guard(backend->device);
+  wb200_status st = launch_rope_split(format, qkv, q, k, v, batch, seq, q_heads, kv_heads, head_dim, theta,
+                                      position_offset, static_cast<cudaStream_t>(stream));
+  if (st == WB200_OK) backend->launches += 1;
+  return st;
+}
+
+wb200_status wb200_residual_add(wb200_backend *backend, uint32_t format, const void *a, const void *b, void *out,
+                                uint64_t elements, void *stream) {
+  if (!backend || !a || !b || !out) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard guard(backend->device);
+  wb200_status st = launch_residual_add(format, a, b, out, elements, static_cast<cudaStream_t>(stream));
+  if (st == WB200_OK) backend->launches += 1;
+  return st;
 }
 
 }  // extern "C"

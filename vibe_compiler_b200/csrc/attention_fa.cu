@@ -77,6 +77,7 @@ struct FaParams {
   int out_format;
   int bf16;
   int num_pairs;           // ceil(q_len / 256)
+  int out_token_major;     // out is [batch, q_len, q_heads, head_dim] instead of [batch, q_heads, q_len, head_dim]
   float scale_log2;        // scale * log2(e)
   void *out;
   float *lse, *row_max, *row_sum;
@@ -458,7 +459,9 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       tc_fence_after();
       float coefficient = 1.0f / l_run;
       if (p.zero_fully_masked && l_run == 0.f) coefficient = 0.f;
-      const size_t out_row = (static_cast<size_t>(bh) * p.q_len + row) * kHd;
+      const size_t out_row = p.out_token_major
+                                 ? ((static_cast<size_t>(b) * p.q_len + row) * p.q_heads + h) * kHd
+                                 : (static_cast<size_t>(bh) * p.q_len + row) * kHd;
       uint32_t r[128];
       if (my_tiles > 0) {
 #pragma unroll
@@ -595,6 +598,7 @@ wb200_status launch_attention_fa_umma(const AttentionArgs &a, int sm_count, int 
   p.out_format = a.format;
   p.bf16 = a.format == WB200_BF16;
   p.num_pairs = (a.q_len + 2 * kTileM - 1) / (2 * kTileM);
+  p.out_token_major = a.out_token_major;
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.out = a.out; p.lse = a.lse; p.row_max = a.row_max; p.row_sum = a.row_sum;
   p.status = device_status;

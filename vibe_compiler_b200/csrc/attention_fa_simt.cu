@@ -92,10 +92,11 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) fa_simt_kernel(const Simt
   float coefficient = __fdiv_rn(1.0f, l_run);
   if (a.zero_fully_masked && l_run == 0.0f) coefficient = 0.0f;
   uint8_t *out = static_cast<uint8_t *>(a.out);
+  const size_t out_off = a.out_token_major ? ((static_cast<size_t>(b) * a.q_len + row) * a.q_heads + h) * D : q_off;
 #pragma unroll
   for (int i = 0; i < kMaxDPerLane; ++i)
     if (i < per_lane)
-      store_element_bits(out, q_off + i * 32 + lane, a.format, narrow_bits(__fmul_rn(acc[i], coefficient), a.format));
+      store_element_bits(out, out_off + i * 32 + lane, a.format, narrow_bits(__fmul_rn(acc[i], coefficient), a.format));
   if (lane == 0) {
     const size_t stat = static_cast<size_t>(bh) * a.q_len + row;
     if (a.lse) a.lse[stat] = (l_run == 0.0f) ? -INFINITY : m_run + logf(l_run);

@@ -179,6 +179,26 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_wait_ld();
         const int col0 = n0 + c * 32;
+        if (p.epilogue == WB200_EPI_SWIGLU) {
+          // Columns (2j, 2j+1) hold (gate_j, up_j): out[row, j] = silu(gate) * up, 16 outputs per 32 columns.
+          if (row < p.m && col0 + 32 <= p.n) {
+            uint32_t w[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float o[2];
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const float gate = __uint_as_float(r[4 * j + 2 * h]), up = __uint_as_float(r[4 * j + 2 * h + 1]);
+                o[h] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+              }
+              w[j] = narrow_bits(o[0], p.out_format) | (narrow_bits(o[1], p.out_format) << 16);
+            }
+            uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + static_cast<size_t>(row) * (p.n / 2) + col0 / 2;
+            *reinterpret_cast<uint4 *>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4 *>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+          }
+          continue;
+        }
         if (p.epilogue != WB200_EPI_NONE) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
@@ -249,8 +269,10 @@ bool gemm_umma_supports(const GemmUmmaArgs &a) {
   if ((reinterpret_cast<uintptr_t>(a.a) | reinterpret_cast<uintptr_t>(a.b) |
        reinterpret_cast<uintptr_t>(a.out)) & 15u)
     return false;
-  if (a.epilogue != WB200_EPI_NONE && (a.bias == nullptr || (reinterpret_cast<uintptr_t>(a.bias) & 15u)))
+  if ((a.epilogue == WB200_EPI_BIAS || a.epilogue == WB200_EPI_BIAS_GELU) &&
+      (a.bias == nullptr || (reinterpret_cast<uintptr_t>(a.bias) & 15u)))
     return false;
+  if (a.epilogue == WB200_EPI_SWIGLU && (a.n % 32 != 0 || a.out_format == WB200_F32)) return false;
   return true;
 }
 

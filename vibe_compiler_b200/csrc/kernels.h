@@ -75,6 +75,7 @@ struct AttentionArgs {
   const void *q, *k, *v;
   void *out;
   float *lse, *row_max, *row_sum;
+  int out_token_major;    // 1: out is [batch, q_len, q_heads, head_dim] (rows of a following projection GEMM)
 };
 bool attention_fa_umma_supports(const AttentionArgs &args);
 wb200_status launch_attention_fa_umma(const AttentionArgs &args, int sm_count, int *device_status,
@@ -92,5 +93,13 @@ wb200_status launch_attention_fd(const AttentionArgs &args, uint32_t splits, flo
                                  int finalize, float *state_out, cudaStream_t stream);
 wb200_status launch_attention_fd_merge(const AttentionArgs &args, const float *states,
                                        uint32_t shard_count, cudaStream_t stream);
+
+
+// ---- decoder-layer pieces (layer_ops.cu); device pointers, bf16 / f16 storage
+wb200_status launch_rmsnorm(int format, const void *x, const void *gamma, void *y, int rows, int dim, float eps,
+                            cudaStream_t stream);
+wb200_status launch_rope_split(int format, const void *qkv, void *q, void *k, void *v, int batch, int seq, int q_heads,
+                               int kv_heads, int head_dim, float theta, int position_offset, cudaStream_t stream);
+wb200_status launch_residual_add(int format, const void *a, const void *b, void *out, size_t elements, cudaStream_t stream);
 
 }  // namespace wb200
