@@ -29,6 +29,7 @@ sys.path.insert(0, str(ROOT))
 FA = dict(batch=4, heads=32, kv_heads=32, seq=4096, head_dim=128)
 FD = dict(batch=64, q_heads=32, kv_heads=8, kv_len=32768, head_dim=128)
 GEMM = dict(m=8192, n=8192, k=8192)
+FD_LONG = dict(q_heads=32, kv_heads=8, kv_len=1048576, head_dim=128)
 LAYER = dict(batch=8, seq=2048)   # Llama-style decoder layer: d_model 4096, 32/8 heads, head_dim 128, FFN 14336
 SEED = 20260803
 
@@ -151,7 +152,7 @@ def layer_extra(backend, args, torch, dist, rank, world, device, peak):
     layer = ShardedDecoderLayer(backend, cfg, random_weights(cfg, seed=SEED), rank=rank, world_size=world, device=device)
     gen = torch.Generator(device="cpu").manual_seed(SEED + 5)
     x = torch.randn(LAYER["batch"], LAYER["seq"], cfg.d_model, generator=gen).bfloat16().to(device)
-    total_ms, _ = timed_steps(lambda: layer.forward(x), args.steps, args.warmup, torch, dist=dist, check=backend.poll)
+    total_ms, _ = timed_steps(lambda: layer.forward_fused(x), args.steps, args.warmup, torch, dist=dist, check=backend.poll)
     backend.poll()
     elapsed = torch.tensor([total_ms], device=device)
     if dist is not None:
@@ -311,23 +312,56 @@ def main():
     if not args.skip_extras:
         q = k = v = out = None
         torch.cuda.empty_cache()
-    if not args.skip_extras and world == 1:
-        # ------------------------------------------------------------ FD decode (HBM bound)
+    if not args.skip_extras:
+        # ------------------------------------------------------------ FD decode (HBM bound); every rank runs the same-size batch
         fq = torch.randn(FD["batch"], FD["q_heads"], 1, FD["head_dim"], device=device, generator=gen).bfloat16()
         fk = torch.randn(FD["batch"], FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
         fv = torch.randn(FD["batch"], FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
         fout = torch.empty_like(fq)
         flse = torch.empty(FD["batch"], FD["q_heads"], 1, device=device)
         fd_bytes = 2 * fk.numel() * 2
-        _, fd_ms = timed_steps(lambda: backend.attention_fd(fq, fk, fv, scale, out=fout, lse=flse), args.steps, args.warmup, torch, check=backend.poll)
+        fd_total, fd_launch = timed_steps(lambda: backend.attention_fd(fq, fk, fv, scale, out=fout, lse=flse), args.steps, args.warmup, torch, dist, check=backend.poll)
         backend.poll()
-        fd_gbs = fd_bytes / (fd_ms * 1e-3) / 1e9
-        extras["fd_decode"] = {"workload": "FD decode bf16 B64 Hq32 Hkv8 KV32768 D128, inputs (8.6 GB) larger than L2", "value": fd_gbs,
-                               "unit": "GB/s", "ms_per_step": fd_ms,
+        fd_times = torch.tensor([fd_total, fd_launch], device=device, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(fd_times, op=dist.ReduceOp.MAX)
+        fd_ms, fd_launch_ms = fd_times[0].item() / args.steps, fd_times[1].item()
+        fd_gbs = fd_bytes / (fd_launch_ms * 1e-3) / 1e9
+        extras["fd_decode"] = {"workload": "FD decode bf16 B64 Hq32 Hkv8 KV32768 D128 per GPU, inputs (8.6 GB) larger than L2", "value": world * fd_bytes / (fd_ms * 1e-3) / 1e9,
+                               "unit": "GB/s", "ms_per_step": fd_ms, "scaling": "weak", "n_gpus": world,
                                "roofline": {"bound": "hbm", "achieved": fd_gbs, "peak": peak["hbm_gbs"], "unit": "GB/s",
-                                            "frac": fd_gbs / peak["hbm_gbs"], "traffic": None, "peak_source": peak["source"]}}
+                                            "frac": fd_gbs / peak["hbm_gbs"], "traffic": None, "peak_source": peak["source"], "launch_ms": fd_launch_ms}}
         del fq, fk, fv
         torch.cuda.empty_cache()
+        # ------------------------------------------------------------ long-context decode: the KV sequence is sharded over the ranks
+        from vibe_compiler_b200.sharding import sequence_range, sharded_decode
+        lo, hi = sequence_range(FD_LONG["kv_len"], world, rank)
+        shared_gen = torch.Generator(device=device).manual_seed(SEED + 77)   # the query is the same on every rank
+        lq = torch.randn(1, FD_LONG["q_heads"], 1, FD_LONG["head_dim"], device=device, generator=shared_gen).bfloat16()
+        lk = torch.randn(1, FD_LONG["kv_heads"], hi - lo, FD_LONG["head_dim"], device=device, generator=gen).bfloat16()
+        lv = torch.randn(1, FD_LONG["kv_heads"], hi - lo, FD_LONG["head_dim"], device=device, generator=gen).bfloat16()
+        lout = torch.empty_like(lq)
+        group = None
+
+        def long_step():
+            sharded_decode(lambda b, e: backend.attention_fd_partial(lq, lk, lv, scale), lambda st: backend.attention_fd_merge(st, lq, out=lout),
+                           FD_LONG["kv_len"], group)
+        long_total, _ = timed_steps(long_step, args.steps, args.warmup, torch, dist, check=backend.poll)
+        backend.poll()
+        long_t = torch.tensor([long_total], device=device, dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(long_t, op=dist.ReduceOp.MAX)
+        long_ms = long_t.item() / args.steps
+        long_bytes = 2 * FD_LONG["kv_heads"] * FD_LONG["kv_len"] * FD_LONG["head_dim"] * 2
+        long_gbs = long_bytes / (long_ms * 1e-3) / 1e9
+        extras["fd_long_context"] = {"workload": f"FD decode bf16 B1 Hq32 Hkv8 KV1048576 D128, KV sequence sharded over {world} rank(s); exchange = all-gather of (acc, m, l) states",
+                                     "value": long_gbs, "unit": "GB/s", "ms_per_step": long_ms, "scaling": "strong", "n_gpus": world,
+                                     "exchange_bytes_per_rank": FD_LONG["q_heads"] * (FD_LONG["head_dim"] + 2) * 4,
+                                     "roofline": {"bound": "hbm", "achieved": long_gbs / world, "peak": peak["hbm_gbs"], "unit": "GB/s per GPU",
+                                                  "frac": long_gbs / world / peak["hbm_gbs"], "traffic": None, "peak_source": peak["source"]}}
+        del lk, lv
+        torch.cuda.empty_cache()
+    if not args.skip_extras and world == 1:
         # ------------------------------------------------------------ GEMM + bias + GELU (tensor bound)
         ga = (torch.rand(GEMM["m"], GEMM["k"], device=device, generator=gen) * 2 - 1).bfloat16()
         gb = (torch.rand(GEMM["k"], GEMM["n"], device=device, generator=gen) * 2 - 1).bfloat16()

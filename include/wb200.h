@@ -40,7 +40,8 @@ typedef enum wb200_status {
   WB200_ERR_CUDA = 5,             /* a CUDA runtime call failed; message carries the CUDA error    */
   WB200_ERR_DEVICE_TIMEOUT = 6,   /* a bounded device-side wait gave up; context remains usable    */
   WB200_ERR_NO_DEVICE = 7,        /* no sm_100 device / extension cannot run                       */
-  WB200_ERR_LIMIT = 8             /* a fixed capacity of an entry point was exceeded               */
+  WB200_ERR_LIMIT = 8,            /* a fixed capacity of an entry point was exceeded               */
+  WB200_ERR_CALLBACK = 9          /* a caller-supplied callback reported a failure                 */
 } wb200_status;
 
 /* Logical formats. Ordinals equal the reference's LogicalFormat enum and its Data_Format codes
@@ -342,6 +343,42 @@ wb200_status wb200_rope_split(wb200_backend *backend, uint32_t format, const voi
                               float theta, uint32_t position_offset, void *stream);
 wb200_status wb200_residual_add(wb200_backend *backend, uint32_t format, const void *a, const void *b, void *out,
                                 uint64_t elements, void *stream);
+
+/* One rank's shard of a Llama-style decoder layer forward as ONE call: RMSNorm -> fused QKV projection ->
+ * rotary + head-major split -> causal grouped-query flash attention -> output projection -> [sum over shards]
+ * -> residual -> RMSNorm -> gate/up projection with SwiGLU epilogue -> down projection -> [sum over shards]
+ * -> residual. The reference lowers such a block to GEMM / attention / elementwise command regions and realises
+ * the two sums with Tile collectives (lib/Wafer/Transforms/Tile/DistributedCollectiveMovement.cpp:675-735); the
+ * block its own tests run is test/Board/PyTorch/wafer_pytorch_board_cases.py:817-867. Ten kernels are enqueued
+ * on `stream`; nothing is allocated: the caller passes `workspace` of at least
+ * wb200_decoder_layer_workspace_bytes() bytes (256-byte aligned). All pointers are device pointers.
+ *   q_heads, kv_heads, ffn   this shard's query heads, KV heads and FFN columns
+ *   wqkv  [d_model, (q_heads + 2 kv_heads) head_dim]   columns [q heads | k heads | v heads]
+ *   wo    [q_heads head_dim, d_model]
+ *   wgu   [d_model, 2 ffn]   gate and up columns interleaved: (gate_0, up_0, gate_1, up_1, ...)
+ *   wdown [ffn, d_model]
+ * `allreduce` (may be null for a single shard) is called twice, after the kernels producing the partial sum have
+ * been enqueued, with a buffer inside `workspace` holding `elements` values of `format`; it must enqueue an
+ * in-place sum over the shards ordered after the work already on `stream` and before work enqueued on it later
+ * (an NCCL all-reduce on that stream, or on another stream with event edges), and return 0. */
+typedef int32_t (*wb200_allreduce_fn)(void *user, void *device_buffer, uint64_t elements, uint32_t format, void *stream);
+typedef struct wb200_decoder_layer_params {
+  uint32_t batch, seq, d_model, head_dim;
+  uint32_t q_heads, kv_heads, ffn;
+  uint32_t format;             /* WB200_BF16 or WB200_F16 */
+  float eps, rope_theta;
+  uint32_t position_offset, reserved;
+  const void *x;               /* [batch * seq, d_model] */
+  void *out;                   /* [batch * seq, d_model] */
+  const void *norm1, *wqkv, *wo, *norm2, *wgu, *wdown;
+  void *workspace;
+  uint64_t workspace_bytes;
+  wb200_allreduce_fn allreduce;
+  void *allreduce_user;
+  void *stream;
+} wb200_decoder_layer_params;
+uint64_t wb200_decoder_layer_workspace_bytes(const wb200_decoder_layer_params *params);
+wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_layer_params *params);
 
 /* Reads and clears the device status word of asynchronous (WB200_MEM_DEVICE) calls after
  * synchronising `stream`. Returns WB200_ERR_DEVICE_TIMEOUT if a kernel gave up a bounded wait. */

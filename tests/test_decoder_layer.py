@@ -123,3 +123,59 @@ def test_layer_pieces_against_f32(backend):
     prod = a2.double() @ w.double()
     want_act = torch.nn.functional.silu(prod[:, 0::2]) * prod[:, 1::2]
     assert ((act.double() - want_act).abs().max() / want_act.abs().max()).item() <= 1e-2
+
+
+@pytest.mark.gpu
+def test_single_call_layer_equals_the_composed_calls(backend):
+    from vibe_compiler_b200.decoder_layer import ShardedDecoderLayer
+    cfg = fixture.CFG
+    weights = random_weights(cfg)
+    x = fixture.layer_input().cuda()
+    layer = ShardedDecoderLayer(backend, cfg, weights)
+    assert torch.equal(layer.forward_fused(x), layer.forward(x))
+    assert torch.equal(layer.forward_fused(x), layer.forward(x))      # workspace reuse
+
+    # two shards: the callback of shard 0 adds what shard 1 computed with the composed calls
+    shards = [ShardedDecoderLayer(backend, cfg, weights, rank=r, world_size=2) for r in range(2)]
+    b, s, d = x.shape
+    tokens = x.reshape(b * s, d)
+    partials = [shard.attention_partial(tokens, b, s) for shard in shards]
+    x1 = backend.residual_add(tokens, (partials[0].float() + partials[1].float()).bfloat16())
+    ffn = [shard.ffn_partial(x1) for shard in shards]
+    want = backend.residual_add(x1, (ffn[0].float() + ffn[1].float()).bfloat16()).reshape(b, s, d)
+    others = iter([partials[1], ffn[1]])
+    calls = []
+
+    def fake_all_reduce(t):
+        calls.append(t.numel())
+        other = next(others)
+        t.copy_((t.view_as(other).float() + other.float()).bfloat16().view_as(t))
+    s0 = shards[0]
+    got, _ = backend.decoder_layer(x, norm1=s0.norm1, wqkv=s0.wqkv, wo=s0.wo, norm2=s0.norm2, wgu=s0.wgu, wdown=s0.wdown, q_heads=s0.hq,
+                                   kv_heads=s0.hkv, head_dim=cfg.head_dim, eps=cfg.eps, rope_theta=cfg.rope_theta, allreduce=fake_all_reduce)
+    torch.cuda.synchronize()
+    backend.poll()
+    assert calls == [b * s * d, b * s * d]
+    assert torch.equal(got, want)
+
+
+@pytest.mark.gpu
+def test_single_call_layer_reports_callback_failure_and_small_workspace(backend):
+    from vibe_compiler_b200.backend import WB200Error
+    from vibe_compiler_b200.decoder_layer import ShardedDecoderLayer
+    cfg = fixture.CFG
+    layer = ShardedDecoderLayer(backend, cfg, random_weights(cfg))
+    x = fixture.layer_input().cuda()
+    kwargs = dict(norm1=layer.norm1, wqkv=layer.wqkv, wo=layer.wo, norm2=layer.norm2, wgu=layer.wgu, wdown=layer.wdown, q_heads=layer.hq,
+                  kv_heads=layer.hkv, head_dim=cfg.head_dim, eps=cfg.eps, rope_theta=cfg.rope_theta)
+
+    def broken(_tensor):
+        raise RuntimeError("link down")
+    with pytest.raises(RuntimeError, match="link down"):
+        backend.decoder_layer(x, allreduce=broken, **kwargs)
+    torch.cuda.synchronize()
+    backend.poll()
+    with pytest.raises(WB200Error):
+        backend.decoder_layer(x[:, :3], **kwargs)          # 6 tokens: not a multiple of 8
+    out, _ = backend.decoder_layer(x, **kwargs)              # the backend is still usable
+    assert torch.isfinite(out.float()).all()

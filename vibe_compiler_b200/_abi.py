@@ -14,8 +14,8 @@ LIBRARY_PATH = PACKAGE_DIR / "libwb200.so"
 MAX_RANK = 8
 
 # wb200_status
-OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_NAN_DOMAIN, ERR_BUDGET, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_LIMIT = range(9)
-STATUS_NAMES = ["ok", "invalid-argument", "unsupported", "nan-domain", "budget", "cuda", "device-timeout", "no-device", "limit"]
+OK, ERR_INVALID_ARGUMENT, ERR_UNSUPPORTED, ERR_NAN_DOMAIN, ERR_BUDGET, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE, ERR_LIMIT, ERR_CALLBACK = range(10)
+STATUS_NAMES = ["ok", "invalid-argument", "unsupported", "nan-domain", "budget", "cuda", "device-timeout", "no-device", "limit", "callback"]
 
 # wb200_format (ordinals of the reference's LogicalFormat / Data_Format codes)
 I8, I16, F16, BF16, I32, F32, TF32, BOOL, U8, U16, U32, I64, U64, FORMAT_NONE = range(14)
@@ -114,6 +114,19 @@ class GemmEpilogueParams(C.Structure):
 
 
 # Every exported symbol with its C signature; tests check the library exports exactly these.
+ALLREDUCE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p)
+
+
+class DecoderLayerParams(C.Structure):
+    _fields_ = [("batch", C.c_uint32), ("seq", C.c_uint32), ("d_model", C.c_uint32), ("head_dim", C.c_uint32),
+                ("q_heads", C.c_uint32), ("kv_heads", C.c_uint32), ("ffn", C.c_uint32), ("format", C.c_uint32),
+                ("eps", C.c_float), ("rope_theta", C.c_float), ("position_offset", C.c_uint32), ("reserved", C.c_uint32),
+                ("x", C.c_void_p), ("out", C.c_void_p),
+                ("norm1", C.c_void_p), ("wqkv", C.c_void_p), ("wo", C.c_void_p), ("norm2", C.c_void_p), ("wgu", C.c_void_p), ("wdown", C.c_void_p),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
+                ("allreduce", ALLREDUCE_FN), ("allreduce_user", C.c_void_p), ("stream", C.c_void_p)]
+
+
 SIGNATURES = {
     "wb200_abi_version": (C.c_int, []),
     "wb200_last_error": (C.c_char_p, []),
@@ -139,6 +152,8 @@ SIGNATURES = {
     "wb200_rmsnorm": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p]),
     "wb200_rope_split": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_uint32] * 5 + [C.c_float, C.c_uint32, C.c_void_p]),
     "wb200_residual_add": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
+    "wb200_decoder_layer_workspace_bytes": (C.c_uint64, [C.POINTER(DecoderLayerParams)]),
+    "wb200_decoder_layer": (C.c_int, [C.c_void_p, C.POINTER(DecoderLayerParams)]),
     "wb200_spm_create": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(C.c_void_p)]),
     "wb200_spm_destroy": (None, [C.c_void_p]),
     "wb200_spm_write": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]),

@@ -413,3 +413,46 @@ class B200TargetModelBackend:
         self._check(self._lib.wb200_residual_add(self._handle, _TORCH_FORMATS[a.dtype], a.data_ptr(), b.data_ptr(), out.data_ptr(),
                                                  a.numel(), stream))
         return out
+
+    def decoder_layer(self, x, *, norm1, wqkv, wo, norm2, wgu, wdown, q_heads: int, kv_heads: int, head_dim: int, eps: float,
+                      rope_theta: float, position_offset: int = 0, allreduce=None, workspace=None, out=None,
+                      stream: Optional[int] = None):
+        """One shard of a Llama-style decoder layer forward through the single C-ABI call wb200_decoder_layer.
+        x: [batch, seq, d_model] CUDA tensor. `allreduce(tensor)` must enqueue an in-place sum over the shards
+        (torch.distributed.all_reduce); `workspace` is a uint8 CUDA tensor that is reused if large enough.
+        Returns (out, workspace)."""
+        batch, seq, d_model = x.shape
+        p = abi.DecoderLayerParams()
+        p.batch, p.seq, p.d_model, p.head_dim = batch, seq, d_model, head_dim
+        p.q_heads, p.kv_heads, p.ffn = q_heads, kv_heads, wdown.shape[0]
+        p.format = _TORCH_FORMATS[x.dtype]
+        p.eps, p.rope_theta, p.position_offset = eps, rope_theta, position_offset
+        needed = self._lib.wb200_decoder_layer_workspace_bytes(C.byref(p))
+        if needed == 0:
+            raise WB200Error(abi.ERR_UNSUPPORTED, self._lib.wb200_last_error().decode())
+        if workspace is None or workspace.numel() < needed:
+            workspace = torch.empty(needed, dtype=torch.uint8, device=x.device)
+        if out is None:
+            out = torch.empty_like(x)
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream
+        p.x, p.out = x.data_ptr(), out.data_ptr()
+        p.norm1, p.wqkv, p.wo, p.norm2, p.wgu, p.wdown = (t.data_ptr() for t in (norm1, wqkv, wo, norm2, wgu, wdown))
+        p.workspace, p.workspace_bytes, p.stream = workspace.data_ptr(), workspace.numel(), stream
+        failure = []
+
+        def reduce_callback(_user, pointer, elements, _format, _stream):
+            try:
+                begin = pointer - workspace.data_ptr()
+                allreduce(workspace[begin:begin + elements * x.element_size()].view(x.dtype))
+                return 0
+            except Exception as error:   # must not propagate through the C frame
+                failure.append(error)
+                return 1
+        callback = abi.ALLREDUCE_FN(reduce_callback) if allreduce is not None else abi.ALLREDUCE_FN()
+        p.allreduce = callback
+        status = self._lib.wb200_decoder_layer(self._handle, C.byref(p))
+        if failure:
+            raise failure[0]
+        self._check(status)
+        return out, workspace

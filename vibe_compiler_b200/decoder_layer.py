@@ -117,6 +117,20 @@ class ShardedDecoderLayer:
         return self.backend.residual_add(x1, partial2).reshape(batch, seq, d)
 
 
+    def forward_fused(self, x: torch.Tensor, position_offset: int = 0) -> torch.Tensor:
+        """Same computation through the single C-ABI call (wb200_decoder_layer): ten kernels enqueued by one call, the
+        two sums through a callback into torch.distributed, intermediates in one reused workspace."""
+        reduce = None
+        if self.world > 1:
+            import torch.distributed as dist
+            reduce = lambda t: dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)   # noqa: E731
+        out, self._workspace = self.backend.decoder_layer(
+            x, norm1=self.norm1, wqkv=self.wqkv, wo=self.wo, norm2=self.norm2, wgu=self.wgu, wdown=self.wdown, q_heads=self.hq,
+            kv_heads=self.hkv, head_dim=self.cfg.head_dim, eps=self.cfg.eps, rope_theta=self.cfg.rope_theta,
+            position_offset=position_offset, allreduce=reduce, workspace=getattr(self, "_workspace", None))
+        return out
+
+
 def layer_flops(cfg: LayerConfig, batch: int, seq: int) -> int:
     """Algorithmic flop of one forward pass (causal attention counts visible pairs only)."""
     t = batch * seq
