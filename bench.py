@@ -189,7 +189,7 @@ def run_reference(args):
             "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "note": "CPU restatement of the reference's numeric path (reference sources need LLVM/MLIR/SystemC: not buildable here)"}
-    print(json.dumps(line))
+    emit(line)
     return 0
 
 
@@ -224,7 +224,20 @@ def run_profile_case(name: str):
     return 0
 
 
+def emit(line: dict):
+    """The JSON line goes to the process's original stdout; everything else written to file descriptor 1 meanwhile
+    (NCCL's version banner comes from C code) has been pointed at stderr by main()."""
+    os.write(RESULT_FD, (json.dumps(line) + "\n").encode())
+
+
+RESULT_FD = 1
+
+
 def main():
+    global RESULT_FD
+    sys.stdout.flush()
+    RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
@@ -402,7 +415,7 @@ def main():
             line["cpu_baseline"] = {"value": cpu_flops / cpu_seconds / 1e12, "unit": "TFLOP/s", "cores": cpu_threads, "kind": "port",
                                     "sample": cpu_desc, "seconds": cpu_seconds}
         line.update(extras)
-        print(json.dumps(line))
+        emit(line)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

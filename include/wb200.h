@@ -405,6 +405,86 @@ wb200_status wb200_target_call_gemm(wb200_spm_image *image, uint64_t lhs, uint64
                                     uint32_t lhs_orientation, uint32_t rhs_orientation,
                                     uint32_t policy);
 
+/* Movement commands of the TargetCall ABI on device-resident memory images, same argument order as the reference
+ * decoder (lib/Wafer/Target/TargetCallDecoder.cpp:52-81); executors replaced:
+ * lib/Wafer/Simulator/Kernel/TargetModelMovement.cpp:52-146 (strided DMA, gather / scatter) and
+ * lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:874-899 (memset). A strided byte layout is
+ * {inner_bytes, strides[3], iterations[3]}, dimension 0 fastest; byte_count must equal inner_bytes * segments.
+ *   rdma:  DDR image, strided  -> scratch-pad image, contiguous
+ *   wdma:  scratch-pad image, contiguous -> DDR image, strided
+ *   gather_scatter: scratch-pad strided -> same scratch-pad strided, with snapshot semantics (the whole source is
+ *                   read before anything is written; overlapping ranges go through a staging buffer)
+ *   memset: element_count elements of `format` set to the low bits of `value_bits`
+ * Synchronous: each call returns after its kernels have completed. */
+wb200_status wb200_target_call_rdma(wb200_spm_image *ddr, wb200_spm_image *spm, uint64_t source, uint64_t destination,
+                                    uint32_t byte_count, uint32_t inner_bytes, const uint32_t strides[3],
+                                    const uint32_t iterations[3]);
+wb200_status wb200_target_call_wdma(wb200_spm_image *spm, wb200_spm_image *ddr, uint64_t source, uint64_t destination,
+                                    uint32_t byte_count, uint32_t inner_bytes, const uint32_t strides[3],
+                                    const uint32_t iterations[3]);
+wb200_status wb200_target_call_gather_scatter(wb200_spm_image *spm, uint64_t source, uint64_t destination,
+                                              uint32_t byte_count, uint32_t inner_bytes,
+                                              const uint32_t source_strides[3], const uint32_t source_iterations[3],
+                                              const uint32_t destination_strides[3],
+                                              const uint32_t destination_iterations[3]);
+wb200_status wb200_target_call_memset(wb200_spm_image *spm, uint64_t destination, uint32_t value_bits,
+                                      uint32_t element_count, uint32_t format);
+
+/* ------------------------------------------------------------------ Tile program replay (Seam 2, whole invocation) */
+/* Executes the per-Tile target LLVM modules the reference compiler emits (text form, one module per Tile) the way the
+ * reference's host execution does: it admits the closed integer subset of LLVM IR of
+ * lib/Wafer/Simulator/Invocation/TargetCallExecution.cpp:188-294 (integer binary ops, icmp, phi, select, casts, freeze,
+ * br / switch, smin / smax / umin / umax, calls to wafer_tx81_* descriptors) and routes every wafer_tx81_* call to
+ * the device executors above in place of waferTargetCallDispatch (TargetCallExecution.cpp:116-119). Tiles run as
+ * cooperatively scheduled interpreters on the calling thread, like the reference's SC_THREAD coroutines; Direct-DTE
+ * sends and receives are matched by (sender Tile, receiver Tile, receiver FSM) and a send issue blocks until its
+ * receiver is prepared (lib/Wafer/Simulator/SystemC/SystemCTargetModel.cpp:1110-1200). Entry arguments are planned
+ * from the !wafer.target.entry_arguments metadata (lib/Wafer/CodeGen/LLVM/TargetLLVMTranslation.cpp:119-140) into one
+ * DDR arena. Calls outside {ncc_join, direct_dte_{begin,begin_after_prepare,send_prepare,send_issue,recv_prepare,wait,
+ * finish}, rdma, wdma, gather_scatter, memset, gemm, gemm_oriented} are rejected with WB200_ERR_UNSUPPORTED at load. */
+typedef struct wb200_tile_program wb200_tile_program;
+typedef struct wb200_program_stats {
+  uint64_t instructions;              /* IR instructions interpreted */
+  uint64_t commands;                  /* wafer_tx81_* calls issued */
+  uint64_t gemm_commands, movement_commands, fill_commands, transfer_commands, sync_commands;
+  uint64_t gemm_fused_multiply_adds;  /* sum of m * k * n * batch */
+  uint64_t bytes_moved;               /* payload bytes of DMA, gather / scatter, fill and Direct-DTE transfers */
+  uint64_t gpu_launches;
+  float device_ms;                    /* command stream only (CUDA events); excludes host <-> device tensor copies */
+  uint32_t reserved;
+} wb200_program_stats;
+/* One issued command in a trace: `kind` indexes wb200_program_command_name(); args in ABI order without the worker.
+ * The trace also holds one "direct_dte_transfer" record (sender Tile, receiver Tile, source, destination, bytes) at
+ * the point of the command order where a matched Direct-DTE payload moves. */
+typedef struct wb200_program_command {
+  uint32_t tile, kind, argc, reserved;
+  uint64_t args[17];
+} wb200_program_command;
+
+/* `backend` may be null: the program can then be inspected and traced but not run. `spm_bytes` is the scratch-pad
+ * capacity per Tile (0: 3 MiB). */
+wb200_status wb200_tile_program_load(wb200_backend *backend, const char *const *module_texts, uint32_t tile_count,
+                                     uint64_t spm_bytes, wb200_tile_program **out);
+void wb200_tile_program_destroy(wb200_tile_program *program);
+/* External tensors in resource-index order. `compact_bytes` is the row-major size run() exchanges. */
+wb200_status wb200_tile_program_tensor_count(const wb200_tile_program *program, uint32_t *inputs, uint32_t *outputs);
+wb200_status wb200_tile_program_tensor_info(const wb200_tile_program *program, uint32_t is_output, uint32_t index,
+                                            wb200_tensor_desc *desc, uint64_t *compact_bytes);
+/* Where the address plan put an external tensor: its DDR address and physical size, and the arena's extent. */
+wb200_status wb200_tile_program_placement(const wb200_tile_program *program, uint32_t is_output, uint32_t index,
+                                          uint64_t *address, uint64_t *physical_bytes, uint64_t *ddr_base,
+                                          uint64_t *ddr_bytes);
+/* Interprets all Tiles without touching a device and records the issued commands in scheduling order.
+ * `records` may be null to query `count`. */
+wb200_status wb200_tile_program_trace(wb200_tile_program *program, wb200_program_command *records, uint64_t capacity,
+                                      uint64_t *count, wb200_program_stats *stats);
+const char *wb200_program_command_name(uint32_t kind);
+/* Runs the invocation: host compact row-major inputs are packed into their physical DDR layout, all Tiles execute,
+ * outputs are unpacked to `outputs`. `gemm_policy`: wb200_gemm_policy for psum-free, untransposed GEMM commands
+ * (commands with a partial sum always take the bit-exact sequential-k path). */
+wb200_status wb200_tile_program_run(wb200_tile_program *program, const void *const *inputs, void *const *outputs,
+                                    uint32_t gemm_policy, wb200_program_stats *stats);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,244 @@
+"""Replay of the reference compiler's shipped per-Tile target LLVM modules (GEMM optimisation ladder: seven plans x
+16 Tiles of out[4096,4096] = arg1[4096,1024] . arg0[1024,4096], bf16).
+
+CPU: the parser / interpreter / scheduler (device-free trace), the IR subset and its error reports, the CPU trace
+replay on a tiny hand-written program. GPU: all seven plans bit for bit against the committed CPU-replay hashes, one
+plan against the live CPU replay, every plan under the reference's similarity gate against the f32 matrix product."""
+import hashlib
+import importlib.util
+import json
+import lzma
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers
+from vibe_compiler_b200 import _abi as abi
+from vibe_compiler_b200.backend import WB200Error
+from vibe_compiler_b200.tile_program import TileProgram
+
+ROOT = Path(__file__).resolve().parent.parent
+FIXTURE = json.loads(lzma.decompress((ROOT / "tests" / "golden" / "gemm_tile_modules.json.xz").read_bytes()))
+EXPECTED = json.loads((ROOT / "tests" / "golden" / "gemm_tile_program_expected.json").read_text())
+_spec = importlib.util.spec_from_file_location("make_tile_program_expected", ROOT / "tests" / "golden" / "make_tile_program_expected.py")
+expected_tools = importlib.util.module_from_spec(_spec)
+_spec.loader.exec_module(expected_tools)
+
+PLANS = sorted(FIXTURE["plans"])
+
+
+def _module(body: str, arguments: str = "i64 %0, i64 %1", rows=None, tile: int = 0) -> str:
+    rows = rows or ['!{i64 0, !"external-input", i64 0, !"", !"f32", !"tensor", i64 1024, i64 256, !"read-only", i64 16, i64 16, i64 0}',
+                    '!{i64 1, !"external-output", i64 0, !"", !"f32", !"tensor", i64 1024, i64 256, !"write-only", i64 16, i64 16, i64 0}']
+    names = ", ".join(f"!{10 + i}" for i in range(len(rows)))
+    meta = "\n".join(f"!{10 + i} = {row}" for i, row in enumerate(rows))
+    return (f"define void @entry({arguments}) {{\n{body}\n}}\n!wafer.target.tile_id = !{{!2}}\n!wafer.target.entry_arguments = !{{{names}}}\n"
+            f"!2 = !{{i64 {tile}}}\n{meta}\n")
+
+
+# A 16x16 f32 matrix is read row-reversed, transposed in the scratch-pad and written back.
+REVERSE_ROWS = _module("""
+  br label %3
+3:
+  %4 = phi i64 [ 0, %2 ], [ %9, %6 ]
+  %5 = icmp ult i64 %4, 16
+  br i1 %5, label %6, label %10
+6:
+  %7 = sub i64 15, %4
+  %8 = mul i64 %7, 64
+  %src = add i64 %0, %8
+  %dstoff = shl i64 %4, 6
+  %dst = add i64 4096, %dstoff
+  call void @wafer_tx81_rdma(i64 %src, i64 %dst, i32 64, i32 64, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  %9 = add nuw i64 %4, 1
+  br label %3
+10:
+  call void @wafer_tx81_gather_scatter(i64 4096, i64 8192, i32 1024, i32 4, i32 4, i32 64, i32 0, i32 16, i32 16, i32 1, i32 64, i32 4, i32 0, i32 16, i32 16, i32 1, i32 0)
+  call void @wafer_tx81_ncc_join(i32 1)
+  call void @wafer_tx81_wdma(i64 8192, i64 %1, i32 1024, i32 1024, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  ret void
+""")
+
+
+def test_every_shipped_plan_parses_schedules_and_covers_the_product():
+    for plan in PLANS:
+        program = TileProgram(FIXTURE["plans"][plan])
+        assert [t.shape for t in program.inputs] == [(1, 1024, 4096), (1, 4096, 1024)]
+        assert [t.shape for t in program.outputs] == [(1, 4096, 4096)]
+        commands, stats = program.trace()
+        assert stats["gemm_fused_multiply_adds"] == 4096 * 4096 * 1024       # every (m, n, k) triple exactly once
+        assert stats["commands"] == sum(1 for c in commands if c.name != "direct_dte_transfer")
+        sends = sum(1 for c in commands if c.name == "wafer_tx81_direct_dte_send_issue")
+        assert stats["transfer_commands"] == sends == sum(1 for c in commands if c.name == "direct_dte_transfer")
+        out_bytes = sum(c.args[2] for c in commands if c.name == "wafer_tx81_wdma")
+        assert out_bytes == 4096 * 4096 * 2                                   # the output is written exactly once
+
+
+def test_interpreter_runs_a_small_program_and_the_cpu_replay_executes_its_trace():
+    from oracle import binding, trace_replay
+    binding.build()
+    program = TileProgram([REVERSE_ROWS])
+    commands, stats = program.trace()
+    assert [c.name for c in commands].count("wafer_tx81_rdma") == 16 and stats["movement_commands"] == 18
+    place_in, place_out = program.placement(False, 0), program.placement(True, 0)
+    ddr = np.zeros(place_in["ddr_bytes"], dtype=np.uint8)
+    matrix = np.arange(256, dtype=np.float32).reshape(16, 16)
+    at = place_in["address"] - place_in["ddr_base"]
+    ddr[at:at + 1024] = matrix.view(np.uint8).reshape(-1)
+    trace_replay.replay(commands, ddr, 1, spm_bytes=1 << 16)
+    at = place_out["address"] - place_out["ddr_base"]
+    got = ddr[at:at + 1024].view(np.float32).reshape(16, 16)
+    assert np.array_equal(got, matrix[::-1].T)
+
+
+def test_integer_subset_semantics():
+    body = """
+  %a = add i32 4000000000, 100
+  %b = zext i32 %a to i64
+  %c = sext i32 %a to i64
+  %d = icmp slt i64 %c, 0
+  %e = select i1 %d, i64 %b, i64 7
+  %f = udiv i64 %e, 3
+  %g = call i64 @llvm.smin.i64(i64 %c, i64 5)
+  %h = ashr i64 %g, 60
+  %i = trunc i64 %h to i8
+  %j = zext i8 %i to i64
+  %k = lshr i64 %f, 0
+  switch i64 %j, label %bad [
+    i64 255, label %good
+  ]
+bad:
+  ret void
+good:
+  %len = and i64 %k, 1023
+  %m = urem i64 %len, 1000
+  %n = xor i64 %m, 1
+  %o = or i64 %n, 64
+  %q = freeze i64 %o
+  call void @wafer_tx81_memset(i64 %q, i32 1, i32 4, i32 5, i32 0)
+  ret void
+"""
+    commands, stats = TileProgram([_module(body)]).trace()
+    # 4000000100 is negative as i32: the select keeps the zero-extended value and smin keeps the sign-extended one,
+    # whose arithmetic shift gives all ones -> 255 after trunc / zext -> the switch case is taken.
+    expected = ((((4000000100 // 3) & 1023) % 1000) ^ 1) | 64
+    assert [(c.name, c.args[0]) for c in commands] == [("wafer_tx81_memset", expected)]
+    assert stats["fill_commands"] == 1 and stats["instructions"] >= 18
+
+
+def test_negative_numbers_take_the_signed_paths():
+    body = """
+  %a = sub i64 0, 9
+  %b = sdiv i64 %a, 2
+  %c = srem i64 %a, 4
+  %d = add i64 %b, %c
+  %e = sub i64 0, %d
+  %f = call i64 @llvm.umax.i64(i64 %e, i64 2)
+  call void @wafer_tx81_memset(i64 %f, i32 0, i32 1, i32 5, i32 0)
+  ret void
+"""
+    commands, _ = TileProgram([_module(body)]).trace()
+    assert commands[0].args[0] == 5          # -9 / 2 = -4 (toward zero), -9 % 4 = -1, -(-5) = 5
+
+
+@pytest.mark.parametrize("body, fragment", [
+    ("  %x = fadd float 1.0, 2.0\n  ret void", "outside"),
+    ("  %p = inttoptr i64 %0 to ptr\n  ret void", "outside"),
+    ("  call void @wafer_tx81_elementwise_exp(i64 0, i64 64, i32 16, i32 5, i32 0)\n  ret void", "outside the executed command set"),
+    ("  call void @wafer_tx81_memset(i64 0, i32 0, i32 4)\n  ret void", "does not match its descriptor"),
+    ("  br label %nowhere", "unknown block"),
+    ("  %x = add i64 1, 2", "no terminator"),
+])
+def test_modules_outside_the_subset_are_rejected_at_load(body, fragment):
+    with pytest.raises(WB200Error, match=fragment):
+        TileProgram([_module(body)])
+
+
+def test_runtime_faults_are_reported_not_executed():
+    with pytest.raises(WB200Error, match="outside the memory image"):
+        TileProgram([_module("  call void @wafer_tx81_memset(i64 3145720, i32 0, i32 4, i32 5, i32 0)\n  ret void")]).trace()
+    with pytest.raises(WB200Error, match="byte_count differs"):
+        TileProgram([_module("  call void @wafer_tx81_rdma(i64 %0, i64 0, i32 100, i32 64, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)\n  ret void")]).trace()
+    with pytest.raises(WB200Error, match="division"):
+        TileProgram([_module("  %x = udiv i64 %0, 0\n  ret void")]).trace()
+    rows = ['!{i64 0, !"transport-status", i64 0, !"direct_dte_status", !"u32", !"tensor", i64 64, i64 64, !"read-write", i64 1, i64 0}']
+    waiting = """
+  call void @wafer_tx81_direct_dte_begin(i64 %0, i32 2)
+  %h = call i64 @wafer_tx81_direct_dte_recv_prepare(i64 0, i32 64, i32 TILE, i32 PEER, i32 0)
+  call void @wafer_tx81_direct_dte_wait(i64 %h)
+  call void @wafer_tx81_direct_dte_finish()
+  ret void
+"""
+    modules = [_module(waiting.replace("TILE", str(t)).replace("PEER", str(1 - t)), "i64 %0", rows, tile=t) for t in range(2)]
+    with pytest.raises(WB200Error, match="deadlock"):
+        TileProgram(modules).trace()          # both Tiles wait to receive, nobody sends
+    with pytest.raises(WB200Error, match="no-device|without a backend"):
+        TileProgram([REVERSE_ROWS]).run([np.zeros((16, 16), np.float32)])
+
+
+def test_direct_dte_send_blocks_until_the_receiver_is_prepared():
+    rows = ['!{i64 0, !"transport-status", i64 0, !"direct_dte_status", !"u32", !"tensor", i64 64, i64 64, !"read-write", i64 1, i64 0}']
+    sender = """
+  call void @wafer_tx81_direct_dte_begin(i64 %0, i32 2)
+  call void @wafer_tx81_memset(i64 128, i32 1065353216, i32 16, i32 5, i32 0)
+  call void @wafer_tx81_ncc_join(i32 1)
+  %h = call i64 @wafer_tx81_direct_dte_send_prepare(i64 128, i64 256, i32 64, i32 0, i32 1, i32 3, i32 0)
+  call void @wafer_tx81_direct_dte_send_issue(i64 %h)
+  call void @wafer_tx81_direct_dte_wait(i64 %h)
+  call void @wafer_tx81_direct_dte_finish()
+  ret void
+"""
+    receiver = """
+  call void @wafer_tx81_direct_dte_begin(i64 %0, i32 2)
+  call void @wafer_tx81_memset(i64 0, i32 0, i32 1024, i32 5, i32 0)
+  %h = call i64 @wafer_tx81_direct_dte_recv_prepare(i64 256, i32 64, i32 1, i32 0, i32 3)
+  call void @wafer_tx81_direct_dte_wait(i64 %h)
+  call void @wafer_tx81_direct_dte_finish()
+  ret void
+"""
+    commands, stats = TileProgram([_module(sender, "i64 %0", rows, 0), _module(receiver, "i64 %0", rows, 1)]).trace()
+    names = [(c.tile, c.name.replace("wafer_tx81_", "")) for c in commands]
+    # Tile 0 runs first and stops inside send_issue; the payload moves when Tile 1 prepares its receive
+    assert names.index((0, "direct_dte_send_issue")) < names.index((1, "direct_dte_recv_prepare")) < names.index((0, "direct_dte_transfer"))
+    assert names.index((0, "direct_dte_transfer")) < names.index((0, "direct_dte_wait"))
+    assert stats["transfer_commands"] == 1 and stats["bytes_moved"] == 64 + 64 + 4096
+
+
+# ------------------------------------------------------------------------------------------------ GPU
+def _as_torch(bits: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(bits.view(np.int16).copy()).view(torch.bfloat16)
+
+
+@pytest.mark.gpu
+def test_small_program_runs_on_the_device(backend):
+    program = TileProgram([REVERSE_ROWS], backend, spm_bytes=1 << 16)
+    matrix = np.random.default_rng(3).standard_normal((16, 16)).astype(np.float32)
+    (out,), stats = program.run([matrix])
+    assert np.array_equal(out.view(np.float32), matrix[::-1].T)
+    assert stats["gpu_launches"] == 18 and stats["device_ms"] > 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("plan", PLANS)
+def test_shipped_plan_replays_bit_exactly(backend, oracle, plan):
+    inputs = expected_tools.program_inputs()
+    assert hashlib.sha256(b"".join(a.tobytes() for a in inputs)).hexdigest() == EXPECTED["inputs_sha256"]
+    program = TileProgram(FIXTURE["plans"][plan], backend)
+    (out,), stats = program.run(inputs, abi.GEMM_FORMAL)
+    assert stats["gemm_commands"] in (256, 1024) and stats["gpu_launches"] >= stats["gemm_commands"] + stats["movement_commands"]
+    assert hashlib.sha256(out.tobytes()).hexdigest() == EXPECTED["plans"][plan]["sha256"]
+    # the reference's acceptance gate against the source program: out = arg1 . arg0
+    want = (_as_torch(inputs[1]).float()[0].cuda() @ _as_torch(inputs[0]).float()[0].cuda()).bfloat16().cpu()
+    helpers.reference_gate(oracle, "bf16", out.reshape(-1), helpers.bits(want).reshape(-1))
+    program.close()
+
+
+@pytest.mark.gpu
+def test_one_plan_against_the_live_cpu_replay(backend):
+    plan = "tensor-winner"
+    inputs = expected_tools.program_inputs()
+    want = expected_tools.cpu_replay(FIXTURE["plans"][plan], inputs, threads=16)
+    (out,), _ = TileProgram(FIXTURE["plans"][plan], backend).run(inputs)
+    assert np.array_equal(out, want)

@@ -127,6 +127,19 @@ class DecoderLayerParams(C.Structure):
                 ("allreduce", ALLREDUCE_FN), ("allreduce_user", C.c_void_p), ("stream", C.c_void_p)]
 
 
+class ProgramStats(C.Structure):
+    _fields_ = [("instructions", C.c_uint64), ("commands", C.c_uint64), ("gemm_commands", C.c_uint64), ("movement_commands", C.c_uint64),
+                ("fill_commands", C.c_uint64), ("transfer_commands", C.c_uint64), ("sync_commands", C.c_uint64),
+                ("gemm_fused_multiply_adds", C.c_uint64), ("bytes_moved", C.c_uint64), ("gpu_launches", C.c_uint64),
+                ("device_ms", C.c_float), ("reserved", C.c_uint32)]
+
+
+class ProgramCommand(C.Structure):
+    _fields_ = [("tile", C.c_uint32), ("kind", C.c_uint32), ("argc", C.c_uint32), ("reserved", C.c_uint32), ("args", C.c_uint64 * 17)]
+
+
+_U32x3 = C.POINTER(C.c_uint32)
+
 SIGNATURES = {
     "wb200_abi_version": (C.c_int, []),
     "wb200_last_error": (C.c_char_p, []),
@@ -154,6 +167,18 @@ SIGNATURES = {
     "wb200_residual_add": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
     "wb200_decoder_layer_workspace_bytes": (C.c_uint64, [C.POINTER(DecoderLayerParams)]),
     "wb200_decoder_layer": (C.c_int, [C.c_void_p, C.POINTER(DecoderLayerParams)]),
+    "wb200_target_call_rdma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, _U32x3, _U32x3]),
+    "wb200_target_call_wdma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, _U32x3, _U32x3]),
+    "wb200_target_call_gather_scatter": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, _U32x3, _U32x3, _U32x3, _U32x3]),
+    "wb200_target_call_memset": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "wb200_tile_program_load": (C.c_int, [C.c_void_p, C.POINTER(C.c_char_p), C.c_uint32, C.c_uint64, C.POINTER(C.c_void_p)]),
+    "wb200_tile_program_destroy": (None, [C.c_void_p]),
+    "wb200_tile_program_tensor_count": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32)]),
+    "wb200_tile_program_tensor_info": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(TensorDesc), C.POINTER(C.c_uint64)]),
+    "wb200_tile_program_placement": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint32] + [C.POINTER(C.c_uint64)] * 4),
+    "wb200_tile_program_trace": (C.c_int, [C.c_void_p, C.POINTER(ProgramCommand), C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(ProgramStats)]),
+    "wb200_program_command_name": (C.c_char_p, [C.c_uint32]),
+    "wb200_tile_program_run": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_uint32, C.POINTER(ProgramStats)]),
     "wb200_spm_create": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(C.c_void_p)]),
     "wb200_spm_destroy": (None, [C.c_void_p]),
     "wb200_spm_write": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]),

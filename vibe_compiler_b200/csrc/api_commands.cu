@@ -300,12 +300,6 @@ wb200_status wb200_reduce(wb200_backend *backend, const wb200_reduce_request *r,
 }  // extern "C"
 
 // ------------------------------------------------------------------ TargetCall ABI (Seam 2)
-struct wb200_spm_image {
-  wb200_backend *backend;
-  uint64_t base, bytes;
-  uint8_t *device;
-};
-
 extern "C" {
 
 wb200_status wb200_spm_create(wb200_backend *backend, uint64_t base_address, uint64_t bytes, wb200_spm_image **out) {
@@ -328,9 +322,7 @@ void wb200_spm_destroy(wb200_spm_image *image) {
 }
 
 static wb200_status spm_range(const wb200_spm_image *image, uint64_t address, uint64_t bytes, const char *what) {
-  if (address < image->base || bytes > image->bytes || address - image->base > image->bytes - bytes)
-    return fail(WB200_ERR_INVALID_ARGUMENT, std::string(what) + " lies outside the scratch-pad image");
-  return WB200_OK;
+  return wb200::image_range(image, address, bytes, what);
 }
 
 wb200_status wb200_spm_write(wb200_spm_image *image, uint64_t address, const uint8_t *src, uint64_t bytes) {
@@ -353,10 +345,20 @@ wb200_status wb200_spm_read(wb200_spm_image *image, uint64_t address, uint8_t *d
   return WB200_OK;
 }
 
-wb200_status wb200_target_call_gemm(wb200_spm_image *image, uint64_t lhs, uint64_t rhs, uint64_t dst, uint64_t psum,
-                                    uint32_t m, uint32_t k, uint32_t n, uint32_t batch, uint32_t in_format,
-                                    uint32_t out_format, uint32_t psum_format, uint32_t lhs_orientation,
-                                    uint32_t rhs_orientation, uint32_t policy) {
+}  // extern "C"
+
+namespace wb200 {
+
+wb200_status image_range(const wb200_spm_image *image, uint64_t address, uint64_t bytes, const char *what) {
+  if (address < image->base || bytes > image->bytes || address - image->base > image->bytes - bytes)
+    return fail(WB200_ERR_INVALID_ARGUMENT, std::string(what) + " lies outside the memory image");
+  return WB200_OK;
+}
+
+wb200_status enqueue_image_gemm(wb200_spm_image *image, uint64_t lhs, uint64_t rhs, uint64_t dst, uint64_t psum,
+                                uint32_t m, uint32_t k, uint32_t n, uint32_t batch, uint32_t in_format,
+                                uint32_t out_format, uint32_t psum_format, uint32_t lhs_orientation,
+                                uint32_t rhs_orientation, uint32_t policy) {
   if (!image) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
   if (m == 0 || k == 0 || n == 0 || batch == 0 || m > 65535 || n > 65535 || k > 16384 || batch > 4096)
     return fail(WB200_ERR_INVALID_ARGUMENT, "GEMM extents outside the command domain");
@@ -405,8 +407,21 @@ wb200_status wb200_target_call_gemm(wb200_spm_image *image, uint64_t lhs, uint64
   g.dst = image->device + (dst - image->base);
   const char *implementation = "";
   const int effective_policy = (policy == WB200_GEMM_TENSOR && !has_psum && !lt && !rt) ? WB200_GEMM_TENSOR : WB200_GEMM_FORMAL;
-  if ((st = run_device_gemm(backend, g, effective_policy, 4, backend->stream, &implementation)) != WB200_OK) return st;
-  return read_device_status(backend, backend->stream, nullptr);
+  return run_device_gemm(backend, g, effective_policy, 4, backend->stream, &implementation);
+}
+
+}  // namespace wb200
+
+extern "C" {
+
+wb200_status wb200_target_call_gemm(wb200_spm_image *image, uint64_t lhs, uint64_t rhs, uint64_t dst, uint64_t psum,
+                                    uint32_t m, uint32_t k, uint32_t n, uint32_t batch, uint32_t in_format,
+                                    uint32_t out_format, uint32_t psum_format, uint32_t lhs_orientation,
+                                    uint32_t rhs_orientation, uint32_t policy) {
+  wb200_status st = enqueue_image_gemm(image, lhs, rhs, dst, psum, m, k, n, batch, in_format, out_format, psum_format,
+                                       lhs_orientation, rhs_orientation, policy);
+  if (st != WB200_OK) return st;
+  return read_device_status(image->backend, image->backend->stream, nullptr);
 }
 
 }  // extern "C"

@@ -41,7 +41,22 @@ struct wb200_backend {
   }
 };
 
+// One flat device-resident memory image (a Tile's scratch-pad, or a DDR arena) addressed by the byte
+// addresses the TargetCall ABI carries.
+struct wb200_spm_image {
+  wb200_backend *backend;
+  uint64_t base, bytes;
+  uint8_t *device;
+};
+
 namespace wb200 {
+
+wb200_status image_range(const wb200_spm_image *image, uint64_t address, uint64_t bytes, const char *what);
+// wafer_tx81_gemm on a scratch-pad image, enqueued on the backend stream without synchronising.
+wb200_status enqueue_image_gemm(wb200_spm_image *image, uint64_t lhs, uint64_t rhs, uint64_t dst, uint64_t psum,
+                                uint32_t m, uint32_t k, uint32_t n, uint32_t batch, uint32_t in_format,
+                                uint32_t out_format, uint32_t psum_format, uint32_t lhs_orientation,
+                                uint32_t rhs_orientation, uint32_t policy);
 
 struct DeviceGuard {
   int previous = -1;

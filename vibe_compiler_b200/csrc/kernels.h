@@ -102,4 +102,16 @@ wb200_status launch_rope_split(int format, const void *qkv, void *q, void *k, vo
                                int kv_heads, int head_dim, float theta, int position_offset, cudaStream_t stream);
 wb200_status launch_residual_add(int format, const void *a, const void *b, void *out, size_t elements, cudaStream_t stream);
 
+// ---- movement commands on device-resident memory images (tile_movement.cu)
+struct StridedLayout {
+  uint32_t inner_bytes;
+  uint32_t strides[3];
+  uint32_t iterations[3];
+};
+uint64_t strided_segments(const StridedLayout &layout);
+uint64_t strided_span(const StridedLayout &layout);   // bytes from the first to one past the last byte touched
+wb200_status launch_strided_copy(const uint8_t *src, const StridedLayout &from, uint8_t *dst, const StridedLayout &to,
+                                 cudaStream_t stream);
+wb200_status launch_fill(uint8_t *dst, uint32_t value_bits, uint64_t count, int element_bytes, cudaStream_t stream);
+
 }  // namespace wb200
