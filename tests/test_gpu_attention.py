@@ -49,6 +49,40 @@ def test_fa_tensor_core_kernel(backend, oracle, shape, dtype):
     helpers.reference_gate(oracle, fmt, helpers.bits(out), want["out"])
 
 
+@pytest.mark.parametrize("shape", [
+    # more (batch, head, 256-row) items than SMs: every CTA of the persistent grid walks several items, with ragged
+    # last tiles, GQA, causal offsets and items whose second Q tile is empty
+    (3, 20, 5, 640, 640, True), (2, 40, 40, 600, 900, True), (5, 16, 4, 520, 300, False), (2, 96, 8, 300, 300, True)])
+def test_fa_persistent_grid_walks_many_items(backend, oracle, shape):
+    b, hq, hkv, sq, skv, causal = shape
+    q, k, v = make_qkv(b, hq, hkv, sq, skv, 128, torch.bfloat16, seed=7)
+    scale = 128 ** -0.5
+    lse = torch.empty(b, hq, sq)
+    start = skv - sq if causal else 0
+    out = backend.attention_fa(q, k, v, scale, causal, lse=lse, query_start=start)
+    want = oracle.attention("bf16", helpers.bits(q), helpers.bits(k), helpers.bits(v), scale, causal, tile_n=128, threads=16, query_start=start)
+    check_against_oracle(oracle, "bf16", out, lse, want)
+
+
+def test_fa_persistent_and_plain_grid_agree():
+    # WB200_FA_PERSISTENT=0 launches one CTA per item; the arithmetic per item is the same, so the bits must agree.
+    import subprocess, sys
+    code = ("import sys, torch; sys.path.insert(0, %r);"
+            "from vibe_compiler_b200.backend import B200TargetModelBackend as B;"
+            "from tests.test_gpu_attention import make_qkv;"
+            "q, k, v = make_qkv(2, 48, 8, 1100, 1100, 128, torch.bfloat16);"
+            "be = B(0); lse = torch.empty(2, 48, 1100);"
+            "out = be.attention_fa(q, k, v, 128 ** -0.5, True, lse=lse);"
+            "torch.save((out, lse), sys.argv[1])") % str(helpers.ROOT)
+    outs = []
+    for mode in ("0", "1"):
+        path = f"/tmp/wb200_fa_persistent{mode}.pt"
+        subprocess.run([sys.executable, "-c", code, path], check=True, env=dict(os.environ, WB200_FA_PERSISTENT=mode), timeout=300)
+        outs.append(torch.load(path))
+    assert torch.equal(outs[0][0].view(torch.int16), outs[1][0].view(torch.int16))
+    assert torch.equal(outs[0][1], outs[1][1])
+
+
 def test_fa_both_p_placements_agree(oracle):
     # The kernel keeps the rounded P either in TMEM or in shared memory (WB200_FA_P_IN_TMEM); both are the same
     # arithmetic, so the outputs must be identical bit for bit. Run each in a fresh process (the mode is read once).

@@ -9,15 +9,26 @@
 // split across workers. Scores are kept in the log2 domain (scale*log2e folded into one f32
 // constant) so exp is one ex2 per element.
 //
-// One CTA owns 256 query rows of one (batch, head): two 128-row Q tiles, each with its own S and O
+// One work item is 256 query rows of one (batch, head): two 128-row Q tiles, each with its own S and O
 // accumulators in TMEM (S0 S1 O0 O1 = 4 x 128 columns) and its own softmax warpgroup, so the tensor
-// pipe works on one tile while the other tile's softmax runs. Warp 0 = TMA producer (Q once, then
-// K0 V0 K1 V1 ... through a ring of 32 KiB slots), warp 1 = MMA issuer and TMEM owner, warps 4-7 /
-// 8-11 = softmax + rescale + epilogue for Q tile 0 / 1 (thread = query row, so row max and row sum
-// need no shuffles; setmaxnreg moves registers from warpgroup 0 to the softmax warpgroups). kPInTmem selects where the rounded P lives: in TMEM, aliasing the first 64
-// columns of S (A operand read from TMEM, 5 ring slots), or in shared memory (3 ring slots).
+// pipe works on one tile while the other tile's softmax runs. A persistent grid of one CTA per SM walks
+// a host-made plan of items (longest-processing-time assignment, heaviest first), so the loads and first
+// scores of an item overlap the softmax tail and write-out of the previous one and every CTA ends at
+// nearly the same time. Warp 0 = TMA producer (per item: Q, then K0 V0 K1 V1 ... through a ring of
+// 32 KiB slots that runs on across items), warp 1 = MMA issuer and TMEM owner, warps 4-7 / 8-11 =
+// softmax + rescale + epilogue for Q tile 0 / 1 (thread = query row, so row max and row sum need no
+// shuffles; setmaxnreg moves registers from warpgroup 0 to the softmax warpgroups). All mbarriers are
+// reused across items with running completion counts as parities. kPInTmem selects where the rounded
+// P lives: in TMEM, aliasing the first 64 columns of S (A operand read from TMEM, 5 ring slots), or in
+// shared memory (3 ring slots).
 // Roofline: tensor pipe; algorithmic work is 4 * head_dim flop per visible (query, key) pair.
+#include <algorithm>
+#include <map>
+#include <mutex>
+#include <queue>
+#include <tuple>
 #include <type_traits>
+#include <vector>
 
 #include "kernels.h"
 #include "ptx_sm100.cuh"
@@ -60,11 +71,23 @@ struct FaSmem {
 };
 
 #ifdef WB200_FA_TRACE
-// Debug build only: clock64 time stamps of one CTA, read back through wb200_debug_fa_trace.
+// Debug builds only: clock64 time stamps of CTA 0, read back through wb200_debug_fa_trace. -DWB200_FA_TRACE=1 keeps
+// the per-item stamps (a few per work item), -DWB200_FA_TRACE=2 adds the per-tile stamps (which perturb the loop).
 __device__ long long g_fa_trace[8192];
-#define FA_TRACE(slot, index) do { if (blockIdx.x == 0) g_fa_trace[(slot) * 64 + ((index) & 63)] = clock64(); } while (0)
+#define FA_TRACE_ITEM(slot, index) do { if (blockIdx.x == 0) g_fa_trace[(slot) * 64 + ((index) & 63)] = clock64(); } while (0)
+__device__ __forceinline__ long long fa_global_ns() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+#define FA_TRACE_NS(slot, index) do { if (blockIdx.x == 0) g_fa_trace[(slot) * 64 + ((index) & 63)] = fa_global_ns(); } while (0)
+#define FA_TRACE_CTA(which) do { if (blockIdx.x < 256) g_fa_trace[2560 + blockIdx.x * 2 + (which)] = fa_global_ns(); } while (0)
+#if WB200_FA_TRACE >= 2
+#define FA_TRACE(slot, index) FA_TRACE_ITEM(slot, index)
 #else
 #define FA_TRACE(slot, index) do { } while (0)
+#endif
+#else
+#define FA_TRACE(slot, index) do { } while (0)
+#define FA_TRACE_ITEM(slot, index) do { } while (0)
+#define FA_TRACE_NS(slot, index) do { } while (0)
+#define FA_TRACE_CTA(which) do { } while (0)
 #endif
 
 struct FaParams {
@@ -78,6 +101,8 @@ struct FaParams {
   int bf16;
   int num_pairs;           // ceil(q_len / 256)
   int out_token_major;     // out is [batch, q_len, q_heads, head_dim] instead of [batch, q_heads, q_len, head_dim]
+  const int *plan;         // [grid][plan_stride] item ids of each CTA in execution order, -1 terminated
+  int plan_stride;
   float scale_log2;        // scale * log2(e)
   void *out;
   float *lse, *row_max, *row_sum;
@@ -145,6 +170,49 @@ __device__ __forceinline__ int kv_tiles_for(const FaParams &p, int row0) {
   return static_cast<int>(last / kTileN) + 1;
 }
 
+// One work item = 256 query rows (two Q tiles) of one (batch, head); item g covers pair num_pairs-1 - g / (batch*heads)
+// of (batch, head) g % (batch*heads), so low ids are the heaviest under a causal mask. The launcher deals the items to
+// the CTAs of a persistent grid with a longest-processing-time plan (each CTA: its items, heaviest first), so every
+// CTA ends at nearly the same time; the kernel only walks its row of the plan.
+struct FaItem {
+  int valid;
+  int bh, bh_kv, b, h;
+  int row_base;
+  int n0, n1;       // KV tiles Q tile 0 / 1 visits (scalars: a runtime-indexed array would live in local memory)
+  int n_max;
+  __device__ __forceinline__ int tiles(int t) const { return t ? n1 : n0; }
+};
+__device__ __forceinline__ FaItem fa_item(const FaParams &p, int k) {
+  FaItem item;
+  // 32-bit arithmetic only: a 64-bit division is an out-of-line call, and a call inside the MMA warp's code costs
+  // about 8 % per KV step of its issue loop.
+  const int id = p.plan[static_cast<size_t>(blockIdx.x) * p.plan_stride + k];
+  const unsigned g = static_cast<unsigned>(id);
+  const unsigned bh_count = static_cast<unsigned>(p.batch * p.q_heads);
+  item.valid = id >= 0;
+  item.bh = item.bh_kv = item.b = item.h = item.row_base = item.n0 = item.n1 = item.n_max = 0;
+  if (!item.valid) return item;
+  const unsigned pair_rank = g / bh_count;
+  const int pair = p.num_pairs - 1 - static_cast<int>(pair_rank);   // heaviest pairs first
+  item.bh = static_cast<int>(g - pair_rank * bh_count);
+  item.b = item.bh / p.q_heads;
+  item.h = item.bh % p.q_heads;
+  item.bh_kv = item.b * p.kv_heads + item.h / p.group;
+  item.row_base = pair * 2 * kTileM;
+  item.n0 = kv_tiles_for(p, item.row_base);
+  item.n1 = kv_tiles_for(p, item.row_base + kTileM);
+  item.n_max = item.n0 > item.n1 ? item.n0 : item.n1;
+  return item;
+}
+// First item at or after position k that has KV tiles to visit (items without any are handled by the softmax
+// warps alone); advances k past it.
+__device__ __forceinline__ FaItem fa_next_working_item(const FaParams &p, int &k) {
+  while (true) {
+    const FaItem item = fa_item(p, k++);
+    if (!item.valid || item.n_max > 0) return item;
+  }
+}
+
 template <bool kPInTmem, bool kBf16>
 __global__ void __launch_bounds__(kFaThreads, 1)
 fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -163,19 +231,14 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   // P of one tile is published in two halves (keys 0-63, 64-127) so PV can start on the first half.
   auto p_part = [&](int t, int part) { return bar_base + 8u * (2 * L::kSlots + 3 + kPParts * t + part); };
   auto o_done = [&](int t) { return bar_base + 8u * (2 * L::kSlots + 3 + 2 * kPParts + t); };
+  const uint32_t q_empty = bar_base + 8u * (2 * L::kSlots + 5 + 2 * kPParts);   // every S product of an item has finished
   uint8_t *bar_ptr = smem + L::kBarOff;
-  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bar_ptr + 8 * (2 * L::kSlots + 5 + 2 * kPParts));
-  volatile int *abort_word = reinterpret_cast<volatile int *>(bar_ptr + 8 * (2 * L::kSlots + 6 + 2 * kPParts));
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bar_ptr + 8 * (2 * L::kSlots + 6 + 2 * kPParts));
+  volatile int *abort_word = reinterpret_cast<volatile int *>(bar_ptr + 8 * (2 * L::kSlots + 7 + 2 * kPParts));
+  // All barriers are reused across work items; every role keeps running completion counts for the parities.
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bh_count = p.batch * p.q_heads;
-  const int pair = p.num_pairs - 1 - static_cast<int>(blockIdx.x) / bh_count;  // heaviest pairs first
-  const int bh = static_cast<int>(blockIdx.x) % bh_count;
-  const int b = bh / p.q_heads, h = bh % p.q_heads;
-  const int bh_kv = b * p.kv_heads + h / p.group;
-  const int row_base = pair * 2 * kTileM;
-  const int n_tiles[2] = {kv_tiles_for(p, row_base), kv_tiles_for(p, row_base + kTileM)};
-  const int n_max = n_tiles[0] > n_tiles[1] ? n_tiles[0] : n_tiles[1];
+  if (threadIdx.x == 0) { FA_TRACE_ITEM(100, 0); FA_TRACE_NS(120, 0); FA_TRACE_CTA(0); }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::kSlots; ++s) {
@@ -183,6 +246,7 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       mbar_init(kv_empty(s), 1);
     }
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int t = 0; t < 2; ++t) {
       mbar_init(s_full(t), 1);
       for (int part = 0; part < kPParts; ++part) mbar_init(p_part(t, part), kTileM);
@@ -202,36 +266,45 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) FA_TRACE_ITEM(101, 0);
 
   // setmaxnreg.inc blocks until the CTA's own register pool can supply the request, so the totals after
-  // reallocation (128 * 88 + 256 * 208) must not exceed what the CTA was launched with (384 * 168).
-  static_assert(128 * 88 + 256 * 208 <= kFaThreads * 168, "setmaxnreg totals exceed the launch allocation");
+  // reallocation (128 * 104 + 256 * 200) must not exceed what the CTA was launched with (384 * 168).
+  static_assert(128 * 104 + 256 * 200 <= kFaThreads * 168, "setmaxnreg totals exceed the launch allocation");
   if (warp < 4) {
-  setmaxnreg_dec<88>();
+  setmaxnreg_dec<104>();
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0 && n_max > 0) {
-      mbar_arrive_expect_tx(q_full, 2 * kTileBytesFa);
-      for (int t = 0; t < 2; ++t)
-        for (int c = 0; c < 2; ++c)
-          tma_load_3d(smem_base + L::kQOff + t * kTileBytesFa + c * kBlockBytes, &tmap_q, q_full, c * 64,
-                      row_base + t * kTileM, bh);
+    if (lane == 0) {
       int slot = 0;
-      uint32_t phase = 0;
+      uint32_t phase = 0, q_loads = 0;
       bool ok = true;
-      for (int i = 0; ok && i < 2 * n_max; ++i) {  // ring position 2j = K_j, 2j+1 = V_j
-        if (!mbar_wait(kv_empty(slot), phase ^ 1u, abort_word)) { ok = false; break; }
-        mbar_arrive_expect_tx(kv_full(slot), kTileBytesFa);
-        const CUtensorMap *map = (i & 1) ? &tmap_v : &tmap_k;
-        const uint32_t dst = smem_base + L::kRingOff + slot * kTileBytesFa;
-        tma_load_3d(dst, map, kv_full(slot), 0, (i >> 1) * kTileN, bh_kv);
-        tma_load_3d(dst + kBlockBytes, map, kv_full(slot), 64, (i >> 1) * kTileN, bh_kv);
-        if (++slot == L::kSlots) { slot = 0; phase ^= 1u; }
+      int k = 0;
+      while (ok) {
+        const FaItem item = fa_next_working_item(p, k);
+        if (!item.valid) break;
+        // The Q buffer is free once every S product of the previous item has finished.
+        if (q_loads > 0 && !mbar_wait(q_empty, (q_loads - 1) & 1u, abort_word, 101)) break;
+        ++q_loads;
+        mbar_arrive_expect_tx(q_full, 2 * kTileBytesFa);
+        for (int t = 0; t < 2; ++t)
+          for (int c = 0; c < 2; ++c)
+            tma_load_3d(smem_base + L::kQOff + t * kTileBytesFa + c * kBlockBytes, &tmap_q, q_full, c * 64,
+                        item.row_base + t * kTileM, item.bh);
+        for (int i = 0; i < 2 * item.n_max; ++i) {  // ring position 2j = K_j, 2j+1 = V_j
+          if (!mbar_wait(kv_empty(slot), phase ^ 1u, abort_word, 102)) { ok = false; break; }
+          mbar_arrive_expect_tx(kv_full(slot), kTileBytesFa);
+          const CUtensorMap *map = (i & 1) ? &tmap_v : &tmap_k;
+          const uint32_t dst = smem_base + L::kRingOff + slot * kTileBytesFa;
+          tma_load_3d(dst, map, kv_full(slot), 0, (i >> 1) * kTileN, item.bh_kv);
+          tma_load_3d(dst + kBlockBytes, map, kv_full(slot), 64, (i >> 1) * kTileN, item.bh_kv);
+          if (++slot == L::kSlots) { slot = 0; phase ^= 1u; }
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0 && n_max > 0) {
+    if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_f16(kTileM, kTileN, kBf16, false, false);
       const uint32_t idesc_o = umma_idesc_f16(kTileM, kHd, kBf16, false, true);
       int slot = 0;
@@ -241,7 +314,7 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       // Descriptors differ only in the 14-bit start-address field, so a tile's descriptor is built once
       // and each k-step adds a compile-time constant to it.
       const uint64_t q_desc[2] = {umma_desc_kmajor(smem_base + L::kQOff), umma_desc_kmajor(smem_base + L::kQOff + kTileBytesFa)};
-#ifdef WB200_FA_TRACE
+#if defined(WB200_FA_TRACE) && WB200_FA_TRACE >= 2
       int s_count[2] = {0, 0};
 #endif
       auto issue_s = [&](int t, uint32_t k_addr) {
@@ -253,7 +326,7 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           umma_f16_ss(d_tmem, q_desc[t] + off, k_desc + off, idesc_s, ks != 0 ? 1u : 0u);
         }
         umma_commit(s_full(t));
-#ifdef WB200_FA_TRACE
+#if defined(WB200_FA_TRACE) && WB200_FA_TRACE >= 2
         FA_TRACE(0 + t, s_count[t]++);
 #endif
       };
@@ -275,15 +348,28 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (part == kPParts - 1) umma_commit(o_done(t));
       };
 
-      ok = mbar_wait(q_full, 0, abort_word);
+      // Work items follow one another on the same barriers; base[t] counts the tiles Q-tile slot t has consumed in
+      // earlier items, q_count the Q loads, so every parity is a running count.
+      uint32_t base[2] = {0, 0};
+      uint32_t q_count = 0;
+      int item_cursor = 0;
+      FaItem item = fa_next_working_item(p, item_cursor);
+      while (ok && item.valid) {
+      const int n_tiles[2] = {item.n0, item.n1};
+      const int n_max = item.n_max;
+      ok = mbar_wait(q_full, q_count & 1u, abort_word);
+      ++q_count;
+      FA_TRACE_ITEM(102, 0);
       // K_0: first scores of both tiles.
       if (ok) ok = mbar_wait(kv_full(slot), phase, abort_word);
       if (ok) {
+        FA_TRACE_ITEM(103, 0);
         tc_fence_after();
         const uint32_t k_addr = smem_base + L::kRingOff + slot * kTileBytesFa;
         for (int t = 0; t < 2; ++t)
           if (n_tiles[t] > 0) issue_s(t, k_addr);
         umma_commit(kv_empty(slot));
+        if (n_max == 1) umma_commit(q_empty);   // the only S products of the item are in flight
         advance();
       }
       for (int j = 0; ok && j < n_max; ++j) {
@@ -303,7 +389,7 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           if (j < n_tiles[t]) {
 #pragma unroll
             for (int part = 0; part < kPParts; ++part) {
-              if (!mbar_wait_spin(p_part(t, part), j & 1, abort_word)) { ok = false; break; }
+              if (!mbar_wait_spin(p_part(t, part), (base[t] + j) & 1u, abort_word)) { ok = false; break; }
               if (WB200_FA_FENCE_EVERY_PART || part == 0) tc_fence_after();
               if (part == 0) FA_TRACE(2 + t, j);
               issue_pv_part(t, part, v_addr, j > 0);
@@ -323,34 +409,53 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (!ok) break;
         umma_commit(kv_empty(v_slot));
         if (has_next) umma_commit(kv_empty(k_slot));
+        if (j + 2 == n_max) umma_commit(q_empty);   // the last S products of the item are in flight: Q may be replaced
       }
+      base[0] += n_tiles[0];
+      base[1] += n_tiles[1];
+      item = fa_next_working_item(p, item_cursor);
+      }   // items
     }
   }
   } else {
-    setmaxnreg_inc<208>();
+    setmaxnreg_inc<200>();
     // ------------------------------------------------------------ softmax / rescale / epilogue
     const int t = (warp - 4) >> 2;          // Q tile of this warpgroup
     const int quarter = warp & 3;           // TMEM lane quarter this warp may access
     const int row_in_tile = quarter * 32 + lane;
-    const int row = row_base + t * kTileM + row_in_tile;   // query row inside the head
     const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
     const uint32_t s_addr = tmem_base + lane_sel + kColS0 + t * 128;
     const uint32_t o_addr = tmem_base + lane_sel + kColO0 + t * 128;
-    const int my_tiles = n_tiles[t];
+    uint32_t tiles_done = 0;   // S tiles of this Q-tile slot consumed so far, over all items (barrier parities)
+    bool ok = true;
+    for (int item_index = 0; ok; ++item_index) {
+    // Only the row, the tile count and the mask limit stay live through the tile loop; the output coordinates are
+    // recomputed after it (the softmax threads need every register for the 128 scores they hold).
+    int row_base, my_tiles;
+    {
+      const FaItem item = fa_item(p, item_index);
+      if (!item.valid) break;
+      row_base = item.row_base;
+      my_tiles = item.tiles(t);
+    }
+    const int row = row_base + t * kTileM + row_in_tile;   // query row inside the head
     // m_ref is the exponent reference the stored P, l and acc are scaled by; m_true is the running row
     // maximum. The reference moves to the new maximum only when the maximum has grown by more than
     // kRescaleThreshold (log2 units), so P stays below 2^8 and the rescale of acc is rare. acc / l and
     // m_ref + log2(l) do not depend on the reference chosen, and every rounding keeps its relative error.
     constexpr float kRescaleThreshold = 8.0f;
     float m_ref = -INFINITY, m_true = -INFINITY, l_run = 0.f;
-    bool ok = true;
-    const long long causal_limit = p.causal ? p.causal_offset + row : 0x7fffffffffffLL;
+    // Last visible key of this row, relative to key 0, clamped to 32 bits (rows see keys <= limit).
+    long long limit64 = static_cast<long long>(p.kv_visible) - 1;
+    if (p.causal && p.causal_offset + row < limit64) limit64 = p.causal_offset + row;
+    const int row_limit = limit64 < -1 ? -1 : static_cast<int>(limit64);
 
-    for (int j = 0; ok && j < my_tiles; ++j) {
-      if (!mbar_wait(s_full(t), j & 1, abort_word)) { ok = false; break; }
+    for (int j = 0; ok && j < my_tiles; ++j, ++tiles_done) {
+      if (!mbar_wait(s_full(t), tiles_done & 1u, abort_word, 110 + t)) { ok = false; break; }
       tc_fence_after();
       const bool tracer = lane == 0;
       if (tracer) FA_TRACE(8 + 16 * t + quarter, j);
+      if (tracer && j == 0 && quarter == 0) FA_TRACE_ITEM(110 + t, item_index);
       const int key0 = j * kTileN;
       uint32_t r[128];
 #pragma unroll
@@ -360,11 +465,10 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       const bool need_mask = (key0 + kTileN > p.kv_visible) ||
                              (p.causal && key0 + kTileN - 1 > p.causal_offset + row_base + t * kTileM);
       if (need_mask) {
+        const int visible_in_tile = row_limit - key0;   // keys i <= visible_in_tile of this tile are visible
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
-          const int key = key0 + i;
-          if (!(key < p.kv_visible && key <= causal_limit)) r[i] = 0xff800000u;   // -inf
-        }
+        for (int i = 0; i < 128; ++i)
+          if (i > visible_in_tile) r[i] = 0xff800000u;   // -inf
       }
       // Row maximum: four independent chains of 3-input max.
       float mx[4];
@@ -389,7 +493,7 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
       // acc' = acc * alpha (rare): needs PV of the previous tile to have landed in TMEM, and must be done
       // before any PV of this tile is issued, i.e. before the first half of P is published.
       if (j > 0) {
-        if (!mbar_wait(o_done(t), (j - 1) & 1, abort_word)) { ok = false; break; }
+        if (!mbar_wait(o_done(t), (tiles_done - 1) & 1u, abort_word, 112 + t)) { ok = false; break; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll 1
@@ -454,11 +558,15 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     }
 
     // Finalize: out = acc * (1 / l), rounded once to the storage type.
-    if (ok && my_tiles > 0) ok = mbar_wait(o_done(t), (my_tiles - 1) & 1, abort_word);
+    if (threadIdx.x == 256) FA_TRACE_ITEM(104, item_index);
+    if (ok && my_tiles > 0) ok = mbar_wait(o_done(t), (tiles_done - 1) & 1u, abort_word, 114 + t);
+    if (threadIdx.x == 256) FA_TRACE_ITEM(105, item_index);
     if (ok && row_base + t * kTileM < p.q_len) {
       tc_fence_after();
       float coefficient = 1.0f / l_run;
       if (p.zero_fully_masked && l_run == 0.f) coefficient = 0.f;
+      const FaItem where = fa_item(p, item_index);
+      const int bh = where.bh, b = where.b, h = where.h;
       const size_t out_row = p.out_token_major
                                  ? ((static_cast<size_t>(b) * p.q_len + row) * p.q_heads + h) * kHd
                                  : (static_cast<size_t>(bh) * p.q_len + row) * kHd;
@@ -503,10 +611,13 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (p.row_sum) p.row_sum[stat] = (l_run == 0.f) ? 0.f : l_run * exp2f(m_ref - m_true);
       }
     }
+    if (threadIdx.x == 256) { FA_TRACE_ITEM(106, item_index); FA_TRACE_NS(121, item_index); }
+    }   // items
   }
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) { FA_TRACE(107, 0); FA_TRACE_CTA(1); }
   if (*abort_word != 0) {
     for (int i = 0; i < 64; ++i) __nanosleep(10000);
     if (threadIdx.x == 0) atomicExch(p.status, *abort_word);
@@ -518,9 +629,77 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   }
 }
 
+// Host mirror of kv_tiles_for.
+int host_kv_tiles(const FaParams &p, long long row0) {
+  long long last = static_cast<long long>(p.kv_visible) - 1;
+  if (p.causal) last = std::min(last, p.causal_offset + row0 + (kTileM - 1));
+  if (row0 >= p.q_len || last < 0) return 0;
+  return static_cast<int>(last / kTileN) + 1;
+}
+
+// The plan of a launch shape: longest-processing-time assignment of the items to `grid` CTAs (weight = KV steps of
+// the longer Q tile plus a constant for the hand-over), each CTA's items in descending weight. Plans are cached per
+// device and shape in device memory; a plan is a few KiB and is built once.
+struct PlanKey {
+  int device, num_pairs, bh_count, q_len, kv_visible, causal, grid;
+  long long causal_offset;
+  bool operator<(const PlanKey &o) const {
+    return std::tie(device, num_pairs, bh_count, q_len, kv_visible, causal, grid, causal_offset) <
+           std::tie(o.device, o.num_pairs, o.bh_count, o.q_len, o.kv_visible, o.causal, o.grid, o.causal_offset);
+  }
+};
+struct PlanEntry { int *device_plan; int stride; };
+
+wb200_status get_plan(const FaParams &p, int grid, const int **plan, int *stride) {
+  static std::mutex mutex;
+  static std::map<PlanKey, PlanEntry> cache;
+  PlanKey key{0, p.num_pairs, p.batch * p.q_heads, p.q_len, p.kv_visible, p.causal, grid, p.causal_offset};
+  WB200_CUDA_CHECK(cudaGetDevice(&key.device));
+  std::lock_guard<std::mutex> lock(mutex);
+  auto found = cache.find(key);
+  if (found != cache.end()) { *plan = found->second.device_plan; *stride = found->second.stride; return WB200_OK; }
+  const int bh_count = key.bh_count, items = p.num_pairs * bh_count;
+  std::vector<int> weight(p.num_pairs);
+  for (int pair = 0; pair < p.num_pairs; ++pair) {
+    const long long row0 = static_cast<long long>(pair) * 2 * kTileM;
+    weight[pair] = std::max(host_kv_tiles(p, row0), host_kv_tiles(p, row0 + kTileM)) * 4 + 2;   // quarter steps; hand-over = half a step
+  }
+  std::vector<int> order(items);
+  for (int g = 0; g < items; ++g) order[g] = g;
+  auto weight_of = [&](int g) { return weight[p.num_pairs - 1 - g / bh_count]; };
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return weight_of(a) > weight_of(b); });
+  std::vector<std::vector<int>> rows(grid);
+  using Load = std::pair<long long, int>;   // (load, CTA): the least loaded CTA takes the next item
+  std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+  for (int c = 0; c < grid; ++c) heap.push({0, c});
+  for (int g : order) {
+    Load least = heap.top();
+    heap.pop();
+    rows[least.second].push_back(g);
+    heap.push({least.first + weight_of(g), least.second});
+  }
+  size_t longest = 0;
+  for (const auto &row : rows) longest = std::max(longest, row.size());
+  const int row_stride = static_cast<int>(longest) + 1;
+  std::vector<int> flat(static_cast<size_t>(grid) * row_stride, -1);
+  for (int c = 0; c < grid; ++c) std::copy(rows[c].begin(), rows[c].end(), flat.begin() + static_cast<size_t>(c) * row_stride);
+  if (cache.size() >= 256) {   // bound the cache: drop everything once no kernel can still be reading a plan
+    WB200_CUDA_CHECK(cudaDeviceSynchronize());
+    for (auto &entry : cache) cudaFree(entry.second.device_plan);
+    cache.clear();
+  }
+  PlanEntry entry{nullptr, row_stride};
+  WB200_CUDA_CHECK(cudaMalloc(&entry.device_plan, flat.size() * sizeof(int)));
+  WB200_CUDA_CHECK(cudaMemcpy(entry.device_plan, flat.data(), flat.size() * sizeof(int), cudaMemcpyHostToDevice));
+  cache[key] = entry;
+  *plan = entry.device_plan;
+  *stride = row_stride;
+  return WB200_OK;
+}
+
 template <bool kPInTmem>
-wb200_status launch_variant(const AttentionArgs &a, const FaParams &p, const CUtensorMap &tq,
-                            const CUtensorMap &tk, const CUtensorMap &tv, cudaStream_t stream) {
+wb200_status launch_variant(const AttentionArgs &a, FaParams p, const CUtensorMap &tq,
+                            const CUtensorMap &tk, const CUtensorMap &tv, int sm_count, cudaStream_t stream) {
   using L = FaSmem<kPInTmem>;
   auto kernel_bf16 = fa_umma_kernel<kPInTmem, true>;
   auto kernel_f16 = fa_umma_kernel<kPInTmem, false>;
@@ -532,7 +711,17 @@ wb200_status launch_variant(const AttentionArgs &a, const FaParams &p, const CUt
                                           static_cast<int>(L::kBytes)));
     attribute_set = true;
   }
-  const int grid = p.num_pairs * a.batch * a.q_heads;
+  // Persistent grid: one CTA per SM walks its share of the items, so the first loads and scores of an item overlap
+  // the softmax tail and write-out of the previous one. WB200_FA_PERSISTENT=0 launches one CTA per item instead.
+  const int items = p.num_pairs * a.batch * a.q_heads;
+  static int persistent = -1;
+  if (persistent < 0) {
+    const char *env = getenv("WB200_FA_PERSISTENT");
+    persistent = (env && env[0] == '0') ? 0 : 1;
+  }
+  const int grid = (persistent && items > sm_count) ? sm_count : items;
+  wb200_status st = get_plan(p, grid, &p.plan, &p.plan_stride);
+  if (st != WB200_OK) return st;
   if (a.format == WB200_BF16)
     kernel_bf16<<<grid, kFaThreads, L::kBytes, stream>>>(tq, tk, tv, p);
   else
@@ -571,7 +760,7 @@ bool attention_fa_umma_supports(const AttentionArgs &a) {
 
 wb200_status launch_attention_fa_umma(const AttentionArgs &a, int sm_count, int *device_status,
                                       cudaStream_t stream) {
-  (void)sm_count;
+  if (sm_count <= 0) sm_count = 148;
   if (!attention_fa_umma_supports(a))
     return fail(WB200_ERR_UNSUPPORTED, "attention request outside the tcgen05 prefill kernel's domain");
   CUtensorMap tq, tk, tv;
@@ -598,12 +787,14 @@ wb200_status launch_attention_fa_umma(const AttentionArgs &a, int sm_count, int 
   p.out_format = a.format;
   p.bf16 = a.format == WB200_BF16;
   p.num_pairs = (a.q_len + 2 * kTileM - 1) / (2 * kTileM);
+  if (static_cast<long long>(p.num_pairs) * a.batch * a.q_heads > (1LL << 24))
+    return fail(WB200_ERR_UNSUPPORTED, "more than 2^24 (batch, head, 256-row) items in one attention launch");
   p.out_token_major = a.out_token_major;
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.out = a.out; p.lse = a.lse; p.row_max = a.row_max; p.row_sum = a.row_sum;
   p.status = device_status;
-  if (p_in_tmem_mode()) return launch_variant<true>(a, p, tq, tk, tv, stream);
-  return launch_variant<false>(a, p, tq, tk, tv, stream);
+  if (p_in_tmem_mode()) return launch_variant<true>(a, p, tq, tk, tv, sm_count, stream);
+  return launch_variant<false>(a, p, tq, tk, tv, sm_count, stream);
 }
 
 }  // namespace wb200
