@@ -32,6 +32,12 @@ GEMM = dict(m=8192, n=8192, k=8192)
 FD_LONG = dict(q_heads=32, kv_heads=8, kv_len=1048576, head_dim=128)
 LAYER = dict(batch=8, seq=2048)   # Llama-style decoder layer: d_model 4096, 32/8 heads, head_dim 128, FFN 14336
 SEED = 20260803
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised under profiles/,
+# taken on reduced cases (bench.py --profile-case) and scaled to a full launch by the units processed.
+TRAFFIC = {
+    "fa": 2 * (533.9e6 + 45.0e6),      # profiles/fa_umma_kernel_cfg2.md: batch 2 of 4 captured
+    "fd": 8 * (1.073832e9 + 6.2e6),    # profiles/fd_partial_kernel_cfg3.md: batch 8 of 64 captured
+}
 
 
 def fa_flops(batch, heads, seq, d):
@@ -343,7 +349,7 @@ def main():
         extras["fd_decode"] = {"workload": "FD decode bf16 B64 Hq32 Hkv8 KV32768 D128 per GPU, inputs (8.6 GB) larger than L2", "value": world * fd_bytes / (fd_ms * 1e-3) / 1e9,
                                "unit": "GB/s", "ms_per_step": fd_ms, "scaling": "weak", "n_gpus": world,
                                "roofline": {"bound": "hbm", "achieved": fd_gbs, "peak": peak["hbm_gbs"], "unit": "GB/s",
-                                            "frac": fd_gbs / peak["hbm_gbs"], "traffic": None, "peak_source": peak["source"], "launch_ms": fd_launch_ms}}
+                                            "frac": fd_gbs / peak["hbm_gbs"], "traffic": TRAFFIC["fd"], "peak_source": peak["source"], "launch_ms": fd_launch_ms}}
         del fq, fk, fv
         torch.cuda.empty_cache()
         # ------------------------------------------------------------ long-context decode: the KV sequence is sharded over the ranks
@@ -405,7 +411,7 @@ def main():
                        "l2": "inputs (Q+K+V 403 MB) larger than the 126 MB L2",
                        "parallelism": f"independent (batch, head) units, {world} rank(s), no collective"},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peak["bf16_tflops"], "traffic": None, "peak_source": peak["source"],
+                         "frac": achieved / peak["bf16_tflops"], "traffic": TRAFFIC["fa"], "peak_source": peak["source"],
                          "frac_of_sustained": achieved / peak["bf16_tflops_sustained"], "launch_ms": launch_ms},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
             "gpu_launches": launches,

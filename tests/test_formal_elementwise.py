@@ -1,0 +1,142 @@
+"""Formal (bit-exact) elementwise family: the exact-rational oracle against the reference's vectors (CPU), and the
+GPU entry point wb200_elementwise_formal against the oracle bit for bit, IEEE flags included (GPU).
+Reference vectors: unittests/Simulator/Reference/FormalTensorNumericTest.cpp:189-249."""
+import numpy as np
+import pytest
+
+from oracle import formal_scalar as F
+from vibe_compiler_b200 import _abi as abi
+from vibe_compiler_b200.backend import NumericTensor, PhysicalTensorDescriptor
+
+FMT = {"f16": abi.F16, "bf16": abi.BF16, "f32": abi.F32}
+DTYPE = {"f16": np.uint16, "bf16": np.uint16, "f32": np.uint32}
+ARITHMETIC = ["abs", "neg", "recip", "square", "max", "min", "add", "sub", "mul", "relu"]
+RELATIONS = ["eq", "ne", "ge", "gt", "le", "lt"]
+BOOL = 7
+
+
+def test_reference_vectors():
+    assert F.evaluate("add", "f32", "f32", 0x3f800000, 0x40400000) == (0x40800000, 0)
+    assert F.evaluate("add", "f32", "f32", 0x40000000, 0x40800000) == (0x40c00000, 0)
+    assert F.evaluate("ne", "f16", "bool", 0x7e00, 0x3c00) == (1, 0)          # a NaN operand: only `ne` holds
+    assert F.evaluate("ne", "f16", "bool", 0x3c00, 0x3c00) == (0, 0)
+    assert [F.evaluate("logic_xor", "bool", "bool", a, b)[0] for a, b in ((0, 0), (1, 0), (1, 1))] == [0, 1, 0]
+
+
+def test_flag_definitions():
+    assert F.evaluate("recip", "f32", "f32", 0x40400000)[1] == F.INEXACT                       # 1 / 3
+    assert F.evaluate("recip", "f32", "f32", 0x40000000) == (0x3f000000, 0)                    # 1 / 2 exact
+    assert F.evaluate("recip", "f16", "f16", 0x8000) == (0xfc00, F.DIV_BY_ZERO)                # 1 / -0 = -inf
+    assert F.evaluate("add", "f16", "f16", 0x7bff, 0x7bff) == (0x7c00, F.OVERFLOW | F.INEXACT)
+    assert F.evaluate("mul", "f16", "f16", 0x0001, 0x0001) == (0x0000, F.UNDERFLOW | F.INEXACT)
+    assert F.evaluate("sub", "f32", "f32", 0x7f800000, 0x7f800000) == (0x7fc00000, F.INVALID)  # inf - inf
+    assert F.evaluate("mul", "bf16", "bf16", 0x0000, 0x7f80) == (0x7fc0, F.INVALID)            # 0 * inf
+    assert F.evaluate("abs", "bf16", "bf16", 0xff81) == (0x7fc0, F.INVALID)                    # signalling NaN
+    assert F.evaluate("max", "f32", "f32", 0x80000000, 0x00000000) == (0x00000000, 0)          # max(-0, +0) = +0
+    assert F.evaluate("min", "f32", "f32", 0x80000000, 0x00000000) == (0x80000000, 0)
+    assert F.evaluate("relu", "f16", "f16", 0x8000) == (0x8000, 0)                             # -0 is kept
+    assert F.evaluate("add", "f16", "f16", 0x3c00, 0xbc00) == (0x0000, 0)                      # x + (-x) = +0, exact
+    # subnormal result that is exact raises nothing; the same magnitude reached inexactly raises underflow
+    assert F.evaluate("mul", "f16", "f16", 0x0400, 0x3800) == (0x0200, 0)
+    assert F.evaluate("mul", "f16", "f16", 0x0401, 0x3800)[1] == F.UNDERFLOW | F.INEXACT
+
+
+def _patterns(fmt, count, rng):
+    bits = 32 if fmt == "f32" else 16
+    values = rng.integers(0, 2 ** bits, count, dtype=np.uint64)
+    exp_mask = {"f16": 0x7c00, "bf16": 0x7f80, "f32": 0x7f800000}[fmt]
+    special = [0, 1 << (bits - 1), exp_mask, exp_mask | (1 << (bits - 1)), exp_mask | 1, F.canonical_nan(fmt), 1, exp_mask - 1,
+               {"f16": 0x3c00, "bf16": 0x3f80, "f32": 0x3f800000}[fmt], {"f16": 0x0400, "bf16": 0x0080, "f32": 0x00800000}[fmt]]
+    values[:len(special)] = special
+    rng.shuffle(values)
+    return values.astype(DTYPE[fmt])
+
+
+def _run(backend, op, fmt, out_fmt, a, b=None):
+    key = PhysicalTensorDescriptor(FMT[fmt], abi.LAYOUT_TENSOR, [len(a)])
+    out_key = PhysicalTensorDescriptor(BOOL if out_fmt == "bool" else FMT[out_fmt], abi.LAYOUT_TENSOR, [len(a)])
+    out_bytes = (len(a) + 7) // 8 if out_fmt == "bool" else len(a) * np.dtype(DTYPE[out_fmt]).itemsize
+    template = np.full(out_bytes, 0xFF, dtype=np.uint8)
+    inputs = [NumericTensor(key, a)] + ([NumericTensor(key, b)] if b is not None else [])
+    result = backend.execute_elementwise(op, inputs, NumericTensor(out_key, template), formal=True)
+    return result.destination.storage, result.evidence
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["f16", "bf16", "f32"])
+def test_formal_arithmetic_matches_the_exact_oracle(backend, fmt):
+    rng = np.random.default_rng(20260803)
+    n = 1501                                    # not a multiple of 8
+    a, b = _patterns(fmt, n, rng), _patterns(fmt, n, rng)
+    for op in ARITHMETIC:
+        unary = op in F.UNARY
+        storage, evidence = _run(backend, op, fmt, fmt, a, None if unary else b)
+        got = storage.view(DTYPE[fmt])
+        want, flags = [], 0
+        for x, y in zip(a, b):
+            bits, f = F.evaluate(op, fmt, fmt, int(x), int(y))
+            want.append(bits)
+            flags |= f
+        assert np.array_equal(got, np.array(want, dtype=DTYPE[fmt])), op
+        assert evidence.flags == flags, (op, evidence.flags, flags)
+        assert evidence.scalar_evaluations == n
+
+
+@pytest.mark.gpu
+def test_flags_per_element(backend):
+    # one element per request, so the flags of that element are seen in isolation
+    rng = np.random.default_rng(5)
+    for fmt in ("f16", "bf16", "f32"):
+        a, b = _patterns(fmt, 60, rng), _patterns(fmt, 60, rng)
+        for op in ("recip", "square", "add", "sub", "mul"):
+            for x, y in zip(a, b):
+                one = np.array([x], dtype=DTYPE[fmt])
+                other = None if op in F.UNARY else np.array([y], dtype=DTYPE[fmt])
+                storage, evidence = _run(backend, op, fmt, fmt, one, other)
+                assert (int(storage.view(DTYPE[fmt])[0]), evidence.flags) == F.evaluate(op, fmt, fmt, int(x), int(y)), (fmt, op, hex(x), hex(y))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["f16", "bf16", "f32"])
+def test_relations_to_bool_and_to_numbers(backend, fmt):
+    rng = np.random.default_rng(9)
+    n = 203
+    a = _patterns(fmt, n, rng)
+    b = a.copy()
+    b[::3] = _patterns(fmt, len(b[::3]), rng)          # a mix of equal and unequal pairs
+    for op in RELATIONS:
+        want = [F.evaluate(op, fmt, "bool", int(x), int(y))[0] for x, y in zip(a, b)]
+        storage, evidence = _run(backend, op, fmt, "bool", a, b)
+        unpacked = np.unpackbits(storage, bitorder="little")
+        assert list(unpacked[:n]) == want, op
+        assert all(unpacked[n:] == 1)                   # bits past the tensor keep the template's value
+        numeric, _ = _run(backend, op, fmt, "bf16", a, b)
+        assert list(numeric.view(np.uint16)) == [0x3f80 if t else 0 for t in want]
+
+
+@pytest.mark.gpu
+def test_logic_on_packed_bool(backend):
+    rng = np.random.default_rng(3)
+    n = 77
+    bits_a, bits_b = rng.integers(0, 2, n), rng.integers(0, 2, n)
+    a, b = np.packbits(bits_a.astype(np.uint8), bitorder="little"), np.packbits(bits_b.astype(np.uint8), bitorder="little")
+    key = PhysicalTensorDescriptor(BOOL, abi.LAYOUT_TENSOR, [n])
+    template = np.zeros(len(a), dtype=np.uint8)
+    for op, fn in (("logic_not", lambda x, y: 1 - x), ("logic_and", lambda x, y: x & y), ("logic_or", lambda x, y: x | y), ("logic_xor", lambda x, y: x ^ y)):
+        inputs = [NumericTensor(key, a)] + ([] if op == "logic_not" else [NumericTensor(key, b)])
+        result = backend.execute_elementwise(op, inputs, NumericTensor(key, template), formal=True)
+        got = np.unpackbits(result.destination.storage, bitorder="little")[:n]
+        assert list(got) == list(fn(bits_a, bits_b)), op
+        assert result.evidence.flags == 0
+
+
+@pytest.mark.gpu
+def test_formal_entry_rejects_what_it_does_not_cover(backend):
+    from vibe_compiler_b200.backend import WB200Error
+    a = np.zeros(8, dtype=np.uint16)
+    with pytest.raises(WB200Error, match="outside the formal"):
+        _run(backend, "exp", "f16", "f16", a)
+    with pytest.raises(WB200Error, match="arity"):
+        _run(backend, "add", "f16", "f16", a)
+    with pytest.raises(WB200Error, match="result format"):
+        _run(backend, "add", "f16", "f32", a, a)

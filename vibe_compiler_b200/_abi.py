@@ -154,6 +154,7 @@ SIGNATURES = {
     "wb200_pack": (C.c_int, [C.c_void_p, C.POINTER(TensorDesc), C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_uint64]),
     "wb200_gemm": (C.c_int, [C.c_void_p, C.POINTER(GemmRequest), C.POINTER(C.c_int), C.POINTER(Evidence)]),
     "wb200_elementwise": (C.c_int, [C.c_void_p, C.POINTER(ElementwiseRequest), C.POINTER(Evidence)]),
+    "wb200_elementwise_formal": (C.c_int, [C.c_void_p, C.POINTER(ElementwiseRequest), C.POINTER(Evidence)]),
     "wb200_convert": (C.c_int, [C.c_void_p, C.POINTER(ConvertRequest), C.POINTER(Evidence)]),
     "wb200_reduce": (C.c_int, [C.c_void_p, C.POINTER(ReduceRequest), C.POINTER(Evidence)]),
     "wb200_attention_fa": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams)]),

@@ -206,7 +206,9 @@ class B200TargetModelBackend:
         return BackendResult(NumericTensor(operation.destination, out), _evidence(evidence))
 
     def execute_elementwise(self, operation: str, inputs: Sequence[NumericTensor], destination_template: NumericTensor,
-                            max_scalar_evaluations: int = 2 ** 62) -> BackendResult:
+                            max_scalar_evaluations: int = 2 ** 62, formal: bool = False) -> BackendResult:
+        """Managed-reference elementwise (NaN rejected, flags zero) or, with formal=True, the bit-exact formal family
+        (relations, logic, NaN canonicalisation, IEEE flags in evidence.flags)."""
         req = abi.ElementwiseRequest()
         req.operation = abi.ELEMENTWISE_OPS[operation]
         req.input_count = len(inputs)
@@ -223,7 +225,8 @@ class B200TargetModelBackend:
         req.destination_template, req.destination_out, req.destination_bytes = tmpl.ctypes.data, out.ctypes.data, tmpl.size
         req.max_scalar_evaluations = max_scalar_evaluations
         evidence = abi.Evidence()
-        self._check(self._lib.wb200_elementwise(self._handle, C.byref(req), C.byref(evidence)))
+        entry = self._lib.wb200_elementwise_formal if formal else self._lib.wb200_elementwise
+        self._check(entry(self._handle, C.byref(req), C.byref(evidence)))
         return BackendResult(NumericTensor(destination_template.key, out), _evidence(evidence))
 
     def execute_convert(self, opcode: int, source: NumericTensor, destination_template: NumericTensor,

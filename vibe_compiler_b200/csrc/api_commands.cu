@@ -201,6 +201,66 @@ wb200_status wb200_elementwise(wb200_backend *backend, const wb200_elementwise_r
   return WB200_OK;
 }
 
+wb200_status wb200_elementwise_formal(wb200_backend *backend, const wb200_elementwise_request *r, wb200_evidence *evidence) {
+  if (!backend || !r) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  int arity;
+  bool relation = false, logic = false;
+  switch (r->operation) {
+    case WB200_EW_MAX: case WB200_EW_MIN: case WB200_EW_ADD: case WB200_EW_SUB: case WB200_EW_MUL: arity = 2; break;
+    case WB200_EW_EQ: case WB200_EW_NE: case WB200_EW_GE: case WB200_EW_GT: case WB200_EW_LE: case WB200_EW_LT: arity = 2; relation = true; break;
+    case WB200_EW_LOGIC_AND: case WB200_EW_LOGIC_OR: case WB200_EW_LOGIC_XOR: arity = 2; logic = true; break;
+    case WB200_EW_LOGIC_NOT: arity = 1; logic = true; break;
+    case WB200_EW_ABS: case WB200_EW_RECIP: case WB200_EW_SQUARE: case WB200_EW_NEG: case WB200_EW_RELU: arity = 1; break;
+    default: return fail(WB200_ERR_UNSUPPORTED, "elementwise operation is outside the formal binary-arithmetic, relation and logic family");
+  }
+  if (static_cast<int>(r->input_count) != arity) return fail(WB200_ERR_INVALID_ARGUMENT, "elementwise input arity does not match semantics");
+  const wb200_tensor_desc &dst = r->destination, &first = r->inputs[0];
+  const bool bool_out = dst.format == WB200_BOOL, bool_in = first.format == WB200_BOOL;
+  if (logic ? !(bool_out && (bool_in || is_float_format(first.format))) : !is_float_format(first.format))
+    return fail(WB200_ERR_UNSUPPORTED, "formal elementwise operands must be F16, BF16 or F32 (Bool for logic)");
+  if (!logic && !(relation ? (bool_out || is_float_format(dst.format)) : dst.format == first.format))
+    return fail(WB200_ERR_UNSUPPORTED, "formal elementwise result format does not fit the operation");
+  auto packed_ok = [](const wb200_tensor_desc &d) { return d.format != WB200_BOOL || d.layout == WB200_LAYOUT_TENSOR || d.layout == WB200_LAYOUT_NTENSOR; };
+  if (!packed_ok(dst) || !packed_ok(first)) return fail(WB200_ERR_UNSUPPORTED, "bit-packed Bool tensors are taken in Tensor / NTensor layout only");
+  LayoutMap out_map, in_map; wb200_geometry out_geo, in_geo;
+  wb200_status st = check_storage(dst, r->destination_bytes, r->destination_template, "destination template", &out_map, &out_geo);
+  if (st != WB200_OK) return st;
+  if (!r->destination_out) return fail(WB200_ERR_INVALID_ARGUMENT, "destination_out is null");
+  uint64_t total_bytes = r->destination_bytes, logical = out_map.element_count;
+  for (int i = 0; i < arity; ++i) {
+    const wb200_tensor_desc &in = r->inputs[i];
+    if (in.format != first.format || in.layout != first.layout || !same_shape(in, dst))
+      return fail(WB200_ERR_INVALID_ARGUMENT, "elementwise tensors do not have one same-shape domain");
+    if ((st = check_storage(in, r->input_bytes[i], r->input_storage[i], "input", &in_map, &in_geo)) != WB200_OK) return st;
+    total_bytes += r->input_bytes[i];
+    logical += in_map.element_count;
+  }
+  if ((st = check_budget(backend, out_map.element_count, r->max_scalar_evaluations, total_bytes, logical)) != WB200_OK) return st;
+  DeviceGuard guard(backend->device);
+  cudaStream_t stream = backend->stream;
+  void *d_in[2] = {nullptr, nullptr}, *d_dst, *d_flags;
+  for (int i = 0; i < arity; ++i) {
+    if ((st = backend->buffer(i, r->input_bytes[i], &d_in[i])) != WB200_OK) return st;
+    WB200_CUDA_CHECK(cudaMemcpyAsync(d_in[i], r->input_storage[i], r->input_bytes[i], cudaMemcpyHostToDevice, stream));
+  }
+  if ((st = backend->buffer(2, r->destination_bytes, &d_dst)) != WB200_OK) return st;
+  if ((st = backend->buffer(3, sizeof(uint32_t), &d_flags)) != WB200_OK) return st;
+  WB200_CUDA_CHECK(cudaMemcpyAsync(d_dst, r->destination_template, r->destination_bytes, cudaMemcpyHostToDevice, stream));
+  WB200_CUDA_CHECK(cudaMemsetAsync(d_flags, 0, sizeof(uint32_t), stream));
+  st = launch_elementwise_formal(r->operation, first.format, dst.format, arity, static_cast<const uint8_t *>(d_in[0]),
+                                 static_cast<const uint8_t *>(d_in[1]), static_cast<uint8_t *>(d_dst), in_map, out_map,
+                                 static_cast<uint32_t *>(d_flags), stream);
+  if (st != WB200_OK) return st;
+  backend->launches += 1;
+  uint32_t flags = 0;
+  WB200_CUDA_CHECK(cudaMemcpyAsync(&flags, d_flags, sizeof(flags), cudaMemcpyDeviceToHost, stream));
+  WB200_CUDA_CHECK(cudaMemcpyAsync(r->destination_out, d_dst, r->destination_bytes, cudaMemcpyDeviceToHost, stream));
+  WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
+  fill_evidence(backend, evidence, "sm100a-formal-elementwise");
+  if (evidence) { evidence->scalar_evaluations = out_map.element_count; evidence->gpu_launches = 1; evidence->flags = flags; }
+  return WB200_OK;
+}
+
 wb200_status wb200_convert(wb200_backend *backend, const wb200_convert_request *r, wb200_evidence *evidence) {
   if (!backend || !r) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
   if (r->opcode < 139 || r->opcode > 174) return fail(WB200_ERR_INVALID_ARGUMENT, "convert opcode is not a target route");

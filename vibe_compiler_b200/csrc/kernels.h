@@ -52,6 +52,11 @@ wb200_status launch_gemm_formal(const GemmFormalArgs &args, cudaStream_t stream)
 wb200_status launch_elementwise(int op, int format, int input_count, const uint8_t *in0,
                                 const uint8_t *in1, uint8_t *dst, const LayoutMap &map, int *nan_flag,
                                 cudaStream_t stream);
+// Formal (bit-exact, NaN-canonicalising, flag-raising) elementwise family; `flags_word` collects the OR of the
+// per-element IEEE flags (bit0 invalid, bit1 divByZero, bit2 overflow, bit3 underflow, bit4 inexact).
+wb200_status launch_elementwise_formal(int op, int in_format, int out_format, int input_count, const uint8_t *in0, const uint8_t *in1,
+                                       uint8_t *dst, const LayoutMap &in_map, const LayoutMap &out_map, uint32_t *flags_word,
+                                       cudaStream_t stream);
 wb200_status launch_convert(int src_format, int dst_format, const uint8_t *src, uint8_t *dst,
                             const LayoutMap &src_map, const LayoutMap &dst_map, int *nan_flag,
                             cudaStream_t stream);

@@ -130,6 +130,163 @@ codec_kernel(const T *src, T *dst, const LayoutMap map, int pack) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------ formal elementwise
+// Bit-exact evaluation of the reference's formal elementwise family
+// (lib/Wafer/Simulator/Reference/Formal/FormalNumericElementwise.cpp:23-248): arithmetic in the operand format with
+// one RNE rounding, NaN results canonicalised (not rejected), relations to Bool or to 1.0 / 0.0, logic on "bits != 0",
+// and the IEEE exception flags. Arithmetic runs in f32 and is narrowed once: for f16 / bf16 the double rounding is
+// innocuous (24 >= 2 * 11 + 2), for f32 the hardware operation is the RNE operation. Inexactness comes from
+// error-free transformations, not from a wider re-computation.
+constexpr uint32_t kFlagInvalid = 1u, kFlagDivByZero = 2u, kFlagOverflow = 4u, kFlagUnderflow = 8u, kFlagInexact = 16u;
+
+struct FormatTraits { uint32_t sign, exp_mask, mant_mask, quiet_bit, canonical_nan, one; int precision; float min_normal; };
+__device__ __forceinline__ FormatTraits traits_of(int format) {
+  if (format == WB200_F32) return {0x80000000u, 0x7f800000u, 0x007fffffu, 0x00400000u, 0x7fc00000u, 0x3f800000u, 24, 1.17549435e-38f};
+  if (format == WB200_BF16) return {0x8000u, 0x7f80u, 0x007fu, 0x0040u, 0x7fc0u, 0x3f80u, 8, 1.17549435e-38f};
+  return {0x8000u, 0x7c00u, 0x03ffu, 0x0200u, 0x7e00u, 0x3c00u, 11, 6.10351562e-05f};
+}
+
+// |value| rounded to `precision` bits with an unbounded exponent range is below the smallest normal number.
+__device__ __forceinline__ bool tiny_after_rounding(double value, int precision, float min_normal) {
+  if (value == 0.0) return false;
+  int exponent;
+  const double mantissa = frexp(fabs(value), &exponent);                 // [0.5, 1)
+  const double rounded = ldexp(rint(ldexp(mantissa, precision)), exponent - precision);
+  return rounded < static_cast<double>(min_normal);
+}
+
+__device__ uint32_t formal_scalar(int op, int format, int out_format, uint32_t a, uint32_t b, uint32_t *flags_out) {
+  const FormatTraits t = traits_of(format);
+  uint32_t flags = 0;
+  const bool binary = !(op == WB200_EW_ABS || op == WB200_EW_NEG || op == WB200_EW_RECIP || op == WB200_EW_SQUARE || op == WB200_EW_RELU);
+  auto is_nan = [&](uint32_t v) { return (v & t.exp_mask) == t.exp_mask && (v & t.mant_mask) != 0; };
+  auto is_snan = [&](uint32_t v) { return is_nan(v) && (v & t.quiet_bit) == 0; };
+  auto is_zero = [&](uint32_t v) { return (v & ~t.sign) == 0; };
+  auto is_inf = [&](uint32_t v) { return (v & ~t.sign) == t.exp_mask; };
+  const bool nan = is_nan(a) || (binary && is_nan(b));
+  if (is_snan(a) || (binary && is_snan(b))) flags |= kFlagInvalid;
+  const float x = widen_bits(a, format), y = binary ? widen_bits(b, format) : 0.f;
+  uint32_t result;
+  if (op >= WB200_EW_EQ && op <= WB200_EW_LT) {
+    bool truth;
+    if (nan) truth = op == WB200_EW_NE;
+    else switch (op) {
+      case WB200_EW_EQ: truth = x == y; break;
+      case WB200_EW_NE: truth = x != y; break;
+      case WB200_EW_GE: truth = x >= y; break;
+      case WB200_EW_GT: truth = x > y; break;
+      case WB200_EW_LE: truth = x <= y; break;
+      default: truth = x < y; break;
+    }
+    *flags_out = flags;
+    if (out_format == WB200_BOOL) return truth ? 1u : 0u;
+    return truth ? traits_of(out_format).one : 0u;
+  }
+  if (nan && (op == WB200_EW_ABS || op == WB200_EW_NEG || op == WB200_EW_MAX || op == WB200_EW_MIN || op == WB200_EW_RELU)) {
+    *flags_out = flags;
+    return t.canonical_nan;
+  }
+  switch (op) {
+    case WB200_EW_ABS: result = a & ~t.sign; break;
+    case WB200_EW_NEG: result = a ^ t.sign; break;
+    case WB200_EW_RELU: result = ((a & t.sign) && !is_zero(a)) ? 0u : a; break;
+    case WB200_EW_MAX:
+    case WB200_EW_MIN:
+      if (is_zero(a) && is_zero(b)) {
+        const bool negative = op == WB200_EW_MAX ? ((a & t.sign) && (b & t.sign)) : ((a & t.sign) || (b & t.sign));
+        result = negative ? t.sign : 0u;
+      } else {
+        const bool choose_rhs = op == WB200_EW_MAX ? x < y : x > y;
+        result = choose_rhs ? b : a;
+      }
+      break;
+    default: {
+      // recip, square, add, sub, mul: one RNE rounding in the operand format
+      float r32;
+      bool inexact32 = false, finite_inputs = !is_inf(a) && !(binary && is_inf(b)) && !nan;
+      if (op == WB200_EW_RECIP) {
+        r32 = __fdiv_rn(1.0f, x);
+        if (!nan && is_zero(a)) flags |= kFlagDivByZero;
+        // 1 / x is representable only when x is a power of two
+        if (finite_inputs && !is_zero(a)) inexact32 = (__float_as_uint(fabsf(x)) & 0x007fffffu) != 0 && (__float_as_uint(fabsf(x)) & 0x7f800000u) != 0;
+        if (finite_inputs && !is_zero(a) && (__float_as_uint(fabsf(x)) & 0x7f800000u) == 0)   // subnormal f32 operand: power of two iff one bit set
+          inexact32 = (__float_as_uint(fabsf(x)) & (__float_as_uint(fabsf(x)) - 1u)) != 0;
+      } else if (op == WB200_EW_ADD || op == WB200_EW_SUB) {
+        const float yy = op == WB200_EW_SUB ? -y : y;
+        r32 = __fadd_rn(x, yy);
+        if (finite_inputs && isfinite(r32)) {
+          const float bb = __fsub_rn(r32, x);
+          const float err = __fadd_rn(__fsub_rn(x, __fsub_rn(r32, bb)), __fsub_rn(yy, bb));
+          inexact32 = err != 0.f;
+        }
+      } else {
+        const float yy = op == WB200_EW_SQUARE ? x : y;
+        r32 = __fmul_rn(x, yy);
+        if (finite_inputs) inexact32 = static_cast<double>(r32) != static_cast<double>(x) * static_cast<double>(yy);
+        if (finite_inputs && inexact32 && tiny_after_rounding(static_cast<double>(x) * static_cast<double>(yy), t.precision, t.min_normal))
+          flags |= kFlagUnderflow;
+      }
+      if (r32 != r32) {
+        if (!nan) flags |= kFlagInvalid;   // inf - inf, 0 * inf
+        result = t.canonical_nan;
+        break;
+      }
+      result = narrow_bits(r32, format);
+      const bool inexact = inexact32 || widen_bits(result, format) != r32;
+      if (finite_inputs && !(flags & kFlagDivByZero)) {
+        if (is_inf(result)) flags |= kFlagOverflow | kFlagInexact;
+        else if (inexact) {
+          flags |= kFlagInexact;
+          if ((result & t.exp_mask) == 0) flags |= kFlagUnderflow;   // subnormal or zero after rounding, and inexact
+        }
+      }
+      break;
+    }
+  }
+  *flags_out = flags;
+  return result;
+}
+
+__device__ __forceinline__ uint32_t formal_load(const uint8_t *base, int format, const LayoutMap &map, int64_t i) {
+  if (format == WB200_BOOL) return (base[i >> 3] >> (i & 7)) & 1u;   // bit-packed, least significant bit first
+  return load_element_bits(base, physical_index(map, i), format);
+}
+
+// One thread per 8 consecutive logical elements, so that a bit-packed Bool destination byte has a single writer.
+__global__ void __launch_bounds__(kThreads)
+formal_elementwise_kernel(int op, int in_format, int out_format, int input_count, const uint8_t *in0, const uint8_t *in1, uint8_t *dst,
+                          const LayoutMap in_map, const LayoutMap out_map, uint32_t *flags_word) {
+  const int64_t groups = (out_map.element_count + 7) / 8;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  uint32_t flags = 0;
+  const bool logic = op >= WB200_EW_LOGIC_NOT && op <= WB200_EW_LOGIC_XOR;
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < groups; g += stride) {
+    uint32_t packed = 0;
+    const int64_t first = g * 8;
+    const int count = out_map.element_count - first < 8 ? static_cast<int>(out_map.element_count - first) : 8;
+    for (int e = 0; e < count; ++e) {
+      const int64_t i = first + e;
+      const uint32_t a = formal_load(in0, in_format, in_map, i);
+      const uint32_t b = input_count > 1 ? formal_load(in1, in_format, in_map, i) : 0u;
+      uint32_t value, element_flags = 0;
+      if (logic) {
+        const bool lhs = a != 0, rhs = b != 0;
+        value = op == WB200_EW_LOGIC_NOT ? !lhs : op == WB200_EW_LOGIC_AND ? (lhs && rhs) : op == WB200_EW_LOGIC_OR ? (lhs || rhs) : (lhs != rhs);
+      } else {
+        value = formal_scalar(op, in_format, out_format, a, b, &element_flags);
+      }
+      flags |= element_flags;
+      if (out_format == WB200_BOOL) packed |= (value & 1u) << e;
+      else store_element_bits(dst, physical_index(out_map, i), out_format, value);
+    }
+    if (out_format == WB200_BOOL) {
+      const uint32_t keep = count == 8 ? 0u : (0xffu << count) & 0xffu;   // bits past the tensor keep the template's value
+      dst[g] = static_cast<uint8_t>((dst[g] & keep) | packed);
+    }
+  }
+  if (flags) atomicOr(flags_word, flags);
+}
+
 int grid_for(int64_t elements) {
   int64_t blocks = (elements + kThreads - 1) / kThreads;
   if (blocks < 1) blocks = 1;
@@ -156,6 +313,15 @@ wb200_status launch_codec(const uint8_t *src, uint8_t *dst, const LayoutMap &map
 wb200_status launch_elementwise(int op, int format, int input_count, const uint8_t *in0, const uint8_t *in1,
                                 uint8_t *dst, const LayoutMap &map, int *nan_flag, cudaStream_t stream) {
   elementwise_kernel<<<grid_for(map.element_count), kThreads, 0, stream>>>(op, format, input_count, in0, in1, dst, map, nan_flag);
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
+}
+
+wb200_status launch_elementwise_formal(int op, int in_format, int out_format, int input_count, const uint8_t *in0, const uint8_t *in1,
+                                       uint8_t *dst, const LayoutMap &in_map, const LayoutMap &out_map, uint32_t *flags_word,
+                                       cudaStream_t stream) {
+  formal_elementwise_kernel<<<grid_for((out_map.element_count + 7) / 8), kThreads, 0, stream>>>(op, in_format, out_format, input_count, in0, in1,
+                                                                                                dst, in_map, out_map, flags_word);
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }
