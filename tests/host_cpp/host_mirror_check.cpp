@@ -62,8 +62,12 @@ int main() {
         if (got.size() != 8 || got[i * 4 + j] != want) { std::printf("GEMM mismatch at %d,%d\n", i, j); return 9; }
       }
     if (r.destination.storage.size() != gemm.tensors.destinationTemplate.storage.size()) return 10;
-    if (r.evidence.matmul_invocations != 1 || r.evidence.reorder_invocations > 1 || r.evidence.evidence_kind == 0 ||
-        r.evidence.digest[0] == 0 || r.evidence.implementation[0] == 0) { std::printf("GEMM evidence incomplete\n"); return 11; }
+    // The tensor policy reports one matmul invocation and no formal FMAs (the oneDNN seam's rule); the formal policy
+    // reports its m * k * n fused multiply-adds instead.
+    const bool counted = policy == WB200_GEMM_TENSOR ? (r.evidence.matmul_invocations == 1 && r.evidence.formal_fused_multiply_adds == 0)
+                                                     : (r.evidence.formal_fused_multiply_adds == 2 * 3 * 4);
+    if (!counted || r.evidence.reorder_invocations > 1 || r.evidence.evidence_kind == 0 || r.evidence.digest[0] == 0 ||
+        r.evidence.implementation[0] == 0) { std::printf("GEMM evidence incomplete\n"); return 11; }
   }
 
   // Elementwise add on a 1-D Tensor, then the NaN rejection of the managed contract.

@@ -242,3 +242,38 @@ def test_one_plan_against_the_live_cpu_replay(backend):
     want = expected_tools.cpu_replay(FIXTURE["plans"][plan], inputs, threads=16)
     (out,), _ = TileProgram(FIXTURE["plans"][plan], backend).run(inputs)
     assert np.array_equal(out, want)
+
+
+@pytest.mark.gpu
+def test_graph_replay_is_reused_and_agrees_with_the_single_stream_order(backend):
+    # The first run captures the invocation (one stream per Tile, Direct-DTE transfers as event edges) into a CUDA
+    # graph; later runs relaunch it. Doubling arg0 doubles every product exactly, so the second run's output must be
+    # exactly twice the first one's; the tensor-core policy (single stream, no graph) must pass the similarity gate.
+    plan = "tensor-candidate-38"
+    inputs = expected_tools.program_inputs()
+    program = TileProgram(FIXTURE["plans"][plan], backend)
+    (first,), stats1 = program.run(inputs)
+    assert hashlib.sha256(first.tobytes()).hexdigest() == EXPECTED["plans"][plan]["sha256"]
+    doubled = (_as_torch(inputs[0]).float() * 2).bfloat16()
+    (second,), stats2 = program.run([doubled.view(torch.int16).numpy().view(np.uint16), inputs[1]])
+    assert torch.equal(_as_torch(second).float(), _as_torch(first).float() * 2)
+    assert stats2["commands"] == stats1["commands"] and stats2["gpu_launches"] == stats1["gpu_launches"]
+    (again,), _ = program.run(inputs)
+    assert np.array_equal(again, first)
+
+
+@pytest.mark.gpu
+def test_single_stream_replay_matches_the_graph_replay():
+    import os, subprocess, sys
+    code = ("import sys, json, lzma, hashlib; sys.path.insert(0, %r);"
+            "from tests.test_tile_program import FIXTURE, expected_tools;"
+            "from vibe_compiler_b200.backend import B200TargetModelBackend as B;"
+            "from vibe_compiler_b200.tile_program import TileProgram;"
+            "(out,), stats = TileProgram(FIXTURE['plans']['tensor-winner'], B(0)).run(expected_tools.program_inputs());"
+            "print(hashlib.sha256(out.tobytes()).hexdigest())") % str(ROOT)
+    digests = []
+    for mode in ("0", "1"):
+        result = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, WB200_REPLAY_GRAPH=mode), capture_output=True, text=True, timeout=300)
+        assert result.returncode == 0, result.stderr[-2000:]
+        digests.append(result.stdout.strip().splitlines()[-1])
+    assert digests[0] == digests[1] == EXPECTED["plans"]["tensor-winner"]["sha256"]

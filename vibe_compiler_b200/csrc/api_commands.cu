@@ -467,7 +467,7 @@ wb200_status enqueue_image_gemm(wb200_spm_image *image, uint64_t lhs, uint64_t r
   g.dst = image->device + (dst - image->base);
   const char *implementation = "";
   const int effective_policy = (policy == WB200_GEMM_TENSOR && !has_psum && !lt && !rt) ? WB200_GEMM_TENSOR : WB200_GEMM_FORMAL;
-  return run_device_gemm(backend, g, effective_policy, 4, backend->stream, &implementation);
+  return run_device_gemm(backend, g, effective_policy, 4, image->work_stream(), &implementation);
 }
 
 }  // namespace wb200

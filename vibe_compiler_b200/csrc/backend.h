@@ -47,6 +47,9 @@ struct wb200_spm_image {
   wb200_backend *backend;
   uint64_t base, bytes;
   uint8_t *device;
+  cudaStream_t stream = nullptr;     // null: the backend stream
+  uint8_t *staging = nullptr;        // private scratch of `bytes` bytes for in-place gather / scatter (null: a backend slot)
+  cudaStream_t work_stream() const { return stream ? stream : backend->stream; }
 };
 
 namespace wb200 {

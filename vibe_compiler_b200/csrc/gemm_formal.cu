@@ -14,6 +14,25 @@ namespace {
 
 constexpr int kTile = 16;
 
+// Physical element index of element (batch, row, col) of a logical [batch, rows, cols] GEMM operand without the
+// divisions of the general row-major-to-physical map (64-bit divisions dominated the kernels' time): the operand's
+// coordinates are already known. Cx of rank 2 / 3 and NCx of rank 3 are resolved here, anything else falls back.
+__device__ __forceinline__ int64_t operand_index(const LayoutMap &map, int64_t batch, int64_t rows, int64_t row, int64_t cols, int64_t col) {
+  const int64_t outer_all = batch * rows + row;
+  if (map.layout == WB200_LAYOUT_TENSOR || map.layout == WB200_LAYOUT_NTENSOR) return outer_all * cols + col;
+  const bool ncx3 = map.layout == WB200_LAYOUT_NCX && map.rank == 3;
+  const bool cx = map.layout == WB200_LAYOUT_CX && (map.rank == 2 || map.rank == 3);
+  if (!(ncx3 || cx) || (map.c_block & (map.c_block - 1)) != 0) return physical_index(map, outer_all * cols + col);
+  const int64_t base = ncx3 ? batch * map.outer_slice_stride : 0;
+  const int64_t outer = ncx3 ? row : outer_all;
+  const int64_t full_c = map.cx_blocks * map.c_block;
+  if (col < full_c) {
+    const int shift = __ffsll(map.c_block) - 1;
+    return base + (col >> shift) * (map.block_outer_elements * map.c_block) + outer * map.c_block + (col & (map.c_block - 1));
+  }
+  return base + map.cx_blocks * map.block_outer_elements * map.c_block + outer * map.c0 + (col - full_c);
+}
+
 struct FormalParams {
   GemmFormalArgs a;
 };
@@ -68,6 +87,83 @@ __global__ void __launch_bounds__(kTile *kTile) gemm_formal_kernel(const FormalP
   }
 }
 
+// Register-tiled variant for commands with at least 32 x 32 outputs: a 64 x 64 output tile per 256-thread block,
+// 4 x 4 outputs per thread, 16-wide k panels staged through shared memory in k-major order. Each output still sees
+// exactly the chain acc = fma(lhs[k], rhs[k], acc) for k = 0, 1, ... (the k tail is not padded: fma(0, 0, -0) would
+// turn a negative zero into +0), so the bits equal the one-output-per-thread kernel's. CUDA-core bound:
+// m * n * k FMAs per command, 0.5 shared-memory loads per FMA.
+constexpr int kBlockM = 64, kBlockN = 64, kPanelK = 16;
+
+__global__ void __launch_bounds__(256) gemm_formal_tiled_kernel(const FormalParams p) {
+  const GemmFormalArgs &a = p.a;
+  __shared__ float lhs_panel[kPanelK][kBlockM];   // [k][m]
+  __shared__ float rhs_panel[kPanelK][kBlockN];   // [k][n]
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int batch = blockIdx.z;
+  const int row0 = blockIdx.y * kBlockM, col0 = blockIdx.x * kBlockN;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+
+  for (int k0 = 0; k0 < a.k; k0 += kPanelK) {
+    // 64 x 16 lhs and 16 x 64 rhs elements, 4 + 4 per thread; consecutive threads take consecutive elements of the
+    // operand's fastest logical dimension.
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int index = threadIdx.x + e * 256;
+      int r, kk;
+      if (a.lhs_transposed) { r = index & 63; kk = index >> 6; } else { kk = index & 15; r = index >> 4; }
+      float value = 0.0f;
+      if (row0 + r < a.m && k0 + kk < a.k) {
+        const int64_t at = a.lhs_transposed ? operand_index(a.lhs_map, batch, a.k, k0 + kk, a.m, row0 + r)
+                                            : operand_index(a.lhs_map, batch, a.m, row0 + r, a.k, k0 + kk);
+        value = widen_bits(load_element_bits(a.lhs, at, a.in_format), a.in_format);
+      }
+      lhs_panel[kk][r] = value;
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int index = threadIdx.x + e * 256;
+      int c, kk;
+      if (a.rhs_transposed) { kk = index & 15; c = index >> 4; } else { c = index & 63; kk = index >> 6; }
+      float value = 0.0f;
+      if (col0 + c < a.n && k0 + kk < a.k) {
+        const int64_t at = a.rhs_transposed ? operand_index(a.rhs_map, batch, a.n, col0 + c, a.k, k0 + kk)
+                                            : operand_index(a.rhs_map, batch, a.k, k0 + kk, a.n, col0 + c);
+        value = widen_bits(load_element_bits(a.rhs, at, a.in_format), a.in_format);
+      }
+      rhs_panel[kk][c] = value;
+    }
+    __syncthreads();
+    const int k_count = min(kPanelK, a.k - k0);
+    for (int kk = 0; kk < k_count; ++kk) {
+      float l[4], r[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) l[i] = lhs_panel[kk][ty + 16 * i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r[j] = rhs_panel[kk][tx + 16 * j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = __fmaf_rn(l[i], r[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int row = row0 + ty + 16 * i, col = col0 + tx + 16 * j;
+      if (row < a.m && col < a.n) {
+        float value = acc[i][j];
+        if (a.has_psum) value = __fadd_rn(value, __uint_as_float(load_element_bits(a.psum, operand_index(a.psum_map, batch, a.m, row, a.n, col), WB200_F32)));
+        store_element_bits(a.dst, operand_index(a.dst_map, batch, a.m, row, a.n, col), a.out_format, narrow_bits(value, a.out_format));
+      }
+    }
+}
+
 }  // namespace
 
 wb200_status launch_gemm_formal(const GemmFormalArgs &args, cudaStream_t stream) {
@@ -77,6 +173,12 @@ wb200_status launch_gemm_formal(const GemmFormalArgs &args, cudaStream_t stream)
     return fail(WB200_ERR_INVALID_ARGUMENT, "GEMM extents must be positive");
   if (args.batch > 65535) return fail(WB200_ERR_UNSUPPORTED, "batch count above 65535");
   FormalParams p{args};
+  if (args.m >= 32 && args.n >= 32) {
+    dim3 grid((args.n + kBlockN - 1) / kBlockN, (args.m + kBlockM - 1) / kBlockM, args.batch);
+    gemm_formal_tiled_kernel<<<grid, 256, 0, stream>>>(p);
+    WB200_CUDA_CHECK(cudaGetLastError());
+    return WB200_OK;
+  }
   dim3 grid((args.n + kTile - 1) / kTile, (args.m + kTile - 1) / kTile, args.batch);
   gemm_formal_kernel<<<grid, kTile * kTile, 0, stream>>>(p);
   WB200_CUDA_CHECK(cudaGetLastError());

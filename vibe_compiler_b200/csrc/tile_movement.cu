@@ -14,15 +14,19 @@ __global__ void __launch_bounds__(256) strided_copy_kernel(const uint8_t *src, u
                                                             uint32_t units_per_segment, uint64_t total_units) {
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
   for (uint64_t u = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; u < total_units; u += stride) {
-    const uint64_t segment = u / units_per_segment;
-    const uint64_t within = (u % units_per_segment) * sizeof(Unit);
-    uint64_t s = segment, from_offset = within, to_offset = within, t = segment;
+    // a command moves at most 4 GiB, so 32-bit division is enough (64-bit division is several times slower)
+    const uint32_t unit = static_cast<uint32_t>(u);
+    const uint32_t segment = unit / units_per_segment;
+    const uint64_t within = static_cast<uint64_t>(unit - segment * units_per_segment) * sizeof(Unit);
+    uint32_t s = segment, t = segment;
+    uint64_t from_offset = within, to_offset = within;
 #pragma unroll
     for (int d = 0; d < 3; ++d) {
-      from_offset += (s % from.iterations[d]) * from.strides[d];
-      s /= from.iterations[d];
-      to_offset += (t % to.iterations[d]) * to.strides[d];
-      t /= to.iterations[d];
+      const uint32_t s_next = s / from.iterations[d], t_next = t / to.iterations[d];
+      from_offset += static_cast<uint64_t>(s - s_next * from.iterations[d]) * from.strides[d];
+      to_offset += static_cast<uint64_t>(t - t_next * to.iterations[d]) * to.strides[d];
+      s = s_next;
+      t = t_next;
     }
     *reinterpret_cast<Unit *>(dst + to_offset) = *reinterpret_cast<const Unit *>(src + from_offset);
   }
