@@ -366,17 +366,21 @@ wb200_status wb200_residual_add(wb200_backend *backend, uint32_t format, const v
  *   wo    [q_heads head_dim, d_model]
  *   wgu   [d_model, 2 ffn]   gate and up columns interleaved: (gate_0, up_0, gate_1, up_1, ...)
  *   wdown [ffn, d_model]
- * `allreduce` (may be null for a single shard) is called twice, after the kernels producing the partial sum have
- * been enqueued, with a buffer inside `workspace` holding `elements` values of `format`; it must enqueue an
- * in-place sum over the shards ordered after the work already on `stream` and before work enqueued on it later
- * (an NCCL all-reduce on that stream, or on another stream with event edges), and return 0. */
+ * `allreduce` (may be null for a single shard) is called twice per part, after the kernels producing the partial sum
+ * have been enqueued, with a buffer inside `workspace` holding `elements` values of `format` and the stream those
+ * kernels were enqueued on; it must enqueue an in-place sum over the shards ordered after the work already on that
+ * stream and before work enqueued on it later (an NCCL all-reduce on that stream, or on another stream with event
+ * edges), and return 0. */
 typedef int32_t (*wb200_allreduce_fn)(void *user, void *device_buffer, uint64_t elements, uint32_t format, void *stream);
 typedef struct wb200_decoder_layer_params {
   uint32_t batch, seq, d_model, head_dim;
   uint32_t q_heads, kv_heads, ffn;
   uint32_t format;             /* WB200_BF16 or WB200_F16 */
   float eps, rope_theta;
-  uint32_t position_offset, reserved;
+  uint32_t position_offset;
+  uint32_t micro_batches;      /* > 1 with an allreduce callback: the batch runs as that many equal parts on two
+                                  internal streams, phase by phase, so that the all-reduce of one part overlaps the
+                                  kernels of the other; the callback then receives the part's stream. 0 / 1: one pass */
   const void *x;               /* [batch * seq, d_model] */
   void *out;                   /* [batch * seq, d_model] */
   const void *norm1, *wqkv, *wo, *norm2, *wgu, *wdown;

@@ -179,3 +179,30 @@ def test_single_call_layer_reports_callback_failure_and_small_workspace(backend)
         backend.decoder_layer(x[:, :3], **kwargs)          # 6 tokens: not a multiple of 8
     out, _ = backend.decoder_layer(x, **kwargs)              # the backend is still usable
     assert torch.isfinite(out.float()).all()
+
+
+@pytest.mark.gpu
+def test_micro_batched_layer_equals_one_pass(backend):
+    # With micro_batches = 2 the two sequences run on the backend's two internal streams and the callback is entered
+    # with the part's stream current; the arithmetic per token is unchanged, so the bits must be.
+    from vibe_compiler_b200.decoder_layer import ShardedDecoderLayer
+    cfg = fixture.CFG
+    layer = ShardedDecoderLayer(backend, cfg, random_weights(cfg))
+    x = fixture.layer_input().cuda()
+    kwargs = dict(norm1=layer.norm1, wqkv=layer.wqkv, wo=layer.wo, norm2=layer.norm2, wgu=layer.wgu, wdown=layer.wdown, q_heads=layer.hq,
+                  kv_heads=layer.hkv, head_dim=cfg.head_dim, eps=cfg.eps, rope_theta=cfg.rope_theta)
+    seen = []
+
+    def identity(tensor):
+        seen.append((torch.cuda.current_stream().cuda_stream, tensor.numel()))
+    one, _ = backend.decoder_layer(x, allreduce=identity, micro_batches=1, **kwargs)
+    two, _ = backend.decoder_layer(x, allreduce=identity, micro_batches=2, **kwargs)
+    torch.cuda.synchronize()
+    backend.poll()
+    assert torch.equal(one, two)
+    tokens = x.shape[0] * x.shape[1] * x.shape[2]
+    assert [n for _, n in seen] == [tokens, tokens] + [tokens // 2] * 4
+    main = seen[0][0]
+    part_streams = [s for s, _ in seen[2:]]
+    assert all(s != main for s in part_streams) and part_streams[0] != part_streams[1]
+    assert part_streams[:2] == part_streams[2:]          # attention phase of both parts, then FFN phase of both parts

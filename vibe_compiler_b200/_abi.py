@@ -120,7 +120,7 @@ ALLREDUCE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_void_p, C.c_uint64, C.c_ui
 class DecoderLayerParams(C.Structure):
     _fields_ = [("batch", C.c_uint32), ("seq", C.c_uint32), ("d_model", C.c_uint32), ("head_dim", C.c_uint32),
                 ("q_heads", C.c_uint32), ("kv_heads", C.c_uint32), ("ffn", C.c_uint32), ("format", C.c_uint32),
-                ("eps", C.c_float), ("rope_theta", C.c_float), ("position_offset", C.c_uint32), ("reserved", C.c_uint32),
+                ("eps", C.c_float), ("rope_theta", C.c_float), ("position_offset", C.c_uint32), ("micro_batches", C.c_uint32),
                 ("x", C.c_void_p), ("out", C.c_void_p),
                 ("norm1", C.c_void_p), ("wqkv", C.c_void_p), ("wo", C.c_void_p), ("norm2", C.c_void_p), ("wgu", C.c_void_p), ("wdown", C.c_void_p),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),

@@ -419,7 +419,7 @@ class B200TargetModelBackend:
 
     def decoder_layer(self, x, *, norm1, wqkv, wo, norm2, wgu, wdown, q_heads: int, kv_heads: int, head_dim: int, eps: float,
                       rope_theta: float, position_offset: int = 0, allreduce=None, workspace=None, out=None,
-                      stream: Optional[int] = None):
+                      micro_batches: int = 1, stream: Optional[int] = None):
         """One shard of a Llama-style decoder layer forward through the single C-ABI call wb200_decoder_layer.
         x: [batch, seq, d_model] CUDA tensor. `allreduce(tensor)` must enqueue an in-place sum over the shards
         (torch.distributed.all_reduce); `workspace` is a uint8 CUDA tensor that is reused if large enough.
@@ -430,6 +430,7 @@ class B200TargetModelBackend:
         p.q_heads, p.kv_heads, p.ffn = q_heads, kv_heads, wdown.shape[0]
         p.format = _TORCH_FORMATS[x.dtype]
         p.eps, p.rope_theta, p.position_offset = eps, rope_theta, position_offset
+        p.micro_batches = micro_batches if allreduce is not None else 1
         needed = self._lib.wb200_decoder_layer_workspace_bytes(C.byref(p))
         if needed == 0:
             raise WB200Error(abi.ERR_UNSUPPORTED, self._lib.wb200_last_error().decode())
@@ -444,10 +445,15 @@ class B200TargetModelBackend:
         p.workspace, p.workspace_bytes, p.stream = workspace.data_ptr(), workspace.numel(), stream
         failure = []
 
-        def reduce_callback(_user, pointer, elements, _format, _stream):
+        def reduce_callback(_user, pointer, elements, _format, part_stream):
             try:
                 begin = pointer - workspace.data_ptr()
-                allreduce(workspace[begin:begin + elements * x.element_size()].view(x.dtype))
+                view = workspace[begin:begin + elements * x.element_size()].view(x.dtype)
+                if part_stream and part_stream != stream:
+                    with torch.cuda.stream(torch.cuda.ExternalStream(part_stream)):
+                        allreduce(view)
+                else:
+                    allreduce(view)
                 return 0
             except Exception as error:   # must not propagate through the C frame
                 failure.append(error)

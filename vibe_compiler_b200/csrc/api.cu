@@ -47,6 +47,10 @@ void wb200_backend_destroy(wb200_backend *backend) {
   for (auto &slot : backend->slots)
     if (slot.ptr) cudaFree(slot.ptr);
   if (backend->d_status) cudaFree(backend->d_status);
+  for (cudaStream_t aux : backend->aux_stream)
+    if (aux) { cudaStreamSynchronize(aux); cudaStreamDestroy(aux); }
+  for (cudaEvent_t event : backend->aux_event)
+    if (event) cudaEventDestroy(event);
   if (backend->stream) cudaStreamDestroy(backend->stream);
   delete backend;
 }

@@ -64,14 +64,47 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
   if (st != WB200_OK) return st;
   if (p->workspace_bytes < plan.total) return fail(WB200_ERR_LIMIT, "workspace smaller than wb200_decoder_layer_workspace_bytes()");
   if (reinterpret_cast<uintptr_t>(p->workspace) % kAlign) return fail(WB200_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
+  // Micro-batches: the batch is cut into `micro_batches` equal parts that run on the backend's two auxiliary streams,
+  // phase by phase, so that the all-reduce of one part overlaps the kernels of the other.
+  const uint32_t parts = (p->micro_batches > 1 && p->allreduce) ? p->micro_batches : 1;
+  if (parts > 1 && (p->batch % parts != 0 || ((static_cast<uint64_t>(p->batch / parts) * p->seq) % 8) != 0))
+    return fail(WB200_ERR_INVALID_ARGUMENT, "micro_batches must divide the batch into parts of a multiple of 8 tokens");
   DeviceGuard guard(backend->device);
-  cudaStream_t stream = static_cast<cudaStream_t>(p->stream);
-  uint8_t *ws = static_cast<uint8_t *>(p->workspace);
-  void *h = ws + plan.off_h, *qkv = ws + plan.off_qkv, *q = ws + plan.off_q, *k = ws + plan.off_k, *v = ws + plan.off_v;
-  void *attn = ws + plan.off_attn, *partial = ws + plan.off_partial, *x1 = ws + plan.off_x1, *act = ws + plan.off_act;
-  const int tokens = static_cast<int>(plan.tokens), d = p->d_model, fmt = p->format;
+  cudaStream_t user_stream = static_cast<cudaStream_t>(p->stream);
+  if (parts > 1 && (st = backend->auxiliary_streams()) != WB200_OK) return st;
+  const int fmt = p->format, d = p->d_model;
+  const size_t part_tokens = plan.tokens / parts;
+  const size_t e = 2;
 
-  auto gemm = [&](const void *a, const void *b, void *out, int m, int n, int kk, int epilogue) -> wb200_status {
+  struct Part {
+    cudaStream_t stream;
+    const uint8_t *x;
+    uint8_t *out, *h, *qkv, *q, *k, *v, *attn, *partial, *x1, *act;
+  };
+  auto part_of = [&](uint32_t index) {
+    // every buffer of the whole-batch plan is cut at token granularity; the head-major Q / K / V buffers are cut at
+    // batch granularity, which is the same thing because a part is a whole number of sequences
+    uint8_t *ws = static_cast<uint8_t *>(p->workspace);
+    const size_t t0 = index * part_tokens;
+    Part part;
+    part.stream = parts > 1 ? backend->aux_stream[index & 1] : user_stream;
+    part.x = static_cast<const uint8_t *>(p->x) + t0 * d * e;
+    part.out = static_cast<uint8_t *>(p->out) + t0 * d * e;
+    part.h = ws + plan.off_h + t0 * d * e;
+    part.qkv = ws + plan.off_qkv + t0 * plan.qkv_cols * e;
+    part.q = ws + plan.off_q + t0 * plan.attn_cols * e;
+    part.k = ws + plan.off_k + t0 * p->kv_heads * p->head_dim * e;
+    part.v = ws + plan.off_v + t0 * p->kv_heads * p->head_dim * e;
+    part.attn = ws + plan.off_attn + t0 * plan.attn_cols * e;
+    part.partial = ws + plan.off_partial + t0 * d * e;
+    part.x1 = ws + plan.off_x1 + t0 * d * e;
+    part.act = ws + plan.off_act + t0 * p->ffn * e;
+    return part;
+  };
+  const int tokens = static_cast<int>(part_tokens);
+  const int part_batch = static_cast<int>(p->batch / parts);
+
+  auto gemm = [&](cudaStream_t stream, const void *a, const void *b, void *out, int m, int n, int kk, int epilogue) -> wb200_status {
     GemmUmmaArgs g{};
     g.m = m; g.n = n; g.k = kk;
     g.in_format = fmt; g.out_format = fmt;
@@ -81,41 +114,65 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
     if (s == WB200_OK) backend->launches += 1;
     return s;
   };
-  auto reduce = [&](void *buffer) -> wb200_status {
+  auto reduce = [&](const Part &part) -> wb200_status {
     if (!p->allreduce) return WB200_OK;
-    if (p->allreduce(p->allreduce_user, buffer, static_cast<uint64_t>(tokens) * d, p->format, p->stream) != 0)
+    if (p->allreduce(p->allreduce_user, part.partial, static_cast<uint64_t>(tokens) * d, p->format, part.stream) != 0)
       return fail(WB200_ERR_CALLBACK, "the all-reduce callback reported a failure");
     return WB200_OK;
   };
+  // RMSNorm -> QKV -> rotary split -> attention -> output projection -> [sum over shards]
+  auto attention_phase = [&](const Part &part) -> wb200_status {
+    wb200_status s;
+    if ((s = launch_rmsnorm(fmt, part.x, p->norm1, part.h, tokens, d, p->eps, part.stream)) != WB200_OK) return s;
+    backend->launches += 1;
+    if ((s = gemm(part.stream, part.h, p->wqkv, part.qkv, tokens, static_cast<int>(plan.qkv_cols), d, WB200_EPI_NONE)) != WB200_OK) return s;
+    if ((s = launch_rope_split(fmt, part.qkv, part.q, part.k, part.v, part_batch, p->seq, p->q_heads, p->kv_heads, p->head_dim, p->rope_theta,
+                               static_cast<int>(p->position_offset), part.stream)) != WB200_OK) return s;
+    backend->launches += 1;
+    AttentionArgs a{};
+    a.batch = part_batch; a.q_heads = p->q_heads; a.kv_heads = p->kv_heads; a.q_len = p->seq; a.kv_len = p->seq; a.head_dim = p->head_dim;
+    a.format = fmt; a.causal = 1; a.zero_fully_masked = 0;
+    a.scale = 1.0f / sqrtf(static_cast<float>(p->head_dim));
+    a.causal_offset = 0; a.kv_valid = p->seq;
+    a.q = part.q; a.k = part.k; a.v = part.v; a.out = part.attn;
+    a.out_token_major = 1;
+    s = attention_fa_umma_supports(a) ? launch_attention_fa_umma(a, backend->sm_count, backend->d_status, part.stream)
+                                      : launch_attention_fa_simt(a, part.stream);
+    if (s != WB200_OK) return s;
+    backend->launches += 1;
+    if ((s = gemm(part.stream, part.attn, p->wo, part.partial, tokens, d, static_cast<int>(plan.attn_cols), WB200_EPI_NONE)) != WB200_OK) return s;
+    return reduce(part);
+  };
+  // residual -> RMSNorm -> gate/up with SwiGLU epilogue -> down projection -> [sum over shards] -> residual
+  auto ffn_phase = [&](const Part &part) -> wb200_status {
+    wb200_status s;
+    if ((s = launch_residual_add(fmt, part.x, part.partial, part.x1, static_cast<size_t>(tokens) * d, part.stream)) != WB200_OK) return s;
+    backend->launches += 1;
+    if ((s = launch_rmsnorm(fmt, part.x1, p->norm2, part.h, tokens, d, p->eps, part.stream)) != WB200_OK) return s;
+    backend->launches += 1;
+    if ((s = gemm(part.stream, part.h, p->wgu, part.act, tokens, 2 * static_cast<int>(p->ffn), d, WB200_EPI_SWIGLU)) != WB200_OK) return s;
+    if ((s = gemm(part.stream, part.act, p->wdown, part.partial, tokens, d, static_cast<int>(p->ffn), WB200_EPI_NONE)) != WB200_OK) return s;
+    if ((s = reduce(part)) != WB200_OK) return s;
+    if ((s = launch_residual_add(fmt, part.x1, part.partial, part.out, static_cast<size_t>(tokens) * d, part.stream)) != WB200_OK) return s;
+    backend->launches += 1;
+    return WB200_OK;
+  };
 
-  if ((st = launch_rmsnorm(fmt, p->x, p->norm1, h, tokens, d, p->eps, stream)) != WB200_OK) return st;
-  backend->launches += 1;
-  if ((st = gemm(h, p->wqkv, qkv, tokens, static_cast<int>(plan.qkv_cols), d, WB200_EPI_NONE)) != WB200_OK) return st;
-  if ((st = launch_rope_split(fmt, qkv, q, k, v, p->batch, p->seq, p->q_heads, p->kv_heads, p->head_dim, p->rope_theta,
-                              static_cast<int>(p->position_offset), stream)) != WB200_OK) return st;
-  backend->launches += 1;
-  AttentionArgs a{};
-  a.batch = p->batch; a.q_heads = p->q_heads; a.kv_heads = p->kv_heads; a.q_len = p->seq; a.kv_len = p->seq; a.head_dim = p->head_dim;
-  a.format = fmt; a.causal = 1; a.zero_fully_masked = 0;
-  a.scale = 1.0f / sqrtf(static_cast<float>(p->head_dim));
-  a.causal_offset = 0; a.kv_valid = p->seq;
-  a.q = q; a.k = k; a.v = v; a.out = attn;
-  a.out_token_major = 1;
-  st = attention_fa_umma_supports(a) ? launch_attention_fa_umma(a, backend->sm_count, backend->d_status, stream)
-                                     : launch_attention_fa_simt(a, stream);
-  if (st != WB200_OK) return st;
-  backend->launches += 1;
-  if ((st = gemm(attn, p->wo, partial, tokens, d, static_cast<int>(plan.attn_cols), WB200_EPI_NONE)) != WB200_OK) return st;
-  if ((st = reduce(partial)) != WB200_OK) return st;
-  if ((st = launch_residual_add(fmt, p->x, partial, x1, plan.tokens * d, stream)) != WB200_OK) return st;
-  backend->launches += 1;
-  if ((st = launch_rmsnorm(fmt, x1, p->norm2, h, tokens, d, p->eps, stream)) != WB200_OK) return st;
-  backend->launches += 1;
-  if ((st = gemm(h, p->wgu, act, tokens, 2 * static_cast<int>(p->ffn), d, WB200_EPI_SWIGLU)) != WB200_OK) return st;
-  if ((st = gemm(act, p->wdown, partial, tokens, d, static_cast<int>(p->ffn), WB200_EPI_NONE)) != WB200_OK) return st;
-  if ((st = reduce(partial)) != WB200_OK) return st;
-  if ((st = launch_residual_add(fmt, x1, partial, p->out, plan.tokens * d, stream)) != WB200_OK) return st;
-  backend->launches += 1;
+  if (parts > 1) {   // fork: the auxiliary streams start after the work already on the caller's stream
+    WB200_CUDA_CHECK(cudaEventRecord(backend->aux_event[0], user_stream));
+    for (int i = 0; i < 2; ++i) WB200_CUDA_CHECK(cudaStreamWaitEvent(backend->aux_stream[i], backend->aux_event[0], 0));
+  }
+  // Phase by phase over the parts, so that the all-reduces are issued in the order their inputs become ready.
+  for (uint32_t i = 0; i < parts; ++i)
+    if ((st = attention_phase(part_of(i))) != WB200_OK) return st;
+  for (uint32_t i = 0; i < parts; ++i)
+    if ((st = ffn_phase(part_of(i))) != WB200_OK) return st;
+  if (parts > 1) {   // join
+    for (int i = 0; i < 2; ++i) {
+      WB200_CUDA_CHECK(cudaEventRecord(backend->aux_event[1 + i], backend->aux_stream[i]));
+      WB200_CUDA_CHECK(cudaStreamWaitEvent(user_stream, backend->aux_event[1 + i], 0));
+    }
+  }
   return WB200_OK;
 }
 

@@ -23,6 +23,15 @@ struct wb200_backend {
   char digest[96] = {0};
   struct Slot { void *ptr = nullptr; size_t bytes = 0; };
   std::vector<Slot> slots;
+  // Two auxiliary streams and three events for calls that overlap independent parts of their work (created on first use).
+  cudaStream_t aux_stream[2] = {nullptr, nullptr};
+  cudaEvent_t aux_event[3] = {nullptr, nullptr, nullptr};
+  wb200_status auxiliary_streams() {
+    if (aux_stream[0]) return WB200_OK;
+    for (int i = 0; i < 2; ++i) WB200_CUDA_CHECK(cudaStreamCreateWithFlags(&aux_stream[i], cudaStreamNonBlocking));
+    for (int i = 0; i < 3; ++i) WB200_CUDA_CHECK(cudaEventCreateWithFlags(&aux_event[i], cudaEventDisableTiming));
+    return WB200_OK;
+  }
 
   // Grow-only staging buffer number `index`.
   wb200_status buffer(size_t index, size_t bytes, void **out) {

@@ -117,7 +117,7 @@ class ShardedDecoderLayer:
         return self.backend.residual_add(x1, partial2).reshape(batch, seq, d)
 
 
-    def forward_fused(self, x: torch.Tensor, position_offset: int = 0) -> torch.Tensor:
+    def forward_fused(self, x: torch.Tensor, position_offset: int = 0, micro_batches: Optional[int] = None) -> torch.Tensor:
         """Same computation through the single C-ABI call (wb200_decoder_layer): ten kernels enqueued by one call, the
         two sums through a callback into torch.distributed, intermediates in one reused workspace."""
         reduce = None
@@ -127,7 +127,8 @@ class ShardedDecoderLayer:
         out, self._workspace = self.backend.decoder_layer(
             x, norm1=self.norm1, wqkv=self.wqkv, wo=self.wo, norm2=self.norm2, wgu=self.wgu, wdown=self.wdown, q_heads=self.hq,
             kv_heads=self.hkv, head_dim=self.cfg.head_dim, eps=self.cfg.eps, rope_theta=self.cfg.rope_theta,
-            position_offset=position_offset, allreduce=reduce, workspace=getattr(self, "_workspace", None))
+            position_offset=position_offset, allreduce=reduce, workspace=getattr(self, "_workspace", None),
+            micro_batches=(micro_batches if micro_batches is not None else (2 if (self.world > 1 and x.shape[0] % 2 == 0) else 1)))
         return out
 
 
