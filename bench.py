@@ -362,9 +362,12 @@ def main():
         lout = torch.empty_like(lq)
         group = None
 
+        lstate = torch.empty(1, FD_LONG["q_heads"], FD_LONG["head_dim"] + 2, device=device)
+        lgathered = torch.empty(world, 1, FD_LONG["q_heads"], FD_LONG["head_dim"] + 2, device=device)
+
         def long_step():
-            sharded_decode(lambda b, e: backend.attention_fd_partial(lq, lk, lv, scale), lambda st: backend.attention_fd_merge(st, lq, out=lout),
-                           FD_LONG["kv_len"], group)
+            sharded_decode(lambda b, e: backend.attention_fd_partial(lq, lk, lv, scale, state=lstate), lambda st: backend.attention_fd_merge(st, lq, out=lout),
+                           FD_LONG["kv_len"], group, lgathered)
         long_total, _ = timed_steps(long_step, args.steps, args.warmup, torch, dist, check=backend.poll)
         backend.poll()
         long_t = torch.tensor([long_total], device=device, dtype=torch.float64)

@@ -6,7 +6,7 @@ seven plans x 16 Tiles of the same source program (out[4096,4096] = arg1[4096,10
 together with the kernel medians of the table in that folder's README. The modules are compiler OUTPUT (data), kept
 byte for byte; they are the inputs of the Tile-program replay tests.
 
-    python tests/golden/make_tile_module_fixture.py [reference root]
+    python tests/golden/make_tile_module_fixture.py <reference checkout root>
 """
 import json
 import lzma
@@ -19,7 +19,9 @@ LADDER = "docs/data/board-performance/gemm-optimization-ladder-20261020-ir"
 
 
 def main():
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference") / LADDER
+    if len(sys.argv) != 2:
+        raise SystemExit(__doc__)
+    root = Path(sys.argv[1]) / LADDER
     plans = {}
     for plan_dir in sorted(p for p in root.iterdir() if (p / "target-llvm").is_dir()):
         modules = [path.read_text() for path in sorted((plan_dir / "target-llvm").glob("tile_*.ll"))]

@@ -9,7 +9,7 @@ reference's spatial flash-decoding materialisation
 """
 from __future__ import annotations
 
-from typing import Callable, Tuple
+from typing import Callable, Optional, Tuple
 
 import torch
 
@@ -34,13 +34,15 @@ def sequence_range(kv_len: int, world_size: int, rank: int, granule: int = 64) -
 
 
 def sharded_decode(state_fn: Callable[[int, int], torch.Tensor], merge_fn: Callable[[torch.Tensor], torch.Tensor],
-                   kv_len: int, group=None) -> torch.Tensor:
+                   kv_len: int, group=None, gathered: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Sequence-sharded flash-decoding step.
 
     state_fn(begin, end) -> this rank's [batch, q_heads, D + 2] float32 state for keys [begin, end)
                             (B200TargetModelBackend.attention_fd_partial on the GPU);
     merge_fn(states)     -> finalized output from [world, batch, q_heads, D + 2] states in shard order
                             (B200TargetModelBackend.attention_fd_merge).
+    gathered             -> optional preallocated [world, batch, q_heads, D + 2] buffer, so that a decode loop
+                            allocates nothing per step.
     The only exchange is one all-gather of the states (D + 2 floats per query head and rank).
     """
     import torch.distributed as dist
@@ -50,6 +52,8 @@ def sharded_decode(state_fn: Callable[[int, int], torch.Tensor], merge_fn: Calla
     state = state_fn(begin, end).contiguous()
     if world == 1:
         return merge_fn(state.unsqueeze(0))
-    gathered = [torch.empty_like(state) for _ in range(world)]
-    dist.all_gather(gathered, state, group=group)
-    return merge_fn(torch.stack(gathered))   # index = rank = ascending KV order
+    if gathered is None:
+        gathered = torch.empty((world,) + tuple(state.shape), dtype=state.dtype, device=state.device)
+    # rank r's state lands in gathered[r]: ascending KV order (the flat view keeps chunk shapes equal to the input's)
+    dist.all_gather_into_tensor(gathered.view((world * state.shape[0],) + tuple(state.shape[1:])), state, group=group)
+    return merge_fn(gathered)
