@@ -51,6 +51,7 @@ void wb200_backend_destroy(wb200_backend *backend) {
     if (aux) { cudaStreamSynchronize(aux); cudaStreamDestroy(aux); }
   for (cudaEvent_t event : backend->aux_event)
     if (event) cudaEventDestroy(event);
+  for (cudaEvent_t event : backend->pipeline_event) cudaEventDestroy(event);
   if (backend->stream) cudaStreamDestroy(backend->stream);
   delete backend;
 }

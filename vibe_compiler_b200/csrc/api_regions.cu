@@ -84,6 +84,66 @@ wb200_status run_fa(wb200_backend *backend, const AttentionArgs &a, cudaStream_t
   return st;
 }
 
+// Host-buffer prefill as a three-stage pipeline over chunks of (batch, kv-head) units: chunk c is copied in on one
+// auxiliary stream, computed on the backend stream and copied out on the other auxiliary stream, so the copy-out of a
+// chunk overlaps the copy-in of the next ones (PCIe is full duplex) and the kernels hide behind both. A unit is one
+// KV head with its group of query heads; consecutive units are contiguous in Q, K, V, out and the statistics, so a
+// chunk of n units is the attention problem {batch = n, q_heads = group, kv_heads = 1}.
+wb200_status run_fa_host_pipelined(wb200_backend *backend, const wb200_attention_params *p, const AttentionArgs &whole) {
+  const size_t eb = element_bytes_of(p->format);
+  const uint32_t group = p->q_heads / p->kv_heads;
+  const uint32_t units = p->batch * p->kv_heads;
+  const uint32_t chunks = units < 8 ? units : 8;
+  const size_t q_unit = static_cast<size_t>(group) * p->q_len * p->head_dim * eb;       // also the out bytes of a unit
+  const size_t kv_unit = static_cast<size_t>(p->kv_len) * p->head_dim * eb;
+  const size_t stat_unit = static_cast<size_t>(group) * p->q_len * sizeof(float);
+  wb200_status st;
+  void *dq, *dk, *dv, *dout, *dl = nullptr, *dm = nullptr, *ds = nullptr;
+  if ((st = backend->buffer(0, q_unit * units, &dq)) != WB200_OK) return st;
+  if ((st = backend->buffer(1, kv_unit * units, &dk)) != WB200_OK) return st;
+  if ((st = backend->buffer(2, kv_unit * units, &dv)) != WB200_OK) return st;
+  if ((st = backend->buffer(3, q_unit * units, &dout)) != WB200_OK) return st;
+  if (p->lse && (st = backend->buffer(4, stat_unit * units, &dl)) != WB200_OK) return st;
+  if (p->row_max && (st = backend->buffer(5, stat_unit * units, &dm)) != WB200_OK) return st;
+  if (p->row_sum && (st = backend->buffer(6, stat_unit * units, &ds)) != WB200_OK) return st;
+  if ((st = backend->auxiliary_streams()) != WB200_OK) return st;
+  if ((st = backend->pipeline_events(2 * chunks)) != WB200_OK) return st;
+  cudaStream_t copy_in = backend->aux_stream[0], compute = backend->stream, copy_out = backend->aux_stream[1];
+  // the auxiliary streams start after whatever the backend stream still has in flight (it owns the staging buffers)
+  WB200_CUDA_CHECK(cudaEventRecord(backend->aux_event[0], compute));
+  WB200_CUDA_CHECK(cudaStreamWaitEvent(copy_in, backend->aux_event[0], 0));
+  WB200_CUDA_CHECK(cudaStreamWaitEvent(copy_out, backend->aux_event[0], 0));
+  auto at = [](const void *base, size_t offset) { return static_cast<const uint8_t *>(base) + offset; };
+  auto at_mut = [](void *base, size_t offset) { return static_cast<uint8_t *>(base) + offset; };
+  uint32_t first = 0;
+  for (uint32_t c = 0; c < chunks; ++c) {
+    const uint32_t count = units / chunks + (c < units % chunks ? 1 : 0);
+    const size_t q_at = first * q_unit, kv_at = first * kv_unit, stat_at = first * stat_unit;
+    WB200_CUDA_CHECK(cudaMemcpyAsync(at_mut(dq, q_at), at(p->q, q_at), count * q_unit, cudaMemcpyHostToDevice, copy_in));
+    WB200_CUDA_CHECK(cudaMemcpyAsync(at_mut(dk, kv_at), at(p->k, kv_at), count * kv_unit, cudaMemcpyHostToDevice, copy_in));
+    WB200_CUDA_CHECK(cudaMemcpyAsync(at_mut(dv, kv_at), at(p->v, kv_at), count * kv_unit, cudaMemcpyHostToDevice, copy_in));
+    WB200_CUDA_CHECK(cudaEventRecord(backend->pipeline_event[2 * c], copy_in));
+    WB200_CUDA_CHECK(cudaStreamWaitEvent(compute, backend->pipeline_event[2 * c], 0));
+    AttentionArgs a = whole;
+    a.batch = static_cast<int>(count); a.q_heads = static_cast<int>(group); a.kv_heads = 1;
+    a.q = at_mut(dq, q_at); a.k = at_mut(dk, kv_at); a.v = at_mut(dv, kv_at); a.out = at_mut(dout, q_at);
+    a.lse = dl ? reinterpret_cast<float *>(at_mut(dl, stat_at)) : nullptr;
+    a.row_max = dm ? reinterpret_cast<float *>(at_mut(dm, stat_at)) : nullptr;
+    a.row_sum = ds ? reinterpret_cast<float *>(at_mut(ds, stat_at)) : nullptr;
+    if ((st = run_fa(backend, a, compute)) != WB200_OK) return st;
+    WB200_CUDA_CHECK(cudaEventRecord(backend->pipeline_event[2 * c + 1], compute));
+    WB200_CUDA_CHECK(cudaStreamWaitEvent(copy_out, backend->pipeline_event[2 * c + 1], 0));
+    WB200_CUDA_CHECK(cudaMemcpyAsync(at_mut(p->out, q_at), at(dout, q_at), count * q_unit, cudaMemcpyDeviceToHost, copy_out));
+    if (p->lse) WB200_CUDA_CHECK(cudaMemcpyAsync(at_mut(p->lse, stat_at), at(dl, stat_at), count * stat_unit, cudaMemcpyDeviceToHost, copy_out));
+    if (p->row_max) WB200_CUDA_CHECK(cudaMemcpyAsync(at_mut(p->row_max, stat_at), at(dm, stat_at), count * stat_unit, cudaMemcpyDeviceToHost, copy_out));
+    if (p->row_sum) WB200_CUDA_CHECK(cudaMemcpyAsync(at_mut(p->row_sum, stat_at), at(ds, stat_at), count * stat_unit, cudaMemcpyDeviceToHost, copy_out));
+    first += count;
+  }
+  WB200_CUDA_CHECK(cudaStreamSynchronize(copy_in));
+  WB200_CUDA_CHECK(cudaStreamSynchronize(copy_out));
+  return read_device_status(backend, compute, nullptr);
+}
+
 }  // namespace
 
 extern "C" {
@@ -96,6 +156,7 @@ wb200_status wb200_attention_fa(wb200_backend *backend, const wb200_attention_pa
   if (st != WB200_OK) return st;
   DeviceGuard guard(backend->device);
   if (p->memory == WB200_MEM_DEVICE) return run_fa(backend, a, static_cast<cudaStream_t>(p->stream));
+  if (p->batch * p->kv_heads >= 2 && !a.out_token_major) return run_fa_host_pipelined(backend, p, a);
   StagedAttention s;
   s.args = a;
   if ((st = stage_attention_inputs(backend, p, &s, true)) != WB200_OK) return st;

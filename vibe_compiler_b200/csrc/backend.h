@@ -26,6 +26,15 @@ struct wb200_backend {
   // Two auxiliary streams and three events for calls that overlap independent parts of their work (created on first use).
   cudaStream_t aux_stream[2] = {nullptr, nullptr};
   cudaEvent_t aux_event[3] = {nullptr, nullptr, nullptr};
+  std::vector<cudaEvent_t> pipeline_event;   // edges of host-buffer pipelines, grown on demand
+  wb200_status pipeline_events(size_t count) {
+    while (pipeline_event.size() < count) {
+      cudaEvent_t event;
+      WB200_CUDA_CHECK(cudaEventCreateWithFlags(&event, cudaEventDisableTiming));
+      pipeline_event.push_back(event);
+    }
+    return WB200_OK;
+  }
   wb200_status auxiliary_streams() {
     if (aux_stream[0]) return WB200_OK;
     for (int i = 0; i < 2; ++i) WB200_CUDA_CHECK(cudaStreamCreateWithFlags(&aux_stream[i], cudaStreamNonBlocking));
