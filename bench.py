@@ -158,7 +158,8 @@ def layer_extra(backend, args, torch, dist, rank, world, device, peak):
     layer = ShardedDecoderLayer(backend, cfg, random_weights(cfg, seed=SEED), rank=rank, world_size=world, device=device)
     gen = torch.Generator(device="cpu").manual_seed(SEED + 5)
     x = torch.randn(LAYER["batch"], LAYER["seq"], cfg.d_model, generator=gen).bfloat16().to(device)
-    total_ms, _ = timed_steps(lambda: layer.forward_fused(x), args.steps, args.warmup, torch, dist=dist, check=backend.poll)
+    parts = int(os.environ.get("WB200_LAYER_MICRO_BATCHES", "0")) or None   # default: 2 when tensor parallel
+    total_ms, _ = timed_steps(lambda: layer.forward_fused(x, micro_batches=parts), args.steps, args.warmup, torch, dist=dist, check=backend.poll)
     backend.poll()
     elapsed = torch.tensor([total_ms], device=device)
     if dist is not None:
@@ -368,7 +369,23 @@ def main():
         def long_step():
             sharded_decode(lambda b, e: backend.attention_fd_partial(lq, lk, lv, scale, state=lstate), lambda st: backend.attention_fd_merge(st, lq, out=lout),
                            FD_LONG["kv_len"], group, lgathered)
-        long_total, _ = timed_steps(long_step, args.steps, args.warmup, torch, dist, check=backend.poll)
+        long_step()
+        torch.cuda.synchronize()
+        backend.poll()
+        step, graphed = long_step, None
+        if world == 1:
+            # One rank: the step has no collective, and its three launches replay as one CUDA graph. With several ranks the
+            # step stays eager (a captured NCCL all-gather has to be released before the process group is torn down).
+            from vibe_compiler_b200.sharding import GraphedDecodeStep
+            eager_out = lout.clone()
+            graphed = GraphedDecodeStep(lambda b, e: backend.attention_fd_partial(lq, lk, lv, scale, state=lstate),
+                                        lambda st: backend.attention_fd_merge(st, lq, out=lout), FD_LONG["kv_len"], lgathered, group)
+            graphed()
+            torch.cuda.synchronize()
+            assert torch.equal(eager_out, lout), "graph replay of the decode step disagrees with the eager step"
+            step = graphed
+        long_total, _ = timed_steps(step, args.steps, args.warmup, torch, dist, check=backend.poll)
+        del step, graphed
         backend.poll()
         long_t = torch.tensor([long_total], device=device, dtype=torch.float64)
         if dist is not None:
@@ -376,7 +393,7 @@ def main():
         long_ms = long_t.item() / args.steps
         long_bytes = 2 * FD_LONG["kv_heads"] * FD_LONG["kv_len"] * FD_LONG["head_dim"] * 2
         long_gbs = long_bytes / (long_ms * 1e-3) / 1e9
-        extras["fd_long_context"] = {"workload": f"FD decode bf16 B1 Hq32 Hkv8 KV1048576 D128, KV sequence sharded over {world} rank(s); exchange = all-gather of (acc, m, l) states",
+        extras["fd_long_context"] = {"workload": f"FD decode bf16 B1 Hq32 Hkv8 KV1048576 D128, KV sequence sharded over {world} rank(s); exchange = all-gather of (acc, m, l) states" + ("; the step replays as one CUDA graph" if world == 1 else ""),
                                      "value": long_gbs, "unit": "GB/s", "ms_per_step": long_ms, "scaling": "strong", "n_gpus": world,
                                      "exchange_bytes_per_rank": FD_LONG["q_heads"] * (FD_LONG["head_dim"] + 2) * 4,
                                      "roofline": {"bound": "hbm", "achieved": long_gbs / world, "peak": peak["hbm_gbs"], "unit": "GB/s per GPU",

@@ -57,3 +57,30 @@ def sharded_decode(state_fn: Callable[[int, int], torch.Tensor], merge_fn: Calla
     # rank r's state lands in gathered[r]: ascending KV order (the flat view keeps chunk shapes equal to the input's)
     dist.all_gather_into_tensor(gathered.view((world * state.shape[0],) + tuple(state.shape[1:])), state, group=group)
     return merge_fn(gathered)
+
+
+class GraphedDecodeStep:
+    """One sequence-sharded decode step (local state, all-gather, merge) captured once into a CUDA graph and replayed:
+    a decode step is four small launches plus one collective, so at small per-rank KV lengths the launch path, not the
+    HBM stream, sets its time. The callables must use preallocated tensors only (captured addresses are replayed).
+    With more than one rank the graph holds an NCCL all-gather: release the step object (and synchronise) before the
+    process group is destroyed - a process that tore the group down while the graph was alive did not exit.
+
+        step = GraphedDecodeStep(state_fn, merge_fn, kv_len, gathered, group)
+        step()          # replays; outputs are in the tensors merge_fn writes
+    """
+
+    def __init__(self, state_fn, merge_fn, kv_len: int, gathered: torch.Tensor, group=None, warmup: int = 2):
+        self._graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(warmup):                      # first calls size the library's scratch buffers and NCCL's
+                sharded_decode(state_fn, merge_fn, kv_len, group, gathered)
+            side.synchronize()
+            with torch.cuda.graph(self._graph, stream=side):
+                sharded_decode(state_fn, merge_fn, kv_len, group, gathered)
+        torch.cuda.current_stream().wait_stream(side)
+
+    def __call__(self):
+        self._graph.replay()
