@@ -200,7 +200,10 @@ wb200_status wb200_elementwise(wb200_backend *backend, const wb200_elementwise_r
 /* The formal (bit-exact) elementwise family of lib/Wafer/Simulator/Reference/Formal/FormalNumericElementwise.cpp:23-248,
  * which the reference runs when the managed backend declines: abs, neg, recip, square, max, min, add, sub, mul, relu in the
  * operand format with one RNE rounding; eq / ne / ge / gt / le / lt to Bool or to 1.0 / 0.0 of a float format (with a NaN
- * operand only `ne` holds); logic not / and / or / xor on "bits != 0" to Bool. NaN results are the canonical quiet NaN
+ * operand only `ne` holds); logic not / and / or / xor on "bits != 0" to Bool; and, for F16 / BF16 operands, the
+ * correctly rounded functions of lib/Wafer/Simulator/Reference/Numeric/MPFRNumeric.cpp:372-470, 560-682 (sqrt, rsqrt,
+ * log2, ln, pow2, exp, sin, cos, tanh, sigmoid, softplus: the exact function rounded once to nearest-even with
+ * gradual underflow; F32 operands are declined). NaN results are the canonical quiet NaN
  * (nothing is rejected); `evidence->flags` is the OR of the IEEE flags over all elements. Bool tensors are bit-packed,
  * least significant bit first, and are taken in Tensor / NTensor layout. */
 wb200_status wb200_elementwise_formal(wb200_backend *backend, const wb200_elementwise_request *request,

@@ -135,8 +135,62 @@ def test_formal_entry_rejects_what_it_does_not_cover(backend):
     from vibe_compiler_b200.backend import WB200Error
     a = np.zeros(8, dtype=np.uint16)
     with pytest.raises(WB200Error, match="outside the formal"):
-        _run(backend, "exp", "f16", "f16", a)
+        _run(backend, "exp_lp", "f16", "f16", a)
+    with pytest.raises(WB200Error, match="F16 and BF16"):
+        _run(backend, "exp", "f32", "f32", np.zeros(8, dtype=np.uint32))
     with pytest.raises(WB200Error, match="arity"):
         _run(backend, "add", "f16", "f16", a)
     with pytest.raises(WB200Error, match="result format"):
         _run(backend, "add", "f16", "f32", a, a)
+
+
+# ------------------------------------------------------------------------------------------------ function family
+def _function_expected():
+    import json
+    from pathlib import Path
+    return json.loads((Path(__file__).resolve().parent / "golden" / "formal_function_expected.json").read_text())
+
+
+def test_function_oracle_reference_vectors():
+    # unittests/Simulator/Reference/FormalTensorNumericTest.cpp:236-248: bf16 exp(0) = 1.0, signalling NaN -> canonical NaN + invalid
+    assert F.evaluate_function("exp", "bf16", 0x0000) == (0x3f80, 0)
+    assert F.evaluate_function("exp", "bf16", 0x7f81) == (0x7fc0, F.INVALID)
+    assert F.evaluate_function("sqrt", "f16", 0x4400) == (0x4000, 0)                              # sqrt(4) = 2, exact
+    assert F.evaluate_function("log2", "f16", 0x4800) == (0x4200, 0)                              # log2(8) = 3, exact
+    assert F.evaluate_function("rsqrt", "f16", 0x8000) == (0xfc00, F.DIV_BY_ZERO)                 # the reference's own -0 rule
+    assert F.evaluate_function("ln", "bf16", 0xbf80) == (0x7fc0, F.INVALID)
+    assert F.evaluate_function("exp", "f16", 0x4d00) == (0x7c00, F.OVERFLOW | F.INEXACT)          # e^20 > 65504
+    assert F.evaluate_function("exp", "f16", 0xcd00)[1] == F.UNDERFLOW | F.INEXACT
+    assert F.evaluate_function("sigmoid", "bf16", 0x0000) == (0x3f00, 0)
+    assert F.evaluate_function("tanh", "bf16", 0xff80) == (0xbf80, 0)
+    expected = _function_expected()
+    for key, entry in list(expected.items())[::5]:                                                # the fixture is what the oracle says
+        fmt, op = key.split(":")
+        for bits, (result, flags) in list(entry["samples"].items())[::16]:
+            assert F.evaluate_function(op, fmt, int(bits)) == (result, flags), (key, bits)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["f16", "bf16"])
+def test_function_family_over_the_complete_operand_space(backend, fmt):
+    import hashlib
+    expected = _function_expected()
+    everything = np.arange(65536, dtype=np.uint16)
+    for op in F.FUNCTIONS:
+        entry = expected[f"{fmt}:{op}"]
+        storage, evidence = _run(backend, op, fmt, fmt, everything)
+        got = storage.view(np.uint16)
+        if hashlib.sha256(got.tobytes()).hexdigest() != entry["sha256"]:
+            wrong = [(bits, int(got[int(bits)]), want[0]) for bits, want in entry["samples"].items() if int(got[int(bits)]) != want[0]]
+            raise AssertionError(f"{fmt} {op}: result table differs from the 200-bit evaluation; sampled mismatches {wrong[:8]}")
+        assert evidence.flags == entry["flags_or"], (op, evidence.flags, entry["flags_or"])
+
+
+@pytest.mark.gpu
+def test_function_family_flags_per_element(backend):
+    expected = _function_expected()
+    for key, entry in expected.items():
+        fmt, op = key.split(":")
+        for bits, (result, flags) in list(entry["samples"].items())[::3]:
+            storage, evidence = _run(backend, op, fmt, fmt, np.array([int(bits)], dtype=np.uint16))
+            assert (int(storage.view(np.uint16)[0]), evidence.flags) == (result, flags), (key, hex(int(bits)))

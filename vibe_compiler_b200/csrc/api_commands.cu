@@ -211,7 +211,13 @@ wb200_status wb200_elementwise_formal(wb200_backend *backend, const wb200_elemen
     case WB200_EW_LOGIC_AND: case WB200_EW_LOGIC_OR: case WB200_EW_LOGIC_XOR: arity = 2; logic = true; break;
     case WB200_EW_LOGIC_NOT: arity = 1; logic = true; break;
     case WB200_EW_ABS: case WB200_EW_RECIP: case WB200_EW_SQUARE: case WB200_EW_NEG: case WB200_EW_RELU: arity = 1; break;
-    default: return fail(WB200_ERR_UNSUPPORTED, "elementwise operation is outside the formal binary-arithmetic, relation and logic family");
+    case WB200_EW_SQRT: case WB200_EW_RSQRT: case WB200_EW_LOG2: case WB200_EW_LN: case WB200_EW_POW2: case WB200_EW_EXP:
+    case WB200_EW_SIN: case WB200_EW_COS: case WB200_EW_TANH: case WB200_EW_SIGMOID: case WB200_EW_SOFTPLUS:
+      arity = 1;
+      if (r->inputs[0].format != WB200_F16 && r->inputs[0].format != WB200_BF16)
+        return fail(WB200_ERR_UNSUPPORTED, "the correctly rounded function family takes F16 and BF16 operands (F32 needs more than f64 evaluation)");
+      break;
+    default: return fail(WB200_ERR_UNSUPPORTED, "elementwise operation is outside the formal arithmetic, relation, logic and function families");
   }
   if (static_cast<int>(r->input_count) != arity) return fail(WB200_ERR_INVALID_ARGUMENT, "elementwise input arity does not match semantics");
   const wb200_tensor_desc &dst = r->destination, &first = r->inputs[0];

@@ -247,6 +247,97 @@ __device__ uint32_t formal_scalar(int op, int format, int out_format, uint32_t a
   return result;
 }
 
+// Correctly rounded unary functions of the reference's MPFR family for the 16-bit formats
+// (lib/Wafer/Simulator/Reference/Numeric/MPFRNumeric.cpp:560-682: the function evaluated exactly, rounded once to
+// nearest-even with gradual underflow; sigmoid and softplus as whole functions, :372-470). The value is computed in
+// f64 (a few ulp of f64) and narrowed with a single rounding (f64 -> f32 with round-to-odd, then RNE to 11 or 8 bits);
+// a misrounding needs the true value within 2^-50 of a rounding boundary of a 16-bit format, and the complete input
+// space (65 536 operands per function and format) is checked against a 200-bit evaluation. f32 operands are not
+// taken: f64 evaluation cannot guarantee their rounding.
+__device__ __forceinline__ uint32_t narrow_from_double(double value, int format) {
+  float f = __double2float_rz(value);
+  if (static_cast<double>(f) != value && isfinite(f)) f = __uint_as_float(__float_as_uint(f) | 1u);   // sticky bit: round to odd
+  return narrow_bits(f, format);
+}
+
+__device__ uint32_t formal_mpfr_scalar(int op, int format, uint32_t a, uint32_t *flags_out) {
+  const FormatTraits t = traits_of(format);
+  uint32_t flags = 0;
+  const bool nan = (a & t.exp_mask) == t.exp_mask && (a & t.mant_mask) != 0;
+  if (nan) {
+    *flags_out = (a & t.quiet_bit) ? 0u : kFlagInvalid;
+    return t.canonical_nan;
+  }
+  const bool negative = (a & t.sign) != 0, zero = (a & ~t.sign) == 0, inf = (a & ~t.sign) == t.exp_mask;
+  const double x = static_cast<double>(widen_bits(a, format));
+  const uint32_t pos_inf = t.exp_mask, neg_inf = t.exp_mask | t.sign;
+  auto finish = [&](uint32_t bits, uint32_t f) { *flags_out = f; return bits; };
+  double value;
+  bool exact = false;
+  switch (op) {
+    case WB200_EW_SQRT:
+      if (zero) return finish(a, 0);                                   // sqrt(-0) = -0
+      if (negative) return finish(t.canonical_nan, kFlagInvalid);
+      if (inf) return finish(pos_inf, 0);
+      value = sqrt(x);
+      exact = fma(value, value, -x) == 0.0;
+      break;
+    case WB200_EW_RSQRT:
+      if (zero) return finish(negative ? neg_inf : pos_inf, kFlagDivByZero);
+      if (negative) return finish(t.canonical_nan, kFlagInvalid);
+      if (inf) return finish(0u, 0);
+      value = 1.0 / sqrt(x);
+      { int e; exact = frexp(x, &e) == 0.5 && ((e - 1) & 1) == 0; }      // x = 4^k
+      break;
+    case WB200_EW_LOG2:
+    case WB200_EW_LN:
+      if (zero) return finish(neg_inf, kFlagDivByZero);
+      if (negative) return finish(t.canonical_nan, kFlagInvalid);
+      if (inf) return finish(pos_inf, 0);
+      if (op == WB200_EW_LOG2) { int e; const bool power = frexp(x, &e) == 0.5; value = power ? static_cast<double>(e - 1) : log2(x); exact = power; }
+      else { value = log(x); exact = x == 1.0; }
+      break;
+    case WB200_EW_POW2:
+    case WB200_EW_EXP:
+      if (inf) return finish(negative ? 0u : pos_inf, 0);
+      value = op == WB200_EW_POW2 ? exp2(x) : exp(x);
+      exact = op == WB200_EW_POW2 ? (x == rint(x)) : zero;
+      break;
+    case WB200_EW_SIN:
+    case WB200_EW_COS:
+      if (inf) return finish(t.canonical_nan, kFlagInvalid);
+      if (zero) return finish(op == WB200_EW_SIN ? a : t.one, 0);
+      value = op == WB200_EW_SIN ? sin(x) : cos(x);
+      break;
+    case WB200_EW_TANH:
+      if (zero) return finish(a, 0);
+      if (inf) return finish(negative ? (t.one | t.sign) : t.one, 0);
+      value = tanh(x);
+      break;
+    case WB200_EW_SIGMOID:
+      if (inf) return finish(negative ? 0u : t.one, 0);
+      if (zero) return finish(narrow_bits(0.5f, format), 0);
+      value = x >= 0.0 ? 1.0 / (1.0 + exp(-x)) : exp(x) / (1.0 + exp(x));
+      break;
+    default:   // softplus = ln(1 + e^x)
+      if (inf) return finish(negative ? 0u : pos_inf, 0);
+      value = x > 0.0 ? x + log1p(exp(-x)) : log1p(exp(x));
+      break;
+  }
+  const uint32_t bits = narrow_from_double(value, format);
+  // Every exactly infinite result was returned above, so an infinite result here is an overflow; 2^x, e^x, sigmoid
+  // and softplus are never exactly zero, so a zero result of theirs is an underflow (this also covers an f64
+  // evaluation that saturated, e.g. 2^1904 or 2^-2000 with an integer operand).
+  const bool never_zero = op == WB200_EW_POW2 || op == WB200_EW_EXP || op == WB200_EW_SIGMOID || op == WB200_EW_SOFTPLUS;
+  if ((bits & ~t.sign) == t.exp_mask) flags |= kFlagOverflow | kFlagInexact;
+  else if ((bits & ~t.sign) == 0 && never_zero) flags |= kFlagUnderflow | kFlagInexact;
+  else if (!exact || static_cast<double>(widen_bits(bits, format)) != value) {
+    flags |= kFlagInexact;
+    if (tiny_after_rounding(value, t.precision, t.min_normal)) flags |= kFlagUnderflow;
+  }
+  return finish(bits, flags);
+}
+
 __device__ __forceinline__ uint32_t formal_load(const uint8_t *base, int format, const LayoutMap &map, int64_t i) {
   if (format == WB200_BOOL) return (base[i >> 3] >> (i & 7)) & 1u;   // bit-packed, least significant bit first
   return load_element_bits(base, physical_index(map, i), format);
@@ -260,6 +351,8 @@ formal_elementwise_kernel(int op, int in_format, int out_format, int input_count
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   uint32_t flags = 0;
   const bool logic = op >= WB200_EW_LOGIC_NOT && op <= WB200_EW_LOGIC_XOR;
+  const bool mpfr_family = op == WB200_EW_SQRT || op == WB200_EW_RSQRT || (op >= WB200_EW_LOG2 && op <= WB200_EW_EXP) ||
+                           (op >= WB200_EW_SIN && op <= WB200_EW_SIGMOID) || op == WB200_EW_SOFTPLUS;
   for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < groups; g += stride) {
     uint32_t packed = 0;
     const int64_t first = g * 8;
@@ -272,6 +365,8 @@ formal_elementwise_kernel(int op, int in_format, int out_format, int input_count
       if (logic) {
         const bool lhs = a != 0, rhs = b != 0;
         value = op == WB200_EW_LOGIC_NOT ? !lhs : op == WB200_EW_LOGIC_AND ? (lhs && rhs) : op == WB200_EW_LOGIC_OR ? (lhs || rhs) : (lhs != rhs);
+      } else if (mpfr_family) {
+        value = formal_mpfr_scalar(op, in_format, a, &element_flags);
       } else {
         value = formal_scalar(op, in_format, out_format, a, b, &element_flags);
       }
