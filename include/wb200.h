@@ -280,6 +280,10 @@ typedef struct wb200_attention_params {
  * replaces the command run materialised from
  * lib/Wafer/Transforms/Linalg/OnlineAttentionDecomposition.cpp:568-594 and finalize
  * lib/Wafer/Transforms/Linalg/OnlineAttentionMaterialization.cpp:196-262. */
+/* Notes on wb200_attention_fa: with WB200_MEM_HOST and at least two (batch, kv-head) units the call pipelines copy-in,
+ * kernels and copy-out over chunks on three streams (use pinned host memory for the overlap). The tcgen05 kernel runs a
+ * persistent grid over a work plan that is built on the first call of each distinct shape (a few KiB of device memory,
+ * one allocation and one copy, cached per device): make that first call outside any stream capture. */
 wb200_status wb200_attention_fa(wb200_backend *backend, const wb200_attention_params *params);
 
 /* Flash-decoding: KV axis split into `kv_splits` >= 2 contiguous intervals (0 = choose), each
