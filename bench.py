@@ -422,6 +422,8 @@ def main():
     if rank == 0:
         cpu_threads = os.cpu_count() or 1
         cpu_seconds, cpu_flops, cpu_desc = cpu_sample(cpu_threads) if world == 1 else (None, None, None)
+        # the reference runs its numeric path on one OS thread (sequential oneDNN, SystemC coroutines): one unit, one thread
+        one_seconds, one_flops, one_desc = cpu_sample(1, units=1) if world == 1 else (None, None, None)
         line = {
             "metric": "fa_prefill_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -439,7 +441,9 @@ def main():
         }
         if cpu_seconds is not None:
             line["cpu_baseline"] = {"value": cpu_flops / cpu_seconds / 1e12, "unit": "TFLOP/s", "cores": cpu_threads, "kind": "port",
-                                    "sample": cpu_desc, "seconds": cpu_seconds}
+                                    "sample": cpu_desc, "seconds": cpu_seconds,
+                                    "single_thread": {"value": one_flops / one_seconds / 1e12, "unit": "TFLOP/s", "cores": 1, "sample": one_desc,
+                                                      "seconds": one_seconds}}
         line.update(extras)
         emit(line)
     if dist is not None:
