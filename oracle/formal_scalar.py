@@ -255,9 +255,9 @@ def evaluate_function(op, fmt, bits):
             exact = huge if value > 0 else tiny
         elif op == "tanh" and abs(value) >= 64:
             exact = (1 - Fraction(1, 2 ** 200)) * (1 if value > 0 else -1)
-        elif op == "sigmoid" and abs(value) >= 256:
+        elif op == "sigmoid" and (value >= 128 or value <= -4096):      # 1 - e^-128 needs 185 bits: the last one 200 resolve
             exact = 1 - Fraction(1, 2 ** 200) if value > 0 else tiny
-        elif op == "softplus" and abs(value) >= 256:
+        elif op == "softplus" and (value >= 128 or value <= -4096):
             exact = value + Fraction(1, 2 ** 300) if value > 0 else tiny
     if exact is None:
         # sin x = x - x^3/6..., cos x = 1 - x^2/2...: for the smallest bf16 operands (2^-133) the second term sits 266
