@@ -505,6 +505,50 @@ const char *wb200_program_command_name(uint32_t kind);
 wb200_status wb200_tile_program_run(wb200_tile_program *program, const void *const *inputs, void *const *outputs,
                                     uint32_t gemm_policy, wb200_program_stats *stats);
 
+/* ------------------------------------------------------------------ Expected-output comparison (acceptance gate) */
+/* Device evaluation of the reference's output gate: compareProgramTensorExpectedOutput and
+ * computeProgramTensorComparisonStatistics (lib/Wafer/Simulator/Invocation/ProgramTensorComparison.cpp:276-403,
+ * :405-503) on two compact little-endian tensors of one floating format. Values are decoded exactly to f64; the
+ * absolute error, the tolerance atol + rtol * |expected| (two separate roundings, no contraction), the ULP distance on
+ * the sign-magnitude order key and every count are the reference's own f64 / integer results. Quantiles are the
+ * nearest-rank order statistics (rank = ceil(q * n), clamped to [1, n]) found by an exact radix select. The four
+ * similarity sums and the two means, which the reference accumulates sequentially in x87 extended precision, are
+ * accumulated in double-double (about 106 bits) and rounded once, so cosine, relative_l2, mean_abs and mean_ulp agree
+ * with the reference to within a few units of 1e-16 relative rather than bit for bit. */
+typedef enum wb200_comparison_outcome {
+  WB200_CMP_MATCH = 0,
+  WB200_CMP_INVALID_TOLERANCE = 1,  /* negative / non-finite tolerance, or atol + rtol * |expected| overflowed */
+  WB200_CMP_ACTUAL_NONFINITE = 2,
+  WB200_CMP_EXPECTED_NONFINITE = 3,
+  WB200_CMP_NUMERIC_MISMATCH = 4,
+  WB200_CMP_EMPTY = 5,              /* similarity was requested on an empty tensor */
+  WB200_CMP_RAW_MISMATCH = 6        /* wb200_compare_raw only */
+} wb200_comparison_outcome;
+typedef struct wb200_comparison {
+  uint32_t outcome;  /* wb200_comparison_outcome */
+  uint32_t reserved;
+  uint64_t element;  /* the element (or byte) the outcome names: first non-finite / overflowing / differing one */
+  uint64_t element_count, exact_count, mismatch_count;
+  double exact_fraction, mean_abs, p99_abs, p999_abs, max_abs;
+  double cosine, relative_l2, mean_ulp;
+  uint64_t p99_ulp, p999_ulp, max_ulp;
+  /* Elementwise mismatches (|actual - expected| > tolerance), in the reference's tie rules: the first in index order,
+   * the first one attaining the largest absolute error, the first one attaining the largest error / tolerance. */
+  uint64_t first_mismatch, max_abs_mismatch, max_ratio_mismatch;
+  char detail[512];  /* the reference's detail text for a failing outcome (its "%e" number format); empty on a match */
+} wb200_comparison;
+/* `format`: WB200_F16, WB200_BF16 or WB200_F32; `memory`: where `actual` and `expected` live (wb200_memory).
+ * `use_similarity` != 0 selects the cosine / relative-L2 gate (minimum_cosine in [0, 1], maximum_relative_l2 >= 0);
+ * otherwise every element must be within tolerance. Statistics are filled whenever the tensors are non-empty and
+ * finite. The status is WB200_OK for every outcome; it reports only malformed calls and CUDA failures. */
+wb200_status wb200_compare(wb200_backend *backend, uint32_t format, uint64_t count, const void *actual,
+                           const void *expected, uint32_t memory, double atol, double rtol, uint32_t use_similarity,
+                           double minimum_cosine, double maximum_relative_l2, wb200_comparison *out);
+/* Exact comparison for every non-floating element type (ProgramTensorComparison.cpp:306-323): outcome MATCH or
+ * RAW_MISMATCH with `element` = the first differing byte. */
+wb200_status wb200_compare_raw(wb200_backend *backend, uint64_t bytes, const void *actual, const void *expected,
+                               uint32_t memory, wb200_comparison *out);
+
 #ifdef __cplusplus
 }
 #endif

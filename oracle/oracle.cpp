@@ -589,7 +589,7 @@ int oracle_compare(int format, int64_t count, const void *actual, const void *ex
     const double d = fabs(a - e);
     abs_err[i] = d;
     abs_sum += d;
-    if (ab == eb || a == e) out->exact_count += (ab == eb);
+    out->exact_count += (d == 0.0);  // +0 against -0 counts as exact (:477-478)
     const uint64_t u = a == e ? 0 : (key(ab) >= key(eb) ? key(ab) - key(eb) : key(eb) - key(ab));
     ulp[i] = u;
     ulp_sum += u;

@@ -81,7 +81,8 @@ def test_comparator_statistics(oracle):
     actual = np.array([1.0, -2.0, -0.0, 4.0 + 2 ** -21], dtype=np.float32)
     stats = oracle.compare("f32", actual.view(np.uint32), expected.view(np.uint32), atol=0.0, rtol=0.0)
     assert stats["element_count"] == 4 and stats["mismatch_count"] == 1
-    assert stats["max_ulp"] == 1 and stats["exact_count"] == 2  # signed zeros are equal but not bit-identical
+    # signed zeros differ in bits but count as exact (ProgramTensorComparisonTest.cpp:360-367)
+    assert stats["max_ulp"] == 1 and stats["exact_count"] == 3
     assert stats["cosine"] > 0.999999 and stats["relative_l2"] < 1e-6
     zero = np.zeros(4, dtype=np.uint32)
     assert oracle.compare("f32", zero, zero)["cosine"] == 1.0

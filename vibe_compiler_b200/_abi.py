@@ -138,6 +138,18 @@ class ProgramCommand(C.Structure):
     _fields_ = [("tile", C.c_uint32), ("kind", C.c_uint32), ("argc", C.c_uint32), ("reserved", C.c_uint32), ("args", C.c_uint64 * 17)]
 
 
+class Comparison(C.Structure):
+    _fields_ = [("outcome", C.c_uint32), ("reserved", C.c_uint32), ("element", C.c_uint64),
+                ("element_count", C.c_uint64), ("exact_count", C.c_uint64), ("mismatch_count", C.c_uint64),
+                ("exact_fraction", C.c_double), ("mean_abs", C.c_double), ("p99_abs", C.c_double), ("p999_abs", C.c_double),
+                ("max_abs", C.c_double), ("cosine", C.c_double), ("relative_l2", C.c_double), ("mean_ulp", C.c_double),
+                ("p99_ulp", C.c_uint64), ("p999_ulp", C.c_uint64), ("max_ulp", C.c_uint64),
+                ("first_mismatch", C.c_uint64), ("max_abs_mismatch", C.c_uint64), ("max_ratio_mismatch", C.c_uint64),
+                ("detail", C.c_char * 512)]
+
+
+CMP_MATCH, CMP_INVALID_TOLERANCE, CMP_ACTUAL_NONFINITE, CMP_EXPECTED_NONFINITE, CMP_NUMERIC_MISMATCH, CMP_EMPTY, CMP_RAW_MISMATCH = range(7)
+
 _U32x3 = C.POINTER(C.c_uint32)
 
 SIGNATURES = {
@@ -180,6 +192,9 @@ SIGNATURES = {
     "wb200_tile_program_trace": (C.c_int, [C.c_void_p, C.POINTER(ProgramCommand), C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(ProgramStats)]),
     "wb200_program_command_name": (C.c_char_p, [C.c_uint32]),
     "wb200_tile_program_run": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_uint32, C.POINTER(ProgramStats)]),
+    "wb200_compare": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p, C.c_void_p, C.c_uint32, C.c_double, C.c_double,
+                                C.c_uint32, C.c_double, C.c_double, C.POINTER(Comparison)]),
+    "wb200_compare_raw": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(Comparison)]),
     "wb200_spm_create": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(C.c_void_p)]),
     "wb200_spm_destroy": (None, [C.c_void_p]),
     "wb200_spm_write": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64]),
