@@ -450,6 +450,26 @@ wb200_status wb200_target_call_gather_scatter(wb200_spm_image *spm, uint64_t sou
 wb200_status wb200_target_call_memset(wb200_spm_image *spm, uint64_t destination, uint32_t value_bits,
                                       uint32_t element_count, uint32_t format);
 
+/* wafer_tx81_elementwise_<op> on a scratch-pad image (lib/Wafer/Target/TargetCall.cpp:86-95, decode
+ * lib/Wafer/Target/TargetCallDecoder.cpp:231-268): operands are 1-D Tensor vectors of `count` elements of `format`;
+ * relations write bit-packed Bool, or 1.0 / 0.0 of `format` when `relation_numeric_or_rhs_group` is 1; logic calls write
+ * Bool. Arithmetic and relation calls take the second operand in one of four forms
+ * (lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:296-372): a full vector; a unit of `rhs_unit_elements`
+ * elements repeated (index % unit); for arithmetic calls one 64-element row per group of `relation_numeric_or_rhs_group`
+ * elements (index / group * 64 + index % 64); or, with `scalar_flag` = 1, the immediate bits in `rhs_or_scalar_bits`.
+ * Unary and logic calls ignore the three extra fields. Every form runs the formal family of wb200_elementwise_formal;
+ * `flags` (may be null) receives the OR of the IEEE flags. */
+wb200_status wb200_target_call_elementwise(wb200_spm_image *image, uint32_t operation, uint64_t lhs, uint64_t rhs_or_scalar_bits,
+                                           uint64_t dst, uint32_t count, uint32_t format, uint32_t rhs_unit_elements,
+                                           uint32_t scalar_flag, uint32_t relation_numeric_or_rhs_group, uint32_t *flags);
+/* wafer_tx81_pool_{sum,max,min} (kind 116 / 117 / 119; lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:466-583):
+ * NCx [n, h, w, c] input and output, `kernel_strides` = {kernel w, kernel h, stride w, stride h}, all `pads` zero; each
+ * output folds its window in (kh, kw) order with the formal max / min, or for sum (F32 only) adds every tap to +0.
+ * Average and the indexed kinds are declined like in the reference. */
+wb200_status wb200_target_call_pool(wb200_spm_image *image, uint32_t kind, uint64_t input, uint64_t dst, const uint32_t source_shape[4],
+                                    const uint32_t destination_shape[4], const uint32_t pads[4], const uint32_t kernel_strides[4],
+                                    uint32_t format, uint32_t *flags);
+
 /* ------------------------------------------------------------------ Tile program replay (Seam 2, whole invocation) */
 /* Executes the per-Tile target LLVM modules the reference compiler emits (text form, one module per Tile) the way the
  * reference's host execution does: it admits the closed integer subset of LLVM IR of

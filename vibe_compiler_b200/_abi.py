@@ -192,6 +192,8 @@ SIGNATURES = {
     "wb200_tile_program_trace": (C.c_int, [C.c_void_p, C.POINTER(ProgramCommand), C.c_uint64, C.POINTER(C.c_uint64), C.POINTER(ProgramStats)]),
     "wb200_program_command_name": (C.c_char_p, [C.c_uint32]),
     "wb200_tile_program_run": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_uint32, C.POINTER(ProgramStats)]),
+    "wb200_target_call_elementwise": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint64] + [C.c_uint32] * 5 + [C.POINTER(C.c_uint32)]),
+    "wb200_target_call_pool": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, _U32x3, _U32x3, _U32x3, _U32x3, C.c_uint32, C.POINTER(C.c_uint32)]),
     "wb200_compare": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p, C.c_void_p, C.c_uint32, C.c_double, C.c_double,
                                 C.c_uint32, C.c_double, C.c_double, C.POINTER(Comparison)]),
     "wb200_compare_raw": (C.c_int, [C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(Comparison)]),

@@ -10,6 +10,7 @@ computes as a whole. Every method calls the device library; nothing is computed 
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
@@ -108,9 +109,17 @@ class B200TargetModelBackend:
             raise WB200Error(status, self._lib.wb200_last_error().decode())
         self._handle = handle
         self.device = device
+        self._dependents = weakref.WeakSet()   # objects holding device state of this backend (images, programs)
+
+    def adopt(self, dependent) -> None:
+        """Registers an object whose `close()` must run before the backend is destroyed (finalisers of one garbage
+        cycle run in no particular order)."""
+        self._dependents.add(dependent)
 
     def close(self):
         if getattr(self, "_handle", None):
+            for dependent in list(getattr(self, "_dependents", ())):
+                dependent.close()
             self._lib.wb200_backend_destroy(self._handle)
             self._handle = None
 

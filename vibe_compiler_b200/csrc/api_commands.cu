@@ -476,7 +476,156 @@ wb200_status enqueue_image_gemm(wb200_spm_image *image, uint64_t lhs, uint64_t r
   return run_device_gemm(backend, g, effective_policy, 4, image->work_stream(), &implementation);
 }
 
+
+// wafer_tx81_elementwise_<op> on a scratch-pad image: 1-D Tensor operands of `count` elements, the result format
+// chosen by the operation class, the second operand in one of its four forms
+// (lib/Wafer/Target/TargetCallDecoder.cpp:231-268, lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:288-400).
+wb200_status enqueue_image_elementwise(wb200_spm_image *image, uint32_t operation, uint64_t lhs, uint64_t rhs_or_scalar_bits,
+                                       uint64_t dst, uint32_t count, uint32_t format, uint32_t rhs_unit_elements,
+                                       uint32_t scalar_flag, uint32_t relation_numeric_or_rhs_group, uint32_t *d_flags) {
+  if (!image) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  int arity;
+  bool relation = false, logic = false;
+  switch (operation) {
+    case WB200_EW_MAX: case WB200_EW_MIN: case WB200_EW_ADD: case WB200_EW_SUB: case WB200_EW_MUL: arity = 2; break;
+    case WB200_EW_EQ: case WB200_EW_NE: case WB200_EW_GE: case WB200_EW_GT: case WB200_EW_LE: case WB200_EW_LT: arity = 2; relation = true; break;
+    case WB200_EW_LOGIC_AND: case WB200_EW_LOGIC_OR: case WB200_EW_LOGIC_XOR: arity = 2; logic = true; break;
+    case WB200_EW_LOGIC_NOT: arity = 1; logic = true; break;
+    case WB200_EW_ABS: case WB200_EW_RECIP: case WB200_EW_SQUARE: case WB200_EW_NEG: case WB200_EW_RELU: arity = 1; break;
+    case WB200_EW_SQRT: case WB200_EW_RSQRT: case WB200_EW_LOG2: case WB200_EW_LN: case WB200_EW_POW2: case WB200_EW_EXP:
+    case WB200_EW_SIN: case WB200_EW_COS: case WB200_EW_TANH: case WB200_EW_SIGMOID: case WB200_EW_SOFTPLUS:
+      arity = 1;
+      if (format != WB200_F16 && format != WB200_BF16)
+        return fail(WB200_ERR_UNSUPPORTED, "the correctly rounded function family takes F16 and BF16 operands");
+      break;
+    default: return fail(WB200_ERR_UNSUPPORTED, "elementwise operation has no formal evaluation");
+  }
+  if (count == 0) return fail(WB200_ERR_INVALID_ARGUMENT, "elementwise element count must be positive");
+  if (logic ? !(format == WB200_BOOL || is_float_format(format)) : !is_float_format(format))
+    return fail(WB200_ERR_UNSUPPORTED, "elementwise operand format must be F16, BF16 or F32 (Bool for logic)");
+  const bool extras = arity == 2 && !logic;   // only arithmetic and relation calls carry the three extra fields
+  if (!extras) rhs_unit_elements = scalar_flag = relation_numeric_or_rhs_group = 0;
+  if (scalar_flag > 1) return fail(WB200_ERR_INVALID_ARGUMENT, "elementwise scalar flag must be 0 or 1");
+  if (scalar_flag && rhs_or_scalar_bits > 0xffffffffull) return fail(WB200_ERR_INVALID_ARGUMENT, "elementwise scalar bits must fit uint32");
+  if (relation && relation_numeric_or_rhs_group > 1) return fail(WB200_ERR_INVALID_ARGUMENT, "relation numeric_result must be 0 or 1");
+  const uint32_t rhs_group = relation ? 0u : relation_numeric_or_rhs_group;
+  const int out_format = logic ? WB200_BOOL : relation ? (relation_numeric_or_rhs_group ? static_cast<int>(format) : WB200_BOOL) : static_cast<int>(format);
+  RhsBroadcast rhs;
+  uint64_t rhs_elements = count;
+  if (scalar_flag) {
+    rhs.mode = WB200_RHS_SCALAR;
+    rhs.parameter = static_cast<uint32_t>(rhs_or_scalar_bits);
+    rhs_elements = 0;
+  } else if (rhs_group) {
+    if (rhs_group < 64 || rhs_group % 64 != 0 || count % rhs_group != 0)
+      return fail(WB200_ERR_INVALID_ARGUMENT, "grouped second operand needs whole groups that are multiples of 64 elements");
+    rhs.mode = WB200_RHS_GROUP;
+    rhs.parameter = rhs_group;
+  } else if (rhs_unit_elements) {
+    rhs.mode = WB200_RHS_UNIT;
+    rhs.parameter = rhs_unit_elements;
+    rhs_elements = rhs_unit_elements;
+  }
+  auto vector = [](uint32_t fmt, uint64_t elements) {
+    wb200_tensor_desc d{};
+    d.format = static_cast<uint8_t>(fmt);
+    d.layout = WB200_LAYOUT_TENSOR;
+    d.rank = 1;
+    d.shape[0] = elements;
+    return d;
+  };
+  LayoutMap in_map, out_map, rhs_map;
+  wb200_geometry in_geo, out_geo, rhs_geo{};
+  wb200_status st;
+  if ((st = make_layout_map(vector(format, count), &in_map, &in_geo)) != WB200_OK) return st;
+  if ((st = make_layout_map(vector(out_format, count), &out_map, &out_geo)) != WB200_OK) return st;
+  if ((st = spm_range(image, lhs, in_geo.physical_bytes, "lhs")) != WB200_OK) return st;
+  if ((st = spm_range(image, dst, out_geo.physical_bytes, "destination")) != WB200_OK) return st;
+  if (arity == 2 && rhs_elements) {
+    if ((st = make_layout_map(vector(format, rhs_elements), &rhs_map, &rhs_geo)) != WB200_OK) return st;
+    if ((st = spm_range(image, rhs_or_scalar_bits, rhs_geo.physical_bytes, "rhs")) != WB200_OK) return st;
+  }
+  wb200_backend *backend = image->backend;
+  DeviceGuard guard(backend->device);
+  const uint8_t *d_lhs = image->device + (lhs - image->base);
+  const uint8_t *d_rhs = (arity == 2 && rhs_elements) ? image->device + (rhs_or_scalar_bits - image->base) : nullptr;
+  st = launch_elementwise_formal(operation, format, out_format, arity, d_lhs, d_rhs, image->device + (dst - image->base), in_map,
+                                 out_map, d_flags, image->work_stream(), rhs);
+  if (st == WB200_OK) backend->launches += 1;
+  return st;
+}
+
+// wafer_tx81_pool_{max,min,sum} on a scratch-pad image (NCx [n, h, w, c] in and out, no padding, no index output).
+wb200_status enqueue_image_pool(wb200_spm_image *image, uint32_t kind, uint64_t input, uint64_t dst, const uint32_t source_shape[4],
+                                const uint32_t destination_shape[4], const uint32_t pads[4], const uint32_t kernel_strides[4],
+                                uint32_t format, uint32_t *d_flags) {
+  if (!image || !source_shape || !destination_shape || !pads || !kernel_strides) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  int combine;
+  switch (kind) {
+    case 117: combine = WB200_EW_MAX; break;
+    case 119: combine = WB200_EW_MIN; break;
+    case 116:
+      if (format != WB200_F32) return fail(WB200_ERR_UNSUPPORTED, "plain sum pooling currently qualifies F32 accumulation only");
+      combine = WB200_EW_ADD;
+      break;
+    default: return fail(WB200_ERR_UNSUPPORTED, "pooling kind has no qualified plain numeric implementation");
+  }
+  if (!is_float_format(format)) return fail(WB200_ERR_UNSUPPORTED, "pooling operands must be F16, BF16 or F32");
+  for (int i = 0; i < 4; ++i)
+    if (pads[i] != 0) return fail(WB200_ERR_UNSUPPORTED, "plain pooling requires explicit input padding and no index output");
+  if (source_shape[0] != destination_shape[0] || source_shape[3] != destination_shape[3])
+    return fail(WB200_ERR_INVALID_ARGUMENT, "pooling must preserve batch and channel extents");
+  for (int axis = 0; axis < 2; ++axis) {
+    const uint64_t source = source_shape[axis + 1], kernel = kernel_strides[1 - axis], stride = kernel_strides[3 - axis];
+    if (kernel == 0 || stride == 0 || source < kernel || (source - kernel) / stride + 1 != destination_shape[axis + 1])
+      return fail(WB200_ERR_INVALID_ARGUMENT, "pooling result disagrees with its window geometry");
+  }
+  auto describe = [&](const uint32_t shape[4]) {
+    wb200_tensor_desc d{};
+    d.format = static_cast<uint8_t>(format);
+    d.layout = WB200_LAYOUT_NCX;
+    d.rank = 4;
+    for (int i = 0; i < 4; ++i) d.shape[i] = shape[i];
+    return d;
+  };
+  LayoutMap src_map, dst_map;
+  wb200_geometry src_geo, dst_geo;
+  wb200_status st;
+  if ((st = make_layout_map(describe(source_shape), &src_map, &src_geo)) != WB200_OK) return st;
+  if ((st = make_layout_map(describe(destination_shape), &dst_map, &dst_geo)) != WB200_OK) return st;
+  if ((st = spm_range(image, input, src_geo.physical_bytes, "pooling input")) != WB200_OK) return st;
+  if ((st = spm_range(image, dst, dst_geo.physical_bytes, "pooling destination")) != WB200_OK) return st;
+  wb200_backend *backend = image->backend;
+  DeviceGuard guard(backend->device);
+  const PoolWindow window{kernel_strides[0], kernel_strides[1], kernel_strides[2], kernel_strides[3]};
+  st = launch_pool_formal(combine, format, image->device + (input - image->base), image->device + (dst - image->base), src_map,
+                          dst_map, window, d_flags, image->work_stream());
+  if (st == WB200_OK) backend->launches += 1;
+  return st;
+}
+
 }  // namespace wb200
+
+namespace {
+// Runs `enqueue(d_flags)` with a zeroed device flag word and reads the OR of the IEEE flags back.
+template <typename Enqueue>
+wb200_status with_flag_word(wb200_spm_image *image, uint32_t *flags, Enqueue enqueue) {
+  if (!image) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  wb200_backend *backend = image->backend;
+  DeviceGuard guard(backend->device);
+  void *word;
+  wb200_status st = backend->buffer(3, sizeof(uint32_t), &word);
+  if (st != WB200_OK) return st;
+  cudaStream_t stream = image->work_stream();
+  WB200_CUDA_CHECK(cudaMemsetAsync(word, 0, sizeof(uint32_t), stream));
+  if ((st = enqueue(static_cast<uint32_t *>(word))) != WB200_OK) return st;
+  uint32_t host = 0;
+  WB200_CUDA_CHECK(cudaMemcpyAsync(&host, word, sizeof(host), cudaMemcpyDeviceToHost, stream));
+  WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
+  if (flags) *flags = host;
+  return WB200_OK;
+}
+}  // namespace
 
 extern "C" {
 
@@ -488,6 +637,23 @@ wb200_status wb200_target_call_gemm(wb200_spm_image *image, uint64_t lhs, uint64
                                        lhs_orientation, rhs_orientation, policy);
   if (st != WB200_OK) return st;
   return read_device_status(image->backend, image->backend->stream, nullptr);
+}
+
+wb200_status wb200_target_call_elementwise(wb200_spm_image *image, uint32_t operation, uint64_t lhs, uint64_t rhs_or_scalar_bits,
+                                           uint64_t dst, uint32_t count, uint32_t format, uint32_t rhs_unit_elements,
+                                           uint32_t scalar_flag, uint32_t relation_numeric_or_rhs_group, uint32_t *flags) {
+  return with_flag_word(image, flags, [&](uint32_t *word) {
+    return enqueue_image_elementwise(image, operation, lhs, rhs_or_scalar_bits, dst, count, format, rhs_unit_elements, scalar_flag,
+                                     relation_numeric_or_rhs_group, word);
+  });
+}
+
+wb200_status wb200_target_call_pool(wb200_spm_image *image, uint32_t kind, uint64_t input, uint64_t dst, const uint32_t source_shape[4],
+                                    const uint32_t destination_shape[4], const uint32_t pads[4], const uint32_t kernel_strides[4],
+                                    uint32_t format, uint32_t *flags) {
+  return with_flag_word(image, flags, [&](uint32_t *word) {
+    return enqueue_image_pool(image, kind, input, dst, source_shape, destination_shape, pads, kernel_strides, format, word);
+  });
 }
 
 }  // extern "C"

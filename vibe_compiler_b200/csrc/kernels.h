@@ -54,9 +54,21 @@ wb200_status launch_elementwise(int op, int format, int input_count, const uint8
                                 cudaStream_t stream);
 // Formal (bit-exact, NaN-canonicalising, flag-raising) elementwise family; `flags_word` collects the OR of the
 // per-element IEEE flags (bit0 invalid, bit1 divByZero, bit2 overflow, bit3 underflow, bit4 inexact).
+// How the second operand of a binary formal elementwise command is addressed: the same index as the first, a unit of
+// `parameter` elements repeated, one 64-element row per group of `parameter` elements, or the immediate bits `parameter`.
+enum { WB200_RHS_SAME = 0, WB200_RHS_UNIT = 1, WB200_RHS_GROUP = 2, WB200_RHS_SCALAR = 3 };
+struct RhsBroadcast {
+  uint32_t mode = WB200_RHS_SAME, parameter = 0;
+};
+struct PoolWindow {
+  uint32_t kernel_w, kernel_h, stride_w, stride_h;
+};
 wb200_status launch_elementwise_formal(int op, int in_format, int out_format, int input_count, const uint8_t *in0, const uint8_t *in1,
                                        uint8_t *dst, const LayoutMap &in_map, const LayoutMap &out_map, uint32_t *flags_word,
-                                       cudaStream_t stream);
+                                       cudaStream_t stream, RhsBroadcast rhs = RhsBroadcast());
+// Plain pooling over NCx [n, h, w, c] tensors: `combine` is WB200_EW_MAX, WB200_EW_MIN or WB200_EW_ADD.
+wb200_status launch_pool_formal(int combine, int format, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map,
+                                const LayoutMap &dst_map, PoolWindow window, uint32_t *flags_word, cudaStream_t stream);
 wb200_status launch_convert(int src_format, int dst_format, const uint8_t *src, uint8_t *dst,
                             const LayoutMap &src_map, const LayoutMap &dst_map, int *nan_flag,
                             cudaStream_t stream);

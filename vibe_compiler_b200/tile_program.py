@@ -50,6 +50,8 @@ class TileProgram:
         if status != abi.OK:
             raise WB200Error(status, self._lib.wb200_last_error().decode())
         self._handle = handle
+        if backend is not None:
+            backend.adopt(self)
         n_in, n_out = C.c_uint32(), C.c_uint32()
         self._check(self._lib.wb200_tile_program_tensor_count(handle, C.byref(n_in), C.byref(n_out)))
         self.inputs = [self._info(0, i) for i in range(n_in.value)]
