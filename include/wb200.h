@@ -225,6 +225,16 @@ typedef struct wb200_convert_request { /* FormalConvertOperation + operands */
 wb200_status wb200_convert(wb200_backend *backend, const wb200_convert_request *request,
                            wb200_evidence *evidence);
 
+/* The formal scalar conversion routes (lib/Wafer/Target/PhysicalTensor/TargetScalarConversion.cpp:166-361), which the
+ * reference runs when the managed backend declines: opcodes 143..174 between I16 / I32 and F16 / BF16 / F32 / TF32 and
+ * between those floating formats, `rounding_mode` 0 nearest-even, 1 toward zero, 2 toward +inf, 3 toward -inf on the routes
+ * that carry one (4, stochastic, and the zero-point routes 139..142 are WB200_ERR_UNSUPPORTED like in the reference).
+ * TF32 keeps its 19 semantic bits in storage [31:13]; other low bits set is an invalid source encoding. NaN becomes the
+ * canonical quiet NaN (invalid for a signalling one); floating -> integer refuses NaN, infinity and values outside the
+ * destination range after rounding (WB200_ERR_NAN_DOMAIN, nothing written). evidence->flags: the OR of the IEEE flags
+ * (inexact; overflow also when a directed mode returns the largest finite value; underflow by tininess after rounding). */
+wb200_status wb200_convert_formal(wb200_backend *backend, const wb200_convert_request *request, wb200_evidence *evidence);
+
 typedef struct wb200_reduce_request { /* FormalReduceOperation + operands */
   uint32_t operation; /* wb200_reduce_op */
   uint32_t dimension; /* wb200_reduce_dim */
@@ -462,6 +472,11 @@ wb200_status wb200_target_call_memset(wb200_spm_image *spm, uint64_t destination
 wb200_status wb200_target_call_elementwise(wb200_spm_image *image, uint32_t operation, uint64_t lhs, uint64_t rhs_or_scalar_bits,
                                            uint64_t dst, uint32_t count, uint32_t format, uint32_t rhs_unit_elements,
                                            uint32_t scalar_flag, uint32_t relation_numeric_or_rhs_group, uint32_t *flags);
+/* wafer_tx81_convert_<route> on a scratch-pad image (lib/Wafer/Target/TargetCall.cpp:101-106, decode
+ * lib/Wafer/Target/TargetCallDecoder.cpp:283-308): 1-D Tensor vectors of `count` elements in the route's formats, executed
+ * by the formal conversion of wb200_convert_formal. A refused element fails the call before anything is written. */
+wb200_status wb200_target_call_convert(wb200_spm_image *image, uint32_t opcode, uint64_t source, uint64_t destination, uint32_t count,
+                                       uint32_t zero_point, uint32_t rounding_mode, uint32_t *flags);
 /* wafer_tx81_pool_{sum,max,min} (kind 116 / 117 / 119; lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:466-583):
  * NCx [n, h, w, c] input and output, `kernel_strides` = {kernel w, kernel h, stride w, stride h}, all `pads` zero; each
  * output folds its window in (kh, kw) order with the formal max / min, or for sum (F32 only) adds every tap to +0.

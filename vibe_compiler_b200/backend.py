@@ -239,7 +239,9 @@ class B200TargetModelBackend:
         return BackendResult(NumericTensor(destination_template.key, out), _evidence(evidence))
 
     def execute_convert(self, opcode: int, source: NumericTensor, destination_template: NumericTensor,
-                        rounding_mode: int = 0, max_scalar_evaluations: int = 2 ** 62) -> BackendResult:
+                        rounding_mode: int = 0, max_scalar_evaluations: int = 2 ** 62, formal: bool = False) -> BackendResult:
+        """`formal` selects the bit-exact scalar conversion with the four rounding modes, integer routes and IEEE flags
+        (wb200_convert_formal) instead of the managed nearest-even floating routes."""
         req = abi.ConvertRequest()
         req.opcode, req.rounding_mode = opcode, rounding_mode
         src, tmpl = _u8(source.storage), _u8(destination_template.storage)
@@ -249,7 +251,8 @@ class B200TargetModelBackend:
         req.destination_template, req.destination_out, req.destination_bytes = tmpl.ctypes.data, out.ctypes.data, tmpl.size
         req.max_scalar_evaluations = max_scalar_evaluations
         evidence = abi.Evidence()
-        self._check(self._lib.wb200_convert(self._handle, C.byref(req), C.byref(evidence)))
+        entry = self._lib.wb200_convert_formal if formal else self._lib.wb200_convert
+        self._check(entry(self._handle, C.byref(req), C.byref(evidence)))
         return BackendResult(NumericTensor(destination_template.key, out), _evidence(evidence))
 
     def execute_reduce(self, operation: str, dimension: str, source: NumericTensor, destination_template: NumericTensor,

@@ -1,0 +1,342 @@
+// Formal scalar conversion routes on the device: the integer <-> floating and floating <-> floating conversions of
+// lib/Wafer/Target/PhysicalTensor/TargetScalarConversion.cpp:166-361 with its four deterministic rounding modes, IEEE
+// flags (tininess after rounding at unbounded exponent range, lib/Wafer/Target/PhysicalTensor/TargetFloatArithmetic.cpp:
+// 82-158; the directed-overflow completion of TargetScalarConversion.cpp:60-76, 128-136) and its refusals. Every value
+// is handled as an exact dyadic sign * significand * 2^exponent in integer arithmetic, so no rounding depends on the
+// device's floating-point unit. HBM-bound: source bytes in, destination bytes out.
+#include "backend.h"
+
+using namespace wb200;
+
+namespace {
+
+constexpr int kThreads = 256;
+enum { MODE_NEAREST_EVEN = 0, MODE_TOWARD_ZERO = 1, MODE_TOWARD_POSITIVE = 2, MODE_TOWARD_NEGATIVE = 3 };
+enum { FLAG_INVALID = 1, FLAG_OVERFLOW = 4, FLAG_UNDERFLOW = 8, FLAG_INEXACT = 16 };
+enum { ERR_NON_FINITE = 1, ERR_OUT_OF_RANGE = 2, ERR_SOURCE_ENCODING = 3 };
+
+// precision (significand bits with the hidden one), exponent bits, unused low storage bits (TF32 keeps its 19
+// semantic bits in storage [31:13]).
+struct FloatSpec {
+  int precision, exponent_bits, shift;
+};
+__host__ __device__ inline bool float_spec(int format, FloatSpec *spec) {
+  switch (format) {
+    case WB200_F16: *spec = {11, 5, 0}; return true;
+    case WB200_BF16: *spec = {8, 8, 0}; return true;
+    case WB200_F32: *spec = {24, 8, 0}; return true;
+    case WB200_TF32: *spec = {11, 8, 13}; return true;
+    default: return false;
+  }
+}
+__host__ __device__ inline int integer_width(int format) {
+  return format == WB200_I8 ? 8 : format == WB200_I16 ? 16 : format == WB200_I32 ? 32 : 0;
+}
+
+__device__ __forceinline__ int top_bit(unsigned long long value) { return 63 - __clzll(static_cast<long long>(value)); }
+
+__device__ __forceinline__ bool round_up(int mode, bool negative, unsigned long long kept, unsigned long long lost, int shift) {
+  if (lost == 0) return false;
+  switch (mode) {
+    case MODE_NEAREST_EVEN: {
+      const unsigned long long half = 1ull << (shift - 1);
+      return lost > half || (lost == half && (kept & 1));
+    }
+    case MODE_TOWARD_POSITIVE: return !negative;
+    case MODE_TOWARD_NEGATIVE: return negative;
+    default: return false;
+  }
+}
+
+// Drops `shift` low bits of `significand` under `mode`. A shift past the whole significand leaves a value below half
+// a unit, which only a directed mode rounds away from zero.
+__device__ __forceinline__ unsigned long long shift_right_rounded(unsigned long long significand, int shift, int mode, bool negative,
+                                                                  bool *inexact) {
+  if (shift <= 0) return significand << -shift;
+  if (shift > 62) {
+    *inexact = significand != 0;
+    const bool away = significand != 0 && ((mode == MODE_TOWARD_POSITIVE && !negative) || (mode == MODE_TOWARD_NEGATIVE && negative));
+    return away ? 1ull : 0ull;
+  }
+  const unsigned long long kept = significand >> shift, lost = significand & ((1ull << shift) - 1);
+  *inexact = lost != 0;
+  return kept + (round_up(mode, negative, kept, lost, shift) ? 1ull : 0ull);
+}
+
+// sign * significand * 2^exponent -> destination float bits.
+__device__ uint32_t round_to_float(bool negative, unsigned long long significand, int exponent, const FloatSpec &spec, int mode,
+                                   bool float_source, uint32_t *flags) {
+  const int fraction_bits = spec.precision - 1;
+  const uint32_t sign = negative ? 1u << (fraction_bits + spec.exponent_bits) : 0u;
+  if (significand == 0) return sign << spec.shift;
+  const int bias = (1 << (spec.exponent_bits - 1)) - 1, minimum = 1 - bias, maximum = bias;
+  const int top = top_bit(significand) + exponent;
+  // Tininess is judged after rounding to `precision` bits with an unbounded exponent range.
+  bool tiny_inexact = false;
+  unsigned long long unbounded = shift_right_rounded(significand, top_bit(significand) + 1 - spec.precision, mode, negative, &tiny_inexact);
+  int unbounded_top = top;
+  if (unbounded >> spec.precision) unbounded_top += 1;
+  const bool tiny = unbounded_top < minimum;
+  const bool exceeds_maximum = top > maximum || (top == maximum && unbounded_top > maximum) ||
+                               (top == maximum && [&] {   // magnitude above the largest finite value
+                                 const int width = top_bit(significand) + 1;
+                                 if (width <= spec.precision) return false;
+                                 const unsigned long long ones = ((1ull << spec.precision) - 1) << (width - spec.precision);
+                                 return significand > ones;
+                               }());
+  const int quantum = (top > minimum ? top : minimum) - fraction_bits;
+  bool inexact = false;
+  unsigned long long rounded = shift_right_rounded(significand, quantum - exponent, mode, negative, &inexact);
+  int biased;
+  if (rounded >> spec.precision) {   // carried into the next binade
+    rounded >>= 1;
+    biased = quantum + fraction_bits + 1 + bias;
+  } else if (rounded >> fraction_bits) {
+    biased = quantum + fraction_bits + bias;
+  } else {
+    biased = 0;                      // subnormal or zero
+  }
+  const uint32_t all_ones = (1u << spec.exponent_bits) - 1;
+  const bool returns_finite = mode == MODE_TOWARD_ZERO || (mode == MODE_TOWARD_POSITIVE && negative) || (mode == MODE_TOWARD_NEGATIVE && !negative);
+  uint32_t semantic;
+  if (biased >= static_cast<int>(all_ones)) {
+    if (returns_finite) semantic = ((all_ones - 1) << fraction_bits) | ((1u << fraction_bits) - 1);
+    else semantic = all_ones << fraction_bits;
+    *flags |= FLAG_OVERFLOW | FLAG_INEXACT;
+  } else {
+    semantic = (static_cast<uint32_t>(biased) << fraction_bits) | (static_cast<uint32_t>(rounded) & ((1u << fraction_bits) - 1));
+    if (inexact) *flags |= FLAG_INEXACT;
+    if (exceeds_maximum && returns_finite) *flags |= FLAG_OVERFLOW | FLAG_INEXACT;
+    if (float_source && inexact && tiny) *flags |= FLAG_UNDERFLOW;
+  }
+  return (sign | semantic) << spec.shift;
+}
+
+// One element. Returns false (with *error set) when the reference refuses the value.
+__device__ bool convert_scalar(int src_format, int dst_format, int mode, uint32_t bits, uint32_t *result, uint32_t *flags, int *error) {
+  FloatSpec src_spec{}, dst_spec{};
+  const bool src_float = float_spec(src_format, &src_spec), dst_float = float_spec(dst_format, &dst_spec);
+  bool negative;
+  unsigned long long significand;
+  int exponent = 0;
+  if (!src_float) {
+    const int width = integer_width(src_format);
+    const long long value = width == 32 ? static_cast<int>(bits) : static_cast<short>(bits & 0xffffu);
+    negative = value < 0;
+    significand = static_cast<unsigned long long>(negative ? -value : value);
+  } else {
+    if (src_spec.shift && (bits & ((1u << src_spec.shift) - 1))) { *error = ERR_SOURCE_ENCODING; return false; }
+    const uint32_t semantic = bits >> src_spec.shift;
+    const int fraction_bits = src_spec.precision - 1;
+    const uint32_t fraction = semantic & ((1u << fraction_bits) - 1);
+    const uint32_t field = (semantic >> fraction_bits) & ((1u << src_spec.exponent_bits) - 1);
+    negative = (semantic >> (fraction_bits + src_spec.exponent_bits)) & 1u;
+    const int bias = (1 << (src_spec.exponent_bits - 1)) - 1;
+    if (field == (1u << src_spec.exponent_bits) - 1) {
+      if (!dst_float) { *error = ERR_NON_FINITE; return false; }
+      const int dst_fraction = dst_spec.precision - 1;
+      const uint32_t all_ones = (1u << dst_spec.exponent_bits) - 1;
+      if (fraction == 0) {
+        *result = (((negative ? 1u : 0u) << (dst_fraction + dst_spec.exponent_bits)) | (all_ones << dst_fraction)) << dst_spec.shift;
+      } else {
+        if (!(fraction >> (fraction_bits - 1))) *flags |= FLAG_INVALID;   // signalling NaN
+        *result = ((all_ones << dst_fraction) | (1u << (dst_fraction - 1))) << dst_spec.shift;
+      }
+      return true;
+    }
+    significand = field ? (fraction | (1u << fraction_bits)) : fraction;
+    exponent = (field ? static_cast<int>(field) : 1) - bias - fraction_bits;
+  }
+  if (dst_float) {
+    *result = round_to_float(negative, significand, exponent, dst_spec, mode, src_float, flags);
+    return true;
+  }
+  // floating -> integer: round to an integer under `mode`, then the value must fit the signed destination width.
+  const int width = integer_width(dst_format);
+  if (significand == 0) { *result = 0; return true; }
+  if (top_bit(significand) + exponent >= 40) { *error = ERR_OUT_OF_RANGE; return false; }
+  bool inexact = false;
+  const unsigned long long magnitude = shift_right_rounded(significand, -exponent, mode, negative, &inexact);
+  const unsigned long long limit = 1ull << (width - 1);
+  if (negative ? magnitude > limit : magnitude > limit - 1) { *error = ERR_OUT_OF_RANGE; return false; }
+  if (inexact) *flags |= FLAG_INEXACT;
+  const long long value = negative ? -static_cast<long long>(magnitude) : static_cast<long long>(magnitude);
+  *result = static_cast<uint32_t>(static_cast<unsigned long long>(value) & (width == 32 ? 0xffffffffull : (1ull << width) - 1));
+  return true;
+}
+
+__device__ __forceinline__ uint32_t load_bits(const uint8_t *base, int64_t index, int bytes) {
+  return bytes == 4 ? reinterpret_cast<const uint32_t *>(base)[index] : bytes == 2 ? reinterpret_cast<const uint16_t *>(base)[index] : base[index];
+}
+__device__ __forceinline__ void store_bits(uint8_t *base, int64_t index, int bytes, uint32_t bits) {
+  if (bytes == 4) reinterpret_cast<uint32_t *>(base)[index] = bits;
+  else if (bytes == 2) reinterpret_cast<uint16_t *>(base)[index] = static_cast<uint16_t>(bits);
+  else base[index] = static_cast<uint8_t>(bits);
+}
+
+// `first_error`: the smallest (element << 8 | error code) over all refused elements; `store` = 0 only validates.
+__global__ void __launch_bounds__(kThreads)
+formal_convert_kernel(int src_format, int dst_format, int mode, const uint8_t *src, uint8_t *dst, const LayoutMap src_map,
+                      const LayoutMap dst_map, int store, uint32_t *flags_word, unsigned long long *first_error) {
+  const int src_bytes = format_bits(src_format) / 8, dst_bytes = format_bits(dst_format) / 8;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  uint32_t flags = 0;
+  unsigned long long error_key = ~0ull;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < src_map.element_count; i += stride) {
+    uint32_t result = 0, element_flags = 0;
+    int error = 0;
+    if (convert_scalar(src_format, dst_format, mode, load_bits(src, physical_index(src_map, i), src_bytes), &result, &element_flags, &error)) {
+      flags |= element_flags;
+      if (store) store_bits(dst, physical_index(dst_map, i), dst_bytes, result);
+    } else {
+      const unsigned long long key = (static_cast<unsigned long long>(i) << 8) | static_cast<unsigned>(error);
+      error_key = key < error_key ? key : error_key;
+    }
+  }
+  if (flags && store) atomicOr(flags_word, flags);
+  if (error_key != ~0ull) atomicMin(first_error, error_key);
+}
+
+struct Route {
+  int source, destination, parameter;   // parameter: 0 none, 1 rounding mode, 2 zero point
+};
+// lib/Wafer/Target/TargetFormat.cpp:163-200.
+bool find_route(uint32_t opcode, Route *route) {
+  static const Route table[36] = {
+      {WB200_I8, WB200_F16, 2},   {WB200_I8, WB200_BF16, 2},  {WB200_I8, WB200_F32, 2},    {WB200_I8, WB200_TF32, 2},
+      {WB200_I16, WB200_F16, 0},  {WB200_I16, WB200_BF16, 1}, {WB200_I16, WB200_F32, 1},   {WB200_I16, WB200_TF32, 1},
+      {WB200_I32, WB200_F16, 1},  {WB200_I32, WB200_BF16, 1}, {WB200_I32, WB200_F32, 1},   {WB200_I32, WB200_TF32, 1},
+      {WB200_BF16, WB200_I8, 0},  {WB200_BF16, WB200_I16, 1}, {WB200_BF16, WB200_I32, 1},  {WB200_BF16, WB200_F16, 0},
+      {WB200_BF16, WB200_F32, 0}, {WB200_BF16, WB200_TF32, 0}, {WB200_F16, WB200_I8, 1},   {WB200_F16, WB200_I16, 1},
+      {WB200_F16, WB200_I32, 1},  {WB200_F16, WB200_BF16, 1}, {WB200_F16, WB200_F32, 0},   {WB200_F16, WB200_TF32, 0},
+      {WB200_F32, WB200_I8, 1},   {WB200_F32, WB200_I16, 1},  {WB200_F32, WB200_I32, 1},   {WB200_F32, WB200_F16, 1},
+      {WB200_F32, WB200_BF16, 1}, {WB200_F32, WB200_TF32, 1}, {WB200_TF32, WB200_I8, 1},   {WB200_TF32, WB200_I16, 1},
+      {WB200_TF32, WB200_I32, 1}, {WB200_TF32, WB200_F16, 0}, {WB200_TF32, WB200_BF16, 1}, {WB200_TF32, WB200_F32, 0}};
+  if (opcode < 139 || opcode > 174) return false;
+  *route = table[opcode - 139];
+  return true;
+}
+
+wb200_status check_route(uint32_t opcode, uint32_t rounding_mode, Route *route, int *mode) {
+  if (!find_route(opcode, route)) return fail(WB200_ERR_INVALID_ARGUMENT, "convert opcode is not a target route");
+  if (route->parameter == 2)
+    return fail(WB200_ERR_UNSUPPORTED, "unsupported-operation: parameterless scalar conversion has inconsistent parameters (zero-point routes have no formal evaluation)");
+  if (rounding_mode > 4) return fail(WB200_ERR_INVALID_ARGUMENT, "convert rounding mode is out of range");
+  if (route->parameter == 1 && rounding_mode == 4)
+    return fail(WB200_ERR_UNSUPPORTED, "unsupported-operation: scalar conversion accepts only deterministic rounding modes");
+  *mode = route->parameter == 1 ? static_cast<int>(rounding_mode) : MODE_NEAREST_EVEN;
+  return WB200_OK;
+}
+
+wb200_status refusal(unsigned long long key) {
+  const std::string where = " at element " + std::to_string(key >> 8);
+  switch (key & 0xff) {
+    case ERR_NON_FINITE: return fail(WB200_ERR_NAN_DOMAIN, "float-to-integer-non-finite: NaN and infinity do not produce a floating-to-integer result" + where);
+    case ERR_OUT_OF_RANGE: return fail(WB200_ERR_NAN_DOMAIN, "float-to-integer-out-of-range: finite input is outside the destination integer range after rounding" + where);
+    default: return fail(WB200_ERR_INVALID_ARGUMENT, "invalid-source-encoding: non-canonical TF32 storage bits" + where);
+  }
+}
+
+// Validates every element first where the route can refuse one, so that a refused command writes nothing.
+wb200_status run_convert(wb200_backend *backend, const Route &route, int mode, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map,
+                         const LayoutMap &dst_map, cudaStream_t stream, uint32_t *flags) {
+  void *scratch;
+  wb200_status st = backend->buffer(3, 16, &scratch);
+  if (st != WB200_OK) return st;
+  uint32_t *d_flags = static_cast<uint32_t *>(scratch);
+  unsigned long long *d_error = reinterpret_cast<unsigned long long *>(static_cast<uint8_t *>(scratch) + 8);
+  WB200_CUDA_CHECK(cudaMemsetAsync(d_flags, 0, 8, stream));
+  WB200_CUDA_CHECK(cudaMemsetAsync(d_error, 0xff, 8, stream));
+  int64_t blocks = (src_map.element_count + kThreads - 1) / kThreads;
+  blocks = blocks < 1 ? 1 : blocks > 148 * 16 ? 148 * 16 : blocks;
+  const bool can_refuse = integer_width(route.destination) != 0 || route.source == WB200_TF32;
+  unsigned long long error = ~0ull;
+  if (can_refuse) {
+    formal_convert_kernel<<<static_cast<int>(blocks), kThreads, 0, stream>>>(route.source, route.destination, mode, src, dst, src_map, dst_map, 0, d_flags, d_error);
+    WB200_CUDA_CHECK(cudaGetLastError());
+    backend->launches += 1;
+    WB200_CUDA_CHECK(cudaMemcpyAsync(&error, d_error, sizeof(error), cudaMemcpyDeviceToHost, stream));
+    WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
+    if (error != ~0ull) return refusal(error);
+  }
+  formal_convert_kernel<<<static_cast<int>(blocks), kThreads, 0, stream>>>(route.source, route.destination, mode, src, dst, src_map, dst_map, 1, d_flags, d_error);
+  WB200_CUDA_CHECK(cudaGetLastError());
+  backend->launches += 1;
+  uint32_t host_flags = 0;
+  WB200_CUDA_CHECK(cudaMemcpyAsync(&host_flags, d_flags, sizeof(host_flags), cudaMemcpyDeviceToHost, stream));
+  WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
+  if (flags) *flags = host_flags;
+  return WB200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+wb200_status wb200_convert_formal(wb200_backend *backend, const wb200_convert_request *r, wb200_evidence *evidence) {
+  if (!backend || !r) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  Route route;
+  int mode;
+  wb200_status st = check_route(r->opcode, r->rounding_mode, &route, &mode);
+  if (st != WB200_OK) return st;
+  const wb200_tensor_desc &src = r->source, &dst = r->destination;
+  if (src.format != route.source || dst.format != route.destination)
+    return fail(WB200_ERR_INVALID_ARGUMENT, "source-format-mismatch: convert descriptors do not have the route's formats");
+  if (!same_shape(src, dst)) return fail(WB200_ERR_INVALID_ARGUMENT, "convert tensors do not have one same-shape domain");
+  LayoutMap src_map, dst_map;
+  wb200_geometry src_geo, dst_geo;
+  if ((st = check_storage(src, r->source_bytes, r->source_storage, "source", &src_map, &src_geo)) != WB200_OK) return st;
+  if ((st = check_storage(dst, r->destination_bytes, r->destination_template, "destination template", &dst_map, &dst_geo)) != WB200_OK) return st;
+  if (!r->destination_out) return fail(WB200_ERR_INVALID_ARGUMENT, "destination_out is null");
+  if ((st = check_budget(backend, dst_map.element_count, r->max_scalar_evaluations, r->source_bytes + r->destination_bytes,
+                         2 * static_cast<uint64_t>(dst_map.element_count))) != WB200_OK) return st;
+  DeviceGuard guard(backend->device);
+  cudaStream_t stream = backend->stream;
+  void *d_src, *d_dst;
+  if ((st = backend->buffer(0, r->source_bytes, &d_src)) != WB200_OK) return st;
+  if ((st = backend->buffer(2, r->destination_bytes, &d_dst)) != WB200_OK) return st;
+  WB200_CUDA_CHECK(cudaMemcpyAsync(d_src, r->source_storage, r->source_bytes, cudaMemcpyHostToDevice, stream));
+  WB200_CUDA_CHECK(cudaMemcpyAsync(d_dst, r->destination_template, r->destination_bytes, cudaMemcpyHostToDevice, stream));
+  uint32_t flags = 0;
+  const uint64_t before = backend->launches;
+  if ((st = run_convert(backend, route, mode, static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), src_map, dst_map, stream, &flags)) != WB200_OK) return st;
+  WB200_CUDA_CHECK(cudaMemcpyAsync(r->destination_out, d_dst, r->destination_bytes, cudaMemcpyDeviceToHost, stream));
+  WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
+  fill_evidence(backend, evidence, "sm100a-formal-convert");
+  if (evidence) {
+    evidence->scalar_evaluations = dst_map.element_count;
+    evidence->gpu_launches = static_cast<uint32_t>(backend->launches - before);
+    evidence->flags = flags;
+  }
+  return WB200_OK;
+}
+
+wb200_status wb200_target_call_convert(wb200_spm_image *image, uint32_t opcode, uint64_t source, uint64_t destination, uint32_t count,
+                                       uint32_t zero_point, uint32_t rounding_mode, uint32_t *flags) {
+  (void)zero_point;   // only the zero-point routes read it, and those are declined below
+  if (!image) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  Route route;
+  int mode;
+  wb200_status st = check_route(opcode, rounding_mode, &route, &mode);
+  if (st != WB200_OK) return st;
+  if (count == 0) return fail(WB200_ERR_INVALID_ARGUMENT, "convert element count must be positive");
+  auto vector = [&](int format) {
+    wb200_tensor_desc d{};
+    d.format = static_cast<uint8_t>(format);
+    d.layout = WB200_LAYOUT_TENSOR;
+    d.rank = 1;
+    d.shape[0] = count;
+    return d;
+  };
+  LayoutMap src_map, dst_map;
+  wb200_geometry src_geo, dst_geo;
+  if ((st = make_layout_map(vector(route.source), &src_map, &src_geo)) != WB200_OK) return st;
+  if ((st = make_layout_map(vector(route.destination), &dst_map, &dst_geo)) != WB200_OK) return st;
+  if ((st = image_range(image, source, src_geo.physical_bytes, "convert source")) != WB200_OK) return st;
+  if ((st = image_range(image, destination, dst_geo.physical_bytes, "convert destination")) != WB200_OK) return st;
+  DeviceGuard guard(image->backend->device);
+  return run_convert(image->backend, route, mode, image->device + (source - image->base), image->device + (destination - image->base), src_map,
+                     dst_map, image->work_stream(), flags);
+}
+
+}  // extern "C"

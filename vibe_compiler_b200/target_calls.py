@@ -82,3 +82,11 @@ class ScratchPad:
                                                      dst, four(source_shape), four(destination_shape), four(pads),
                                                      four(kernel_strides), format, C.byref(flags)))
         return flags.value
+
+    def convert(self, opcode: int, source: int, destination: int, count: int, *, rounding_mode: int = 0, zero_point: int = 0) -> int:
+        """`opcode`: a target convert route (139..174). Returns the OR of the IEEE flags; a refused element raises and
+        leaves the destination untouched."""
+        flags = C.c_uint32()
+        self._check(self._lib.wb200_target_call_convert(self._handle, opcode, source, destination, count, zero_point, rounding_mode,
+                                                        C.byref(flags)))
+        return flags.value
