@@ -8,6 +8,8 @@ Executes, on numpy byte images, the command list the library's device-free trace
   GEMM command (Cx operands, f32 psum)    lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:662-872 with the
                                           formal arithmetic of Reference/Numeric/FormalTensorNumeric.cpp:271-361
   Direct-DTE payload copy                 lib/Wafer/Simulator/SystemC/SystemCTargetModel.cpp:1182-1200
+  elementwise forms, convert              lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:288-464 with the
+                                          exact-rational scalar oracles (formal_scalar.py, formal_convert.py)
 Pinned by the end-to-end identity the shipped modules must satisfy: out == arg1 . arg0 of the source dot_general.
 Only tests may import this module.
 """
@@ -41,13 +43,91 @@ def _scatter(image, base, address, inner, strides, iterations, payload):
     image[index.reshape(-1)] = payload
 
 
-def replay(commands, ddr: np.ndarray, tile_count: int, spm_bytes: int = 3 << 20, threads: int = 1):
+ELEMENTWISE_NAMES = ["abs", "recip", "square", "sqrt", "rsqrt", "neg", "max", "min", "add", "sub", "mul", None, "eq", "ne", "ge", "gt", "le",
+                     "lt", "logic_not", "logic_and", "logic_or", "logic_xor", "log2", "ln", "pow2", "exp", "exp_lp", "sin", "cos", "tanh",
+                     "sigmoid", "relu", "satrelu", "leakyrelu", "softplus"]
+_FUNCTIONS = ("sqrt", "rsqrt", "log2", "ln", "pow2", "exp", "sin", "cos", "tanh", "sigmoid", "softplus")
+_BOOL = 7
+_WORD = {1: np.uint8, 2: np.uint16, 4: np.uint32}
+
+
+def _read_vector(image, address, fmt, count):
+    if fmt == _BOOL:
+        return np.unpackbits(image[address:address + (count + 7) // 8], bitorder="little")[:count].astype(np.uint64)
+    width = FORMAT_BYTES[fmt]
+    return image[address:address + count * width].view(_WORD[width]).astype(np.uint64)
+
+
+def _write_vector(image, address, fmt, values):
+    if fmt == _BOOL:
+        count = len(values)
+        bits = np.unpackbits(image[address:address + (count + 7) // 8], bitorder="little")
+        bits[:count] = np.asarray(values, dtype=np.uint8)
+        image[address:address + (count + 7) // 8] = np.packbits(bits, bitorder="little")
+        return
+    width = FORMAT_BYTES[fmt]
+    image[address:address + len(values) * width] = np.asarray(values, dtype=_WORD[width]).view(np.uint8)
+
+
+def _elementwise(image, c):
+    """One wafer_tx81_elementwise_* record -> flags. Operand expansion follows TargetModelTensorNumeric.cpp:347-372."""
+    from . import formal_scalar as F
+    a, op = c.args, ELEMENTWISE_NAMES[c.operation]
+    unary, full = c.name.endswith("_unary"), c.name.endswith("_binary")
+    rhs_at, dst_at, count, fmt = (0, a[1], a[2], a[3]) if unary else (a[1], a[2], a[3], a[4])
+    unit, scalar, last = (a[5], a[6], a[7]) if full else (0, 0, 0)
+    relation = op in ("eq", "ne", "ge", "gt", "le", "lt")
+    logic = op.startswith("logic_")
+    out_fmt = _BOOL if logic or (relation and not last) else fmt
+    name = lambda f: "bool" if f == _BOOL else FORMAT_NAMES[f]
+    lhs = _read_vector(image, a[0], fmt, count)
+    if unary:
+        rhs = np.zeros(count, dtype=np.uint64)
+    elif scalar:
+        rhs = np.full(count, rhs_at, dtype=np.uint64)
+    elif not relation and last:
+        rows = _read_vector(image, rhs_at, fmt, count)
+        rhs = np.array([rows[i // last * 64 + i % 64] for i in range(count)], dtype=np.uint64)
+    elif unit:
+        rhs = np.resize(_read_vector(image, rhs_at, fmt, unit), count)
+    else:
+        rhs = _read_vector(image, rhs_at, fmt, count)
+    out, flags = [], 0
+    for x, y in zip(lhs, rhs):
+        bits, f = F.evaluate_function(op, name(fmt), int(x)) if op in _FUNCTIONS else F.evaluate(op, name(fmt), name(out_fmt), int(x), int(y))
+        out.append(bits)
+        flags |= f
+    _write_vector(image, dst_at, out_fmt, out)
+    return flags
+
+
+def _convert(image, c):
+    from . import formal_convert as K
+    a = c.args
+    _, source, destination, _ = K.ROUTES[c.operation]
+    codes = {"i8": 0, "i16": 1, "i32": 4, "f16": 2, "bf16": 3, "f32": 5, "tf32": 6}
+    values = _read_vector(image, a[0], codes[source], a[2])
+    out, flags = [], 0
+    for x in values:
+        bits, f = K.convert(c.operation, a[4], int(x))
+        out.append(bits)
+        flags |= f
+    _write_vector(image, a[1], codes[destination], out)
+    return flags
+
+
+def replay(commands, ddr: np.ndarray, tile_count: int, spm_bytes: int = 3 << 20, threads: int = 1, report: dict = None):
     """commands: iterable of objects with .tile, .name, .args (the library's trace). `ddr` is the DDR arena (uint8,
     address DDR_BASE at index 0) with the inputs already in place; it is updated in place."""
     spm = [np.zeros(spm_bytes, dtype=np.uint8) for _ in range(tile_count)]
+    numeric_flags = 0
     for c in commands:
         a, name = c.args, c.name
-        if name in ("wafer_tx81_rdma", "wafer_tx81_wdma"):
+        if name.startswith("wafer_tx81_elementwise_"):
+            numeric_flags |= _elementwise(spm[c.tile], c)
+        elif name == "wafer_tx81_convert":
+            numeric_flags |= _convert(spm[c.tile], c)
+        elif name in ("wafer_tx81_rdma", "wafer_tx81_wdma"):
             inner, strides, iterations = a[3], a[4:7], a[7:10]
             segments = int(np.prod(iterations))
             assert inner * segments == a[2]
@@ -84,4 +164,6 @@ def replay(commands, ddr: np.ndarray, tile_count: int, spm_bytes: int = 3 << 20,
             size = binding.geometry(fout, layout, shape)["physical_bytes"]
             image[dst_at:dst_at + size] = binding.pack(fout, layout, shape, out, image[dst_at:dst_at + size].copy())
         # joins, Direct-DTE lifecycle, prepares and waits carry no data
+    if report is not None:
+        report["numeric_flags"] = numeric_flags   # OR of the IEEE flags of the elementwise / convert commands
     return ddr

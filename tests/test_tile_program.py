@@ -93,6 +93,77 @@ def test_interpreter_runs_a_small_program_and_the_cpu_replay_executes_its_trace(
     assert np.array_equal(got, matrix[::-1].T)
 
 
+# 256 f32 values: y = relu(x + 0.5) * unit[i % 4]; mask = (y >= 1) as numbers; out = bf16(y * mask) rounded toward +inf.
+NUMERIC = _module("""
+  call void @wafer_tx81_rdma(i64 %0, i64 0, i32 1024, i32 1024, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  call void @wafer_tx81_rdma(i64 %1, i64 4096, i32 16, i32 16, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  call void @wafer_tx81_ncc_join(i32 1)
+  call void @wafer_tx81_elementwise_add(i64 0, i64 1056964608, i64 8192, i32 256, i32 5, i32 0, i32 1, i32 0, i32 1)
+  call void @wafer_tx81_elementwise_relu(i64 8192, i64 8192, i32 256, i32 5, i32 1)
+  call void @wafer_tx81_elementwise_mul(i64 8192, i64 4096, i64 12288, i32 256, i32 5, i32 4, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_elementwise_ge(i64 12288, i64 1065353216, i64 16384, i32 256, i32 5, i32 0, i32 1, i32 1, i32 1)
+  call void @wafer_tx81_elementwise_ge(i64 12288, i64 1065353216, i64 24576, i32 256, i32 5, i32 0, i32 1, i32 0, i32 1)
+  call void @wafer_tx81_elementwise_logic_not(i64 24576, i64 24640, i32 256, i32 7, i32 1)
+  call void @wafer_tx81_elementwise_logic_or(i64 24576, i64 24640, i64 24704, i32 256, i32 7, i32 1)
+  call void @wafer_tx81_elementwise_mul(i64 12288, i64 16384, i64 12288, i32 256, i32 5, i32 0, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_convert_fp32_bf16(i64 12288, i64 20480, i32 256, i32 0, i32 2, i32 1)
+  call void @wafer_tx81_wdma(i64 20480, i64 %2, i32 512, i32 512, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 3, i32 0)
+  call void @wafer_tx81_wdma(i64 24704, i64 %3, i32 32, i32 32, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 8, i32 0)
+  ret void
+""", arguments="i64 %0, i64 %1, i64 %2, i64 %3", rows=[
+    '!{i64 0, !"external-input", i64 0, !"", !"f32", !"tensor", i64 1024, i64 256, !"read-only", i64 16, i64 16, i64 0}',
+    '!{i64 1, !"external-input", i64 1, !"", !"f32", !"tensor", i64 16, i64 4, !"read-only", i64 4, i64 0}',
+    '!{i64 2, !"external-output", i64 0, !"", !"bf16", !"tensor", i64 512, i64 256, !"write-only", i64 16, i64 16, i64 0}',
+    '!{i64 3, !"external-output", i64 1, !"", !"u8", !"tensor", i64 32, i64 32, !"write-only", i64 32, i64 0}'])
+
+
+def _numeric_inputs():
+    rng = np.random.default_rng(20260803)
+    x = rng.standard_normal(256).astype(np.float32) * 2
+    x[:4] = [np.float32(3.0e38), -0.5, np.float32(1e-40), 2.0]
+    return x.reshape(16, 16), np.array([1.0, -2.0, 0.333251953125, 3.0e38], dtype=np.float32)
+
+
+def _numeric_cpu_replay(program):
+    from oracle import binding, trace_replay
+    binding.build()
+    commands, _ = program.trace()
+    x, unit = _numeric_inputs()
+    places = [program.placement(False, 0), program.placement(False, 1), program.placement(True, 0), program.placement(True, 1)]
+    ddr = np.zeros(places[0]["ddr_bytes"], dtype=np.uint8)
+    for place, array in zip(places, (x, unit)):
+        at = place["address"] - place["ddr_base"]
+        ddr[at:at + array.nbytes] = array.view(np.uint8).reshape(-1)
+    report = {}
+    trace_replay.replay(commands, ddr, 1, spm_bytes=1 << 16, report=report)
+    at, mask_at = places[2]["address"] - places[2]["ddr_base"], places[3]["address"] - places[3]["ddr_base"]
+    return commands, ddr[at:at + 512].view(np.uint16).copy(), ddr[mask_at:mask_at + 32].copy(), report["numeric_flags"]
+
+
+def test_elementwise_and_convert_calls_are_traced_and_replayed_on_the_cpu():
+    program = TileProgram([NUMERIC], spm_bytes=1 << 16)
+    commands, out, mask, flags = _numeric_cpu_replay(program)
+    names = [(c.name, c.operation) for c in commands if "elementwise" in c.name or "convert" in c.name]
+    assert names == [("wafer_tx81_elementwise_binary", 8), ("wafer_tx81_elementwise_unary", 31), ("wafer_tx81_elementwise_binary", 10),
+                     ("wafer_tx81_elementwise_binary", 14), ("wafer_tx81_elementwise_binary", 14), ("wafer_tx81_elementwise_unary", 18),
+                     ("wafer_tx81_elementwise_logic", 20), ("wafer_tx81_elementwise_binary", 10), ("wafer_tx81_convert", 167)]
+    x, unit = _numeric_inputs()
+    y = np.maximum(x.reshape(-1) + np.float32(0.5), 0) * np.tile(unit, 64)
+    want = np.where(y >= 1, y, np.float32(0)).astype(np.float32)
+    assert np.all(mask == 0xff)                                     # (y >= 1) or not (y >= 1)
+    got = (out.astype(np.uint32) << 16).view(np.float32)
+    finite = np.isfinite(want)
+    assert np.all(got[finite] >= want[finite]) and np.all(got[finite] <= want[finite] * np.float32(1.0079) + 1e-30)   # rounded up
+    assert np.isinf(got[3]) and flags & 4 and flags & 16            # 2.5 * 3e38 overflows; most results are inexact
+    for body, fragment in (("call void @wafer_tx81_elementwise_frobnicate(i64 0, i64 0, i32 4, i32 5, i32 1)\n ret void", "outside the executed command set"),
+                           ("call void @wafer_tx81_elementwise_add(i64 0, i64 0, i32 4, i32 5, i32 1)\n ret void", "does not match its descriptor"),
+                           ("call void @wafer_tx81_convert_fp32_fp64(i64 0, i64 0, i32 4, i32 0, i32 0, i32 1)\n ret void", "outside the executed command set")):
+        with pytest.raises(WB200Error, match=fragment):
+            TileProgram([_module(body)])
+    with pytest.raises(WB200Error, match="outside the memory image"):
+        TileProgram([_module("call void @wafer_tx81_elementwise_abs(i64 0, i64 65536, i32 4096, i32 5, i32 1)\n ret void")], spm_bytes=1 << 16).trace()
+
+
 def test_integer_subset_semantics():
     body = """
   %a = add i32 4000000000, 100
@@ -146,7 +217,7 @@ def test_negative_numbers_take_the_signed_paths():
 @pytest.mark.parametrize("body, fragment", [
     ("  %x = fadd float 1.0, 2.0\n  ret void", "outside"),
     ("  %p = inttoptr i64 %0 to ptr\n  ret void", "outside"),
-    ("  call void @wafer_tx81_elementwise_exp(i64 0, i64 64, i32 16, i32 5, i32 0)\n  ret void", "outside the executed command set"),
+    ("  call void @wafer_tx81_reduce_sum(i64 0, i64 64, i32 0, i32 1, i32 1, i32 1, i32 16, i32 5, i32 0)\n  ret void", "outside the executed command set"),
     ("  call void @wafer_tx81_memset(i64 0, i32 0, i32 4)\n  ret void", "does not match its descriptor"),
     ("  br label %nowhere", "unknown block"),
     ("  %x = add i64 1, 2", "no terminator"),
@@ -218,6 +289,34 @@ def test_small_program_runs_on_the_device(backend):
     (out,), stats = program.run([matrix])
     assert np.array_equal(out.view(np.float32), matrix[::-1].T)
     assert stats["gpu_launches"] == 18 and stats["device_ms"] > 0
+
+
+@pytest.mark.gpu
+def test_numeric_program_matches_the_cpu_replay_bit_for_bit(backend):
+    program = TileProgram([NUMERIC], backend, spm_bytes=1 << 16)
+    _, want_out, want_mask, want_flags = _numeric_cpu_replay(program)
+    x, unit = _numeric_inputs()
+    for _ in range(2):                                              # the second run relaunches the captured graph
+        (out, mask), stats = program.run([x, unit])
+        assert np.array_equal(out.reshape(-1), want_out) and np.array_equal(mask.reshape(-1), want_mask)
+        assert stats["numeric_flags"] == want_flags and stats["commands"] == 14
+    refusing = _module("""
+  call void @wafer_tx81_rdma(i64 %0, i64 0, i32 1024, i32 1024, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  call void @wafer_tx81_convert_fp32_int32(i64 0, i64 4096, i32 256, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_wdma(i64 4096, i64 %1, i32 1024, i32 1024, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 4, i32 0)
+  ret void
+""", rows=['!{i64 0, !"external-input", i64 0, !"", !"f32", !"tensor", i64 1024, i64 256, !"read-only", i64 16, i64 16, i64 0}',
+           '!{i64 1, !"external-output", i64 0, !"", !"i32", !"tensor", i64 1024, i64 256, !"write-only", i64 16, i64 16, i64 0}'])
+    program = TileProgram([refusing], backend, spm_bytes=1 << 16)
+    values = np.arange(256, dtype=np.float32).reshape(16, 16) - 100.25
+    (out,), stats = program.run([values])
+    assert np.array_equal(out.view(np.int32).reshape(-1), np.rint(values.reshape(-1)).astype(np.int32)) and stats["numeric_flags"] == 16
+    values[7, 3] = np.inf
+    with pytest.raises(WB200Error, match="float-to-integer-non-finite.* at element 115"):
+        program.run([values])
+    values[7, 3] = 1.0
+    (out,), _ = program.run([values])                               # the program stays usable after a refused run
+    assert out.view(np.int32).reshape(-1)[115] == 1
 
 
 @pytest.mark.gpu

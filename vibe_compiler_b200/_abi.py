@@ -131,11 +131,11 @@ class ProgramStats(C.Structure):
     _fields_ = [("instructions", C.c_uint64), ("commands", C.c_uint64), ("gemm_commands", C.c_uint64), ("movement_commands", C.c_uint64),
                 ("fill_commands", C.c_uint64), ("transfer_commands", C.c_uint64), ("sync_commands", C.c_uint64),
                 ("gemm_fused_multiply_adds", C.c_uint64), ("bytes_moved", C.c_uint64), ("gpu_launches", C.c_uint64),
-                ("device_ms", C.c_float), ("reserved", C.c_uint32)]
+                ("device_ms", C.c_float), ("numeric_flags", C.c_uint32)]
 
 
 class ProgramCommand(C.Structure):
-    _fields_ = [("tile", C.c_uint32), ("kind", C.c_uint32), ("argc", C.c_uint32), ("reserved", C.c_uint32), ("args", C.c_uint64 * 17)]
+    _fields_ = [("tile", C.c_uint32), ("kind", C.c_uint32), ("argc", C.c_uint32), ("operation", C.c_uint32), ("args", C.c_uint64 * 17)]
 
 
 class Comparison(C.Structure):

@@ -269,7 +269,63 @@ wb200_status run_convert(wb200_backend *backend, const Route &route, int mode, c
   return WB200_OK;
 }
 
+
+struct ImageConvert {
+  Route route;
+  int mode;
+  LayoutMap src_map, dst_map;
+  const uint8_t *src;
+  uint8_t *dst;
+};
+
+// Route, mode and 1-D Tensor placement of one wafer_tx81_convert_<route> call on a scratch-pad image.
+wb200_status plan_image_convert(wb200_spm_image *image, uint32_t opcode, uint64_t source, uint64_t destination, uint32_t count,
+                                uint32_t rounding_mode, ImageConvert *plan) {
+  if (!image) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  wb200_status st = check_route(opcode, rounding_mode, &plan->route, &plan->mode);
+  if (st != WB200_OK) return st;
+  if (count == 0) return fail(WB200_ERR_INVALID_ARGUMENT, "convert element count must be positive");
+  auto vector = [&](int format) {
+    wb200_tensor_desc d{};
+    d.format = static_cast<uint8_t>(format);
+    d.layout = WB200_LAYOUT_TENSOR;
+    d.rank = 1;
+    d.shape[0] = count;
+    return d;
+  };
+  wb200_geometry src_geo, dst_geo;
+  if ((st = make_layout_map(vector(plan->route.source), &plan->src_map, &src_geo)) != WB200_OK) return st;
+  if ((st = make_layout_map(vector(plan->route.destination), &plan->dst_map, &dst_geo)) != WB200_OK) return st;
+  if ((st = image_range(image, source, src_geo.physical_bytes, "convert source")) != WB200_OK) return st;
+  if ((st = image_range(image, destination, dst_geo.physical_bytes, "convert destination")) != WB200_OK) return st;
+  plan->src = image->device ? image->device + (source - image->base) : nullptr;
+  plan->dst = image->device ? image->device + (destination - image->base) : nullptr;
+  return WB200_OK;
+}
+
 }  // namespace
+
+namespace wb200 {
+
+// The same call without a host round trip, for command streams that are captured into a graph: elements the reference
+// refuses are reported through `d_error` (smallest element << 8 | code) for the caller to read after the stream.
+wb200_status enqueue_image_convert(wb200_spm_image *image, uint32_t opcode, uint64_t source, uint64_t destination, uint32_t count,
+                                   uint32_t rounding_mode, bool execute, uint32_t *d_flags, unsigned long long *d_error) {
+  ImageConvert plan;
+  wb200_status st = plan_image_convert(image, opcode, source, destination, count, rounding_mode, &plan);
+  if (st != WB200_OK || !execute) return st;
+  int64_t blocks = (plan.src_map.element_count + kThreads - 1) / kThreads;
+  blocks = blocks < 1 ? 1 : blocks > 148 * 16 ? 148 * 16 : blocks;
+  formal_convert_kernel<<<static_cast<int>(blocks), kThreads, 0, image->work_stream()>>>(plan.route.source, plan.route.destination, plan.mode, plan.src,
+                                                                                         plan.dst, plan.src_map, plan.dst_map, 1, d_flags, d_error);
+  WB200_CUDA_CHECK(cudaGetLastError());
+  image->backend->launches += 1;
+  return WB200_OK;
+}
+
+wb200_status convert_refusal(unsigned long long key) { return refusal(key); }
+
+}  // namespace wb200
 
 extern "C" {
 
@@ -313,30 +369,12 @@ wb200_status wb200_convert_formal(wb200_backend *backend, const wb200_convert_re
 
 wb200_status wb200_target_call_convert(wb200_spm_image *image, uint32_t opcode, uint64_t source, uint64_t destination, uint32_t count,
                                        uint32_t zero_point, uint32_t rounding_mode, uint32_t *flags) {
-  (void)zero_point;   // only the zero-point routes read it, and those are declined below
-  if (!image) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
-  Route route;
-  int mode;
-  wb200_status st = check_route(opcode, rounding_mode, &route, &mode);
+  (void)zero_point;   // only the zero-point routes read it, and those are declined
+  ImageConvert plan;
+  wb200_status st = plan_image_convert(image, opcode, source, destination, count, rounding_mode, &plan);
   if (st != WB200_OK) return st;
-  if (count == 0) return fail(WB200_ERR_INVALID_ARGUMENT, "convert element count must be positive");
-  auto vector = [&](int format) {
-    wb200_tensor_desc d{};
-    d.format = static_cast<uint8_t>(format);
-    d.layout = WB200_LAYOUT_TENSOR;
-    d.rank = 1;
-    d.shape[0] = count;
-    return d;
-  };
-  LayoutMap src_map, dst_map;
-  wb200_geometry src_geo, dst_geo;
-  if ((st = make_layout_map(vector(route.source), &src_map, &src_geo)) != WB200_OK) return st;
-  if ((st = make_layout_map(vector(route.destination), &dst_map, &dst_geo)) != WB200_OK) return st;
-  if ((st = image_range(image, source, src_geo.physical_bytes, "convert source")) != WB200_OK) return st;
-  if ((st = image_range(image, destination, dst_geo.physical_bytes, "convert destination")) != WB200_OK) return st;
   DeviceGuard guard(image->backend->device);
-  return run_convert(image->backend, route, mode, image->device + (source - image->base), image->device + (destination - image->base), src_map,
-                     dst_map, image->work_stream(), flags);
+  return run_convert(image->backend, plan.route, plan.mode, plan.src, plan.dst, plan.src_map, plan.dst_map, image->work_stream(), flags);
 }
 
 }  // extern "C"

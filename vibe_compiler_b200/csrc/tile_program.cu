@@ -47,6 +47,7 @@ struct Inst {
   std::string target_names[2];
   int targets[2] = {-1, -1};
   int command = -1;    // Call: index into kCommands
+  uint32_t operation = 0;   // Call: elementwise operation / convert opcode of the symbol-selected families
   std::vector<Operand> args;
 };
 
@@ -82,7 +83,9 @@ struct Module {
 // ------------------------------------------------------------------------------------------------ commands
 enum Command : int {
   kNccJoin, kDteBegin, kDteBeginAfterPrepare, kDteSendPrepare, kDteSendIssue, kDteRecvPrepare, kDteWait, kDteFinish,
-  kRdma, kWdma, kGatherScatter, kMemset, kGemm, kGemmOriented, kCommandCount
+  kRdma, kWdma, kGatherScatter, kMemset, kGemm, kGemmOriented,
+  // Families whose symbol carries the operation (wafer_tx81_elementwise_<op>, wafer_tx81_convert_<route>):
+  kElementwiseUnary, kElementwiseBinary, kElementwiseLogic, kConvert, kCommandCount
 };
 struct CommandInfo {
   const char *symbol;
@@ -106,11 +109,49 @@ const CommandInfo kCommands[kCommandCount] = {
     {"wafer_tx81_memset", 5, true, false},
     {"wafer_tx81_gemm", 12, true, false},
     {"wafer_tx81_gemm_oriented", 14, true, false},
+    {"wafer_tx81_elementwise_unary", 5, true, false},     // (source, destination; count, format; worker)
+    {"wafer_tx81_elementwise_binary", 9, true, false},    // (lhs, rhs | scalar bits, destination; count, format, rhs unit, scalar flag, numeric | rhs group; worker)
+    {"wafer_tx81_elementwise_logic", 6, true, false},     // (lhs, rhs, destination; count, format; worker)
+    {"wafer_tx81_convert", 6, true, false},               // (source, destination; count, zero point, rounding mode; worker)
 };
 
-int find_command(const std::string &symbol) {
-  for (int i = 0; i < kCommandCount; ++i)
+// Spellings of lib/Wafer/Target/TargetOperation.cpp:181-251 in enumeration order (index 11 is unused) and of the convert
+// routes 139..174 (lib/Wafer/Target/TargetFormat.cpp:163-200).
+const char *const kElementwiseNames[35] = {
+    "abs", "recip", "square", "sqrt", "rsqrt", "neg", "max", "min", "add", "sub", "mul", nullptr, "eq", "ne", "ge", "gt", "le", "lt",
+    "logic_not", "logic_and", "logic_or", "logic_xor", "log2", "ln", "pow2", "exp", "exp_lp", "sin", "cos", "tanh", "sigmoid", "relu",
+    "satrelu", "leakyrelu", "softplus"};
+const char *const kConvertNames[36] = {
+    "int8_fp16", "int8_bf16", "int8_fp32", "int8_tf32", "int16_fp16", "int16_bf16", "int16_fp32", "int16_tf32", "int32_fp16",
+    "int32_bf16", "int32_fp32", "int32_tf32", "bf16_int8", "bf16_int16", "bf16_int32", "bf16_fp16", "bf16_fp32", "bf16_tf32",
+    "fp16_int8", "fp16_int16", "fp16_int32", "fp16_bf16", "fp16_fp32", "fp16_tf32", "fp32_int8", "fp32_int16", "fp32_int32",
+    "fp32_fp16", "fp32_bf16", "fp32_tf32", "tf32_int8", "tf32_int16", "tf32_int32", "tf32_fp16", "tf32_bf16", "tf32_fp32"};
+
+// -> command index, with *operation = the elementwise operation or the convert opcode for the two families.
+int find_command(const std::string &symbol, uint32_t *operation) {
+  *operation = 0;
+  for (int i = 0; i < kElementwiseUnary; ++i)
     if (symbol == kCommands[i].symbol) return i;
+  const std::string elementwise = "wafer_tx81_elementwise_", convert = "wafer_tx81_convert_";
+  if (symbol.compare(0, elementwise.size(), elementwise) == 0) {
+    const std::string name = symbol.substr(elementwise.size());
+    for (uint32_t op = 0; op < 35; ++op)
+      if (kElementwiseNames[op] && name == kElementwiseNames[op]) {
+        *operation = op;
+        const bool binary = (op >= WB200_EW_MAX && op <= WB200_EW_LT) || (op >= WB200_EW_LOGIC_AND && op <= WB200_EW_LOGIC_XOR);
+        if (!binary) return kElementwiseUnary;
+        return op >= WB200_EW_LOGIC_AND ? kElementwiseLogic : kElementwiseBinary;
+      }
+    return -1;
+  }
+  if (symbol.compare(0, convert.size(), convert) == 0) {
+    const std::string name = symbol.substr(convert.size());
+    for (uint32_t route = 0; route < 36; ++route)
+      if (name == kConvertNames[route]) {
+        *operation = 139 + route;
+        return kConvert;
+      }
+  }
   return -1;
 }
 
@@ -319,7 +360,7 @@ struct ModuleParser {
           return true;
         }
       inst->op = Op::Call;
-      inst->command = find_command(name);
+      inst->command = find_command(name, &inst->operation);
       if (inst->command < 0) { error = "call to @" + name + " is outside the executed command set"; return false; }
       const CommandInfo &info = kCommands[inst->command];
       if (static_cast<int>(inst->args.size()) != info.argc || returns != info.returns_value) {
@@ -590,6 +631,9 @@ struct wb200_tile_program {
   wb200_spm_image ddr{};
   std::vector<wb200_spm_image> spm;
   cudaEvent_t begin = nullptr, end = nullptr;
+  // Device words of the numeric commands: [0] the OR of their IEEE flags, [2..3] the first refused convert element
+  // (element << 8 | code, all ones when none). Zeroed before every run, read after it.
+  uint32_t *numeric_words = nullptr;
   // Concurrent replay: one stream per Tile, Direct-DTE transfers as event edges, the whole invocation captured once
   // into a CUDA graph and relaunched on later runs.
   std::vector<cudaStream_t> tile_streams;
@@ -677,13 +721,14 @@ wb200_status plan_addresses(wb200_tile_program *program) {
 }
 
 // ------------------------------------------------------------------------------------------------ command execution
-void record(wb200_tile_program *program, int tile, int kind, const uint64_t *args, int argc) {
+void record(wb200_tile_program *program, int tile, int kind, const uint64_t *args, int argc, uint32_t operation = 0) {
   program->stats.commands += 1;
   if (!program->trace) return;
   wb200_program_command entry{};
   entry.tile = static_cast<uint32_t>(tile);
   entry.kind = static_cast<uint32_t>(kind);
   entry.argc = static_cast<uint32_t>(argc);
+  entry.operation = operation;
   for (int i = 0; i < argc && i < 17; ++i) entry.args[i] = args[i];
   program->trace->push_back(entry);
 }
@@ -970,6 +1015,31 @@ wb200_status execute_call(wb200_tile_program *program, int tile_index, const Ins
       program->stats.bytes_moved += a[2] * (format_bits(static_cast<int>(a[3])) / 8);
       return enqueue_image_fill(spm, a[0], static_cast<uint32_t>(a[1]), static_cast<uint32_t>(a[2]), static_cast<uint32_t>(a[3]), program->execute,
                                 &program->stats.gpu_launches);
+    case kElementwiseUnary:
+    case kElementwiseBinary:
+    case kElementwiseLogic: {
+      // unary (source, destination, count, format); binary (lhs, rhs | scalar bits, destination, count, format, rhs unit,
+      // scalar flag, numeric | rhs group); logic (lhs, rhs, destination, count, format)
+      const bool unary = inst.command == kElementwiseUnary, full = inst.command == kElementwiseBinary;
+      const uint64_t rhs = unary ? 0 : a[1], destination = unary ? a[1] : a[2], count = unary ? a[2] : a[3], format = unary ? a[3] : a[4];
+      record(program, tile_index, inst.command, a, argc, inst.operation);
+      program->stats.bytes_moved += count * (format_bits(static_cast<int>(format)) / 8) * (unary ? 2 : 3);
+      const uint64_t before = program->execute ? program->backend->launches : 0;
+      st = enqueue_image_elementwise(spm, inst.operation, a[0], rhs, destination, static_cast<uint32_t>(count), static_cast<uint32_t>(format),
+                                     full ? static_cast<uint32_t>(a[5]) : 0, full ? static_cast<uint32_t>(a[6]) : 0,
+                                     full ? static_cast<uint32_t>(a[7]) : 0, program->numeric_words, program->execute);
+      if (program->execute) program->stats.gpu_launches += program->backend->launches - before;
+      return st;
+    }
+    case kConvert: {
+      // (source, destination, count, zero point, rounding mode)
+      record(program, tile_index, inst.command, a, argc, inst.operation);
+      const uint64_t before = program->execute ? program->backend->launches : 0;
+      st = enqueue_image_convert(spm, inst.operation, a[0], a[1], static_cast<uint32_t>(a[2]), static_cast<uint32_t>(a[4]), program->execute,
+                                 program->numeric_words, reinterpret_cast<unsigned long long *>(program->numeric_words + 2));
+      if (program->execute) program->stats.gpu_launches += program->backend->launches - before;
+      return st;
+    }
     case kGemm:
     case kGemmOriented: {
       // (lhs, rhs, dst, psum, m, k, n, batch, in format, out format, psum format[, lhs orientation, rhs orientation])
@@ -1244,6 +1314,7 @@ wb200_status wb200_tile_program_load(wb200_backend *backend, const char *const *
     }
     WB200_CUDA_CHECK(cudaEventCreate(&program->begin));
     WB200_CUDA_CHECK(cudaEventCreate(&program->end));
+    WB200_CUDA_CHECK(cudaMalloc(&program->numeric_words, 16));
   }
   *out = program.release();
   return WB200_OK;
@@ -1255,6 +1326,7 @@ void wb200_tile_program_destroy(wb200_tile_program *program) {
     DeviceGuard guard(program->backend->device);
     cudaStreamSynchronize(program->backend->stream);
     if (program->ddr.device) cudaFree(program->ddr.device);
+    if (program->numeric_words) cudaFree(program->numeric_words);
     for (wb200_spm_image &image : program->spm)
       if (image.device) cudaFree(image.device);
     if (program->begin) cudaEventDestroy(program->begin);
@@ -1346,6 +1418,8 @@ wb200_status wb200_tile_program_run(wb200_tile_program *program, const void *con
   static const bool graph_enabled = [] { const char *env = getenv("WB200_REPLAY_GRAPH"); return !(env && env[0] == '0'); }();
   const bool concurrent = graph_enabled && gemm_policy == WB200_GEMM_FORMAL && !program->tile_streams.empty();
   if (concurrent && !program->graph && (st = capture_invocation(program)) != WB200_OK) return st;
+  WB200_CUDA_CHECK(cudaMemsetAsync(program->numeric_words, 0, 8, stream));
+  WB200_CUDA_CHECK(cudaMemsetAsync(program->numeric_words + 2, 0xff, 8, stream));
   WB200_CUDA_CHECK(cudaEventRecord(program->begin, stream));
   if (concurrent) {
     WB200_CUDA_CHECK(cudaGraphLaunch(program->graph, stream));
@@ -1361,6 +1435,13 @@ wb200_status wb200_tile_program_run(wb200_tile_program *program, const void *con
   float elapsed = 0.f;
   WB200_CUDA_CHECK(cudaEventElapsedTime(&elapsed, program->begin, program->end));
   program->stats.device_ms = elapsed;
+  uint32_t numeric[4] = {0, 0, 0, 0};
+  WB200_CUDA_CHECK(cudaMemcpyAsync(numeric, program->numeric_words, sizeof(numeric), cudaMemcpyDeviceToHost, stream));
+  WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
+  unsigned long long refused;
+  memcpy(&refused, numeric + 2, sizeof(refused));
+  if (refused != ~0ull) return convert_refusal(refused);   // a failed command fails the invocation; outputs are not returned
+  program->stats.numeric_flags = numeric[0];
   for (size_t i = 0; i < program->outputs.size(); ++i) {
     const ExternalTensor &tensor = program->outputs[i];
     if (!outputs[i]) return fail(WB200_ERR_INVALID_ARGUMENT, "null output tensor");

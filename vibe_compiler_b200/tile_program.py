@@ -16,7 +16,6 @@ import numpy as np
 from . import _abi as abi
 from .backend import B200TargetModelBackend, WB200Error
 
-_NUMPY_BYTES = {abi.F16: 2, abi.BF16: 2, abi.F32: 4}
 
 
 @dataclass
@@ -32,10 +31,11 @@ class Command:
     tile: int
     name: str
     args: tuple
+    operation: int = 0   # elementwise operation / convert opcode of the wafer_tx81_elementwise_* / convert_* families
 
 
 def _stats(raw: abi.ProgramStats) -> dict:
-    return {name: getattr(raw, name) for name, _ in abi.ProgramStats._fields_ if name != "reserved"}
+    return {name: getattr(raw, name) for name, _ in abi.ProgramStats._fields_ }
 
 
 class TileProgram:
@@ -94,7 +94,7 @@ class TileProgram:
         for r in records:
             if r.kind not in names:
                 names[r.kind] = self._lib.wb200_program_command_name(r.kind).decode()
-            commands.append(Command(r.tile, names[r.kind], tuple(r.args[i] for i in range(r.argc))))
+            commands.append(Command(r.tile, names[r.kind], tuple(r.args[i] for i in range(r.argc)), r.operation))
         return commands, _stats(stats)
 
     def run(self, inputs: Sequence[np.ndarray], gemm_policy: int = abi.GEMM_FORMAL):
@@ -115,7 +115,9 @@ class TileProgram:
         self._check(self._lib.wb200_tile_program_run(self._handle, in_ptrs, out_ptrs, gemm_policy, C.byref(stats)))
         shaped = []
         for raw, info in zip(outs, self.outputs):
-            width = _NUMPY_BYTES.get(info.format, 1)
+            elements = int(np.prod(info.shape)) if info.shape else 1
+            width = info.compact_bytes // elements if elements and info.compact_bytes % elements == 0 else 1
+            width = width if width in (1, 2, 4) else 1
             dtype = {1: np.uint8, 2: np.uint16, 4: np.uint32}[width]
             shaped.append(raw.view(dtype).reshape(info.shape))
         return shaped, _stats(stats)
