@@ -251,6 +251,13 @@ typedef struct wb200_reduce_request { /* FormalReduceOperation + operands */
 wb200_status wb200_reduce(wb200_backend *backend, const wb200_reduce_request *request,
                           wb200_evidence *evidence);
 
+/* The formal reduction (lib/Wafer/Simulator/Reference/Numeric/FormalTensorNumeric.cpp:363-425, step
+ * Reference/Formal/FormalNumericReduce.cpp:12-67), which the reference runs when the managed backend declines: the same domain
+ * as wb200_reduce, but every output folds its inputs in row-major order from +0 (sum) or -inf / +inf (max / min) with the formal
+ * add / maximum / minimum, so a NaN input gives the canonical quiet NaN (invalid for a signalling one) instead of a refusal,
+ * max / min order -0 below +0, and evidence->flags carries the OR of the IEEE flags of all steps. */
+wb200_status wb200_reduce_formal(wb200_backend *backend, const wb200_reduce_request *request, wb200_evidence *evidence);
+
 /* ------------------------------------------------------------------ region level */
 /* Regions are what a run of lowered commands computes as a whole. Buffers are compact row-major.
  * `memory` selects where ALL data pointers of the call live. With WB200_MEM_HOST the call stages
@@ -477,6 +484,11 @@ wb200_status wb200_target_call_elementwise(wb200_spm_image *image, uint32_t oper
  * by the formal conversion of wb200_convert_formal. A refused element fails the call before anything is written. */
 wb200_status wb200_target_call_convert(wb200_spm_image *image, uint32_t opcode, uint64_t source, uint64_t destination, uint32_t count,
                                        uint32_t zero_point, uint32_t rounding_mode, uint32_t *flags);
+/* wafer_tx81_reduce_{sum,max,min} (operation 0 / 1 / 2) on a scratch-pad image (lib/Wafer/Target/TargetCall.cpp:97-99, decode
+ * lib/Wafer/Target/TargetCallDecoder.cpp:270-281): NCx [n, h, w, c] input, NCx destination with the reduced dimensions set to 1,
+ * `dimension` a wb200_reduce_dimension; executed by the formal fold of wb200_reduce_formal. */
+wb200_status wb200_target_call_reduce(wb200_spm_image *image, uint32_t operation, uint64_t source, uint64_t destination, uint32_t dimension,
+                                      const uint32_t nhwc[4], uint32_t format, uint32_t *flags);
 /* wafer_tx81_pool_{sum,max,min} (kind 116 / 117 / 119; lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:466-583):
  * NCx [n, h, w, c] input and output, `kernel_strides` = {kernel w, kernel h, stride w, stride h}, all `pads` zero; each
  * output folds its window in (kh, kw) order with the formal max / min, or for sum (F32 only) adds every tap to +0.
@@ -496,9 +508,9 @@ wb200_status wb200_target_call_pool(wb200_spm_image *image, uint32_t kind, uint6
  * receiver is prepared (lib/Wafer/Simulator/SystemC/SystemCTargetModel.cpp:1110-1200). Entry arguments are planned
  * from the !wafer.target.entry_arguments metadata (lib/Wafer/CodeGen/LLVM/TargetLLVMTranslation.cpp:119-140) into one
  * DDR arena. Calls outside {ncc_join, direct_dte_{begin,begin_after_prepare,send_prepare,send_issue,recv_prepare,wait,
- * finish}, rdma, wdma, gather_scatter, memset, gemm, gemm_oriented, elementwise_<op>, convert_<route>} are rejected with
- * WB200_ERR_UNSUPPORTED at load. Elementwise and convert calls run the formal families of wb200_target_call_elementwise /
- * wb200_target_call_convert; a convert element the reference refuses fails the run after the command stream has drained. */
+ * finish}, rdma, wdma, gather_scatter, memset, gemm, gemm_oriented, elementwise_<op>, convert_<route>, reduce_<op>} are rejected with
+ * WB200_ERR_UNSUPPORTED at load. Elementwise, convert and reduce calls run the formal families of wb200_target_call_elementwise /
+ * wb200_target_call_convert / wb200_target_call_reduce; a convert element the reference refuses fails the run after the command stream has drained. */
 typedef struct wb200_tile_program wb200_tile_program;
 typedef struct wb200_program_stats {
   uint64_t instructions;              /* IR instructions interpreted */

@@ -116,6 +116,33 @@ def _convert(image, c):
     return flags
 
 
+def _reduce(image, c):
+    """One wafer_tx81_reduce record (NCx in and out) -> flags; the fold of FormalTensorNumeric.cpp:363-425."""
+    from . import formal_scalar as F
+    a = c.args
+    shape, fmt = [int(v) for v in a[3:7]], FORMAT_NAMES[a[7]]
+    reduced = {0: (3,), 1: (2,), 2: (1,), 3: (0,), 4: (1, 2), 5: (1, 2, 3)}[a[2]]
+    out_shape = [1 if d in reduced else e for d, e in enumerate(shape)]
+    size = binding.geometry(fmt, "ncx", shape)["physical_bytes"]
+    compact = binding.unpack(fmt, "ncx", shape, image[a[0]:a[0] + size]).reshape(-1)
+    infinity = {"f16": 0x7c00, "bf16": 0x7f80, "f32": 0x7f800000}[fmt]
+    identity = {0: 0, 1: infinity | (0x80000000 if fmt == "f32" else 0x8000), 2: infinity}[c.operation]
+    op = {0: "add", 1: "max", 2: "min"}[c.operation]
+    out = [identity] * int(np.prod(out_shape))
+    kept_shape = [e for d, e in enumerate(shape) if d not in reduced]
+    flags = 0
+    for index, bits in enumerate(compact):
+        coordinates = np.unravel_index(index, shape)
+        kept = [x for d, x in enumerate(coordinates) if d not in reduced]
+        destination = int(np.ravel_multi_index(kept, kept_shape)) if kept else 0
+        out[destination], f = F.evaluate(op, fmt, fmt, int(out[destination]), int(bits))
+        flags |= f
+    out_size = binding.geometry(fmt, "ncx", out_shape)["physical_bytes"]
+    packed = binding.pack(fmt, "ncx", out_shape, np.array(out, dtype=compact.dtype), image[a[1]:a[1] + out_size].copy())
+    image[a[1]:a[1] + out_size] = packed
+    return flags
+
+
 def replay(commands, ddr: np.ndarray, tile_count: int, spm_bytes: int = 3 << 20, threads: int = 1, report: dict = None):
     """commands: iterable of objects with .tile, .name, .args (the library's trace). `ddr` is the DDR arena (uint8,
     address DDR_BASE at index 0) with the inputs already in place; it is updated in place."""
@@ -127,6 +154,8 @@ def replay(commands, ddr: np.ndarray, tile_count: int, spm_bytes: int = 3 << 20,
             numeric_flags |= _elementwise(spm[c.tile], c)
         elif name == "wafer_tx81_convert":
             numeric_flags |= _convert(spm[c.tile], c)
+        elif name == "wafer_tx81_reduce":
+            numeric_flags |= _reduce(spm[c.tile], c)
         elif name in ("wafer_tx81_rdma", "wafer_tx81_wdma"):
             inner, strides, iterations = a[3], a[4:7], a[7:10]
             segments = int(np.prod(iterations))

@@ -170,6 +170,7 @@ SIGNATURES = {
     "wb200_convert": (C.c_int, [C.c_void_p, C.POINTER(ConvertRequest), C.POINTER(Evidence)]),
     "wb200_convert_formal": (C.c_int, [C.c_void_p, C.POINTER(ConvertRequest), C.POINTER(Evidence)]),
     "wb200_reduce": (C.c_int, [C.c_void_p, C.POINTER(ReduceRequest), C.POINTER(Evidence)]),
+    "wb200_reduce_formal": (C.c_int, [C.c_void_p, C.POINTER(ReduceRequest), C.POINTER(Evidence)]),
     "wb200_attention_fa": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams)]),
     "wb200_attention_fd": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams), C.c_uint32]),
     "wb200_attention_fd_static": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams), C.c_uint32]),
@@ -195,6 +196,7 @@ SIGNATURES = {
     "wb200_tile_program_run": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_uint32, C.POINTER(ProgramStats)]),
     "wb200_target_call_elementwise": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint64] + [C.c_uint32] * 5 + [C.POINTER(C.c_uint32)]),
     "wb200_target_call_convert": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32)]),
+    "wb200_target_call_reduce": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint32, _U32x3, C.c_uint32, C.POINTER(C.c_uint32)]),
     "wb200_target_call_pool": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, _U32x3, _U32x3, _U32x3, _U32x3, C.c_uint32, C.POINTER(C.c_uint32)]),
     "wb200_compare": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_void_p, C.c_void_p, C.c_uint32, C.c_double, C.c_double,
                                 C.c_uint32, C.c_double, C.c_double, C.POINTER(Comparison)]),

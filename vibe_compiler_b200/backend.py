@@ -256,7 +256,7 @@ class B200TargetModelBackend:
         return BackendResult(NumericTensor(destination_template.key, out), _evidence(evidence))
 
     def execute_reduce(self, operation: str, dimension: str, source: NumericTensor, destination_template: NumericTensor,
-                       max_scalar_evaluations: int = 2 ** 62) -> BackendResult:
+                       max_scalar_evaluations: int = 2 ** 62, formal: bool = False) -> BackendResult:
         req = abi.ReduceRequest()
         req.operation, req.dimension = abi.REDUCE_OPS[operation], abi.REDUCE_DIMS[dimension]
         src, tmpl = _u8(source.storage), _u8(destination_template.storage)
@@ -266,7 +266,8 @@ class B200TargetModelBackend:
         req.destination_template, req.destination_out, req.destination_bytes = tmpl.ctypes.data, out.ctypes.data, tmpl.size
         req.max_scalar_evaluations = max_scalar_evaluations
         evidence = abi.Evidence()
-        self._check(self._lib.wb200_reduce(self._handle, C.byref(req), C.byref(evidence)))
+        entry = self._lib.wb200_reduce_formal if formal else self._lib.wb200_reduce
+        self._check(entry(self._handle, C.byref(req), C.byref(evidence)))
         return BackendResult(NumericTensor(destination_template.key, out), _evidence(evidence))
 
     # ------------------------------------------------------------------ region level

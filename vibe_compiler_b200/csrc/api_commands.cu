@@ -309,18 +309,17 @@ wb200_status wb200_convert(wb200_backend *backend, const wb200_convert_request *
   return WB200_OK;
 }
 
-wb200_status wb200_reduce(wb200_backend *backend, const wb200_reduce_request *r, wb200_evidence *evidence) {
-  if (!backend || !r) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
-  const wb200_tensor_desc &in = r->input, &dst = r->destination;
-  if ((r->operation != WB200_RED_SUM && r->operation != WB200_RED_MAX && r->operation != WB200_RED_MIN) ||
-      !is_float_format(in.format) || dst.format != in.format || (r->operation == WB200_RED_SUM && in.format != WB200_F32))
+// Domain, reduced dimensions (getTargetReduceLogicalDimensions, lib/Wafer/Target/TargetOperation.cpp:93-139) and the
+// destination shape of a reduce command. Bit d of *mask = logical dimension d is reduced.
+static wb200_status plan_reduce(const wb200_tensor_desc &in, const wb200_tensor_desc &dst, uint32_t operation, uint32_t dimension, uint32_t *mask_out) {
+  if ((operation != WB200_RED_SUM && operation != WB200_RED_MAX && operation != WB200_RED_MIN) ||
+      !is_float_format(in.format) || dst.format != in.format || (operation == WB200_RED_SUM && in.format != WB200_F32))
     return fail(WB200_ERR_UNSUPPORTED, "reduce requires F32 sum or F16/BF16/F32 max/min");
-  // getTargetReduceLogicalDimensions (lib/Wafer/Target/TargetOperation.cpp:93-139)
   const int rank = in.rank;
   uint32_t mask = 0;
   auto trailing = [&](int index) { if (index < rank) mask |= 1u << (rank - 1 - index); return index < rank; };
   bool ok = true;
-  switch (r->dimension) {
+  switch (dimension) {
     case WB200_RED_TRAILING0: ok = trailing(0); break;
     case WB200_RED_TRAILING1: ok = trailing(1); break;
     case WB200_RED_TRAILING2: ok = trailing(2); break;
@@ -335,8 +334,17 @@ wb200_status wb200_reduce(wb200_backend *backend, const wb200_reduce_request *r,
     const uint64_t expected = (mask & (1u << d)) ? 1 : in.shape[d];
     if (dst.shape[d] != expected) return fail(WB200_ERR_INVALID_ARGUMENT, "reduce destination shape does not match the reduced input shape");
   }
+  *mask_out = mask;
+  return WB200_OK;
+}
+
+wb200_status wb200_reduce(wb200_backend *backend, const wb200_reduce_request *r, wb200_evidence *evidence) {
+  if (!backend || !r) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  const wb200_tensor_desc &in = r->input, &dst = r->destination;
+  uint32_t mask = 0;
+  wb200_status st = plan_reduce(in, dst, r->operation, r->dimension, &mask);
+  if (st != WB200_OK) return st;
   LayoutMap in_map, dst_map; wb200_geometry in_geo, dst_geo;
-  wb200_status st;
   if ((st = check_storage(in, r->input_bytes, r->input_storage, "input", &in_map, &in_geo)) != WB200_OK) return st;
   if ((st = check_storage(dst, r->destination_bytes, r->destination_template, "destination template", &dst_map, &dst_geo)) != WB200_OK) return st;
   if (!r->destination_out) return fail(WB200_ERR_INVALID_ARGUMENT, "destination_out is null");
@@ -360,6 +368,39 @@ wb200_status wb200_reduce(wb200_backend *backend, const wb200_reduce_request *r,
   WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
   fill_evidence(backend, evidence, "sm100a-non-nan-f16-bf16-f32-tensor");
   if (evidence) { evidence->scalar_evaluations = in_map.element_count; evidence->gpu_launches = 1; }
+  return WB200_OK;
+}
+
+wb200_status wb200_reduce_formal(wb200_backend *backend, const wb200_reduce_request *r, wb200_evidence *evidence) {
+  if (!backend || !r) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  const wb200_tensor_desc &in = r->input, &dst = r->destination;
+  uint32_t mask = 0;
+  wb200_status st = plan_reduce(in, dst, r->operation, r->dimension, &mask);
+  if (st != WB200_OK) return st;
+  LayoutMap in_map, dst_map; wb200_geometry in_geo, dst_geo;
+  if ((st = check_storage(in, r->input_bytes, r->input_storage, "input", &in_map, &in_geo)) != WB200_OK) return st;
+  if ((st = check_storage(dst, r->destination_bytes, r->destination_template, "destination template", &dst_map, &dst_geo)) != WB200_OK) return st;
+  if (!r->destination_out) return fail(WB200_ERR_INVALID_ARGUMENT, "destination_out is null");
+  if ((st = check_budget(backend, in_map.element_count, r->max_scalar_evaluations, r->input_bytes + r->destination_bytes,
+                         static_cast<uint64_t>(in_map.element_count) + dst_map.element_count)) != WB200_OK) return st;
+  DeviceGuard guard(backend->device);
+  cudaStream_t stream = backend->stream;
+  void *d_src, *d_dst, *d_flags;
+  if ((st = backend->buffer(0, r->input_bytes, &d_src)) != WB200_OK) return st;
+  if ((st = backend->buffer(2, r->destination_bytes, &d_dst)) != WB200_OK) return st;
+  if ((st = backend->buffer(3, sizeof(uint32_t), &d_flags)) != WB200_OK) return st;
+  WB200_CUDA_CHECK(cudaMemcpyAsync(d_src, r->input_storage, r->input_bytes, cudaMemcpyHostToDevice, stream));
+  WB200_CUDA_CHECK(cudaMemcpyAsync(d_dst, r->destination_template, r->destination_bytes, cudaMemcpyHostToDevice, stream));
+  WB200_CUDA_CHECK(cudaMemsetAsync(d_flags, 0, sizeof(uint32_t), stream));
+  if ((st = launch_reduce_formal(r->operation, in.format, static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), in_map, dst_map, mask,
+                                 static_cast<uint32_t *>(d_flags), stream)) != WB200_OK) return st;
+  backend->launches += 1;
+  uint32_t flags = 0;
+  WB200_CUDA_CHECK(cudaMemcpyAsync(&flags, d_flags, sizeof(flags), cudaMemcpyDeviceToHost, stream));
+  WB200_CUDA_CHECK(cudaMemcpyAsync(r->destination_out, d_dst, r->destination_bytes, cudaMemcpyDeviceToHost, stream));
+  WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
+  fill_evidence(backend, evidence, "sm100a-formal-reduce");
+  if (evidence) { evidence->scalar_evaluations = in_map.element_count; evidence->gpu_launches = 1; evidence->flags = flags; }
   return WB200_OK;
 }
 
@@ -556,6 +597,40 @@ wb200_status enqueue_image_elementwise(wb200_spm_image *image, uint32_t operatio
   return st;
 }
 
+// wafer_tx81_reduce_{sum,max,min} on a scratch-pad image: NCx [n, h, w, c] input, NCx destination with the reduced
+// dimensions set to 1 (lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:586-660), executed by the formal fold.
+wb200_status enqueue_image_reduce(wb200_spm_image *image, uint32_t operation, uint64_t source, uint64_t destination, uint32_t dimension,
+                                  const uint32_t nhwc[4], uint32_t format, uint32_t *d_flags, bool execute) {
+  if (!image || !nhwc) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  wb200_tensor_desc in{}, dst{};
+  in.format = dst.format = static_cast<uint8_t>(format);
+  in.layout = dst.layout = WB200_LAYOUT_NCX;
+  in.rank = dst.rank = 4;
+  for (int i = 0; i < 4; ++i) in.shape[i] = dst.shape[i] = nhwc[i];
+  // the destination keeps every dimension the command does not reduce
+  uint32_t mask = 0;
+  {
+    const int trailing[6][3] = {{0, -1, -1}, {1, -1, -1}, {2, -1, -1}, {3, -1, -1}, {2, 1, -1}, {2, 1, 0}};
+    if (dimension > 5) return fail(WB200_ERR_INVALID_ARGUMENT, "reduce dimension is invalid for the fixed ABI shape");
+    for (int i = 0; i < 3; ++i)
+      if (trailing[dimension][i] >= 0) dst.shape[3 - trailing[dimension][i]] = 1;
+  }
+  wb200_status st = plan_reduce(in, dst, operation, dimension, &mask);
+  if (st != WB200_OK) return st;
+  LayoutMap in_map, dst_map;
+  wb200_geometry in_geo, dst_geo;
+  if ((st = make_layout_map(in, &in_map, &in_geo)) != WB200_OK) return st;
+  if ((st = make_layout_map(dst, &dst_map, &dst_geo)) != WB200_OK) return st;
+  if ((st = spm_range(image, source, in_geo.physical_bytes, "reduce source")) != WB200_OK) return st;
+  if ((st = spm_range(image, destination, dst_geo.physical_bytes, "reduce destination")) != WB200_OK) return st;
+  if (!execute) return WB200_OK;
+  DeviceGuard guard(image->backend->device);
+  st = launch_reduce_formal(operation, format, image->device + (source - image->base), image->device + (destination - image->base), in_map,
+                            dst_map, mask, d_flags, image->work_stream());
+  if (st == WB200_OK) image->backend->launches += 1;
+  return st;
+}
+
 // wafer_tx81_pool_{max,min,sum} on a scratch-pad image (NCx [n, h, w, c] in and out, no padding, no index output).
 wb200_status enqueue_image_pool(wb200_spm_image *image, uint32_t kind, uint64_t input, uint64_t dst, const uint32_t source_shape[4],
                                 const uint32_t destination_shape[4], const uint32_t pads[4], const uint32_t kernel_strides[4],
@@ -646,6 +721,13 @@ wb200_status wb200_target_call_elementwise(wb200_spm_image *image, uint32_t oper
   return with_flag_word(image, flags, [&](uint32_t *word) {
     return enqueue_image_elementwise(image, operation, lhs, rhs_or_scalar_bits, dst, count, format, rhs_unit_elements, scalar_flag,
                                      relation_numeric_or_rhs_group, word, true);
+  });
+}
+
+wb200_status wb200_target_call_reduce(wb200_spm_image *image, uint32_t operation, uint64_t source, uint64_t destination, uint32_t dimension,
+                                      const uint32_t nhwc[4], uint32_t format, uint32_t *flags) {
+  return with_flag_word(image, flags, [&](uint32_t *word) {
+    return enqueue_image_reduce(image, operation, source, destination, dimension, nhwc, format, word, true);
   });
 }
 

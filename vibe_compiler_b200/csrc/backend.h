@@ -82,6 +82,8 @@ wb200_status enqueue_image_gemm(wb200_spm_image *image, uint64_t lhs, uint64_t r
 wb200_status enqueue_image_elementwise(wb200_spm_image *image, uint32_t operation, uint64_t lhs, uint64_t rhs_or_scalar_bits,
                                        uint64_t dst, uint32_t count, uint32_t format, uint32_t rhs_unit_elements,
                                        uint32_t scalar_flag, uint32_t relation_numeric_or_rhs_group, uint32_t *d_flags, bool execute);
+wb200_status enqueue_image_reduce(wb200_spm_image *image, uint32_t operation, uint64_t source, uint64_t destination, uint32_t dimension,
+                                  const uint32_t nhwc[4], uint32_t format, uint32_t *d_flags, bool execute);
 wb200_status enqueue_image_pool(wb200_spm_image *image, uint32_t kind, uint64_t input, uint64_t dst, const uint32_t source_shape[4],
                                 const uint32_t destination_shape[4], const uint32_t pads[4], const uint32_t kernel_strides[4],
                                 uint32_t format, uint32_t *d_flags);

@@ -66,6 +66,9 @@ struct PoolWindow {
 wb200_status launch_elementwise_formal(int op, int in_format, int out_format, int input_count, const uint8_t *in0, const uint8_t *in1,
                                        uint8_t *dst, const LayoutMap &in_map, const LayoutMap &out_map, uint32_t *flags_word,
                                        cudaStream_t stream, RhsBroadcast rhs = RhsBroadcast());
+// Formal reduction: NaN-canonicalising, flag-raising fold in row-major input order (bit d of `reduced_mask` = dimension d reduced).
+wb200_status launch_reduce_formal(int op, int format, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map, const LayoutMap &dst_map,
+                                  uint32_t reduced_mask, uint32_t *flags_word, cudaStream_t stream);
 // Plain pooling over NCx [n, h, w, c] tensors: `combine` is WB200_EW_MAX, WB200_EW_MIN or WB200_EW_ADD.
 wb200_status launch_pool_formal(int combine, int format, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map,
                                 const LayoutMap &dst_map, PoolWindow window, uint32_t *flags_word, cudaStream_t stream);

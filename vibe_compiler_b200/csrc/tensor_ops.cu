@@ -389,6 +389,49 @@ formal_elementwise_kernel(int op, int in_format, int out_format, int input_count
   if (flags) atomicOr(flags_word, flags);
 }
 
+// Formal reduction (lib/Wafer/Simulator/Reference/Numeric/FormalTensorNumeric.cpp:363-425 with the step of
+// Reference/Formal/FormalNumericReduce.cpp:12-67): every output starts from +0 (sum) or -inf / +inf (max / min) and folds
+// its inputs in row-major input order with the formal add / maximum / minimum, so NaNs are canonicalised instead of
+// refused and the IEEE flags of every step are collected. One thread per output element.
+__global__ void __launch_bounds__(kThreads)
+formal_reduce_kernel(int op, int format, const uint8_t *src, uint8_t *dst, const LayoutMap src_map, const LayoutMap dst_map,
+                     uint32_t reduced_mask, uint32_t *flags_word) {
+  const int64_t out_index = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (out_index >= dst_map.element_count) return;
+  const int rank = src_map.rank;
+  int64_t coord[WB200_MAX_RANK];
+  int64_t stride[WB200_MAX_RANK];
+  int64_t s = 1;
+  for (int d = rank - 1; d >= 0; --d) { stride[d] = s; s *= src_map.shape[d]; }
+  int64_t remaining = out_index;
+  int64_t reduced_count = 1;
+  for (int d = rank - 1; d >= 0; --d) {
+    if (reduced_mask & (1u << d)) { coord[d] = 0; reduced_count *= src_map.shape[d]; continue; }
+    coord[d] = remaining % src_map.shape[d];
+    remaining /= src_map.shape[d];
+  }
+  const uint32_t infinity = format == WB200_F32 ? 0x7f800000u : format == WB200_BF16 ? 0x7f80u : 0x7c00u;
+  const uint32_t sign = format == WB200_F32 ? 0x80000000u : 0x8000u;
+  uint32_t accumulator = op == WB200_RED_SUM ? 0u : op == WB200_RED_MAX ? (infinity | sign) : infinity;
+  const int combine = op == WB200_RED_SUM ? WB200_EW_ADD : op == WB200_RED_MAX ? WB200_EW_MAX : WB200_EW_MIN;
+  uint32_t flags = 0;
+  for (int64_t r = 0; r < reduced_count; ++r) {
+    int64_t rest = r;
+    for (int d = rank - 1; d >= 0; --d) {
+      if (!(reduced_mask & (1u << d))) continue;
+      coord[d] = rest % src_map.shape[d];
+      rest /= src_map.shape[d];
+    }
+    int64_t linear = 0;
+    for (int d = 0; d < rank; ++d) linear += coord[d] * stride[d];
+    uint32_t step_flags = 0;
+    accumulator = formal_scalar(combine, format, format, accumulator, load_element_bits(src, physical_index(src_map, linear), format), &step_flags);
+    flags |= step_flags;
+  }
+  store_element_bits(dst, physical_index(dst_map, out_index), format, accumulator);
+  if (flags) atomicOr(flags_word, flags);
+}
+
 // Plain pooling (lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:466-583): every output folds its window in
 // (kh, kw) order with the formal max / min / add, so the roundings and the raised flags are those of the reference's
 // window-by-window elementwise passes. Sum starts from +0 and adds every tap; max / min start from the first tap.
@@ -454,6 +497,14 @@ wb200_status launch_elementwise_formal(int op, int in_format, int out_format, in
                                        cudaStream_t stream, RhsBroadcast rhs) {
   formal_elementwise_kernel<<<grid_for((out_map.element_count + 7) / 8), kThreads, 0, stream>>>(op, in_format, out_format, input_count, in0, in1,
                                                                                                 dst, in_map, out_map, rhs, flags_word);
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
+}
+
+wb200_status launch_reduce_formal(int op, int format, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map, const LayoutMap &dst_map,
+                                  uint32_t reduced_mask, uint32_t *flags_word, cudaStream_t stream) {
+  const int64_t blocks = (dst_map.element_count + kThreads - 1) / kThreads;
+  formal_reduce_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), kThreads, 0, stream>>>(op, format, src, dst, src_map, dst_map, reduced_mask, flags_word);
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }

@@ -85,7 +85,7 @@ enum Command : int {
   kNccJoin, kDteBegin, kDteBeginAfterPrepare, kDteSendPrepare, kDteSendIssue, kDteRecvPrepare, kDteWait, kDteFinish,
   kRdma, kWdma, kGatherScatter, kMemset, kGemm, kGemmOriented,
   // Families whose symbol carries the operation (wafer_tx81_elementwise_<op>, wafer_tx81_convert_<route>):
-  kElementwiseUnary, kElementwiseBinary, kElementwiseLogic, kConvert, kCommandCount
+  kElementwiseUnary, kElementwiseBinary, kElementwiseLogic, kConvert, kReduce, kCommandCount
 };
 struct CommandInfo {
   const char *symbol;
@@ -113,6 +113,7 @@ const CommandInfo kCommands[kCommandCount] = {
     {"wafer_tx81_elementwise_binary", 9, true, false},    // (lhs, rhs | scalar bits, destination; count, format, rhs unit, scalar flag, numeric | rhs group; worker)
     {"wafer_tx81_elementwise_logic", 6, true, false},     // (lhs, rhs, destination; count, format; worker)
     {"wafer_tx81_convert", 6, true, false},               // (source, destination; count, zero point, rounding mode; worker)
+    {"wafer_tx81_reduce", 9, true, false},                // (source, destination; dimension, n, h, w, c, format; worker)
 };
 
 // Spellings of lib/Wafer/Target/TargetOperation.cpp:181-251 in enumeration order (index 11 is unused) and of the convert
@@ -132,7 +133,16 @@ int find_command(const std::string &symbol, uint32_t *operation) {
   *operation = 0;
   for (int i = 0; i < kElementwiseUnary; ++i)
     if (symbol == kCommands[i].symbol) return i;
-  const std::string elementwise = "wafer_tx81_elementwise_", convert = "wafer_tx81_convert_";
+  const std::string elementwise = "wafer_tx81_elementwise_", convert = "wafer_tx81_convert_", reduce = "wafer_tx81_reduce_";
+  if (symbol.compare(0, reduce.size(), reduce) == 0) {   // lib/Wafer/Target/TargetOperation.cpp stringifyTargetReduceOperation
+    const char *const names[4] = {"sum", "max", "min", "avg"};
+    for (uint32_t op = 0; op < 4; ++op)
+      if (symbol.substr(reduce.size()) == names[op]) {
+        *operation = op;
+        return kReduce;
+      }
+    return -1;
+  }
   if (symbol.compare(0, elementwise.size(), elementwise) == 0) {
     const std::string name = symbol.substr(elementwise.size());
     for (uint32_t op = 0; op < 35; ++op)
@@ -1028,6 +1038,16 @@ wb200_status execute_call(wb200_tile_program *program, int tile_index, const Ins
       st = enqueue_image_elementwise(spm, inst.operation, a[0], rhs, destination, static_cast<uint32_t>(count), static_cast<uint32_t>(format),
                                      full ? static_cast<uint32_t>(a[5]) : 0, full ? static_cast<uint32_t>(a[6]) : 0,
                                      full ? static_cast<uint32_t>(a[7]) : 0, program->numeric_words, program->execute);
+      if (program->execute) program->stats.gpu_launches += program->backend->launches - before;
+      return st;
+    }
+    case kReduce: {
+      // (source, destination, dimension, n, h, w, c, format)
+      const uint32_t nhwc[4] = {static_cast<uint32_t>(a[3]), static_cast<uint32_t>(a[4]), static_cast<uint32_t>(a[5]), static_cast<uint32_t>(a[6])};
+      record(program, tile_index, inst.command, a, argc, inst.operation);
+      const uint64_t before = program->execute ? program->backend->launches : 0;
+      st = enqueue_image_reduce(spm, inst.operation, a[0], a[1], static_cast<uint32_t>(a[2]), nhwc, static_cast<uint32_t>(a[7]),
+                                program->numeric_words, program->execute);
       if (program->execute) program->stats.gpu_launches += program->backend->launches - before;
       return st;
     }

@@ -90,3 +90,11 @@ class ScratchPad:
         self._check(self._lib.wb200_target_call_convert(self._handle, opcode, source, destination, count, zero_point, rounding_mode,
                                                         C.byref(flags)))
         return flags.value
+
+    def reduce(self, operation: str, source: int, destination: int, dimension: str, nhwc: Sequence[int], format: int) -> int:
+        """`operation`: "sum" | "max" | "min"; `dimension`: a key of _abi.REDUCE_DIMS. Returns the OR of the IEEE flags."""
+        flags = C.c_uint32()
+        shape = (C.c_uint32 * 4)(*[int(v) for v in nhwc])
+        self._check(self._lib.wb200_target_call_reduce(self._handle, abi.REDUCE_OPS[operation], source, destination,
+                                                       abi.REDUCE_DIMS[dimension], shape, format, C.byref(flags)))
+        return flags.value
