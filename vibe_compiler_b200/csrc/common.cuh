@@ -72,6 +72,53 @@ __device__ __forceinline__ void store_element_bits(uint8_t *base, int64_t index,
     reinterpret_cast<uint16_t *>(base)[index] = static_cast<uint16_t>(bits);
 }
 
+// Eight consecutive elements of `bytes` bytes each, starting at element 8 * group of a 16-byte aligned base, moved
+// with 128-bit accesses (two for 4-byte elements, one for 2-byte elements, a 64-bit one for bytes).
+__device__ __forceinline__ void load_group8(const uint8_t *base, int64_t group, int bytes, uint32_t (&v)[8]) {
+  if (bytes == 4) {
+    const uint4 lo = reinterpret_cast<const uint4 *>(base)[2 * group], hi = reinterpret_cast<const uint4 *>(base)[2 * group + 1];
+    v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w; v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+  } else if (bytes == 2) {
+    const uint4 w = reinterpret_cast<const uint4 *>(base)[group];
+    v[0] = w.x & 0xffffu; v[1] = w.x >> 16; v[2] = w.y & 0xffffu; v[3] = w.y >> 16;
+    v[4] = w.z & 0xffffu; v[5] = w.z >> 16; v[6] = w.w & 0xffffu; v[7] = w.w >> 16;
+  } else {
+    const uint2 w = reinterpret_cast<const uint2 *>(base)[group];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[i] = (w.x >> (8 * i)) & 0xffu; v[4 + i] = (w.y >> (8 * i)) & 0xffu; }
+  }
+}
+__device__ __forceinline__ void store_group8(uint8_t *base, int64_t group, int bytes, const uint32_t (&v)[8]) {
+  if (bytes == 4) {
+    reinterpret_cast<uint4 *>(base)[2 * group] = make_uint4(v[0], v[1], v[2], v[3]);
+    reinterpret_cast<uint4 *>(base)[2 * group + 1] = make_uint4(v[4], v[5], v[6], v[7]);
+  } else if (bytes == 2) {
+    reinterpret_cast<uint4 *>(base)[group] = make_uint4((v[0] & 0xffffu) | (v[1] << 16), (v[2] & 0xffffu) | (v[3] << 16),
+                                                        (v[4] & 0xffffu) | (v[5] << 16), (v[6] & 0xffffu) | (v[7] << 16));
+  } else {
+    uint2 w = make_uint2(0u, 0u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { w.x |= (v[i] & 0xffu) << (8 * i); w.y |= (v[4 + i] & 0xffu) << (8 * i); }
+    reinterpret_cast<uint2 *>(base)[group] = w;
+  }
+}
+// True when every pointer is 16-byte aligned (null pointers count as aligned).
+inline bool all_aligned16(const void *a, const void *b = nullptr, const void *c = nullptr) {
+  return ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c)) & 15) == 0;
+}
+
+// ORs every thread's `flags` into *word with one global atomic per block (a single hot word would otherwise serialise
+// one atomic per thread). Every thread of the block must reach the call.
+__device__ __forceinline__ void merge_block_flags(uint32_t *word, uint32_t flags) {
+  __shared__ uint32_t block_flags;
+  if (threadIdx.x == 0) block_flags = 0;
+  __syncthreads();
+  flags = __reduce_or_sync(0xffffffffu, flags);
+  if ((threadIdx.x & 31) == 0 && flags) atomicOr(&block_flags, flags);
+  __syncthreads();
+  if (threadIdx.x == 0 && block_flags) atomicOr(word, block_flags);
+}
+
 // ---------------------------------------------------------------- physical layout
 // Plain-data form of the reference's PhysicalTensorGeometry + offset calculator
 // (lib/Wafer/Target/PhysicalTensor/PhysicalLayout.cpp:111-310), usable on host and device.
@@ -104,6 +151,18 @@ __host__ __device__ inline int64_t physical_index(const LayoutMap &map, int64_t 
   if (c < full_c)
     return base + (c / map.c_block) * (map.block_outer_elements * map.c_block) + outer * map.c_block +
            c % map.c_block;
+  return base + map.cx_blocks * map.block_outer_elements * map.c_block + outer * map.c0 + (c - full_c);
+}
+
+// The same placement for a rank-4 NCx tensor [n, h, w, c] from its coordinates, without the divisions by the shape:
+// `outer` = h * W + w. Agrees with physical_index(map, ((n * H + h) * W + w) * C + c).
+__host__ __device__ inline int64_t physical_index_nhwc(const LayoutMap &map, int64_t n, int64_t outer, int64_t c) {
+  const int64_t full_c = map.cx_blocks * map.c_block;
+  const int64_t base = n * map.outer_slice_stride;
+  if (c < full_c) {
+    const int64_t block = c / map.c_block;
+    return base + block * (map.block_outer_elements * map.c_block) + outer * map.c_block + (c - block * map.c_block);
+  }
   return base + map.cx_blocks * map.block_outer_elements * map.c_block + outer * map.c0 + (c - full_c);
 }
 

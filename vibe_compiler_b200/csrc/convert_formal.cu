@@ -33,13 +33,14 @@ __host__ __device__ inline int integer_width(int format) {
   return format == WB200_I8 ? 8 : format == WB200_I16 ? 16 : format == WB200_I32 ? 32 : 0;
 }
 
-__device__ __forceinline__ int top_bit(unsigned long long value) { return 63 - __clzll(static_cast<long long>(value)); }
+// Every significand of these routes fits 32 bits (|i32| <= 2^31, float significands < 2^24).
+__device__ __forceinline__ int top_bit(uint32_t value) { return 31 - __clz(static_cast<int>(value)); }
 
-__device__ __forceinline__ bool round_up(int mode, bool negative, unsigned long long kept, unsigned long long lost, int shift) {
+__device__ __forceinline__ bool round_up(int mode, bool negative, uint32_t kept, uint32_t lost, int shift) {
   if (lost == 0) return false;
   switch (mode) {
     case MODE_NEAREST_EVEN: {
-      const unsigned long long half = 1ull << (shift - 1);
+      const uint32_t half = 1u << (shift - 1);
       return lost > half || (lost == half && (kept & 1));
     }
     case MODE_TOWARD_POSITIVE: return !negative;
@@ -50,21 +51,23 @@ __device__ __forceinline__ bool round_up(int mode, bool negative, unsigned long 
 
 // Drops `shift` low bits of `significand` under `mode`. A shift past the whole significand leaves a value below half
 // a unit, which only a directed mode rounds away from zero.
-__device__ __forceinline__ unsigned long long shift_right_rounded(unsigned long long significand, int shift, int mode, bool negative,
-                                                                  bool *inexact) {
-  if (shift <= 0) return significand << -shift;
-  if (shift > 62) {
+__device__ __forceinline__ uint32_t shift_right_rounded(uint32_t significand, int shift, int mode, bool negative, bool *inexact) {
+  if (shift <= 0) return significand << -shift;   // callers only widen into fewer than 32 bits
+  if (shift > 31) {                               // the whole significand lies below half a unit (it has at most 32 bits)
     *inexact = significand != 0;
-    const bool away = significand != 0 && ((mode == MODE_TOWARD_POSITIVE && !negative) || (mode == MODE_TOWARD_NEGATIVE && negative));
-    return away ? 1ull : 0ull;
+    const bool above_half = shift == 32 && significand > 0x80000000u;   // only a full-width significand can pass one half
+    const bool tie = shift == 32 && significand == 0x80000000u;
+    const bool away = significand != 0 && ((mode == MODE_TOWARD_POSITIVE && !negative) || (mode == MODE_TOWARD_NEGATIVE && negative) ||
+                                           (mode == MODE_NEAREST_EVEN && above_half && !tie));
+    return away ? 1u : 0u;
   }
-  const unsigned long long kept = significand >> shift, lost = significand & ((1ull << shift) - 1);
+  const uint32_t kept = significand >> shift, lost = significand & ((1u << shift) - 1u);
   *inexact = lost != 0;
-  return kept + (round_up(mode, negative, kept, lost, shift) ? 1ull : 0ull);
+  return kept + (round_up(mode, negative, kept, lost, shift) ? 1u : 0u);
 }
 
 // sign * significand * 2^exponent -> destination float bits.
-__device__ uint32_t round_to_float(bool negative, unsigned long long significand, int exponent, const FloatSpec &spec, int mode,
+__device__ __forceinline__ uint32_t round_to_float(bool negative, uint32_t significand, int exponent, const FloatSpec &spec, int mode,
                                    bool float_source, uint32_t *flags) {
   const int fraction_bits = spec.precision - 1;
   const uint32_t sign = negative ? 1u << (fraction_bits + spec.exponent_bits) : 0u;
@@ -73,7 +76,7 @@ __device__ uint32_t round_to_float(bool negative, unsigned long long significand
   const int top = top_bit(significand) + exponent;
   // Tininess is judged after rounding to `precision` bits with an unbounded exponent range.
   bool tiny_inexact = false;
-  unsigned long long unbounded = shift_right_rounded(significand, top_bit(significand) + 1 - spec.precision, mode, negative, &tiny_inexact);
+  uint32_t unbounded = shift_right_rounded(significand, top_bit(significand) + 1 - spec.precision, mode, negative, &tiny_inexact);
   int unbounded_top = top;
   if (unbounded >> spec.precision) unbounded_top += 1;
   const bool tiny = unbounded_top < minimum;
@@ -81,12 +84,12 @@ __device__ uint32_t round_to_float(bool negative, unsigned long long significand
                                (top == maximum && [&] {   // magnitude above the largest finite value
                                  const int width = top_bit(significand) + 1;
                                  if (width <= spec.precision) return false;
-                                 const unsigned long long ones = ((1ull << spec.precision) - 1) << (width - spec.precision);
+                                 const uint32_t ones = ((1u << spec.precision) - 1u) << (width - spec.precision);
                                  return significand > ones;
                                }());
   const int quantum = (top > minimum ? top : minimum) - fraction_bits;
   bool inexact = false;
-  unsigned long long rounded = shift_right_rounded(significand, quantum - exponent, mode, negative, &inexact);
+  uint32_t rounded = shift_right_rounded(significand, quantum - exponent, mode, negative, &inexact);
   int biased;
   if (rounded >> spec.precision) {   // carried into the next binade
     rounded >>= 1;
@@ -104,7 +107,7 @@ __device__ uint32_t round_to_float(bool negative, unsigned long long significand
     else semantic = all_ones << fraction_bits;
     *flags |= FLAG_OVERFLOW | FLAG_INEXACT;
   } else {
-    semantic = (static_cast<uint32_t>(biased) << fraction_bits) | (static_cast<uint32_t>(rounded) & ((1u << fraction_bits) - 1));
+    semantic = (static_cast<uint32_t>(biased) << fraction_bits) | (rounded & ((1u << fraction_bits) - 1));
     if (inexact) *flags |= FLAG_INEXACT;
     if (exceeds_maximum && returns_finite) *flags |= FLAG_OVERFLOW | FLAG_INEXACT;
     if (float_source && inexact && tiny) *flags |= FLAG_UNDERFLOW;
@@ -113,17 +116,17 @@ __device__ uint32_t round_to_float(bool negative, unsigned long long significand
 }
 
 // One element. Returns false (with *error set) when the reference refuses the value.
-__device__ bool convert_scalar(int src_format, int dst_format, int mode, uint32_t bits, uint32_t *result, uint32_t *flags, int *error) {
+__device__ __forceinline__ bool convert_scalar(int src_format, int dst_format, int mode, uint32_t bits, uint32_t *result, uint32_t *flags, int *error) {
   FloatSpec src_spec{}, dst_spec{};
   const bool src_float = float_spec(src_format, &src_spec), dst_float = float_spec(dst_format, &dst_spec);
   bool negative;
-  unsigned long long significand;
+  uint32_t significand;
   int exponent = 0;
   if (!src_float) {
     const int width = integer_width(src_format);
     const long long value = width == 32 ? static_cast<int>(bits) : static_cast<short>(bits & 0xffffu);
     negative = value < 0;
-    significand = static_cast<unsigned long long>(negative ? -value : value);
+    significand = static_cast<uint32_t>(negative ? -value : value);
   } else {
     if (src_spec.shift && (bits & ((1u << src_spec.shift) - 1))) { *error = ERR_SOURCE_ENCODING; return false; }
     const uint32_t semantic = bits >> src_spec.shift;
@@ -154,14 +157,14 @@ __device__ bool convert_scalar(int src_format, int dst_format, int mode, uint32_
   // floating -> integer: round to an integer under `mode`, then the value must fit the signed destination width.
   const int width = integer_width(dst_format);
   if (significand == 0) { *result = 0; return true; }
-  if (top_bit(significand) + exponent >= 40) { *error = ERR_OUT_OF_RANGE; return false; }
+  if (top_bit(significand) + exponent >= 32) { *error = ERR_OUT_OF_RANGE; return false; }   // |value| >= 2^32 fits no route
   bool inexact = false;
-  const unsigned long long magnitude = shift_right_rounded(significand, -exponent, mode, negative, &inexact);
-  const unsigned long long limit = 1ull << (width - 1);
-  if (negative ? magnitude > limit : magnitude > limit - 1) { *error = ERR_OUT_OF_RANGE; return false; }
+  const uint32_t magnitude = shift_right_rounded(significand, -exponent, mode, negative, &inexact);
+  const uint32_t limit = 1u << (width - 1);
+  if (negative ? magnitude > limit : magnitude > limit - 1u) { *error = ERR_OUT_OF_RANGE; return false; }
   if (inexact) *flags |= FLAG_INEXACT;
-  const long long value = negative ? -static_cast<long long>(magnitude) : static_cast<long long>(magnitude);
-  *result = static_cast<uint32_t>(static_cast<unsigned long long>(value) & (width == 32 ? 0xffffffffull : (1ull << width) - 1));
+  const uint32_t value = negative ? 0u - magnitude : magnitude;   // two's complement
+  *result = width == 32 ? value : value & ((1u << width) - 1u);
   return true;
 }
 
@@ -175,26 +178,99 @@ __device__ __forceinline__ void store_bits(uint8_t *base, int64_t index, int byt
 }
 
 // `first_error`: the smallest (element << 8 | error code) over all refused elements; `store` = 0 only validates.
+// One thread per 8 consecutive elements. kLinear: both tensors in Tensor / NTensor layout; with `vector` set (16-byte
+// aligned pointers) full groups move with 128-bit accesses.
+// kSrc >= 0 fixes both formats at compile time (every route in linear layout), which folds the generic scalar routine.
+template <bool kLinear, int kSrc, int kDst>
 __global__ void __launch_bounds__(kThreads)
-formal_convert_kernel(int src_format, int dst_format, int mode, const uint8_t *src, uint8_t *dst, const LayoutMap src_map,
-                      const LayoutMap dst_map, int store, uint32_t *flags_word, unsigned long long *first_error) {
+formal_convert_kernel(int runtime_src, int runtime_dst, int mode, const uint8_t *src, uint8_t *dst, const LayoutMap src_map,
+                      const LayoutMap dst_map, int store, int vector, uint32_t *flags_word, unsigned long long *first_error) {
+  const int src_format = kSrc >= 0 ? kSrc : runtime_src, dst_format = kSrc >= 0 ? kDst : runtime_dst;
   const int src_bytes = format_bits(src_format) / 8, dst_bytes = format_bits(dst_format) / 8;
+  const int64_t total = src_map.element_count, groups = (total + 7) / 8;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   uint32_t flags = 0;
   unsigned long long error_key = ~0ull;
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < src_map.element_count; i += stride) {
-    uint32_t result = 0, element_flags = 0;
-    int error = 0;
-    if (convert_scalar(src_format, dst_format, mode, load_bits(src, physical_index(src_map, i), src_bytes), &result, &element_flags, &error)) {
-      flags |= element_flags;
-      if (store) store_bits(dst, physical_index(dst_map, i), dst_bytes, result);
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < groups; g += stride) {
+    const int64_t first = g * 8;
+    const int count = total - first < 8 ? static_cast<int>(total - first) : 8;
+    const bool wide = kLinear && vector && count == 8;
+    uint32_t in[8], out[8];
+    if (wide) load_group8(src, g, src_bytes, in);
+    bool refused = false;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      if (e >= count) break;
+      const int64_t i = first + e;
+      if (!wide) in[e] = load_bits(src, kLinear ? i : physical_index(src_map, i), src_bytes);
+      uint32_t element_flags = 0;
+      int error = 0;
+      out[e] = 0;
+      if (convert_scalar(src_format, dst_format, mode, in[e], &out[e], &element_flags, &error)) {
+        flags |= element_flags;
+      } else {
+        refused = true;
+        const unsigned long long key = (static_cast<unsigned long long>(i) << 8) | static_cast<unsigned>(error);
+        error_key = key < error_key ? key : error_key;
+      }
+    }
+    if (!store) continue;
+    if (wide && !refused) {
+      store_group8(dst, g, dst_bytes, out);
     } else {
-      const unsigned long long key = (static_cast<unsigned long long>(i) << 8) | static_cast<unsigned>(error);
-      error_key = key < error_key ? key : error_key;
+      // a group with a refused element keeps that element's destination as it was (the host fails the command anyway)
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (e >= count) break;
+        uint32_t unused_result, unused_flags = 0;
+        int error = 0;
+        if (refused && !convert_scalar(src_format, dst_format, mode, in[e], &unused_result, &unused_flags, &error)) continue;
+        store_bits(dst, kLinear ? first + e : physical_index(dst_map, first + e), dst_bytes, out[e]);
+      }
     }
   }
-  if (flags && store) atomicOr(flags_word, flags);
+  merge_block_flags(flags_word, store ? flags : 0u);
   if (error_key != ~0ull) atomicMin(first_error, error_key);
+}
+
+// Picks the linear, format-specialised instantiation when both layouts allow it.
+void launch_formal_convert(cudaStream_t stream, int src_format, int dst_format, int mode, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map,
+                           const LayoutMap &dst_map, int store, uint32_t *flags_word, unsigned long long *first_error) {
+  auto linear_layout = [](const LayoutMap &m) { return m.layout == WB200_LAYOUT_TENSOR || m.layout == WB200_LAYOUT_NTENSOR; };
+  int64_t blocks = ((src_map.element_count + 7) / 8 + kThreads - 1) / kThreads;
+  blocks = blocks < 1 ? 1 : blocks > 148 * 32 ? 148 * 32 : blocks;
+  const int grid = static_cast<int>(blocks);
+  const int vector = all_aligned16(src, dst);
+#define WB200_CV_LAUNCH(LINEAR, SRC, DST, VECTOR)                                                                                      \
+  formal_convert_kernel<LINEAR, SRC, DST><<<grid, kThreads, 0, stream>>>(src_format, dst_format, mode, src, dst, src_map, dst_map, store, VECTOR, \
+                                                                         flags_word, first_error)
+#define WB200_CV_TO(SRC)                                                                \
+  switch (dst_format) {                                                                 \
+    case WB200_F16: WB200_CV_LAUNCH(true, SRC, WB200_F16, vector); return;              \
+    case WB200_BF16: WB200_CV_LAUNCH(true, SRC, WB200_BF16, vector); return;            \
+    case WB200_F32: WB200_CV_LAUNCH(true, SRC, WB200_F32, vector); return;              \
+    case WB200_TF32: WB200_CV_LAUNCH(true, SRC, WB200_TF32, vector); return;            \
+    case WB200_I8: WB200_CV_LAUNCH(true, SRC, WB200_I8, vector); return;                \
+    case WB200_I16: WB200_CV_LAUNCH(true, SRC, WB200_I16, vector); return;              \
+    case WB200_I32: WB200_CV_LAUNCH(true, SRC, WB200_I32, vector); return;              \
+    default: break;                                                                     \
+  }
+  if (linear_layout(src_map) && linear_layout(dst_map)) {
+    switch (src_format) {
+      case WB200_I16: WB200_CV_TO(WB200_I16) break;
+      case WB200_I32: WB200_CV_TO(WB200_I32) break;
+      case WB200_F16: WB200_CV_TO(WB200_F16) break;
+      case WB200_BF16: WB200_CV_TO(WB200_BF16) break;
+      case WB200_F32: WB200_CV_TO(WB200_F32) break;
+      case WB200_TF32: WB200_CV_TO(WB200_TF32) break;
+      default: break;
+    }
+    WB200_CV_LAUNCH(true, -1, 0, vector);
+    return;
+  }
+  WB200_CV_LAUNCH(false, -1, 0, 0);
+#undef WB200_CV_TO
+#undef WB200_CV_LAUNCH
 }
 
 struct Route {
@@ -247,19 +323,17 @@ wb200_status run_convert(wb200_backend *backend, const Route &route, int mode, c
   unsigned long long *d_error = reinterpret_cast<unsigned long long *>(static_cast<uint8_t *>(scratch) + 8);
   WB200_CUDA_CHECK(cudaMemsetAsync(d_flags, 0, 8, stream));
   WB200_CUDA_CHECK(cudaMemsetAsync(d_error, 0xff, 8, stream));
-  int64_t blocks = (src_map.element_count + kThreads - 1) / kThreads;
-  blocks = blocks < 1 ? 1 : blocks > 148 * 16 ? 148 * 16 : blocks;
   const bool can_refuse = integer_width(route.destination) != 0 || route.source == WB200_TF32;
   unsigned long long error = ~0ull;
   if (can_refuse) {
-    formal_convert_kernel<<<static_cast<int>(blocks), kThreads, 0, stream>>>(route.source, route.destination, mode, src, dst, src_map, dst_map, 0, d_flags, d_error);
+    launch_formal_convert(stream, route.source, route.destination, mode, src, dst, src_map, dst_map, 0, d_flags, d_error);
     WB200_CUDA_CHECK(cudaGetLastError());
     backend->launches += 1;
     WB200_CUDA_CHECK(cudaMemcpyAsync(&error, d_error, sizeof(error), cudaMemcpyDeviceToHost, stream));
     WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
     if (error != ~0ull) return refusal(error);
   }
-  formal_convert_kernel<<<static_cast<int>(blocks), kThreads, 0, stream>>>(route.source, route.destination, mode, src, dst, src_map, dst_map, 1, d_flags, d_error);
+  launch_formal_convert(stream, route.source, route.destination, mode, src, dst, src_map, dst_map, 1, d_flags, d_error);
   WB200_CUDA_CHECK(cudaGetLastError());
   backend->launches += 1;
   uint32_t host_flags = 0;
@@ -314,10 +388,7 @@ wb200_status enqueue_image_convert(wb200_spm_image *image, uint32_t opcode, uint
   ImageConvert plan;
   wb200_status st = plan_image_convert(image, opcode, source, destination, count, rounding_mode, &plan);
   if (st != WB200_OK || !execute) return st;
-  int64_t blocks = (plan.src_map.element_count + kThreads - 1) / kThreads;
-  blocks = blocks < 1 ? 1 : blocks > 148 * 16 ? 148 * 16 : blocks;
-  formal_convert_kernel<<<static_cast<int>(blocks), kThreads, 0, image->work_stream()>>>(plan.route.source, plan.route.destination, plan.mode, plan.src,
-                                                                                         plan.dst, plan.src_map, plan.dst_map, 1, d_flags, d_error);
+  launch_formal_convert(image->work_stream(), plan.route.source, plan.route.destination, plan.mode, plan.src, plan.dst, plan.src_map, plan.dst_map, 1, d_flags, d_error);
   WB200_CUDA_CHECK(cudaGetLastError());
   image->backend->launches += 1;
   return WB200_OK;
