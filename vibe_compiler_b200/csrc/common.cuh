@@ -160,7 +160,7 @@ __host__ __device__ inline int64_t physical_index_nhwc(const LayoutMap &map, int
   const int64_t full_c = map.cx_blocks * map.c_block;
   const int64_t base = n * map.outer_slice_stride;
   if (c < full_c) {
-    const int64_t block = c / map.c_block;
+    const uint32_t block = static_cast<uint32_t>(c) / static_cast<uint32_t>(map.c_block);   // channel counts fit 32 bits
     return base + block * (map.block_outer_elements * map.c_block) + outer * map.c_block + (c - block * map.c_block);
   }
   return base + map.cx_blocks * map.block_outer_elements * map.c_block + outer * map.c0 + (c - full_c);

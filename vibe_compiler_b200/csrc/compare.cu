@@ -478,6 +478,22 @@ extern "C" wb200_status wb200_compare(wb200_backend *backend, uint32_t format, u
       query.shift = query.kind == 0 ? abs_shift[pass] : ulp_shift[pass < 3 ? pass : 2];
       query.prefix = prefix[q];
     }
+    // p99 and p99.9 ask the same question until their prefixes part: count it once and share the histogram
+    int source_of[kQueries];
+    for (int q = 0; q < kQueries; ++q) {
+      source_of[q] = q;
+      for (int earlier = 0; earlier < q; ++earlier)
+        if (params.query[q].active && params.query[earlier].active && params.query[q].kind == params.query[earlier].kind &&
+            params.query[q].shift == params.query[earlier].shift && params.query[q].prefix == params.query[earlier].prefix) {
+          source_of[q] = earlier;
+          break;
+        }
+    }
+    bool wanted[kQueries];
+    for (int q = 0; q < kQueries; ++q) {
+      wanted[q] = params.query[q].active != 0;
+      if (source_of[q] != q) params.query[q].active = 0;
+    }
     WB200_CUDA_CHECK(cudaMemsetAsync(d_histogram, 0, histogram_bytes, stream));
     if (pass == 0)
       st = launch_pass<true>(d_actual, d_expected, count, static_cast<int>(format), atol, rtol, params, d_histogram, d_partials, blocks, stream);
@@ -509,8 +525,8 @@ extern "C" wb200_status wb200_compare(wb200_backend *backend, uint32_t format, u
       }
     }
     for (int q = 0; q < kQueries; ++q) {
-      if (!params.query[q].active) continue;
-      const unsigned long long *bins = histogram.data() + static_cast<size_t>(q) * kBins;
+      if (!wanted[q]) continue;
+      const unsigned long long *bins = histogram.data() + static_cast<size_t>(source_of[q]) * kBins;
       int bin = 0;
       while (bin < kBins - 1 && remaining[q] >= bins[bin]) remaining[q] -= bins[bin++];
       prefix[q] = (prefix[q] << kDigitBits) | static_cast<uint64_t>(bin);

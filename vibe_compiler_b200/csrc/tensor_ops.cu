@@ -426,39 +426,58 @@ formal_elementwise_kernel(int runtime_op, int runtime_format, int out_format, in
 
 // The same fold for rank-4 NCx tensors [n, h, w, c] (every TargetCall-level reduce): coordinates are carried as loop
 // counters, so the only divisions are the three that split the output index.
+template <int kCombine, int kFormat>
 __global__ void __launch_bounds__(kThreads)
-formal_reduce_nhwc_kernel(int op, int format, const uint8_t *src, uint8_t *dst, const LayoutMap src_map, const LayoutMap dst_map,
+formal_reduce_nhwc_kernel(const uint8_t *src, uint8_t *dst, const LayoutMap src_map, const LayoutMap dst_map,
                           uint32_t reduced_mask, uint32_t *flags_word) {
+  constexpr int format = kFormat, combine = kCombine;
   const int64_t out_index = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   uint32_t block_flags_in = 0;
   if (out_index < dst_map.element_count) {
   const uint32_t out_c = static_cast<uint32_t>(dst_map.shape[3]), out_w = static_cast<uint32_t>(dst_map.shape[2]), out_h = static_cast<uint32_t>(dst_map.shape[1]);
-  const int64_t pixel = out_index / out_c;
-  const uint32_t c0 = static_cast<uint32_t>(out_index - pixel * out_c);
-  const int64_t row = pixel / out_w;
-  const uint32_t w0 = static_cast<uint32_t>(pixel - row * out_w);
-  const int64_t n0 = row / out_h;
-  const uint32_t h0 = static_cast<uint32_t>(row - n0 * out_h);
+  const uint32_t index = static_cast<uint32_t>(out_index);    // the launcher admits at most 2^32 - 1 outputs
+  const uint32_t pixel = index / out_c, c0 = index - pixel * out_c;
+  const uint32_t row = pixel / out_w, w0 = pixel - row * out_w;
+  const uint32_t n0 = row / out_h, h0 = row - n0 * out_h;
   // dimension d is bit d of the mask; a reduced dimension runs over its whole input extent from 0
   const uint32_t n_count = (reduced_mask & 1u) ? static_cast<uint32_t>(src_map.shape[0]) : 1u, h_count = (reduced_mask & 2u) ? static_cast<uint32_t>(src_map.shape[1]) : 1u;
   const uint32_t w_count = (reduced_mask & 4u) ? static_cast<uint32_t>(src_map.shape[2]) : 1u, c_count = (reduced_mask & 8u) ? static_cast<uint32_t>(src_map.shape[3]) : 1u;
   const uint32_t in_w = static_cast<uint32_t>(src_map.shape[2]);
   const uint32_t infinity = format == WB200_F32 ? 0x7f800000u : format == WB200_BF16 ? 0x7f80u : 0x7c00u;
   const uint32_t sign = format == WB200_F32 ? 0x80000000u : 0x8000u;
-  uint32_t accumulator = op == WB200_RED_SUM ? 0u : op == WB200_RED_MAX ? (infinity | sign) : infinity;
-  const int combine = op == WB200_RED_SUM ? WB200_EW_ADD : op == WB200_RED_MAX ? WB200_EW_MAX : WB200_EW_MIN;
+  uint32_t accumulator = combine == WB200_EW_ADD ? 0u : combine == WB200_EW_MAX ? (infinity | sign) : infinity;
   uint32_t flags = 0;
-  for (uint32_t n = 0; n < n_count; ++n)
-    for (uint32_t h = 0; h < h_count; ++h)
-      for (uint32_t w = 0; w < w_count; ++w)
-        for (uint32_t c = 0; c < c_count; ++c) {
-          const int64_t in_n = (reduced_mask & 1u) ? n : n0;
-          const uint32_t in_h = (reduced_mask & 2u) ? h : h0, in_wi = (reduced_mask & 4u) ? w : w0, in_c = (reduced_mask & 8u) ? c : c0;
+  if (!(reduced_mask & 8u)) {
+    // The channel is kept: along n, h and w the physical address moves by constant strides (one channel block is
+    // `width` elements wide), so the fold is three strided loops whose loads do not depend on one another.
+    const int64_t full_c = src_map.cx_blocks * src_map.c_block;
+    const int64_t width = static_cast<int64_t>(c0) < full_c ? src_map.c_block : src_map.c0;
+    const int64_t stride_w = width, stride_h = width * in_w, stride_n = src_map.outer_slice_stride;
+    const int64_t base = physical_index_nhwc(src_map, (reduced_mask & 1u) ? 0 : n0,
+                                             static_cast<int64_t>((reduced_mask & 2u) ? 0u : h0) * in_w + ((reduced_mask & 4u) ? 0u : w0), c0);
+    for (uint32_t n = 0; n < n_count; ++n)
+      for (uint32_t h = 0; h < h_count; ++h) {
+        const int64_t row = base + n * stride_n + h * stride_h;
+#pragma unroll 8
+        for (uint32_t w = 0; w < w_count; ++w) {
           uint32_t step_flags = 0;
-          const uint32_t value = load_element_bits(src, physical_index_nhwc(src_map, in_n, static_cast<int64_t>(in_h) * in_w + in_wi, in_c), format);
-          accumulator = formal_scalar(combine, format, format, accumulator, value, &step_flags);
+          accumulator = formal_scalar(combine, format, format, accumulator, load_element_bits(src, row + w * stride_w, format), &step_flags);
           flags |= step_flags;
         }
+      }
+  } else {
+    for (uint32_t n = 0; n < n_count; ++n)
+      for (uint32_t h = 0; h < h_count; ++h)
+        for (uint32_t w = 0; w < w_count; ++w)
+          for (uint32_t c = 0; c < c_count; ++c) {
+            const int64_t in_n = (reduced_mask & 1u) ? n : n0;
+            const uint32_t in_h = (reduced_mask & 2u) ? h : h0, in_wi = (reduced_mask & 4u) ? w : w0;
+            uint32_t step_flags = 0;
+            const uint32_t value = load_element_bits(src, physical_index_nhwc(src_map, in_n, static_cast<int64_t>(in_h) * in_w + in_wi, c), format);
+            accumulator = formal_scalar(combine, format, format, accumulator, value, &step_flags);
+            flags |= step_flags;
+          }
+  }
   store_element_bits(dst, physical_index_nhwc(dst_map, n0, static_cast<int64_t>(h0) * out_w + w0, c0), format, accumulator);
   block_flags_in = flags;
   }
@@ -514,25 +533,27 @@ formal_reduce_kernel(int op, int format, const uint8_t *src, uint8_t *dst, const
 // Plain pooling (lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:466-583): every output folds its window in
 // (kh, kw) order with the formal max / min / add, so the roundings and the raised flags are those of the reference's
 // window-by-window elementwise passes. Sum starts from +0 and adds every tap; max / min start from the first tap.
+template <int kCombine, int kFormat>
 __global__ void __launch_bounds__(kThreads)
-formal_pool_kernel(int combine, int format, const uint8_t *src, uint8_t *dst, const LayoutMap src_map, const LayoutMap dst_map,
+formal_pool_kernel(const uint8_t *src, uint8_t *dst, const LayoutMap src_map, const LayoutMap dst_map,
                    const PoolWindow window, uint32_t *flags_word) {
+  constexpr int combine = kCombine, format = kFormat;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   uint32_t flags = 0;
   const uint32_t out_h = static_cast<uint32_t>(dst_map.shape[1]), out_w = static_cast<uint32_t>(dst_map.shape[2]);
   const uint32_t channels = static_cast<uint32_t>(dst_map.shape[3]), in_w = static_cast<uint32_t>(src_map.shape[2]);
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < dst_map.element_count; i += stride) {
-    const int64_t pixel = i / channels;
-    const uint32_t c = static_cast<uint32_t>(i - pixel * channels);
-    const int64_t row = pixel / out_w;
-    const uint32_t w = static_cast<uint32_t>(pixel - row * out_w);
-    const int64_t n = row / out_h;
-    const uint32_t h = static_cast<uint32_t>(row - n * out_h);
+    const uint32_t index = static_cast<uint32_t>(i);          // the launcher admits at most 2^32 - 1 outputs
+    const uint32_t pixel = index / channels, c = index - pixel * channels;
+    const uint32_t row = pixel / out_w, w = pixel - row * out_w;
+    const uint32_t n = row / out_h, h = row - n * out_h;
     uint32_t result = 0;
+    const int64_t full_c = src_map.cx_blocks * src_map.c_block;
+    const int64_t width = static_cast<int64_t>(c) < full_c ? src_map.c_block : src_map.c0;   // taps of one channel move by constant strides
+    const int64_t corner = physical_index_nhwc(src_map, n, static_cast<int64_t>(h * window.stride_h) * in_w + w * window.stride_w, c);
     for (uint32_t kh = 0; kh < window.kernel_h; ++kh)
       for (uint32_t kw = 0; kw < window.kernel_w; ++kw) {
-        const int64_t outer = static_cast<int64_t>(h * window.stride_h + kh) * in_w + (w * window.stride_w + kw);
-        const uint32_t tap = load_element_bits(src, physical_index_nhwc(src_map, n, outer, c), format);
+        const uint32_t tap = load_element_bits(src, corner + (static_cast<int64_t>(kh) * in_w + kw) * width, format);
         if (kh == 0 && kw == 0 && combine != WB200_EW_ADD) {
           result = tap;
         } else {
@@ -616,8 +637,21 @@ wb200_status launch_elementwise_formal(int op, int in_format, int out_format, in
 wb200_status launch_reduce_formal(int op, int format, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map, const LayoutMap &dst_map,
                                   uint32_t reduced_mask, uint32_t *flags_word, cudaStream_t stream) {
   const int64_t blocks = (dst_map.element_count + kThreads - 1) / kThreads;
-  if (src_map.layout == WB200_LAYOUT_NCX && dst_map.layout == WB200_LAYOUT_NCX && src_map.rank == 4 && dst_map.rank == 4)
-    formal_reduce_nhwc_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), kThreads, 0, stream>>>(op, format, src, dst, src_map, dst_map, reduced_mask, flags_word);
+  if (src_map.layout == WB200_LAYOUT_NCX && dst_map.layout == WB200_LAYOUT_NCX && src_map.rank == 4 && dst_map.rank == 4 &&
+      dst_map.element_count < (1ll << 32))
+  {
+    const int grid = static_cast<int>(blocks < 1 ? 1 : blocks);
+#define WB200_RED_LAUNCH(COMBINE, FORMAT) formal_reduce_nhwc_kernel<COMBINE, FORMAT><<<grid, kThreads, 0, stream>>>(src, dst, src_map, dst_map, reduced_mask, flags_word)
+#define WB200_RED_FORMATS(COMBINE)                                              \
+    if (format == WB200_F32) WB200_RED_LAUNCH(COMBINE, WB200_F32);              \
+    else if (format == WB200_BF16) WB200_RED_LAUNCH(COMBINE, WB200_BF16);       \
+    else WB200_RED_LAUNCH(COMBINE, WB200_F16)
+    if (op == WB200_RED_SUM) { WB200_RED_FORMATS(WB200_EW_ADD); }
+    else if (op == WB200_RED_MAX) { WB200_RED_FORMATS(WB200_EW_MAX); }
+    else { WB200_RED_FORMATS(WB200_EW_MIN); }
+#undef WB200_RED_FORMATS
+#undef WB200_RED_LAUNCH
+  }
   else
     formal_reduce_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), kThreads, 0, stream>>>(op, format, src, dst, src_map, dst_map, reduced_mask, flags_word);
   WB200_CUDA_CHECK(cudaGetLastError());
@@ -626,7 +660,18 @@ wb200_status launch_reduce_formal(int op, int format, const uint8_t *src, uint8_
 
 wb200_status launch_pool_formal(int combine, int format, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map,
                                 const LayoutMap &dst_map, PoolWindow window, uint32_t *flags_word, cudaStream_t stream) {
-  formal_pool_kernel<<<grid_for(dst_map.element_count), kThreads, 0, stream>>>(combine, format, src, dst, src_map, dst_map, window, flags_word);
+  if (dst_map.element_count >= (1ll << 32)) return fail(WB200_ERR_LIMIT, "pooling output has more than 2^32 - 1 elements");
+  const int grid = grid_for(dst_map.element_count);
+#define WB200_POOL_LAUNCH(COMBINE, FORMAT) formal_pool_kernel<COMBINE, FORMAT><<<grid, kThreads, 0, stream>>>(src, dst, src_map, dst_map, window, flags_word)
+#define WB200_POOL_FORMATS(COMBINE)                                             \
+  if (format == WB200_F32) WB200_POOL_LAUNCH(COMBINE, WB200_F32);               \
+  else if (format == WB200_BF16) WB200_POOL_LAUNCH(COMBINE, WB200_BF16);        \
+  else WB200_POOL_LAUNCH(COMBINE, WB200_F16)
+  if (combine == WB200_EW_ADD) { WB200_POOL_FORMATS(WB200_EW_ADD); }
+  else if (combine == WB200_EW_MAX) { WB200_POOL_FORMATS(WB200_EW_MAX); }
+  else { WB200_POOL_FORMATS(WB200_EW_MIN); }
+#undef WB200_POOL_FORMATS
+#undef WB200_POOL_LAUNCH
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }
