@@ -147,6 +147,40 @@ __device__ __forceinline__ bool convert_scalar(int src_format, int dst_format, i
       }
       return true;
     }
+    if (dst_float && dst_format != WB200_TF32) {
+      // Hardware path for finite values that stay clear of the destination's subnormal range: every source value is
+      // an f32 value, the f32 -> f16 / bf16 conversion instructions implement all four IEEE roundings, and the flags
+      // follow from the result (tininess is impossible once |x| is at least the smallest normal number).
+      const float x = src_format == WB200_F16 ? __half2float(__ushort_as_half(static_cast<unsigned short>(bits)))
+                                              : __uint_as_float(src_format == WB200_BF16 ? bits << 16 : bits);
+      if (dst_format == WB200_F32) {   // every route into f32 widens exactly
+        *result = __float_as_uint(x);
+        return true;
+      }
+      const float magnitude = fabsf(x);
+      const float smallest_normal = dst_format == WB200_F16 ? 6.103515625e-05f : 1.17549435e-38f;
+      if (magnitude >= smallest_normal) {
+        const float largest = dst_format == WB200_F16 ? 65504.0f : 3.38953139e38f;
+        uint32_t narrow;
+        if (dst_format == WB200_F16) {
+          const __half h = mode == MODE_NEAREST_EVEN ? __float2half_rn(x) : mode == MODE_TOWARD_ZERO ? __float2half_rz(x)
+                         : mode == MODE_TOWARD_POSITIVE ? __float2half_ru(x) : __float2half_rd(x);
+          narrow = __half_as_ushort(h);
+        } else {
+          const __nv_bfloat16 h = mode == MODE_NEAREST_EVEN ? __float2bfloat16_rn(x) : mode == MODE_TOWARD_ZERO ? __float2bfloat16_rz(x)
+                                : mode == MODE_TOWARD_POSITIVE ? __float2bfloat16_ru(x) : __float2bfloat16_rd(x);
+          narrow = __bfloat16_as_ushort(h);
+        }
+        const uint32_t exponent_mask = dst_format == WB200_F16 ? 0x7c00u : 0x7f80u;
+        const bool became_infinite = (narrow & 0x7fffu) == exponent_mask;
+        const float back = dst_format == WB200_F16 ? __half2float(__ushort_as_half(static_cast<unsigned short>(narrow))) : __uint_as_float(narrow << 16);
+        const bool returns_finite = mode == MODE_TOWARD_ZERO || (mode == MODE_TOWARD_POSITIVE && negative) || (mode == MODE_TOWARD_NEGATIVE && !negative);
+        if (became_infinite || (magnitude > largest && returns_finite)) *flags |= FLAG_OVERFLOW | FLAG_INEXACT;
+        else if (back != x) *flags |= FLAG_INEXACT;
+        *result = narrow;
+        return true;
+      }
+    }
     significand = field ? (fraction | (1u << fraction_bits)) : fraction;
     exponent = (field ? static_cast<int>(field) : 1) - bias - fraction_bits;
   }
