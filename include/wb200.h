@@ -116,7 +116,7 @@ typedef struct wb200_evidence {
   uint32_t evidence_kind; /* 0 none, 2 managed-reference environment */
   uint32_t flags;
   uint32_t gpu_launches;  /* kernels this call launched */
-  uint32_t reserved;
+  uint32_t device_us;     /* device time of those kernels in microseconds (CUDA events; tensor commands only, else 0) */
   char digest[96];         /* "b200:<device name>:sm_<cc>:abi<version>" */
   char implementation[64]; /* kernel family that produced the result */
 } wb200_evidence;

@@ -58,7 +58,7 @@ class Evidence(C.Structure):
     _fields_ = [("matmul_invocations", C.c_uint64), ("reorder_invocations", C.c_uint64),
                 ("formal_fused_multiply_adds", C.c_uint64), ("scalar_evaluations", C.c_uint64),
                 ("evidence_kind", C.c_uint32), ("flags", C.c_uint32), ("gpu_launches", C.c_uint32),
-                ("reserved", C.c_uint32), ("digest", C.c_char * 96), ("implementation", C.c_char * 64)]
+                ("device_us", C.c_uint32), ("digest", C.c_char * 96), ("implementation", C.c_char * 64)]
 
 
 class GemmRequest(C.Structure):

@@ -78,6 +78,7 @@ class Evidence:
     gpu_launches: int = 0
     digest: str = ""
     implementation: str = ""
+    device_us: int = 0   # device time of the call's kernels (tensor commands only)
 
 
 @dataclass
@@ -88,7 +89,7 @@ class BackendResult:
 
 def _evidence(e: abi.Evidence) -> Evidence:
     return Evidence(e.matmul_invocations, e.reorder_invocations, e.formal_fused_multiply_adds, e.scalar_evaluations,
-                    e.evidence_kind, e.flags, e.gpu_launches, e.digest.decode(), e.implementation.decode())
+                    e.evidence_kind, e.flags, e.gpu_launches, e.digest.decode(), e.implementation.decode(), e.device_us)
 
 
 def _u8(array: np.ndarray) -> np.ndarray:

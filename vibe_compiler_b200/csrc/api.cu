@@ -52,6 +52,8 @@ void wb200_backend_destroy(wb200_backend *backend) {
   for (cudaEvent_t event : backend->aux_event)
     if (event) cudaEventDestroy(event);
   for (cudaEvent_t event : backend->pipeline_event) cudaEventDestroy(event);
+  for (cudaEvent_t event : backend->timing_event)
+    if (event) cudaEventDestroy(event);
   if (backend->stream) cudaStreamDestroy(backend->stream);
   delete backend;
 }

@@ -187,16 +187,19 @@ wb200_status wb200_elementwise(wb200_backend *backend, const wb200_elementwise_r
   }
   if ((st = backend->buffer(2, r->destination_bytes, &d_dst)) != WB200_OK) return st;
   WB200_CUDA_CHECK(cudaMemcpyAsync(d_dst, r->destination_template, r->destination_bytes, cudaMemcpyHostToDevice, stream));
+  if ((st = backend->timing_begin(stream)) != WB200_OK) return st;
   st = launch_elementwise(r->operation, dst.format, arity, static_cast<const uint8_t *>(d_in[0]), static_cast<const uint8_t *>(d_in[1]),
                           static_cast<uint8_t *>(d_dst), map, backend->d_status + 1, stream);
   if (st != WB200_OK) return st;
   backend->launches += 1;
+  if ((st = backend->timing_end(stream)) != WB200_OK) return st;
   int nan_flag = 0;
   if ((st = read_device_status(backend, stream, &nan_flag)) != WB200_OK) return st;
   if (nan_flag) return fail(WB200_ERR_NAN_DOMAIN, "managed-reference tensor: value is outside the non-NaN domain");
   WB200_CUDA_CHECK(cudaMemcpyAsync(r->destination_out, d_dst, r->destination_bytes, cudaMemcpyDeviceToHost, stream));
   WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
   fill_evidence(backend, evidence, "sm100a-non-nan-f16-bf16-f32-tensor");
+  if (evidence) evidence->device_us = backend->timing_microseconds();
   if (evidence) { evidence->scalar_evaluations = map.element_count; evidence->gpu_launches = 1; }
   return WB200_OK;
 }
@@ -253,16 +256,19 @@ wb200_status wb200_elementwise_formal(wb200_backend *backend, const wb200_elemen
   if ((st = backend->buffer(3, sizeof(uint32_t), &d_flags)) != WB200_OK) return st;
   WB200_CUDA_CHECK(cudaMemcpyAsync(d_dst, r->destination_template, r->destination_bytes, cudaMemcpyHostToDevice, stream));
   WB200_CUDA_CHECK(cudaMemsetAsync(d_flags, 0, sizeof(uint32_t), stream));
+  if ((st = backend->timing_begin(stream)) != WB200_OK) return st;
   st = launch_elementwise_formal(r->operation, first.format, dst.format, arity, static_cast<const uint8_t *>(d_in[0]),
                                  static_cast<const uint8_t *>(d_in[1]), static_cast<uint8_t *>(d_dst), in_map, out_map,
                                  static_cast<uint32_t *>(d_flags), stream);
   if (st != WB200_OK) return st;
   backend->launches += 1;
+  if ((st = backend->timing_end(stream)) != WB200_OK) return st;
   uint32_t flags = 0;
   WB200_CUDA_CHECK(cudaMemcpyAsync(&flags, d_flags, sizeof(flags), cudaMemcpyDeviceToHost, stream));
   WB200_CUDA_CHECK(cudaMemcpyAsync(r->destination_out, d_dst, r->destination_bytes, cudaMemcpyDeviceToHost, stream));
   WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
   fill_evidence(backend, evidence, "sm100a-formal-elementwise");
+  if (evidence) evidence->device_us = backend->timing_microseconds();
   if (evidence) { evidence->scalar_evaluations = out_map.element_count; evidence->gpu_launches = 1; evidence->flags = flags; }
   return WB200_OK;
 }
@@ -295,16 +301,19 @@ wb200_status wb200_convert(wb200_backend *backend, const wb200_convert_request *
   if ((st = backend->buffer(2, r->destination_bytes, &d_dst)) != WB200_OK) return st;
   WB200_CUDA_CHECK(cudaMemcpyAsync(d_src, r->source_storage, r->source_bytes, cudaMemcpyHostToDevice, stream));
   WB200_CUDA_CHECK(cudaMemcpyAsync(d_dst, r->destination_template, r->destination_bytes, cudaMemcpyHostToDevice, stream));
+  if ((st = backend->timing_begin(stream)) != WB200_OK) return st;
   st = launch_convert(src.format, dst.format, static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), src_map, dst_map,
                       backend->d_status + 1, stream);
   if (st != WB200_OK) return st;
   backend->launches += 1;
+  if ((st = backend->timing_end(stream)) != WB200_OK) return st;
   int nan_flag = 0;
   if ((st = read_device_status(backend, stream, &nan_flag)) != WB200_OK) return st;
   if (nan_flag) return fail(WB200_ERR_NAN_DOMAIN, "managed-reference tensor: input value is outside the non-NaN domain");
   WB200_CUDA_CHECK(cudaMemcpyAsync(r->destination_out, d_dst, r->destination_bytes, cudaMemcpyDeviceToHost, stream));
   WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
   fill_evidence(backend, evidence, "sm100a-non-nan-f16-bf16-f32-tensor");
+  if (evidence) evidence->device_us = backend->timing_microseconds();
   if (evidence) { evidence->scalar_evaluations = dst_map.element_count; evidence->gpu_launches = 1; }
   return WB200_OK;
 }
@@ -357,16 +366,19 @@ wb200_status wb200_reduce(wb200_backend *backend, const wb200_reduce_request *r,
   if ((st = backend->buffer(2, r->destination_bytes, &d_dst)) != WB200_OK) return st;
   WB200_CUDA_CHECK(cudaMemcpyAsync(d_src, r->input_storage, r->input_bytes, cudaMemcpyHostToDevice, stream));
   WB200_CUDA_CHECK(cudaMemcpyAsync(d_dst, r->destination_template, r->destination_bytes, cudaMemcpyHostToDevice, stream));
+  if ((st = backend->timing_begin(stream)) != WB200_OK) return st;
   st = launch_reduce(r->operation, in.format, static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), in_map, dst_map, mask,
                      backend->d_status + 1, stream);
   if (st != WB200_OK) return st;
   backend->launches += 1;
+  if ((st = backend->timing_end(stream)) != WB200_OK) return st;
   int nan_flag = 0;
   if ((st = read_device_status(backend, stream, &nan_flag)) != WB200_OK) return st;
   if (nan_flag) return fail(WB200_ERR_NAN_DOMAIN, "managed-reference tensor: reduce left the non-NaN domain");
   WB200_CUDA_CHECK(cudaMemcpyAsync(r->destination_out, d_dst, r->destination_bytes, cudaMemcpyDeviceToHost, stream));
   WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
   fill_evidence(backend, evidence, "sm100a-non-nan-f16-bf16-f32-tensor");
+  if (evidence) evidence->device_us = backend->timing_microseconds();
   if (evidence) { evidence->scalar_evaluations = in_map.element_count; evidence->gpu_launches = 1; }
   return WB200_OK;
 }
@@ -392,14 +404,17 @@ wb200_status wb200_reduce_formal(wb200_backend *backend, const wb200_reduce_requ
   WB200_CUDA_CHECK(cudaMemcpyAsync(d_src, r->input_storage, r->input_bytes, cudaMemcpyHostToDevice, stream));
   WB200_CUDA_CHECK(cudaMemcpyAsync(d_dst, r->destination_template, r->destination_bytes, cudaMemcpyHostToDevice, stream));
   WB200_CUDA_CHECK(cudaMemsetAsync(d_flags, 0, sizeof(uint32_t), stream));
+  if ((st = backend->timing_begin(stream)) != WB200_OK) return st;
   if ((st = launch_reduce_formal(r->operation, in.format, static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), in_map, dst_map, mask,
                                  static_cast<uint32_t *>(d_flags), stream)) != WB200_OK) return st;
   backend->launches += 1;
+  if ((st = backend->timing_end(stream)) != WB200_OK) return st;
   uint32_t flags = 0;
   WB200_CUDA_CHECK(cudaMemcpyAsync(&flags, d_flags, sizeof(flags), cudaMemcpyDeviceToHost, stream));
   WB200_CUDA_CHECK(cudaMemcpyAsync(r->destination_out, d_dst, r->destination_bytes, cudaMemcpyDeviceToHost, stream));
   WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
   fill_evidence(backend, evidence, "sm100a-formal-reduce");
+  if (evidence) evidence->device_us = backend->timing_microseconds();
   if (evidence) { evidence->scalar_evaluations = in_map.element_count; evidence->gpu_launches = 1; evidence->flags = flags; }
   return WB200_OK;
 }

@@ -26,6 +26,23 @@ struct wb200_backend {
   // Two auxiliary streams and three events for calls that overlap independent parts of their work (created on first use).
   cudaStream_t aux_stream[2] = {nullptr, nullptr};
   cudaEvent_t aux_event[3] = {nullptr, nullptr, nullptr};
+  cudaEvent_t timing_event[2] = {nullptr, nullptr};   // brackets the kernels of one command call (created on first use)
+  wb200_status timing_begin(cudaStream_t s) {
+    if (!timing_event[0])
+      for (int i = 0; i < 2; ++i) WB200_CUDA_CHECK(cudaEventCreate(&timing_event[i]));
+    WB200_CUDA_CHECK(cudaEventRecord(timing_event[0], s));
+    return WB200_OK;
+  }
+  // Call after the stream has been synchronised past timing_end()'s record.
+  wb200_status timing_end(cudaStream_t s) {
+    WB200_CUDA_CHECK(cudaEventRecord(timing_event[1], s));
+    return WB200_OK;
+  }
+  uint32_t timing_microseconds() const {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, timing_event[0], timing_event[1]) != cudaSuccess) return 0;
+    return static_cast<uint32_t>(ms * 1000.f + 0.5f);
+  }
   std::vector<cudaEvent_t> pipeline_event;   // edges of host-buffer pipelines, grown on demand
   wb200_status pipeline_events(size_t count) {
     while (pipeline_event.size() < count) {

@@ -460,11 +460,14 @@ wb200_status wb200_convert_formal(wb200_backend *backend, const wb200_convert_re
   WB200_CUDA_CHECK(cudaMemcpyAsync(d_dst, r->destination_template, r->destination_bytes, cudaMemcpyHostToDevice, stream));
   uint32_t flags = 0;
   const uint64_t before = backend->launches;
+  if ((st = backend->timing_begin(stream)) != WB200_OK) return st;
   if ((st = run_convert(backend, route, mode, static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), src_map, dst_map, stream, &flags)) != WB200_OK) return st;
+  if ((st = backend->timing_end(stream)) != WB200_OK) return st;
   WB200_CUDA_CHECK(cudaMemcpyAsync(r->destination_out, d_dst, r->destination_bytes, cudaMemcpyDeviceToHost, stream));
   WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
   fill_evidence(backend, evidence, "sm100a-formal-convert");
   if (evidence) {
+    evidence->device_us = backend->timing_microseconds();
     evidence->scalar_evaluations = dst_map.element_count;
     evidence->gpu_launches = static_cast<uint32_t>(backend->launches - before);
     evidence->flags = flags;

@@ -56,6 +56,64 @@ elementwise_kernel(int op, int format, int input_count, const uint8_t *in0, cons
   if (saw_nan) atomicExch(nan_flag, 1);
 }
 
+// Linear (Tensor / NTensor) layouts with 16-byte aligned operands: eight elements per thread with 128-bit accesses,
+// the operation and the format fixed at compile time.
+template <int kOp, int kFormat>
+__global__ void __launch_bounds__(kThreads)
+elementwise_linear_kernel(int input_count, const uint8_t *in0, const uint8_t *in1, uint8_t *dst, int64_t total, int *nan_flag) {
+  constexpr int bytes = kFormat == WB200_F32 ? 4 : 2;
+  const int64_t groups = total / 8, stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  bool saw_nan = false;
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < groups; g += stride) {
+    uint32_t a[8], b[8], r[8];
+    load_group8(in0, g, bytes, a);
+    if (input_count > 1) load_group8(in1, g, bytes, b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float x = widen_bits(a[e], kFormat), y = input_count > 1 ? widen_bits(b[e], kFormat) : 0.0f;
+      const float result = apply_elementwise(kOp, x, y);
+      saw_nan |= (x != x) | (y != y) | (result != result);
+      r[e] = narrow_bits(result, kFormat);
+    }
+    store_group8(dst, g, bytes, r);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < total - groups * 8) {   // ragged tail
+    const int64_t i = groups * 8 + threadIdx.x;
+    const float x = widen_bits(load_element_bits(in0, i, kFormat), kFormat);
+    const float y = input_count > 1 ? widen_bits(load_element_bits(in1, i, kFormat), kFormat) : 0.0f;
+    const float result = apply_elementwise(kOp, x, y);
+    saw_nan |= (x != x) | (y != y) | (result != result);
+    store_element_bits(dst, i, kFormat, narrow_bits(result, kFormat));
+  }
+  if (saw_nan) atomicExch(nan_flag, 1);
+}
+
+template <int kSrc, int kDst>
+__global__ void __launch_bounds__(kThreads)
+convert_linear_kernel(const uint8_t *src, uint8_t *dst, int64_t total, int *nan_flag) {
+  constexpr int src_bytes = kSrc == WB200_F32 ? 4 : 2, dst_bytes = kDst == WB200_F32 ? 4 : 2;
+  const int64_t groups = total / 8, stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  bool saw_nan = false;
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < groups; g += stride) {
+    uint32_t a[8], r[8];
+    load_group8(src, g, src_bytes, a);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float x = widen_bits(a[e], kSrc);
+      saw_nan |= (x != x);
+      r[e] = narrow_bits(x, kDst);
+    }
+    store_group8(dst, g, dst_bytes, r);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < total - groups * 8) {
+    const int64_t i = groups * 8 + threadIdx.x;
+    const float x = widen_bits(load_element_bits(src, i, kSrc), kSrc);
+    saw_nan |= (x != x);
+    store_element_bits(dst, i, kDst, narrow_bits(x, kDst));
+  }
+  if (saw_nan) atomicExch(nan_flag, 1);
+}
+
 __global__ void __launch_bounds__(kThreads)
 convert_kernel(int src_format, int dst_format, const uint8_t *src, uint8_t *dst, const LayoutMap src_map,
                const LayoutMap dst_map, int *nan_flag) {
@@ -116,6 +174,61 @@ reduce_kernel(int op, int format, const uint8_t *src, uint8_t *dst, const Layout
     saw_nan |= (acc != acc);
   }
   store_element_bits(dst, physical_index(dst_map, out_index), format, narrow_bits(acc, format));
+  if (saw_nan) atomicExch(nan_flag, 1);
+}
+
+// The same reduction for rank-4 NCx tensors [n, h, w, c] (every TargetCall-level reduce): the output index is split
+// once with 32-bit divisions, and while the channel is kept the fold walks constant strides along n, h and w.
+template <int kOp, int kFormat>
+__global__ void __launch_bounds__(kThreads)
+reduce_nhwc_kernel(const uint8_t *src, uint8_t *dst, const LayoutMap src_map, const LayoutMap dst_map, uint32_t reduced_mask, int *nan_flag) {
+  const int64_t out_index = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (out_index >= dst_map.element_count) return;
+  const uint32_t out_c = static_cast<uint32_t>(dst_map.shape[3]), out_w = static_cast<uint32_t>(dst_map.shape[2]), out_h = static_cast<uint32_t>(dst_map.shape[1]);
+  const uint32_t index = static_cast<uint32_t>(out_index);
+  const uint32_t pixel = index / out_c, c0 = index - pixel * out_c;
+  const uint32_t row = pixel / out_w, w0 = pixel - row * out_w;
+  const uint32_t n0 = row / out_h, h0 = row - n0 * out_h;
+  const uint32_t n_count = (reduced_mask & 1u) ? static_cast<uint32_t>(src_map.shape[0]) : 1u, h_count = (reduced_mask & 2u) ? static_cast<uint32_t>(src_map.shape[1]) : 1u;
+  const uint32_t w_count = (reduced_mask & 4u) ? static_cast<uint32_t>(src_map.shape[2]) : 1u, c_count = (reduced_mask & 8u) ? static_cast<uint32_t>(src_map.shape[3]) : 1u;
+  const uint32_t in_w = static_cast<uint32_t>(src_map.shape[2]);
+  float acc = kOp == WB200_RED_MAX ? -INFINITY : (kOp == WB200_RED_MIN ? INFINITY : 0.0f);
+  bool saw_nan = false;
+  auto step = [&](float value) {
+    saw_nan |= (value != value);
+    if (kOp == WB200_RED_SUM) {
+      acc = __fadd_rn(acc, value);
+    } else if (acc == 0.0f && value == 0.0f) {
+      const bool negative = kOp == WB200_RED_MAX ? (signbit(acc) && signbit(value)) : (signbit(acc) || signbit(value));
+      acc = negative ? -0.0f : 0.0f;
+    } else {
+      acc = kOp == WB200_RED_MAX ? fmaxf(acc, value) : fminf(acc, value);
+    }
+    saw_nan |= (acc != acc);
+  };
+  if (!(reduced_mask & 8u)) {
+    const int64_t full_c = src_map.cx_blocks * src_map.c_block;
+    const int64_t width = static_cast<int64_t>(c0) < full_c ? src_map.c_block : src_map.c0;
+    const int64_t stride_h = width * in_w, stride_n = src_map.outer_slice_stride;
+    const int64_t base = physical_index_nhwc(src_map, (reduced_mask & 1u) ? 0 : n0,
+                                             static_cast<int64_t>((reduced_mask & 2u) ? 0u : h0) * in_w + ((reduced_mask & 4u) ? 0u : w0), c0);
+    for (uint32_t n = 0; n < n_count; ++n)
+      for (uint32_t h = 0; h < h_count; ++h) {
+        const int64_t line = base + n * stride_n + h * stride_h;
+#pragma unroll 8
+        for (uint32_t w = 0; w < w_count; ++w) step(widen_bits(load_element_bits(src, line + w * width, kFormat), kFormat));
+      }
+  } else {
+    for (uint32_t n = 0; n < n_count; ++n)
+      for (uint32_t h = 0; h < h_count; ++h)
+        for (uint32_t w = 0; w < w_count; ++w)
+          for (uint32_t c = 0; c < c_count; ++c) {
+            const int64_t in_n = (reduced_mask & 1u) ? n : n0;
+            const uint32_t in_h = (reduced_mask & 2u) ? h : h0, in_wi = (reduced_mask & 4u) ? w : w0;
+            step(widen_bits(load_element_bits(src, physical_index_nhwc(src_map, in_n, static_cast<int64_t>(in_h) * in_w + in_wi, c), kFormat), kFormat));
+          }
+  }
+  store_element_bits(dst, physical_index_nhwc(dst_map, n0, static_cast<int64_t>(h0) * out_w + w0, c0), kFormat, narrow_bits(acc, kFormat));
   if (saw_nan) atomicExch(nan_flag, 1);
 }
 
@@ -592,7 +705,27 @@ wb200_status launch_codec(const uint8_t *src, uint8_t *dst, const LayoutMap &map
 
 wb200_status launch_elementwise(int op, int format, int input_count, const uint8_t *in0, const uint8_t *in1,
                                 uint8_t *dst, const LayoutMap &map, int *nan_flag, cudaStream_t stream) {
-  elementwise_kernel<<<grid_for(map.element_count), kThreads, 0, stream>>>(op, format, input_count, in0, in1, dst, map, nan_flag);
+  const bool linear = (map.layout == WB200_LAYOUT_TENSOR || map.layout == WB200_LAYOUT_NTENSOR) && all_aligned16(in0, in1, dst);
+  const int64_t groups = map.element_count / 8;
+  int64_t blocks = (groups + kThreads - 1) / kThreads;
+  const int grid = static_cast<int>(blocks < 1 ? 1 : blocks > 148 * 32 ? 148 * 32 : blocks);
+#define WB200_MEW(OP)                                                                                                                     \
+  case OP:                                                                                                                                \
+    if (format == WB200_F32) elementwise_linear_kernel<OP, WB200_F32><<<grid, kThreads, 0, stream>>>(input_count, in0, in1, dst, map.element_count, nan_flag);        \
+    else if (format == WB200_BF16) elementwise_linear_kernel<OP, WB200_BF16><<<grid, kThreads, 0, stream>>>(input_count, in0, in1, dst, map.element_count, nan_flag); \
+    else elementwise_linear_kernel<OP, WB200_F16><<<grid, kThreads, 0, stream>>>(input_count, in0, in1, dst, map.element_count, nan_flag);                          \
+    break;
+  switch (linear ? op : -1) {
+    WB200_MEW(WB200_EW_ABS) WB200_MEW(WB200_EW_NEG) WB200_MEW(WB200_EW_RECIP) WB200_MEW(WB200_EW_SQUARE) WB200_MEW(WB200_EW_MAX)
+    WB200_MEW(WB200_EW_MIN) WB200_MEW(WB200_EW_ADD) WB200_MEW(WB200_EW_SUB) WB200_MEW(WB200_EW_MUL) WB200_MEW(WB200_EW_RELU)
+    WB200_MEW(WB200_EW_SQRT) WB200_MEW(WB200_EW_RSQRT) WB200_MEW(WB200_EW_LOG2) WB200_MEW(WB200_EW_LN) WB200_MEW(WB200_EW_POW2)
+    WB200_MEW(WB200_EW_EXP) WB200_MEW(WB200_EW_EXPLP) WB200_MEW(WB200_EW_SIN) WB200_MEW(WB200_EW_COS) WB200_MEW(WB200_EW_TANH)
+    WB200_MEW(WB200_EW_SIGMOID) WB200_MEW(WB200_EW_SOFTPLUS)
+    default:
+      elementwise_kernel<<<grid_for(map.element_count), kThreads, 0, stream>>>(op, format, input_count, in0, in1, dst, map, nan_flag);
+      break;
+  }
+#undef WB200_MEW
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }
@@ -678,7 +811,24 @@ wb200_status launch_pool_formal(int combine, int format, const uint8_t *src, uin
 
 wb200_status launch_convert(int src_format, int dst_format, const uint8_t *src, uint8_t *dst,
                             const LayoutMap &src_map, const LayoutMap &dst_map, int *nan_flag, cudaStream_t stream) {
-  convert_kernel<<<grid_for(src_map.element_count), kThreads, 0, stream>>>(src_format, dst_format, src, dst, src_map, dst_map, nan_flag);
+  auto linear_layout = [](const LayoutMap &m) { return m.layout == WB200_LAYOUT_TENSOR || m.layout == WB200_LAYOUT_NTENSOR; };
+  const bool linear = linear_layout(src_map) && linear_layout(dst_map) && all_aligned16(src, dst);
+  int64_t blocks = (src_map.element_count / 8 + kThreads - 1) / kThreads;
+  const int grid = static_cast<int>(blocks < 1 ? 1 : blocks > 148 * 32 ? 148 * 32 : blocks);
+#define WB200_MCV(SRC, DST) convert_linear_kernel<SRC, DST><<<grid, kThreads, 0, stream>>>(src, dst, src_map.element_count, nan_flag)
+#define WB200_MCV_TO(SRC)                                        \
+  if (dst_format == WB200_F32) WB200_MCV(SRC, WB200_F32);        \
+  else if (dst_format == WB200_BF16) WB200_MCV(SRC, WB200_BF16); \
+  else WB200_MCV(SRC, WB200_F16)
+  if (linear && is_float_format(src_format) && is_float_format(dst_format)) {
+    if (src_format == WB200_F32) { WB200_MCV_TO(WB200_F32); }
+    else if (src_format == WB200_BF16) { WB200_MCV_TO(WB200_BF16); }
+    else { WB200_MCV_TO(WB200_F16); }
+  } else {
+    convert_kernel<<<grid_for(src_map.element_count), kThreads, 0, stream>>>(src_format, dst_format, src, dst, src_map, dst_map, nan_flag);
+  }
+#undef WB200_MCV_TO
+#undef WB200_MCV
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }
@@ -686,7 +836,22 @@ wb200_status launch_convert(int src_format, int dst_format, const uint8_t *src, 
 wb200_status launch_reduce(int op, int format, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map,
                            const LayoutMap &dst_map, uint32_t reduced_mask, int *nan_flag, cudaStream_t stream) {
   const int64_t blocks = (dst_map.element_count + kThreads - 1) / kThreads;
-  reduce_kernel<<<static_cast<int>(blocks < 1 ? 1 : blocks), kThreads, 0, stream>>>(op, format, src, dst, src_map, dst_map, reduced_mask, nan_flag);
+  const int grid = static_cast<int>(blocks < 1 ? 1 : blocks);
+  if (src_map.layout == WB200_LAYOUT_NCX && dst_map.layout == WB200_LAYOUT_NCX && src_map.rank == 4 && dst_map.rank == 4 &&
+      dst_map.element_count < (1ll << 32)) {
+#define WB200_MRED(OP, FORMAT) reduce_nhwc_kernel<OP, FORMAT><<<grid, kThreads, 0, stream>>>(src, dst, src_map, dst_map, reduced_mask, nan_flag)
+#define WB200_MRED_FORMATS(OP)                                   \
+    if (format == WB200_F32) WB200_MRED(OP, WB200_F32);          \
+    else if (format == WB200_BF16) WB200_MRED(OP, WB200_BF16);   \
+    else WB200_MRED(OP, WB200_F16)
+    if (op == WB200_RED_SUM) { WB200_MRED_FORMATS(WB200_RED_SUM); }
+    else if (op == WB200_RED_MAX) { WB200_MRED_FORMATS(WB200_RED_MAX); }
+    else { WB200_MRED_FORMATS(WB200_RED_MIN); }
+#undef WB200_MRED_FORMATS
+#undef WB200_MRED
+  } else {
+    reduce_kernel<<<grid, kThreads, 0, stream>>>(op, format, src, dst, src_map, dst_map, reduced_mask, nan_flag);
+  }
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }

@@ -83,6 +83,39 @@ def main(argv=None) -> int:
     out_shape = (shape[0], 32, 32, 64)
     report("formal_pool max f32 2x2 stride 2", 4 * count + 4 * count // 4,
            (lambda: pad.pool("max", a_at, c_at, shape, out_shape, (2, 2, 2, 2), abi.F32)))
+    # seam-1 commands take host storage (the reference passes std::vector bytes): the kernel time comes from the
+    # evidence's device_us, the call time is dominated by the two host <-> device copies
+    from ..backend import NumericTensor, PhysicalTensorDescriptor
+    m = min(n, 1 << 26)
+    host_a = rng.standard_normal(m).astype(np.float32)
+    host_b = rng.standard_normal(m).astype(np.float32)
+
+    def boundary(name, bytes_per_call, call):
+        if args.only not in name:
+            return
+        call()
+        samples = sorted(call().evidence.device_us for _ in range(max(3, args.repeats // 2)))
+        seconds = samples[len(samples) // 2] * 1e-6
+        line = {"kernel": name, "elements": m, "bytes": bytes_per_call, "ms": round(seconds * 1e3, 3),
+                "gbs": round(bytes_per_call / seconds / 1e9, 1), "peak_gbs": peak, "frac": round(bytes_per_call / seconds / 1e9 / peak, 3),
+                "timing": "device_us of the evidence (CUDA events around the kernel)"}
+        print(json.dumps(line), flush=True)
+
+    vec = PhysicalTensorDescriptor(abi.F32, abi.LAYOUT_TENSOR, [m])
+    half = PhysicalTensorDescriptor(abi.BF16, abi.LAYOUT_TENSOR, [m])
+    tmpl32, tmpl16 = np.zeros(4 * m, np.uint8), np.zeros(2 * m, np.uint8)
+    boundary("managed elementwise add f32 (wb200_elementwise)", 12 * m,
+             lambda: backend.execute_elementwise("add", [NumericTensor(vec, host_a), NumericTensor(vec, host_b)], NumericTensor(vec, tmpl32)))
+    boundary("managed elementwise exp f32 (wb200_elementwise)", 8 * m,
+             lambda: backend.execute_elementwise("exp", [NumericTensor(vec, host_a)], NumericTensor(vec, tmpl32)))
+    boundary("managed convert fp32_bf16 (wb200_convert)", 6 * m, lambda: backend.execute_convert(167, NumericTensor(vec, host_a), NumericTensor(half, tmpl16)))
+    cx = PhysicalTensorDescriptor(abi.F32, abi.LAYOUT_NCX, [m // (64 * 64 * 64), 64, 64, 64])
+    cx_out = PhysicalTensorDescriptor(abi.F32, abi.LAYOUT_NCX, [m // (64 * 64 * 64), 64, 1, 64])
+    out_bytes = backend.physical_bytes(cx_out)
+    boundary("managed reduce sum f32 over w, NCx (wb200_reduce)", 4 * m + out_bytes,
+             lambda: backend.execute_reduce("sum", "trailing1", NumericTensor(cx, host_a), NumericTensor(cx_out, np.zeros(out_bytes, np.uint8))))
+    boundary("formal elementwise add f32, host storage (wb200_elementwise_formal)", 12 * m,
+             lambda: backend.execute_elementwise("add", [NumericTensor(vec, host_a), NumericTensor(vec, host_b)], NumericTensor(vec, tmpl32), formal=True))
     # the gate on device pointers
     lib = abi.load()
     x = torch.randn(n, device="cuda")
