@@ -155,11 +155,13 @@ def _pool_oracle(kind, fmt, compact, source_shape, destination_shape, kernel_str
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("kind, fmt", [("max", "f16"), ("min", "bf16"), ("max", "f32"), ("sum", "f32")])
-def test_pooling_folds_each_window_in_the_reference_order(backend, kind, fmt):
+@pytest.mark.parametrize("kind, fmt, channels", [("max", "f16", 70), ("min", "bf16", 70), ("max", "f32", 70), ("sum", "f32", 70),
+                                                 ("max", "bf16", 72), ("sum", "f32", 72), ("min", "f16", 128)])
+def test_pooling_folds_each_window_in_the_reference_order(backend, kind, fmt, channels):
     rng = np.random.default_rng(17)
-    source_shape, kernel_strides = (2, 7, 9, 70), (3, 2, 2, 1)       # 70 channels: one full block of 64 and a tail
-    destination_shape = (2, (7 - 2) // 1 + 1, (9 - 3) // 2 + 1, 70)
+    # 70 channels: one full block of 64 and a ragged tail (one channel per thread); 72 and 128: four channels per thread
+    source_shape, kernel_strides = (2, 7, 9, channels), (3, 2, 2, 1)
+    destination_shape = (2, (7 - 2) // 1 + 1, (9 - 3) // 2 + 1, channels)
     compact = _patterns(fmt, int(np.prod(source_shape)), rng, finite=(kind == "sum"))
     if kind == "sum":
         compact[:3] = [0x7f7fffff, 0x7f7fffff, 0x00000001]           # an overflow and a subnormal among the taps

@@ -646,7 +646,32 @@ formal_reduce_kernel(int op, int format, const uint8_t *src, uint8_t *dst, const
 // Plain pooling (lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:466-583): every output folds its window in
 // (kh, kw) order with the formal max / min / add, so the roundings and the raised flags are those of the reference's
 // window-by-window elementwise passes. Sum starts from +0 and adds every tap; max / min start from the first tap.
-template <int kCombine, int kFormat>
+// kVec consecutive channels per thread (1 or 4): with 4 the taps move as one 16-byte (f32) or 8-byte (16-bit) access and
+// the index arithmetic is shared; the launcher picks it when channel counts, strides and pointers allow it.
+template <int kVec>
+__device__ __forceinline__ void load_channels(const uint8_t *base, int64_t index, int format, uint32_t (&v)[kVec]) {
+  if (kVec == 1) {
+    v[0] = load_element_bits(base, index, format);
+  } else if (format == WB200_F32) {
+    const uint4 w = *reinterpret_cast<const uint4 *>(base + index * 4);
+    v[0] = w.x; v[1 % kVec] = w.y; v[2 % kVec] = w.z; v[3 % kVec] = w.w;
+  } else {
+    const uint2 w = *reinterpret_cast<const uint2 *>(base + index * 2);
+    v[0] = w.x & 0xffffu; v[1 % kVec] = w.x >> 16; v[2 % kVec] = w.y & 0xffffu; v[3 % kVec] = w.y >> 16;
+  }
+}
+template <int kVec>
+__device__ __forceinline__ void store_channels(uint8_t *base, int64_t index, int format, const uint32_t (&v)[kVec]) {
+  if (kVec == 1) {
+    store_element_bits(base, index, format, v[0]);
+  } else if (format == WB200_F32) {
+    *reinterpret_cast<uint4 *>(base + index * 4) = make_uint4(v[0], v[1 % kVec], v[2 % kVec], v[3 % kVec]);
+  } else {
+    *reinterpret_cast<uint2 *>(base + index * 2) = make_uint2((v[0] & 0xffffu) | (v[1 % kVec] << 16), (v[2 % kVec] & 0xffffu) | (v[3 % kVec] << 16));
+  }
+}
+
+template <int kCombine, int kFormat, int kVec>
 __global__ void __launch_bounds__(kThreads)
 formal_pool_kernel(const uint8_t *src, uint8_t *dst, const LayoutMap src_map, const LayoutMap dst_map,
                    const PoolWindow window, uint32_t *flags_word) {
@@ -654,28 +679,33 @@ formal_pool_kernel(const uint8_t *src, uint8_t *dst, const LayoutMap src_map, co
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   uint32_t flags = 0;
   const uint32_t out_h = static_cast<uint32_t>(dst_map.shape[1]), out_w = static_cast<uint32_t>(dst_map.shape[2]);
-  const uint32_t channels = static_cast<uint32_t>(dst_map.shape[3]), in_w = static_cast<uint32_t>(src_map.shape[2]);
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < dst_map.element_count; i += stride) {
+  const uint32_t channel_groups = static_cast<uint32_t>(dst_map.shape[3]) / kVec, in_w = static_cast<uint32_t>(src_map.shape[2]);
+  const int64_t total = dst_map.element_count / kVec;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
     const uint32_t index = static_cast<uint32_t>(i);          // the launcher admits at most 2^32 - 1 outputs
-    const uint32_t pixel = index / channels, c = index - pixel * channels;
+    const uint32_t pixel = index / channel_groups, c = (index - pixel * channel_groups) * kVec;
     const uint32_t row = pixel / out_w, w = pixel - row * out_w;
     const uint32_t n = row / out_h, h = row - n * out_h;
-    uint32_t result = 0;
+    uint32_t result[kVec];
     const int64_t full_c = src_map.cx_blocks * src_map.c_block;
     const int64_t width = static_cast<int64_t>(c) < full_c ? src_map.c_block : src_map.c0;   // taps of one channel move by constant strides
     const int64_t corner = physical_index_nhwc(src_map, n, static_cast<int64_t>(h * window.stride_h) * in_w + w * window.stride_w, c);
     for (uint32_t kh = 0; kh < window.kernel_h; ++kh)
       for (uint32_t kw = 0; kw < window.kernel_w; ++kw) {
-        const uint32_t tap = load_element_bits(src, corner + (static_cast<int64_t>(kh) * in_w + kw) * width, format);
-        if (kh == 0 && kw == 0 && combine != WB200_EW_ADD) {
-          result = tap;
-        } else {
+        uint32_t tap[kVec];
+        load_channels<kVec>(src, corner + (static_cast<int64_t>(kh) * in_w + kw) * width, format, tap);
+#pragma unroll
+        for (int v = 0; v < kVec; ++v) {
+          if (kh == 0 && kw == 0) {
+            if (combine != WB200_EW_ADD) { result[v] = tap[v]; continue; }
+            result[v] = 0u;
+          }
           uint32_t element_flags = 0;
-          result = formal_scalar(combine, format, format, result, tap, &element_flags);
+          result[v] = formal_scalar(combine, format, format, result[v], tap[v], &element_flags);
           flags |= element_flags;
         }
       }
-    store_element_bits(dst, physical_index_nhwc(dst_map, n, static_cast<int64_t>(h) * out_w + w, c), format, result);
+    store_channels<kVec>(dst, physical_index_nhwc(dst_map, n, static_cast<int64_t>(h) * out_w + w, c), format, result);
   }
   merge_block_flags(flags_word, flags);
 }
@@ -794,8 +824,17 @@ wb200_status launch_reduce_formal(int op, int format, const uint8_t *src, uint8_
 wb200_status launch_pool_formal(int combine, int format, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map,
                                 const LayoutMap &dst_map, PoolWindow window, uint32_t *flags_word, cudaStream_t stream) {
   if (dst_map.element_count >= (1ll << 32)) return fail(WB200_ERR_LIMIT, "pooling output has more than 2^32 - 1 elements");
-  const int grid = grid_for(dst_map.element_count);
-#define WB200_POOL_LAUNCH(COMBINE, FORMAT) formal_pool_kernel<COMBINE, FORMAT><<<grid, kThreads, 0, stream>>>(src, dst, src_map, dst_map, window, flags_word)
+  // Four channels per thread need every channel run, block and slice to start on a multiple of four elements.
+  auto by_four = [](const LayoutMap &m) {
+    return m.shape[3] % 4 == 0 && m.c_block % 4 == 0 && m.c0 % 4 == 0 && m.outer_slice_stride % 4 == 0;
+  };
+  const bool vec4 = by_four(src_map) && by_four(dst_map) && all_aligned16(src, dst);
+  const int grid = grid_for(dst_map.element_count / (vec4 ? 4 : 1));
+#define WB200_POOL_LAUNCH(COMBINE, FORMAT)                                                                                      \
+  do {                                                                                                                          \
+    if (vec4) formal_pool_kernel<COMBINE, FORMAT, 4><<<grid, kThreads, 0, stream>>>(src, dst, src_map, dst_map, window, flags_word); \
+    else formal_pool_kernel<COMBINE, FORMAT, 1><<<grid, kThreads, 0, stream>>>(src, dst, src_map, dst_map, window, flags_word);     \
+  } while (0)
 #define WB200_POOL_FORMATS(COMBINE)                                             \
   if (format == WB200_F32) WB200_POOL_LAUNCH(COMBINE, WB200_F32);               \
   else if (format == WB200_BF16) WB200_POOL_LAUNCH(COMBINE, WB200_BF16);        \
