@@ -1,7 +1,7 @@
 // Flash-attention prefill on CUDA cores, f32 arithmetic throughout: the path for f32 storage (where
 // the 1e-5 parity bound rules out tensor-core inputs narrower than f32) and for shapes the tcgen05
-// kernel does not take. One warp owns one query row and walks the keys in tiles of 32, applying the
-// reference's online update literally
+// kernel does not take. One warp owns one query row and walks the keys in tiles of 32 that the block's sixteen
+// rows share through shared memory, applying the reference's online update literally
 // (lib/Wafer/Transforms/Linalg/OnlineAttentionDecomposition.cpp:568-594):
 //   s = (q.k)*scale (+mask); m' = max(m, max s); m_e = (m' == -inf ? 0 : m'); alpha = ExpLp(m - m_e);
 //   l = l*alpha + sum ExpLp(s - m_e); acc = acc*alpha + round_to_storage(P) V
@@ -12,8 +12,9 @@
 namespace wb200 {
 namespace {
 
-constexpr int kWarpsPerBlock = 4;
-constexpr int kMaxDPerLane = 8;  // head_dim <= 256
+constexpr int kWarpsPerBlock = 16;   // query rows of one head per block; they share every staged K / V tile
+constexpr int kMaxDPerLane = 8;      // head_dim <= 256
+constexpr int kTileKeys = 32;
 
 struct SimtParams {
   AttentionArgs a;
@@ -23,43 +24,61 @@ struct SimtParams {
 
 __device__ __forceinline__ float exp_lp(float x) { return exp2f(__fmul_rn(x, 0x1.715476p+0f)); }
 
+// Shared memory: q rows [kWarpsPerBlock][D], the K tile [32][D + 1] (the pad keeps the per-lane row reads of the score
+// loop on distinct banks) and the V tile [32][D], all widened to f32 once per block instead of once per query row.
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) fa_simt_kernel(const SimtParams p) {
   const AttentionArgs &a = p.a;
-  extern __shared__ float q_smem[];  // [kWarpsPerBlock][head_dim]
+  extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * kWarpsPerBlock + warp;
   const int bh = blockIdx.y;
   const int b = bh / a.q_heads, h = bh % a.q_heads;
   const int D = a.head_dim;
   const int per_lane = D / 32;
-  if (row >= a.q_len) return;
+  const bool active = row < a.q_len;
+  float *q_smem = smem, *k_tile = smem + kWarpsPerBlock * D, *v_tile = k_tile + kTileKeys * (D + 1);
 
-  const size_t q_off = (static_cast<size_t>(bh) * a.q_len + row) * D;
+  const size_t q_off = (static_cast<size_t>(bh) * a.q_len + (active ? row : 0)) * D;
   const size_t kv_off = (static_cast<size_t>(b) * a.kv_heads + h / p.group) * static_cast<size_t>(a.kv_len) * D;
   const uint8_t *q = static_cast<const uint8_t *>(a.q);
   const uint8_t *k = static_cast<const uint8_t *>(a.k);
   const uint8_t *v = static_cast<const uint8_t *>(a.v);
   float *my_q = q_smem + warp * D;
-  for (int d = lane; d < D; d += 32) my_q[d] = widen_bits(load_element_bits(q, q_off + d, a.format), a.format);
-  __syncwarp();
+  if (active)
+    for (int d = lane; d < D; d += 32) my_q[d] = widen_bits(load_element_bits(q, q_off + d, a.format), a.format);
 
-  long long last = static_cast<long long>(p.kv_visible) - 1;
-  if (a.causal && a.causal_offset + row < last) last = a.causal_offset + row;
-  const int visible = last < 0 ? 0 : static_cast<int>(last + 1);
+  auto visible_of = [&](int r) {
+    long long last = static_cast<long long>(p.kv_visible) - 1;
+    if (a.causal && a.causal_offset + r < last) last = a.causal_offset + r;
+    return last < 0 ? 0 : static_cast<int>(last + 1);
+  };
+  const int visible = active ? visible_of(row) : 0;
+  // the last row of the block sees the most keys
+  const int last_row = min(static_cast<int>(blockIdx.x) * kWarpsPerBlock + kWarpsPerBlock - 1, a.q_len - 1);
+  const int block_visible = visible_of(last_row);
 
   float m_run = -INFINITY, l_run = 0.0f;
   float acc[kMaxDPerLane];
 #pragma unroll
   for (int i = 0; i < kMaxDPerLane; ++i) acc[i] = 0.0f;
 
-  for (int key0 = 0; key0 < visible; key0 += 32) {
+  for (int key0 = 0; key0 < block_visible; key0 += kTileKeys) {
+    __syncthreads();   // the previous tile has been consumed (and, first time round, the q rows are written)
+    const int tile_keys = min(kTileKeys, block_visible - key0);
+    for (int e = threadIdx.x; e < tile_keys * D; e += kWarpsPerBlock * 32) {
+      const int j = e / D, d = e - j * D;
+      const size_t at = kv_off + static_cast<size_t>(key0 + j) * D + d;
+      k_tile[j * (D + 1) + d] = widen_bits(load_element_bits(k, at, a.format), a.format);
+      v_tile[j * D + d] = widen_bits(load_element_bits(v, at, a.format), a.format);
+    }
+    __syncthreads();
+    if (key0 >= visible) continue;   // this row's keys ended in an earlier tile (causal rows above the block's last)
     const int key = key0 + lane;
     float s = -INFINITY;
     if (key < visible) {
       float dot = 0.0f;
-      const size_t k_row = kv_off + static_cast<size_t>(key) * D;
-      for (int d = 0; d < D; ++d)
-        dot = __fmaf_rn(my_q[d], widen_bits(load_element_bits(k, k_row + d, a.format), a.format), dot);
+      const float *k_row = k_tile + lane * (D + 1);
+      for (int d = 0; d < D; ++d) dot = __fmaf_rn(my_q[d], k_row[d], dot);
       s = __fmul_rn(dot, a.scale);
     }
     float tile_max = s;
@@ -78,16 +97,16 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) fa_simt_kernel(const Simt
     const float prob_rounded = widen_bits(narrow_bits(prob, a.format), a.format);
 #pragma unroll
     for (int i = 0; i < kMaxDPerLane; ++i) acc[i] = __fmul_rn(acc[i], alpha);
-    const int count = min(32, visible - key0);
+    const int count = min(kTileKeys, visible - key0);
     for (int j = 0; j < count; ++j) {
       const float pj = __shfl_sync(0xffffffffu, prob_rounded, j);
-      const size_t v_row = kv_off + static_cast<size_t>(key0 + j) * D;
+      const float *v_row = v_tile + j * D;
 #pragma unroll
       for (int i = 0; i < kMaxDPerLane; ++i)
-        if (i < per_lane)
-          acc[i] = __fmaf_rn(pj, widen_bits(load_element_bits(v, v_row + i * 32 + lane, a.format), a.format), acc[i]);
+        if (i < per_lane) acc[i] = __fmaf_rn(pj, v_row[i * 32 + lane], acc[i]);
     }
   }
+  if (!active) return;
 
   float coefficient = __fdiv_rn(1.0f, l_run);
   if (a.zero_fully_masked && l_run == 0.0f) coefficient = 0.0f;
@@ -119,7 +138,10 @@ wb200_status launch_attention_fa_simt(const AttentionArgs &a, cudaStream_t strea
   int64_t visible = a.kv_valid < a.kv_len ? a.kv_valid : a.kv_len;
   p.kv_visible = visible < 0 ? 0 : static_cast<int>(visible);
   dim3 grid((a.q_len + kWarpsPerBlock - 1) / kWarpsPerBlock, a.batch * a.q_heads);
-  fa_simt_kernel<<<grid, kWarpsPerBlock * 32, kWarpsPerBlock * a.head_dim * sizeof(float), stream>>>(p);
+  const size_t smem_bytes = (static_cast<size_t>(kWarpsPerBlock) * a.head_dim + kTileKeys * (a.head_dim + 1) + kTileKeys * a.head_dim) * sizeof(float);
+  if (smem_bytes > 48 * 1024)
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(fa_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)));
+  fa_simt_kernel<<<grid, kWarpsPerBlock * 32, smem_bytes, stream>>>(p);
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }
