@@ -55,15 +55,42 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs: an NVML polling thread (a reading every
+    millisecond or so, since the timed region lasts only milliseconds), or nvidia-smi when NVML cannot be loaded."""
     QUERY = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, device_index: int):
         self.device_index = device_index
         self.proc = None
+        self.thread = None
+        self.samples, self.reason_bits, self.max_clock = [], 0, None
+
+    def _poll(self, nvml, handle):
+        while not self.stop.is_set():
+            try:
+                self.samples.append(float(nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM)))
+                self.reason_bits |= int(nvml.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+            except Exception:
+                break
+            time.sleep(0.0005)
 
     def __enter__(self):
+        try:
+            import pynvml as nvml
+            import threading
+            nvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            index = int(visible.split(",")[self.device_index]) if visible and visible.split(",")[self.device_index].isdigit() else self.device_index
+            handle = nvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_clock = float(nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM))
+            self.stop = threading.Event()
+            self.thread = threading.Thread(target=self._poll, args=(nvml, handle), daemon=True)
+            self.thread.start()
+            return self
+        except Exception:
+            self.thread = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
                                           "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -73,6 +100,14 @@ class ClockSampler:
 
     def __exit__(self, *exc):
         self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.thread:
+            self.stop.set()
+            self.thread.join(timeout=2)
+            if self.samples:
+                reasons = sorted(name for bit, name in self.REASON_BITS.items() if self.reason_bits & bit)
+                self.result = {"sm_mhz": statistics.median(self.samples), "sm_min_mhz": min(self.samples), "sm_max_mhz": self.max_clock,
+                               "reasons": reasons, "samples": len(self.samples), "source": "nvml"}
+            return
         if not self.proc:
             return
         time.sleep(0.15)
@@ -96,7 +131,8 @@ class ClockSampler:
                 if value.lower().startswith("active"):
                     reasons.add(name)
         if clocks:
-            self.result = {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max_clock, "reasons": sorted(reasons), "samples": len(clocks)}
+            self.result = {"sm_mhz": statistics.median(clocks), "sm_max_mhz": max_clock, "reasons": sorted(reasons), "samples": len(clocks),
+                           "source": "nvidia-smi"}
 
 
 def timed_steps(fn, steps, warmup, torch, dist=None, check=None):
