@@ -20,12 +20,15 @@ struct SimtParams {
   AttentionArgs a;
   int group;
   int kv_visible;
+  int vector;   // K and V are 16-byte aligned: the staging loop may use wide loads
 };
 
 __device__ __forceinline__ float exp_lp(float x) { return exp2f(__fmul_rn(x, 0x1.715476p+0f)); }
 
 // Shared memory: q rows [kWarpsPerBlock][D], the K tile [32][D + 1] (the pad keeps the per-lane row reads of the score
 // loop on distinct banks) and the V tile [32][D], all widened to f32 once per block instead of once per query row.
+// kD fixes head_dim at compile time (0: runtime) so the score and PV loops unroll and their shared-memory reads pipeline.
+template <int kD>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) fa_simt_kernel(const SimtParams p) {
   const AttentionArgs &a = p.a;
   extern __shared__ float smem[];
@@ -33,7 +36,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) fa_simt_kernel(const Simt
   const int row = blockIdx.x * kWarpsPerBlock + warp;
   const int bh = blockIdx.y;
   const int b = bh / a.q_heads, h = bh % a.q_heads;
-  const int D = a.head_dim;
+  const int D = kD ? kD : a.head_dim;
   const int per_lane = D / 32;
   const bool active = row < a.q_len;
   float *q_smem = smem, *k_tile = smem + kWarpsPerBlock * D, *v_tile = k_tile + kTileKeys * (D + 1);
@@ -65,12 +68,37 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) fa_simt_kernel(const Simt
   for (int key0 = 0; key0 < block_visible; key0 += kTileKeys) {
     __syncthreads();   // the previous tile has been consumed (and, first time round, the q rows are written)
     const int tile_keys = min(kTileKeys, block_visible - key0);
-    for (int e = threadIdx.x; e < tile_keys * D; e += kWarpsPerBlock * 32) {
-      const int j = e / D, d = e - j * D;
+    // four consecutive elements per thread and step (head_dim is a multiple of 32): the loads of a step are issued
+    // together, 128 bits wide for f32 storage and 64 bits wide for the 16-bit formats
+    const int quads = p.vector ? tile_keys * D / 4 : 0;
+    for (int e = threadIdx.x; e < quads; e += kWarpsPerBlock * 32) {
+      const int j = (e * 4) / D, d = e * 4 - j * D;
       const size_t at = kv_off + static_cast<size_t>(key0 + j) * D + d;
-      k_tile[j * (D + 1) + d] = widen_bits(load_element_bits(k, at, a.format), a.format);
-      v_tile[j * D + d] = widen_bits(load_element_bits(v, at, a.format), a.format);
+      float kf[4], vf[4];
+      if (a.format == WB200_F32) {
+        const float4 kq = *reinterpret_cast<const float4 *>(k + at * 4), vq = *reinterpret_cast<const float4 *>(v + at * 4);
+        kf[0] = kq.x; kf[1] = kq.y; kf[2] = kq.z; kf[3] = kq.w;
+        vf[0] = vq.x; vf[1] = vq.y; vf[2] = vq.z; vf[3] = vq.w;
+      } else {
+        const uint2 kq = *reinterpret_cast<const uint2 *>(k + at * 2), vq = *reinterpret_cast<const uint2 *>(v + at * 2);
+        kf[0] = widen_bits(kq.x & 0xffffu, a.format); kf[1] = widen_bits(kq.x >> 16, a.format);
+        kf[2] = widen_bits(kq.y & 0xffffu, a.format); kf[3] = widen_bits(kq.y >> 16, a.format);
+        vf[0] = widen_bits(vq.x & 0xffffu, a.format); vf[1] = widen_bits(vq.x >> 16, a.format);
+        vf[2] = widen_bits(vq.y & 0xffffu, a.format); vf[3] = widen_bits(vq.y >> 16, a.format);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        k_tile[j * (D + 1) + d + i] = kf[i];
+        v_tile[j * D + d + i] = vf[i];
+      }
     }
+    if (!p.vector)
+      for (int e = threadIdx.x; e < tile_keys * D; e += kWarpsPerBlock * 32) {
+        const int j = e / D, d = e - j * D;
+        const size_t at = kv_off + static_cast<size_t>(key0 + j) * D + d;
+        k_tile[j * (D + 1) + d] = widen_bits(load_element_bits(k, at, a.format), a.format);
+        v_tile[j * D + d] = widen_bits(load_element_bits(v, at, a.format), a.format);
+      }
     __syncthreads();
     if (key0 >= visible) continue;   // this row's keys ended in an earlier tile (causal rows above the block's last)
     const int key = key0 + lane;
@@ -78,6 +106,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) fa_simt_kernel(const Simt
     if (key < visible) {
       float dot = 0.0f;
       const float *k_row = k_tile + lane * (D + 1);
+#pragma unroll 16
       for (int d = 0; d < D; ++d) dot = __fmaf_rn(my_q[d], k_row[d], dot);
       s = __fmul_rn(dot, a.scale);
     }
@@ -98,6 +127,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32) fa_simt_kernel(const Simt
 #pragma unroll
     for (int i = 0; i < kMaxDPerLane; ++i) acc[i] = __fmul_rn(acc[i], alpha);
     const int count = min(kTileKeys, visible - key0);
+#pragma unroll 8
     for (int j = 0; j < count; ++j) {
       const float pj = __shfl_sync(0xffffffffu, prob_rounded, j);
       const float *v_row = v_tile + j * D;
@@ -139,9 +169,18 @@ wb200_status launch_attention_fa_simt(const AttentionArgs &a, cudaStream_t strea
   p.kv_visible = visible < 0 ? 0 : static_cast<int>(visible);
   dim3 grid((a.q_len + kWarpsPerBlock - 1) / kWarpsPerBlock, a.batch * a.q_heads);
   const size_t smem_bytes = (static_cast<size_t>(kWarpsPerBlock) * a.head_dim + kTileKeys * (a.head_dim + 1) + kTileKeys * a.head_dim) * sizeof(float);
-  if (smem_bytes > 48 * 1024)
-    WB200_CUDA_CHECK(cudaFuncSetAttribute(fa_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)));
-  fa_simt_kernel<<<grid, kWarpsPerBlock * 32, smem_bytes, stream>>>(p);
+  // wide staging loads need 16-byte aligned K / V bases; head_dim % 32 == 0 keeps every row aligned
+  p.vector = ((reinterpret_cast<uintptr_t>(a.k) | reinterpret_cast<uintptr_t>(a.v)) & 15) == 0;
+#define WB200_SIMT_LAUNCH(KD)                                                                                                  \
+  do {                                                                                                                         \
+    if (smem_bytes > 48 * 1024)                                                                                                \
+      WB200_CUDA_CHECK(cudaFuncSetAttribute(fa_simt_kernel<KD>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes))); \
+    fa_simt_kernel<KD><<<grid, kWarpsPerBlock * 32, smem_bytes, stream>>>(p);                                                  \
+  } while (0)
+  if (a.head_dim == 64) WB200_SIMT_LAUNCH(64);
+  else if (a.head_dim == 128) WB200_SIMT_LAUNCH(128);
+  else WB200_SIMT_LAUNCH(0);
+#undef WB200_SIMT_LAUNCH
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }
