@@ -90,6 +90,22 @@ int main() {
   auto rejected = backend->execute(add, FormalNumericWorkBudget{});
   if (rejected || rejected.status() != WB200_ERR_NAN_DOMAIN) { std::printf("NaN input was not rejected\n"); return 16; }
 
+  // The formal family takes the same request: the NaN element becomes the canonical quiet NaN instead of a refusal, the
+  // other elements are the same sums, and 1 + 0.5 ... are exact so only no flag or the inexact flag may be raised.
+  auto formal = backend->execute(add, FormalNumericWorkBudget{}, /*formal=*/true);
+  if (!formal) { std::printf("formal execute(add) failed: %s\n", formal.message().c_str()); return 17; }
+  const std::vector<float> formal_got = unpack_f32(raw, vec, formal->destination.storage, 8);
+  for (int i = 0; i < 8; ++i) {
+    if (i == 3) {
+      uint32_t bits;
+      std::memcpy(&bits, &formal_got[i], sizeof(bits));
+      if (bits != 0x7fc00000u) { std::printf("formal NaN is not canonical\n"); return 18; }
+    } else if (formal_got[i] != got[i]) {
+      return 19;
+    }
+  }
+  if (formal->evidence.flags & ~16u) { std::printf("unexpected formal flags %u\n", formal->evidence.flags); return 20; }
+
   wb200_backend_destroy(raw);
   std::printf("PASS\n");
   return 0;

@@ -158,8 +158,11 @@ public:
     return Out(std::optional<TargetModelB200Result>(std::move(result)));
   }
 
+  // `formal` selects the bit-exact family the reference falls back to when its managed backend declines a request
+  // (NaN operands, relations, logic, IEEE flags in evidence.flags): wb200_elementwise_formal / wb200_convert_formal /
+  // wb200_reduce_formal in place of the managed entries.
   Expected<TargetModelB200Result> execute(const TargetModelElementwiseRequest &request,
-                                          FormalNumericWorkBudget scalarBudget) const {
+                                          FormalNumericWorkBudget scalarBudget, bool formal = false) const {
     using Out = Expected<TargetModelB200Result>;
     const auto &op = request.operation;
     if (request.tensors.inputs.size() != op.inputs.size() || op.inputs.size() > 2)
@@ -178,13 +181,13 @@ public:
     r.destination_out = result.destination.storage.data();
     r.destination_bytes = result.destination.storage.size();
     r.max_scalar_evaluations = scalarBudget.maximumScalarEvaluations;
-    wb200_status st = wb200_elementwise(handle_, &r, &result.evidence);
+    wb200_status st = formal ? wb200_elementwise_formal(handle_, &r, &result.evidence) : wb200_elementwise(handle_, &r, &result.evidence);
     if (st != WB200_OK) return Out::failure(st, wb200_last_error());
     return Out(std::move(result));
   }
 
   Expected<TargetModelB200Result> execute(const TargetModelConvertRequest &request,
-                                          FormalNumericWorkBudget scalarBudget) const {
+                                          FormalNumericWorkBudget scalarBudget, bool formal = false) const {
     using Out = Expected<TargetModelB200Result>;
     if (request.tensors.inputs.size() != 1) return Out::failure(WB200_ERR_INVALID_ARGUMENT, "convert takes one input");
     const auto &op = request.operation;
@@ -199,13 +202,13 @@ public:
     r.destination_out = result.destination.storage.data();
     r.destination_bytes = result.destination.storage.size();
     r.max_scalar_evaluations = scalarBudget.maximumScalarEvaluations;
-    wb200_status st = wb200_convert(handle_, &r, &result.evidence);
+    wb200_status st = formal ? wb200_convert_formal(handle_, &r, &result.evidence) : wb200_convert(handle_, &r, &result.evidence);
     if (st != WB200_OK) return Out::failure(st, wb200_last_error());
     return Out(std::move(result));
   }
 
   Expected<TargetModelB200Result> execute(const TargetModelReduceRequest &request,
-                                          FormalNumericWorkBudget scalarBudget) const {
+                                          FormalNumericWorkBudget scalarBudget, bool formal = false) const {
     using Out = Expected<TargetModelB200Result>;
     if (request.tensors.inputs.size() != 1) return Out::failure(WB200_ERR_INVALID_ARGUMENT, "reduce takes one input");
     const auto &op = request.operation;
@@ -220,7 +223,7 @@ public:
     r.destination_out = result.destination.storage.data();
     r.destination_bytes = result.destination.storage.size();
     r.max_scalar_evaluations = scalarBudget.maximumScalarEvaluations;
-    wb200_status st = wb200_reduce(handle_, &r, &result.evidence);
+    wb200_status st = formal ? wb200_reduce_formal(handle_, &r, &result.evidence) : wb200_reduce(handle_, &r, &result.evidence);
     if (st != WB200_OK) return Out::failure(st, wb200_last_error());
     return Out(std::move(result));
   }
