@@ -1,0 +1,51 @@
+"""Replay time of the shipped GEMM Tile programs (16 Tiles x 7 plans, out[4096,4096] = arg1[4096,1024] . arg0[1024,4096], bf16).
+
+    python -m vibe_compiler_b200.microbench.replay [--plan NAME] [--runs N] [--fixture tests/golden/gemm_tile_modules.json.xz]
+
+Prints one JSON line per plan: commands, kernel launches and the device time of the command stream (CUDA events inside
+wb200_tile_program_run; host <-> device tensor copies excluded). WB200_REPLAY_GRAPH=0 in the environment replays the
+commands one by one on a single stream (the form a per-kernel launch list is taken from); the default relaunches the
+captured CUDA graph.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import lzma
+import statistics
+from pathlib import Path
+
+import numpy as np
+
+from ..backend import B200TargetModelBackend
+from ..tile_program import TileProgram
+
+
+def main(argv=None) -> int:
+    root = Path(__file__).resolve().parents[2]
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--plan", default="", help="only the plans whose name contains this text")
+    parser.add_argument("--runs", type=int, default=5)
+    parser.add_argument("--fixture", default=str(root / "tests" / "golden" / "gemm_tile_modules.json.xz"))
+    args = parser.parse_args(argv)
+    fixture = json.loads(lzma.decompress(Path(args.fixture).read_bytes()))
+    backend = B200TargetModelBackend(0)
+    rng = np.random.default_rng(20260803)
+    for plan in sorted(fixture["plans"]):
+        if args.plan not in plan:
+            continue
+        program = TileProgram(fixture["plans"][plan], backend)
+        inputs = [rng.integers(0x3c00, 0x4000, size=t.shape, dtype=np.uint16) for t in program.inputs]   # bf16 values in [0.0078, 2)
+        times, stats = [], None
+        for _ in range(max(2, args.runs)):
+            _, stats = program.run(inputs)
+            times.append(stats["device_ms"])
+        print(json.dumps({"plan": plan, "commands": stats["commands"], "gemm_commands": stats["gemm_commands"],
+                          "movement_commands": stats["movement_commands"], "gpu_launches": stats["gpu_launches"],
+                          "device_ms_first": round(times[0], 3), "device_ms": round(statistics.median(times[1:]), 3)}), flush=True)
+        program.close()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
