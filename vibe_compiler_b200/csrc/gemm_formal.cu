@@ -17,12 +17,15 @@ constexpr int kTile = 16;
 // Physical element index of element (batch, row, col) of a logical [batch, rows, cols] GEMM operand without the
 // divisions of the general row-major-to-physical map (64-bit divisions dominated the kernels' time): the operand's
 // coordinates are already known. Cx of rank 2 / 3 and NCx of rank 3 are resolved here, anything else falls back.
+// kResolved: the host has checked that every operand is in one of the resolved forms, so the general map (and its
+// divisions, which otherwise bloat the unrolled loops past the instruction cache) is not even compiled in.
+template <bool kResolved = false>
 __device__ __forceinline__ int64_t operand_index(const LayoutMap &map, int64_t batch, int64_t rows, int64_t row, int64_t cols, int64_t col) {
   const int64_t outer_all = batch * rows + row;
   if (map.layout == WB200_LAYOUT_TENSOR || map.layout == WB200_LAYOUT_NTENSOR) return outer_all * cols + col;
   const bool ncx3 = map.layout == WB200_LAYOUT_NCX && map.rank == 3;
   const bool cx = map.layout == WB200_LAYOUT_CX && (map.rank == 2 || map.rank == 3);
-  if (!(ncx3 || cx) || (map.c_block & (map.c_block - 1)) != 0) return physical_index(map, outer_all * cols + col);
+  if (!kResolved && (!(ncx3 || cx) || (map.c_block & (map.c_block - 1)) != 0)) return physical_index(map, outer_all * cols + col);
   const int64_t base = ncx3 ? batch * map.outer_slice_stride : 0;
   const int64_t outer = ncx3 ? row : outer_all;
   const int64_t full_c = map.cx_blocks * map.c_block;
@@ -94,7 +97,8 @@ __global__ void __launch_bounds__(kTile *kTile) gemm_formal_kernel(const FormalP
 // m * n * k FMAs per command, 0.5 shared-memory loads per FMA.
 constexpr int kBlockM = 64, kBlockN = 64, kPanelK = 16;
 
-__global__ void __launch_bounds__(256) gemm_formal_tiled_kernel(const FormalParams p) {
+template <bool kResolved>
+__global__ void __launch_bounds__(256, 4) gemm_formal_tiled_kernel(const FormalParams p) {
   const GemmFormalArgs &a = p.a;
   __shared__ float lhs_panel[kPanelK][kBlockM];   // [k][m]
   __shared__ float rhs_panel[kPanelK][kBlockN];   // [k][n]
@@ -117,8 +121,8 @@ __global__ void __launch_bounds__(256) gemm_formal_tiled_kernel(const FormalPara
       if (a.lhs_transposed) { r = index & 63; kk = index >> 6; } else { kk = index & 15; r = index >> 4; }
       float value = 0.0f;
       if (row0 + r < a.m && k0 + kk < a.k) {
-        const int64_t at = a.lhs_transposed ? operand_index(a.lhs_map, batch, a.k, k0 + kk, a.m, row0 + r)
-                                            : operand_index(a.lhs_map, batch, a.m, row0 + r, a.k, k0 + kk);
+        const int64_t at = a.lhs_transposed ? operand_index<kResolved>(a.lhs_map, batch, a.k, k0 + kk, a.m, row0 + r)
+                                            : operand_index<kResolved>(a.lhs_map, batch, a.m, row0 + r, a.k, k0 + kk);
         value = widen_bits(load_element_bits(a.lhs, at, a.in_format), a.in_format);
       }
       lhs_panel[kk][r] = value;
@@ -130,8 +134,8 @@ __global__ void __launch_bounds__(256) gemm_formal_tiled_kernel(const FormalPara
       if (a.rhs_transposed) { kk = index & 15; c = index >> 4; } else { c = index & 63; kk = index >> 6; }
       float value = 0.0f;
       if (col0 + c < a.n && k0 + kk < a.k) {
-        const int64_t at = a.rhs_transposed ? operand_index(a.rhs_map, batch, a.n, col0 + c, a.k, k0 + kk)
-                                            : operand_index(a.rhs_map, batch, a.k, k0 + kk, a.n, col0 + c);
+        const int64_t at = a.rhs_transposed ? operand_index<kResolved>(a.rhs_map, batch, a.n, col0 + c, a.k, k0 + kk)
+                                            : operand_index<kResolved>(a.rhs_map, batch, a.k, k0 + kk, a.n, col0 + c);
         value = widen_bits(load_element_bits(a.rhs, at, a.in_format), a.in_format);
       }
       rhs_panel[kk][c] = value;
@@ -158,8 +162,8 @@ __global__ void __launch_bounds__(256) gemm_formal_tiled_kernel(const FormalPara
       const int row = row0 + ty + 16 * i, col = col0 + tx + 16 * j;
       if (row < a.m && col < a.n) {
         float value = acc[i][j];
-        if (a.has_psum) value = __fadd_rn(value, __uint_as_float(load_element_bits(a.psum, operand_index(a.psum_map, batch, a.m, row, a.n, col), WB200_F32)));
-        store_element_bits(a.dst, operand_index(a.dst_map, batch, a.m, row, a.n, col), a.out_format, narrow_bits(value, a.out_format));
+        if (a.has_psum) value = __fadd_rn(value, __uint_as_float(load_element_bits(a.psum, operand_index<kResolved>(a.psum_map, batch, a.m, row, a.n, col), WB200_F32)));
+        store_element_bits(a.dst, operand_index<kResolved>(a.dst_map, batch, a.m, row, a.n, col), a.out_format, narrow_bits(value, a.out_format));
       }
     }
 }
@@ -175,7 +179,15 @@ wb200_status launch_gemm_formal(const GemmFormalArgs &args, cudaStream_t stream)
   FormalParams p{args};
   if (args.m >= 32 && args.n >= 32) {
     dim3 grid((args.n + kBlockN - 1) / kBlockN, (args.m + kBlockM - 1) / kBlockM, args.batch);
-    gemm_formal_tiled_kernel<<<grid, 256, 0, stream>>>(p);
+    auto resolved = [](const LayoutMap &m) {
+      if (m.layout == WB200_LAYOUT_TENSOR || m.layout == WB200_LAYOUT_NTENSOR) return true;
+      const bool ncx3 = m.layout == WB200_LAYOUT_NCX && m.rank == 3, cx = m.layout == WB200_LAYOUT_CX && (m.rank == 2 || m.rank == 3);
+      return (ncx3 || cx) && (m.c_block & (m.c_block - 1)) == 0;
+    };
+    if (resolved(args.lhs_map) && resolved(args.rhs_map) && resolved(args.dst_map) && (!args.has_psum || resolved(args.psum_map)))
+      gemm_formal_tiled_kernel<true><<<grid, 256, 0, stream>>>(p);
+    else
+      gemm_formal_tiled_kernel<false><<<grid, 256, 0, stream>>>(p);
     WB200_CUDA_CHECK(cudaGetLastError());
     return WB200_OK;
   }

@@ -83,6 +83,16 @@ def main(argv=None) -> int:
     out_shape = (shape[0], 32, 32, 64)
     report("formal_pool max f32 2x2 stride 2", 4 * count + 4 * count // 4,
            (lambda: pad.pool("max", a_at, c_at, shape, out_shape, (2, 2, 2, 2), abi.F32)))
+    # one bit-exact GEMM command of the shipped Tile programs: Cx operands in place, bf16 -> f32 with an f32 partial sum
+    gm, gk, gn = 256, 256, 1024
+    from ..backend import PhysicalTensorDescriptor as _Desc
+    sizes = [backend.physical_bytes(_Desc(abi.BF16, abi.LAYOUT_CX, [gm, gk])), backend.physical_bytes(_Desc(abi.BF16, abi.LAYOUT_CX, [gk, gn])),
+             backend.physical_bytes(_Desc(abi.F32, abi.LAYOUT_CX, [gm, gn]))]
+    lhs_at, rhs_at = 0, (sizes[0] + 0xfff) & ~0xfff
+    dst_at = rhs_at + ((sizes[1] + 0xfff) & ~0xfff)
+    psum_at = dst_at + ((sizes[2] + 0xfff) & ~0xfff)
+    report(f"formal GEMM command {gm}x{gk}x{gn} bf16 -> f32 + psum (FMAs as bytes: 2 flop each)", 2 * gm * gk * gn,
+           (lambda: pad.gemm(lhs_at, rhs_at, dst_at, gm, gk, gn, in_format=abi.BF16, out_format=abi.F32, psum=psum_at, psum_format=abi.F32)))
     # seam-1 commands take host storage (the reference passes std::vector bytes): the kernel time comes from the
     # evidence's device_us, the call time is dominated by the two host <-> device copies
     from ..backend import NumericTensor, PhysicalTensorDescriptor
