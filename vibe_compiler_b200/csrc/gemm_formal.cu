@@ -36,6 +36,25 @@ __device__ __forceinline__ int64_t operand_index(const LayoutMap &map, int64_t b
   return base + map.cx_blocks * map.block_outer_elements * map.c_block + outer * map.c0 + (col - full_c);
 }
 
+// For Tensor layouts and for Cx / NCx operands without a channel tail the physical index separates into a part that
+// depends on the row only and a part that depends on the column only: index = row_part + col_part. The tiled kernel uses
+// this to keep the per-element address arithmetic out of its k loop.
+__host__ __device__ inline bool separable_layout(const LayoutMap &m) {
+  if (m.layout == WB200_LAYOUT_TENSOR || m.layout == WB200_LAYOUT_NTENSOR) return true;
+  const bool ncx3 = m.layout == WB200_LAYOUT_NCX && m.rank == 3, cx = m.layout == WB200_LAYOUT_CX && (m.rank == 2 || m.rank == 3);
+  return (ncx3 || cx) && (m.c_block & (m.c_block - 1)) == 0 && m.c0 == 0;
+}
+__device__ __forceinline__ int64_t row_part(const LayoutMap &map, int64_t batch, int64_t rows, int64_t row, int64_t cols) {
+  if (map.layout == WB200_LAYOUT_TENSOR || map.layout == WB200_LAYOUT_NTENSOR) return (batch * rows + row) * cols;
+  if (map.layout == WB200_LAYOUT_NCX) return batch * map.outer_slice_stride + row * map.c_block;
+  return (batch * rows + row) * map.c_block;
+}
+__device__ __forceinline__ int64_t col_part(const LayoutMap &map, int64_t col) {
+  if (map.layout == WB200_LAYOUT_TENSOR || map.layout == WB200_LAYOUT_NTENSOR) return col;
+  const int shift = __ffsll(map.c_block) - 1;
+  return (col >> shift) * (map.block_outer_elements * map.c_block) + (col & (map.c_block - 1));
+}
+
 struct FormalParams {
   GemmFormalArgs a;
 };
@@ -97,57 +116,70 @@ __global__ void __launch_bounds__(kTile *kTile) gemm_formal_kernel(const FormalP
 // m * n * k FMAs per command, 0.5 shared-memory loads per FMA.
 constexpr int kBlockM = 64, kBlockN = 64, kPanelK = 16;
 
-template <bool kResolved>
+template <bool kResolved, bool kSeparable>
 __global__ void __launch_bounds__(256, 4) gemm_formal_tiled_kernel(const FormalParams p) {
   const GemmFormalArgs &a = p.a;
-  __shared__ float lhs_panel[kPanelK][kBlockM];   // [k][m]
-  __shared__ float rhs_panel[kPanelK][kBlockN];   // [k][n]
+  // rows padded by four floats: the k-fastest staging stores of an untransposed lhs (transposed rhs) spread over the
+  // banks, and every row stays 16-byte aligned for the 128-bit reads of the multiply loop
+  __shared__ __align__(16) float lhs_panel[kPanelK][kBlockM + 4];   // [k][m]
+  __shared__ __align__(16) float rhs_panel[kPanelK][kBlockN + 4];   // [k][n]
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int batch = blockIdx.z;
   const int row0 = blockIdx.y * kBlockM, col0 = blockIdx.x * kBlockN;
-  float acc[4][4];
+  float acc[4][4];   // outputs (row0 + ty * 4 + i, col0 + tx * 4 + j)
 #pragma unroll
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
 
+  // Staging: 64 x 16 lhs and 16 x 64 rhs elements per panel, 4 + 4 per thread; consecutive threads take consecutive
+  // elements of the operand's fastest logical dimension. Element e of a thread: flat index threadIdx.x + 256 e.
+  int l_r[4], l_kk[4], r_c[4], r_kk[4];
+  int64_t l_fixed[4], r_fixed[4];   // kSeparable: the part of the address that does not move with the panel
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int index = threadIdx.x + e * 256;
+    if (a.lhs_transposed) { l_r[e] = index & 63; l_kk[e] = index >> 6; } else { l_kk[e] = index & 15; l_r[e] = index >> 4; }
+    if (a.rhs_transposed) { r_kk[e] = index & 15; r_c[e] = index >> 4; } else { r_c[e] = index & 63; r_kk[e] = index >> 6; }
+    if (kSeparable) {
+      // lhs element (m index row0 + r, k index k0 + kk); rhs element (k index k0 + kk, n index col0 + c)
+      l_fixed[e] = a.lhs_transposed ? col_part(a.lhs_map, row0 + l_r[e]) : row_part(a.lhs_map, batch, a.m, row0 + l_r[e], a.k);
+      r_fixed[e] = a.rhs_transposed ? row_part(a.rhs_map, batch, a.n, col0 + r_c[e], a.k) : col_part(a.rhs_map, col0 + r_c[e]);
+    }
+  }
   for (int k0 = 0; k0 < a.k; k0 += kPanelK) {
-    // 64 x 16 lhs and 16 x 64 rhs elements, 4 + 4 per thread; consecutive threads take consecutive elements of the
-    // operand's fastest logical dimension.
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int index = threadIdx.x + e * 256;
-      int r, kk;
-      if (a.lhs_transposed) { r = index & 63; kk = index >> 6; } else { kk = index & 15; r = index >> 4; }
       float value = 0.0f;
-      if (row0 + r < a.m && k0 + kk < a.k) {
-        const int64_t at = a.lhs_transposed ? operand_index<kResolved>(a.lhs_map, batch, a.k, k0 + kk, a.m, row0 + r)
-                                            : operand_index<kResolved>(a.lhs_map, batch, a.m, row0 + r, a.k, k0 + kk);
+      const int k = k0 + l_kk[e];
+      if (row0 + l_r[e] < a.m && k < a.k) {
+        int64_t at;
+        if (kSeparable) at = l_fixed[e] + (a.lhs_transposed ? row_part(a.lhs_map, batch, a.k, k, a.m) : col_part(a.lhs_map, k));
+        else at = a.lhs_transposed ? operand_index<kResolved>(a.lhs_map, batch, a.k, k, a.m, row0 + l_r[e])
+                                   : operand_index<kResolved>(a.lhs_map, batch, a.m, row0 + l_r[e], a.k, k);
         value = widen_bits(load_element_bits(a.lhs, at, a.in_format), a.in_format);
       }
-      lhs_panel[kk][r] = value;
+      lhs_panel[l_kk[e]][l_r[e]] = value;
     }
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const int index = threadIdx.x + e * 256;
-      int c, kk;
-      if (a.rhs_transposed) { kk = index & 15; c = index >> 4; } else { c = index & 63; kk = index >> 6; }
       float value = 0.0f;
-      if (col0 + c < a.n && k0 + kk < a.k) {
-        const int64_t at = a.rhs_transposed ? operand_index<kResolved>(a.rhs_map, batch, a.n, col0 + c, a.k, k0 + kk)
-                                            : operand_index<kResolved>(a.rhs_map, batch, a.k, k0 + kk, a.n, col0 + c);
+      const int k = k0 + r_kk[e];
+      if (col0 + r_c[e] < a.n && k < a.k) {
+        int64_t at;
+        if (kSeparable) at = r_fixed[e] + (a.rhs_transposed ? col_part(a.rhs_map, k) : row_part(a.rhs_map, batch, a.k, k, a.n));
+        else at = a.rhs_transposed ? operand_index<kResolved>(a.rhs_map, batch, a.n, col0 + r_c[e], a.k, k)
+                                   : operand_index<kResolved>(a.rhs_map, batch, a.k, k, a.n, col0 + r_c[e]);
         value = widen_bits(load_element_bits(a.rhs, at, a.in_format), a.in_format);
       }
-      rhs_panel[kk][c] = value;
+      rhs_panel[r_kk[e]][r_c[e]] = value;
     }
     __syncthreads();
     const int k_count = min(kPanelK, a.k - k0);
     for (int kk = 0; kk < k_count; ++kk) {
-      float l[4], r[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) l[i] = lhs_panel[kk][ty + 16 * i];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) r[j] = rhs_panel[kk][tx + 16 * j];
+      const float4 lv = *reinterpret_cast<const float4 *>(&lhs_panel[kk][ty * 4]);
+      const float4 rv = *reinterpret_cast<const float4 *>(&rhs_panel[kk][tx * 4]);
+      const float l[4] = {lv.x, lv.y, lv.z, lv.w}, r[4] = {rv.x, rv.y, rv.z, rv.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -159,7 +191,7 @@ __global__ void __launch_bounds__(256, 4) gemm_formal_tiled_kernel(const FormalP
   for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const int row = row0 + ty + 16 * i, col = col0 + tx + 16 * j;
+      const int row = row0 + ty * 4 + i, col = col0 + tx * 4 + j;
       if (row < a.m && col < a.n) {
         float value = acc[i][j];
         if (a.has_psum) value = __fadd_rn(value, __uint_as_float(load_element_bits(a.psum, operand_index<kResolved>(a.psum_map, batch, a.m, row, a.n, col), WB200_F32)));
@@ -184,10 +216,13 @@ wb200_status launch_gemm_formal(const GemmFormalArgs &args, cudaStream_t stream)
       const bool ncx3 = m.layout == WB200_LAYOUT_NCX && m.rank == 3, cx = m.layout == WB200_LAYOUT_CX && (m.rank == 2 || m.rank == 3);
       return (ncx3 || cx) && (m.c_block & (m.c_block - 1)) == 0;
     };
-    if (resolved(args.lhs_map) && resolved(args.rhs_map) && resolved(args.dst_map) && (!args.has_psum || resolved(args.psum_map)))
-      gemm_formal_tiled_kernel<true><<<grid, 256, 0, stream>>>(p);
+    const bool all_resolved = resolved(args.lhs_map) && resolved(args.rhs_map) && resolved(args.dst_map) && (!args.has_psum || resolved(args.psum_map));
+    if (all_resolved && separable_layout(args.lhs_map) && separable_layout(args.rhs_map))
+      gemm_formal_tiled_kernel<true, true><<<grid, 256, 0, stream>>>(p);
+    else if (all_resolved)
+      gemm_formal_tiled_kernel<true, false><<<grid, 256, 0, stream>>>(p);
     else
-      gemm_formal_tiled_kernel<false><<<grid, 256, 0, stream>>>(p);
+      gemm_formal_tiled_kernel<false, false><<<grid, 256, 0, stream>>>(p);
     WB200_CUDA_CHECK(cudaGetLastError());
     return WB200_OK;
   }
