@@ -116,7 +116,10 @@ __global__ void __launch_bounds__(kTile *kTile) gemm_formal_kernel(const FormalP
 // m * n * k FMAs per command, 0.5 shared-memory loads per FMA.
 constexpr int kBlockM = 64, kBlockN = 64, kPanelK = 16;
 
-template <bool kResolved, bool kSeparable>
+// kWide (implies kSeparable; 16-bit operands, both untransposed, 16-byte aligned bases, k and n multiples of 8): a thread
+// stages eight consecutive elements with one 128-bit load - threads 0..127 a run of lhs along k, threads 128..255 a run of
+// rhs along n - instead of eight 2-byte loads with eight addresses.
+template <bool kResolved, bool kSeparable, bool kWide>
 __global__ void __launch_bounds__(256, 4) gemm_formal_tiled_kernel(const FormalParams p) {
   const GemmFormalArgs &a = p.a;
   // rows padded by four floats: the k-fastest staging stores of an untransposed lhs (transposed rhs) spread over the
@@ -147,32 +150,66 @@ __global__ void __launch_bounds__(256, 4) gemm_formal_tiled_kernel(const FormalP
       r_fixed[e] = a.rhs_transposed ? row_part(a.rhs_map, batch, a.n, col0 + r_c[e], a.k) : col_part(a.rhs_map, col0 + r_c[e]);
     }
   }
+  // kWide staging roles: lhs run = row (tid >> 1) of the tile, k offset (tid & 1) * 8; rhs run = k row ((tid - 128) >> 3),
+  // columns ((tid - 128) & 7) * 8 .. + 7.
+  const bool wide_lhs = threadIdx.x < 128;
+  const int wide_row = wide_lhs ? (threadIdx.x >> 1) : ((threadIdx.x - 128) >> 3);
+  const int wide_off = wide_lhs ? (threadIdx.x & 1) * 8 : ((threadIdx.x - 128) & 7) * 8;
+  int64_t wide_fixed = 0;
+  if (kWide) wide_fixed = wide_lhs ? row_part(a.lhs_map, batch, a.m, row0 + wide_row, a.k) : col_part(a.rhs_map, col0 + wide_off);
   for (int k0 = 0; k0 < a.k; k0 += kPanelK) {
+    if (kWide) {
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (wide_lhs) {
+        const int k = k0 + wide_off;
+        if (row0 + wide_row < a.m && k < a.k)
+          raw = *reinterpret_cast<const uint4 *>(a.lhs + (wide_fixed + col_part(a.lhs_map, k)) * 2);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float value = 0.0f;
-      const int k = k0 + l_kk[e];
-      if (row0 + l_r[e] < a.m && k < a.k) {
-        int64_t at;
-        if (kSeparable) at = l_fixed[e] + (a.lhs_transposed ? row_part(a.lhs_map, batch, a.k, k, a.m) : col_part(a.lhs_map, k));
-        else at = a.lhs_transposed ? operand_index<kResolved>(a.lhs_map, batch, a.k, k, a.m, row0 + l_r[e])
-                                   : operand_index<kResolved>(a.lhs_map, batch, a.m, row0 + l_r[e], a.k, k);
-        value = widen_bits(load_element_bits(a.lhs, at, a.in_format), a.in_format);
+        for (int i = 0; i < 4; ++i) {
+          lhs_panel[wide_off + 2 * i][wide_row] = widen_bits(w[i] & 0xffffu, a.in_format);
+          lhs_panel[wide_off + 2 * i + 1][wide_row] = widen_bits(w[i] >> 16, a.in_format);
+        }
+      } else {
+        const int k = k0 + wide_row;
+        if (col0 + wide_off < a.n && k < a.k)
+          raw = *reinterpret_cast<const uint4 *>(a.rhs + (wide_fixed + row_part(a.rhs_map, batch, a.k, k, a.n)) * 2);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        float4 lo, hi;
+        lo.x = widen_bits(w[0] & 0xffffu, a.in_format); lo.y = widen_bits(w[0] >> 16, a.in_format);
+        lo.z = widen_bits(w[1] & 0xffffu, a.in_format); lo.w = widen_bits(w[1] >> 16, a.in_format);
+        hi.x = widen_bits(w[2] & 0xffffu, a.in_format); hi.y = widen_bits(w[2] >> 16, a.in_format);
+        hi.z = widen_bits(w[3] & 0xffffu, a.in_format); hi.w = widen_bits(w[3] >> 16, a.in_format);
+        *reinterpret_cast<float4 *>(&rhs_panel[wide_row][wide_off]) = lo;
+        *reinterpret_cast<float4 *>(&rhs_panel[wide_row][wide_off + 4]) = hi;
       }
-      lhs_panel[l_kk[e]][l_r[e]] = value;
-    }
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float value = 0.0f;
-      const int k = k0 + r_kk[e];
-      if (col0 + r_c[e] < a.n && k < a.k) {
-        int64_t at;
-        if (kSeparable) at = r_fixed[e] + (a.rhs_transposed ? col_part(a.rhs_map, k) : row_part(a.rhs_map, batch, a.k, k, a.n));
-        else at = a.rhs_transposed ? operand_index<kResolved>(a.rhs_map, batch, a.n, col0 + r_c[e], a.k, k)
-                                   : operand_index<kResolved>(a.rhs_map, batch, a.k, k, a.n, col0 + r_c[e]);
-        value = widen_bits(load_element_bits(a.rhs, at, a.in_format), a.in_format);
+    } else {
+  #pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float value = 0.0f;
+        const int k = k0 + l_kk[e];
+        if (row0 + l_r[e] < a.m && k < a.k) {
+          int64_t at;
+          if (kSeparable) at = l_fixed[e] + (a.lhs_transposed ? row_part(a.lhs_map, batch, a.k, k, a.m) : col_part(a.lhs_map, k));
+          else at = a.lhs_transposed ? operand_index<kResolved>(a.lhs_map, batch, a.k, k, a.m, row0 + l_r[e])
+                                     : operand_index<kResolved>(a.lhs_map, batch, a.m, row0 + l_r[e], a.k, k);
+          value = widen_bits(load_element_bits(a.lhs, at, a.in_format), a.in_format);
+        }
+        lhs_panel[l_kk[e]][l_r[e]] = value;
       }
-      rhs_panel[r_kk[e]][r_c[e]] = value;
+  #pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float value = 0.0f;
+        const int k = k0 + r_kk[e];
+        if (col0 + r_c[e] < a.n && k < a.k) {
+          int64_t at;
+          if (kSeparable) at = r_fixed[e] + (a.rhs_transposed ? col_part(a.rhs_map, k) : row_part(a.rhs_map, batch, a.k, k, a.n));
+          else at = a.rhs_transposed ? operand_index<kResolved>(a.rhs_map, batch, a.n, col0 + r_c[e], a.k, k)
+                                     : operand_index<kResolved>(a.rhs_map, batch, a.k, k, a.n, col0 + r_c[e]);
+          value = widen_bits(load_element_bits(a.rhs, at, a.in_format), a.in_format);
+        }
+        rhs_panel[r_kk[e]][r_c[e]] = value;
+      }
     }
     __syncthreads();
     const int k_count = min(kPanelK, a.k - k0);
@@ -217,12 +254,17 @@ wb200_status launch_gemm_formal(const GemmFormalArgs &args, cudaStream_t stream)
       return (ncx3 || cx) && (m.c_block & (m.c_block - 1)) == 0;
     };
     const bool all_resolved = resolved(args.lhs_map) && resolved(args.rhs_map) && resolved(args.dst_map) && (!args.has_psum || resolved(args.psum_map));
-    if (all_resolved && separable_layout(args.lhs_map) && separable_layout(args.rhs_map))
-      gemm_formal_tiled_kernel<true, true><<<grid, 256, 0, stream>>>(p);
+    const bool separable = all_resolved && separable_layout(args.lhs_map) && separable_layout(args.rhs_map);
+    const bool wide = separable && args.in_format != WB200_F32 && !args.lhs_transposed && !args.rhs_transposed && args.k % 8 == 0 &&
+                      args.n % 8 == 0 && ((reinterpret_cast<uintptr_t>(args.lhs) | reinterpret_cast<uintptr_t>(args.rhs)) & 15) == 0;
+    if (wide)
+      gemm_formal_tiled_kernel<true, true, true><<<grid, 256, 0, stream>>>(p);
+    else if (separable)
+      gemm_formal_tiled_kernel<true, true, false><<<grid, 256, 0, stream>>>(p);
     else if (all_resolved)
-      gemm_formal_tiled_kernel<true, false><<<grid, 256, 0, stream>>>(p);
+      gemm_formal_tiled_kernel<true, false, false><<<grid, 256, 0, stream>>>(p);
     else
-      gemm_formal_tiled_kernel<false, false><<<grid, 256, 0, stream>>>(p);
+      gemm_formal_tiled_kernel<false, false, false><<<grid, 256, 0, stream>>>(p);
     WB200_CUDA_CHECK(cudaGetLastError());
     return WB200_OK;
   }
