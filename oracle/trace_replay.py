@@ -156,6 +156,17 @@ def replay(commands, ddr: np.ndarray, tile_count: int, spm_bytes: int = 3 << 20,
             numeric_flags |= _convert(spm[c.tile], c)
         elif name == "wafer_tx81_reduce":
             numeric_flags |= _reduce(spm[c.tile], c)
+        elif name == "wafer_tx81_bit2fp":      # TargetModelTensorNumeric.cpp:198-236
+            one = {2: 0x3c00, 3: 0x3f80, 5: 0x3f800000}[a[3]]
+            bits = _read_vector(spm[c.tile], a[0], _BOOL, a[2])
+            _write_vector(spm[c.tile], a[1], a[3], [one if b else 0 for b in bits])
+        elif name == "wafer_tx81_mask_move":   # :238-286
+            one = {2: 0x3c00, 3: 0x3f80, 5: 0x3f800000}[a[4]]
+            source, mask = _read_vector(spm[c.tile], a[0], a[4], a[3]), _read_vector(spm[c.tile], a[1], a[4], a[3])
+            destination = _read_vector(spm[c.tile], a[2], a[4], a[3])
+            if any(m not in (0, one) for m in mask):
+                raise ValueError("MaskMove requires canonical zero/one mask values")
+            _write_vector(spm[c.tile], a[2], a[4], [x if m == one else d for x, m, d in zip(source, mask, destination)])
         elif name in ("wafer_tx81_rdma", "wafer_tx81_wdma"):
             inner, strides, iterations = a[3], a[4:7], a[7:10]
             segments = int(np.prod(iterations))

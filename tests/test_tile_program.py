@@ -173,6 +173,34 @@ def test_elementwise_and_convert_calls_are_traced_and_replayed_on_the_cpu():
         TileProgram([_module("call void @wafer_tx81_elementwise_abs(i64 0, i64 65536, i32 4096, i32 5, i32 1)\n ret void")], spm_bytes=1 << 16).trace()
 
 
+# x where x >= 1, else 7: relation to packed Bool, Bool to numbers, fill, masked move.
+SELECT = _module("""
+  call void @wafer_tx81_rdma(i64 %0, i64 0, i32 1024, i32 1024, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  call void @wafer_tx81_elementwise_ge(i64 0, i64 1065353216, i64 4096, i32 256, i32 5, i32 0, i32 1, i32 0, i32 1)
+  call void @wafer_tx81_bit2fp(i64 4096, i64 8192, i32 256, i32 5, i32 1)
+  call void @wafer_tx81_memset(i64 12288, i32 1088421888, i32 256, i32 5, i32 0)
+  call void @wafer_tx81_mask_move(i64 0, i32 8192, i64 12288, i32 256, i32 5, i32 1)
+  call void @wafer_tx81_wdma(i64 12288, i64 %1, i32 1024, i32 1024, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  ret void
+""")
+
+
+def test_bit2fp_and_mask_move_are_traced_and_replayed_on_the_cpu():
+    from oracle import binding, trace_replay
+    binding.build()
+    program = TileProgram([SELECT], spm_bytes=1 << 16)
+    commands, stats = program.trace()
+    assert [c.name for c in commands if "bit2fp" in c.name or "mask_move" in c.name] == ["wafer_tx81_bit2fp", "wafer_tx81_mask_move"]
+    place_in, place_out = program.placement(False, 0), program.placement(True, 0)
+    ddr = np.zeros(place_in["ddr_bytes"], dtype=np.uint8)
+    x = np.linspace(-3, 3, 256, dtype=np.float32)
+    at = place_in["address"] - place_in["ddr_base"]
+    ddr[at:at + 1024] = x.view(np.uint8)
+    trace_replay.replay(commands, ddr, 1, spm_bytes=1 << 16)
+    at = place_out["address"] - place_out["ddr_base"]
+    assert np.array_equal(ddr[at:at + 1024].view(np.float32), np.where(x >= 1, x, np.float32(7)))
+
+
 def test_integer_subset_semantics():
     body = """
   %a = add i32 4000000000, 100
@@ -298,6 +326,16 @@ def test_small_program_runs_on_the_device(backend):
     (out,), stats = program.run([matrix])
     assert np.array_equal(out.view(np.float32), matrix[::-1].T)
     assert stats["gpu_launches"] == 18 and stats["device_ms"] > 0
+
+
+@pytest.mark.gpu
+def test_select_program_runs_on_the_device(backend):
+    program = TileProgram([SELECT], backend, spm_bytes=1 << 16)
+    x = np.random.default_rng(8).standard_normal((16, 16)).astype(np.float32) * 2
+    for _ in range(2):
+        (out,), stats = program.run([x])
+        assert np.array_equal(out.view(np.float32), np.where(x >= 1, x, np.float32(7)))
+    assert stats["commands"] == 6 and stats["gpu_launches"] == 6
 
 
 @pytest.mark.gpu

@@ -195,6 +195,8 @@ SIGNATURES = {
     "wb200_program_command_name": (C.c_char_p, [C.c_uint32]),
     "wb200_tile_program_run": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_uint32, C.POINTER(ProgramStats)]),
     "wb200_target_call_elementwise": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint64] + [C.c_uint32] * 5 + [C.POINTER(C.c_uint32)]),
+    "wb200_target_call_bit2fp": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32]),
+    "wb200_target_call_mask_move": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32]),
     "wb200_target_call_convert": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32)]),
     "wb200_target_call_reduce": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, C.c_uint32, _U32x3, C.c_uint32, C.POINTER(C.c_uint32)]),
     "wb200_target_call_pool": (C.c_int, [C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint64, _U32x3, _U32x3, _U32x3, _U32x3, C.c_uint32, C.POINTER(C.c_uint32)]),

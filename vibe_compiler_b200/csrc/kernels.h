@@ -133,5 +133,10 @@ uint64_t strided_span(const StridedLayout &layout);   // bytes from the first to
 wb200_status launch_strided_copy(const uint8_t *src, const StridedLayout &from, uint8_t *dst, const StridedLayout &to,
                                  cudaStream_t stream);
 wb200_status launch_fill(uint8_t *dst, uint32_t value_bits, uint64_t count, int element_bytes, cudaStream_t stream);
+// Packed Bool -> 1.0 / 0 of `format`; masked element move (store = 0: validate only; *first_refused = smallest element << 8 | 4
+// whose mask is neither 0 nor 1.0).
+wb200_status launch_bit2fp(const uint8_t *src, uint8_t *dst, uint32_t count, int format, cudaStream_t stream);
+wb200_status launch_mask_move(const uint8_t *src, const uint8_t *mask, uint8_t *dst, uint32_t count, int format, int store,
+                              unsigned long long *first_refused, cudaStream_t stream);
 
 }  // namespace wb200

@@ -38,6 +38,34 @@ __global__ void __launch_bounds__(256) fill_kernel(Element *dst, Element value, 
   for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride) dst[i] = value;
 }
 
+// wafer_tx81_bit2fp (lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:198-236): bit i of the packed Bool source
+// (least significant bit first) becomes 1.0 or +0 of the destination format.
+template <typename T>
+__global__ void __launch_bounds__(256) bit2fp_kernel(const uint8_t *src, T *dst, uint32_t count, T one) {
+  const uint32_t stride = gridDim.x * blockDim.x;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) dst[i] = ((src[i >> 3] >> (i & 7)) & 1u) ? one : static_cast<T>(0);
+}
+
+// wafer_tx81_mask_move (:238-286): destination elements whose mask element is exactly 1.0 take the source element, a
+// zero mask keeps them; any other mask value refuses the command. `store` = 0 only validates; the smallest refused
+// element is reported as (element << 8 | 4).
+template <typename T>
+__global__ void __launch_bounds__(256) mask_move_kernel(const T *src, const T *mask, T *dst, uint32_t count, T one, int store,
+                                                        unsigned long long *first_refused) {
+  const uint32_t stride = gridDim.x * blockDim.x;
+  unsigned long long refused = ~0ull;
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += stride) {
+    const T predicate = mask[i];
+    if (predicate == one) {
+      if (store) dst[i] = src[i];
+    } else if (predicate != 0) {
+      const unsigned long long key = (static_cast<unsigned long long>(i) << 8) | 4ull;
+      refused = key < refused ? key : refused;
+    }
+  }
+  if (refused != ~0ull) atomicMin(first_refused, refused);
+}
+
 int grid_for(uint64_t items) {
   uint64_t blocks = (items + 255) / 256;
   if (blocks > 148u * 8u) blocks = 148u * 8u;
@@ -94,6 +122,33 @@ wb200_status launch_fill(uint8_t *dst, uint32_t value_bits, uint64_t count, int 
     case 4: fill_kernel<uint32_t><<<grid_for(count), 256, 0, stream>>>(reinterpret_cast<uint32_t *>(dst), value_bits, count); break;
     default: return fail(WB200_ERR_UNSUPPORTED, "fill takes 1, 2 or 4 byte elements");
   }
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
+}
+
+wb200_status launch_bit2fp(const uint8_t *src, uint8_t *dst, uint32_t count, int format, cudaStream_t stream) {
+  if (count == 0) return WB200_OK;
+  const int grid = grid_for(count);
+  if (format == WB200_F32) bit2fp_kernel<uint32_t><<<grid, 256, 0, stream>>>(src, reinterpret_cast<uint32_t *>(dst), count, 0x3f800000u);
+  else if (format == WB200_BF16) bit2fp_kernel<uint16_t><<<grid, 256, 0, stream>>>(src, reinterpret_cast<uint16_t *>(dst), count, static_cast<uint16_t>(0x3f80));
+  else if (format == WB200_F16) bit2fp_kernel<uint16_t><<<grid, 256, 0, stream>>>(src, reinterpret_cast<uint16_t *>(dst), count, static_cast<uint16_t>(0x3c00));
+  else return fail(WB200_ERR_UNSUPPORTED, "Bit2FP requires F16, BF16 or F32 output");
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
+}
+
+wb200_status launch_mask_move(const uint8_t *src, const uint8_t *mask, uint8_t *dst, uint32_t count, int format, int store,
+                              unsigned long long *first_refused, cudaStream_t stream) {
+  if (count == 0) return WB200_OK;
+  const int grid = grid_for(count);
+  if (format == WB200_F32)
+    mask_move_kernel<uint32_t><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint32_t *>(src), reinterpret_cast<const uint32_t *>(mask),
+                                                         reinterpret_cast<uint32_t *>(dst), count, 0x3f800000u, store, first_refused);
+  else if (format == WB200_BF16 || format == WB200_F16)
+    mask_move_kernel<uint16_t><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint16_t *>(src), reinterpret_cast<const uint16_t *>(mask),
+                                                         reinterpret_cast<uint16_t *>(dst), count,
+                                                         static_cast<uint16_t>(format == WB200_BF16 ? 0x3f80 : 0x3c00), store, first_refused);
+  else return fail(WB200_ERR_UNSUPPORTED, "MaskMove requires F16, BF16 or F32");
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }

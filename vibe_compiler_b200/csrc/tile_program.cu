@@ -85,7 +85,7 @@ enum Command : int {
   kNccJoin, kDteBegin, kDteBeginAfterPrepare, kDteSendPrepare, kDteSendIssue, kDteRecvPrepare, kDteWait, kDteFinish,
   kRdma, kWdma, kGatherScatter, kMemset, kGemm, kGemmOriented,
   // Families whose symbol carries the operation (wafer_tx81_elementwise_<op>, wafer_tx81_convert_<route>):
-  kElementwiseUnary, kElementwiseBinary, kElementwiseLogic, kConvert, kReduce, kCommandCount
+  kElementwiseUnary, kElementwiseBinary, kElementwiseLogic, kConvert, kReduce, kBit2Fp, kMaskMove, kCommandCount
 };
 struct CommandInfo {
   const char *symbol;
@@ -114,6 +114,8 @@ const CommandInfo kCommands[kCommandCount] = {
     {"wafer_tx81_elementwise_logic", 6, true, false},     // (lhs, rhs, destination; count, format; worker)
     {"wafer_tx81_convert", 6, true, false},               // (source, destination; count, zero point, rounding mode; worker)
     {"wafer_tx81_reduce", 9, true, false},                // (source, destination; dimension, n, h, w, c, format; worker)
+    {"wafer_tx81_bit2fp", 5, true, false},                // (source, destination; count, format; worker)
+    {"wafer_tx81_mask_move", 6, true, false},             // (source, mask, destination, count, format; worker)
 };
 
 // Spellings of lib/Wafer/Target/TargetOperation.cpp:181-251 in enumeration order (index 11 is unused) and of the convert
@@ -132,6 +134,8 @@ const char *const kConvertNames[36] = {
 int find_command(const std::string &symbol, uint32_t *operation) {
   *operation = 0;
   for (int i = 0; i < kElementwiseUnary; ++i)
+    if (symbol == kCommands[i].symbol) return i;
+  for (int i = kBit2Fp; i < kCommandCount; ++i)
     if (symbol == kCommands[i].symbol) return i;
   const std::string elementwise = "wafer_tx81_elementwise_", convert = "wafer_tx81_convert_", reduce = "wafer_tx81_reduce_";
   if (symbol.compare(0, reduce.size(), reduce) == 0) {   // lib/Wafer/Target/TargetOperation.cpp stringifyTargetReduceOperation
@@ -801,6 +805,37 @@ wb200_status enqueue_image_copy(wb200_spm_image *from_image, uint64_t source, co
   return WB200_OK;
 }
 
+// wafer_tx81_bit2fp / wafer_tx81_mask_move on one scratch-pad image (1-D Tensor vectors of `count` elements).
+wb200_status enqueue_image_bit2fp(wb200_spm_image *image, uint64_t source, uint64_t destination, uint32_t count, uint32_t format, bool execute,
+                                  uint64_t *launches) {
+  if (!is_float_format(static_cast<int>(format))) return fail(WB200_ERR_UNSUPPORTED, "Bit2FP requires F16, BF16 or F32 output");
+  if (count == 0) return fail(WB200_ERR_INVALID_ARGUMENT, "Bit2FP element count must be positive");
+  wb200_status st;
+  if ((st = image_range(image, source, (static_cast<uint64_t>(count) + 7) / 8, "Bit2FP source")) != WB200_OK) return st;
+  if ((st = image_range(image, destination, static_cast<uint64_t>(count) * (format_bits(static_cast<int>(format)) / 8), "Bit2FP destination")) != WB200_OK) return st;
+  if (!execute) return WB200_OK;
+  if ((st = launch_bit2fp(image->device + (source - image->base), image->device + (destination - image->base), count, static_cast<int>(format),
+                          image->work_stream())) != WB200_OK) return st;
+  image->backend->launches += 1; *launches += 1;
+  return WB200_OK;
+}
+
+wb200_status enqueue_image_mask_move(wb200_spm_image *image, uint64_t source, uint64_t mask, uint64_t destination, uint32_t count, uint32_t format,
+                                     bool execute, int store, unsigned long long *d_refused, uint64_t *launches) {
+  if (!is_float_format(static_cast<int>(format))) return fail(WB200_ERR_UNSUPPORTED, "MaskMove requires F16, BF16 or F32");
+  if (count == 0) return fail(WB200_ERR_INVALID_ARGUMENT, "MaskMove element count must be positive");
+  const uint64_t bytes = static_cast<uint64_t>(count) * (format_bits(static_cast<int>(format)) / 8);
+  wb200_status st;
+  if ((st = image_range(image, source, bytes, "MaskMove source")) != WB200_OK) return st;
+  if ((st = image_range(image, mask, bytes, "MaskMove mask")) != WB200_OK) return st;
+  if ((st = image_range(image, destination, bytes, "MaskMove destination")) != WB200_OK) return st;
+  if (!execute) return WB200_OK;
+  if ((st = launch_mask_move(image->device + (source - image->base), image->device + (mask - image->base), image->device + (destination - image->base),
+                             count, static_cast<int>(format), store, d_refused, image->work_stream())) != WB200_OK) return st;
+  image->backend->launches += 1; *launches += 1;
+  return WB200_OK;
+}
+
 wb200_status enqueue_image_fill(wb200_spm_image *image, uint64_t destination, uint32_t value_bits, uint32_t count, uint32_t format,
                                 bool execute, uint64_t *launches) {
   const int element = format_bits(static_cast<int>(format)) / 8;
@@ -1041,6 +1076,17 @@ wb200_status execute_call(wb200_tile_program *program, int tile_index, const Ins
       if (program->execute) program->stats.gpu_launches += program->backend->launches - before;
       return st;
     }
+    case kBit2Fp:
+      // (source, destination, count, format)
+      record(program, tile_index, inst.command, a, argc);
+      program->stats.bytes_moved += (a[2] + 7) / 8 + a[2] * (format_bits(static_cast<int>(a[3])) / 8);
+      return enqueue_image_bit2fp(spm, a[0], a[1], static_cast<uint32_t>(a[2]), static_cast<uint32_t>(a[3]), program->execute, &program->stats.gpu_launches);
+    case kMaskMove:
+      // (source, mask, destination, count, format); a mask value other than 0 / 1.0 fails the run after the stream drains
+      record(program, tile_index, inst.command, a, argc);
+      program->stats.bytes_moved += 3 * a[3] * (format_bits(static_cast<int>(a[4])) / 8);
+      return enqueue_image_mask_move(spm, a[0], a[1], a[2], static_cast<uint32_t>(a[3]), static_cast<uint32_t>(a[4]), program->execute, 1,
+                                     reinterpret_cast<unsigned long long *>(program->numeric_words + 2), &program->stats.gpu_launches);
     case kReduce: {
       // (source, destination, dimension, n, h, w, c, format)
       const uint32_t nhwc[4] = {static_cast<uint32_t>(a[3]), static_cast<uint32_t>(a[4]), static_cast<uint32_t>(a[5]), static_cast<uint32_t>(a[6])};
@@ -1460,7 +1506,10 @@ wb200_status wb200_tile_program_run(wb200_tile_program *program, const void *con
   WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
   unsigned long long refused;
   memcpy(&refused, numeric + 2, sizeof(refused));
-  if (refused != ~0ull) return convert_refusal(refused);   // a failed command fails the invocation; outputs are not returned
+  if (refused != ~0ull) {   // a failed command fails the invocation; outputs are not returned
+    if ((refused & 0xff) == 4) return fail(WB200_ERR_UNSUPPORTED, "MaskMove requires canonical zero/one mask values at element " + std::to_string(refused >> 8));
+    return convert_refusal(refused);
+  }
   program->stats.numeric_flags = numeric[0];
   for (size_t i = 0; i < program->outputs.size(); ++i) {
     const ExternalTensor &tensor = program->outputs[i];
@@ -1536,6 +1585,37 @@ wb200_status wb200_target_call_memset(wb200_spm_image *spm, uint64_t destination
   wb200_status st = enqueue_image_fill(spm, destination, value_bits, element_count, format, true, &launches);
   if (st != WB200_OK) return st;
   return read_device_status(spm->backend, spm->backend->stream, nullptr);
+}
+
+wb200_status wb200_target_call_bit2fp(wb200_spm_image *spm, uint64_t source, uint64_t destination, uint32_t element_count, uint32_t format) {
+  if (!spm) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  DeviceGuard guard(spm->backend->device);
+  uint64_t launches = 0;
+  wb200_status st = enqueue_image_bit2fp(spm, source, destination, element_count, format, true, &launches);
+  if (st != WB200_OK) return st;
+  return read_device_status(spm->backend, spm->backend->stream, nullptr);
+}
+
+wb200_status wb200_target_call_mask_move(wb200_spm_image *spm, uint64_t source, uint64_t mask, uint64_t destination, uint32_t element_count,
+                                         uint32_t format) {
+  if (!spm) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  wb200_backend *backend = spm->backend;
+  DeviceGuard guard(backend->device);
+  void *word;
+  wb200_status st = backend->buffer(3, sizeof(unsigned long long), &word);
+  if (st != WB200_OK) return st;
+  cudaStream_t stream = spm->work_stream();
+  uint64_t launches = 0;
+  WB200_CUDA_CHECK(cudaMemsetAsync(word, 0xff, sizeof(unsigned long long), stream));
+  // validate first: a refused mask value leaves the destination untouched
+  if ((st = enqueue_image_mask_move(spm, source, mask, destination, element_count, format, true, 0, static_cast<unsigned long long *>(word), &launches)) != WB200_OK) return st;
+  unsigned long long refused = ~0ull;
+  WB200_CUDA_CHECK(cudaMemcpyAsync(&refused, word, sizeof(refused), cudaMemcpyDeviceToHost, stream));
+  WB200_CUDA_CHECK(cudaStreamSynchronize(stream));
+  if (refused != ~0ull)
+    return fail(WB200_ERR_UNSUPPORTED, "MaskMove requires canonical zero/one mask values at element " + std::to_string(refused >> 8));
+  if ((st = enqueue_image_mask_move(spm, source, mask, destination, element_count, format, true, 1, static_cast<unsigned long long *>(word), &launches)) != WB200_OK) return st;
+  return read_device_status(backend, backend->stream, nullptr);
 }
 
 }  // extern "C"

@@ -98,3 +98,11 @@ class ScratchPad:
         self._check(self._lib.wb200_target_call_reduce(self._handle, abi.REDUCE_OPS[operation], source, destination,
                                                        abi.REDUCE_DIMS[dimension], shape, format, C.byref(flags)))
         return flags.value
+
+    def bit2fp(self, source: int, destination: int, count: int, format: int) -> None:
+        """Packed Bool vector -> 1.0 / 0 of `format`."""
+        self._check(self._lib.wb200_target_call_bit2fp(self._handle, source, destination, count, format))
+
+    def mask_move(self, source: int, mask: int, destination: int, count: int, format: int) -> None:
+        """destination[i] = source[i] where mask[i] is 1.0; a mask value other than 0 / 1.0 raises and writes nothing."""
+        self._check(self._lib.wb200_target_call_mask_move(self._handle, source, mask, destination, count, format))
