@@ -201,6 +201,58 @@ def test_bit2fp_and_mask_move_are_traced_and_replayed_on_the_cpu():
     assert np.array_equal(ddr[at:at + 1024].view(np.float32), np.where(x >= 1, x, np.float32(7)))
 
 
+# bf16, 509 elements: seven elementwise commands, each taking the previous destination as its first operand (vector and
+# immediate second operands, an in-place step, a second operand and a destination that revisit an earlier destination),
+# then a command of another length. The interpreter issues the seven as one fused launch.
+CHAIN = _module("""
+  call void @wafer_tx81_rdma(i64 %0, i64 0, i32 1024, i32 1024, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 3, i32 0)
+  call void @wafer_tx81_rdma(i64 %1, i64 2048, i32 1024, i32 1024, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 3, i32 0)
+  call void @wafer_tx81_memset(i64 4096, i32 0, i32 3072, i32 5, i32 0)
+  call void @wafer_tx81_elementwise_add(i64 0, i64 2048, i64 4096, i32 509, i32 3, i32 0, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_elementwise_mul(i64 4096, i64 16128, i64 6144, i32 509, i32 3, i32 0, i32 1, i32 0, i32 1)
+  call void @wafer_tx81_elementwise_exp(i64 6144, i64 6144, i32 509, i32 3, i32 1)
+  call void @wafer_tx81_elementwise_sub(i64 6144, i64 4096, i64 8192, i32 509, i32 3, i32 0, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_elementwise_relu(i64 8192, i64 10240, i32 509, i32 3, i32 1)
+  call void @wafer_tx81_elementwise_max(i64 10240, i64 2048, i64 4096, i32 509, i32 3, i32 0, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_elementwise_sigmoid(i64 4096, i64 12288, i32 509, i32 3, i32 1)
+  call void @wafer_tx81_elementwise_neg(i64 12288, i64 14336, i32 256, i32 3, i32 1)
+  call void @wafer_tx81_wdma(i64 4096, i64 %2, i32 12288, i32 12288, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 8, i32 0)
+  ret void
+""", arguments="i64 %0, i64 %1, i64 %2", rows=[
+    '!{i64 0, !"external-input", i64 0, !"", !"bf16", !"tensor", i64 1024, i64 512, !"read-only", i64 512, i64 0}',
+    '!{i64 1, !"external-input", i64 1, !"", !"bf16", !"tensor", i64 1024, i64 512, !"read-only", i64 512, i64 0}',
+    '!{i64 2, !"external-output", i64 0, !"", !"u8", !"tensor", i64 12288, i64 12288, !"write-only", i64 12288, i64 0}'])
+
+
+def _chain_inputs():
+    rng = np.random.default_rng(77)
+    x = (rng.standard_normal(512).astype(np.float32) * 3).view(np.uint32) >> 16
+    y = (rng.standard_normal(512).astype(np.float32) * 3).view(np.uint32) >> 16
+    x[:6] = [0x7f80, 0xff80, 0x7fc1, 0x0001, 0x8000, 0x42c8]   # +inf, -inf, a NaN payload, a subnormal, -0, 100
+    y[:6] = [0xff80, 0x3f80, 0x3f80, 0x0001, 0x0000, 0x42c8]
+    return x.astype(np.uint16), y.astype(np.uint16)
+
+
+def _chain_cpu_replay(program):
+    from oracle import binding, trace_replay
+    binding.build()
+    commands, _ = program.trace()
+    places = [program.placement(False, 0), program.placement(False, 1), program.placement(True, 0)]
+    ddr = np.zeros(places[0]["ddr_bytes"], dtype=np.uint8)
+    for place, array in zip(places, _chain_inputs()):
+        at = place["address"] - place["ddr_base"]
+        ddr[at:at + array.nbytes] = array.view(np.uint8)
+    report = {}
+    trace_replay.replay(commands, ddr, 1, spm_bytes=1 << 16, report=report)
+    at = places[2]["address"] - places[2]["ddr_base"]
+    return ddr[at:at + 12288].copy(), report["numeric_flags"]
+
+
+def test_chain_program_is_replayed_on_the_cpu():
+    out, flags = _chain_cpu_replay(TileProgram([CHAIN], spm_bytes=1 << 16))
+    assert out[:1018].any() and not out[1018:2048].any() and flags & 1   # inf - inf and the NaN operand raise invalid
+
+
 def test_integer_subset_semantics():
     body = """
   %a = add i32 4000000000, 100
@@ -336,6 +388,23 @@ def test_select_program_runs_on_the_device(backend):
         (out,), stats = program.run([x])
         assert np.array_equal(out.view(np.float32), np.where(x >= 1, x, np.float32(7)))
     assert stats["commands"] == 6 and stats["gpu_launches"] == 6
+
+
+@pytest.mark.gpu
+def test_elementwise_chain_is_fused_and_matches_the_unfused_replay_and_the_cpu(backend, monkeypatch):
+    expected, expected_flags = _chain_cpu_replay(TileProgram([CHAIN], spm_bytes=1 << 16))
+    fused = TileProgram([CHAIN], backend, spm_bytes=1 << 16)
+    monkeypatch.setenv("WB200_REPLAY_FUSE", "0")
+    unfused = TileProgram([CHAIN], backend, spm_bytes=1 << 16)
+    monkeypatch.delenv("WB200_REPLAY_FUSE")
+    x, y = _chain_inputs()
+    for _ in range(2):   # the first run captures the graph, the second relaunches it
+        (out_fused,), stats_fused = fused.run([x, y])
+        (out_unfused,), stats_unfused = unfused.run([x, y])
+        assert np.array_equal(out_fused.reshape(-1), expected) and np.array_equal(out_unfused.reshape(-1), expected)
+        assert stats_fused["numeric_flags"] == stats_unfused["numeric_flags"] == expected_flags
+        assert stats_fused["commands"] == stats_unfused["commands"] == 12
+        assert stats_unfused["gpu_launches"] == 12 and stats_fused["gpu_launches"] == 6   # seven commands in one launch
 
 
 @pytest.mark.gpu

@@ -66,6 +66,24 @@ struct PoolWindow {
 wb200_status launch_elementwise_formal(int op, int in_format, int out_format, int input_count, const uint8_t *in0, const uint8_t *in1,
                                        uint8_t *dst, const LayoutMap &in_map, const LayoutMap &out_map, uint32_t *flags_word,
                                        cudaStream_t stream, RhsBroadcast rhs = RhsBroadcast());
+// A run of formal elementwise commands over 1-D Tensor vectors of one format and element count in which every command's
+// first operand is the previous command's destination: one launch carries the value in registers from step to step and
+// still writes every step's destination. Second operands are a full vector (WB200_RHS_SAME), immediate bits
+// (WB200_RHS_SCALAR) or absent (unary; scalar = 0).
+constexpr int kMaxChainSteps = 8;
+struct ChainStep {
+  int32_t op;
+  uint32_t rhs_mode, scalar, reserved;
+  const uint8_t *rhs;
+  uint8_t *dst;
+};
+struct ElementwiseChain {
+  int32_t steps, format;
+  int64_t count;
+  const uint8_t *lhs;
+  ChainStep step[kMaxChainSteps];
+};
+wb200_status launch_elementwise_chain(const ElementwiseChain &chain, uint32_t *flags_word, cudaStream_t stream);
 // Formal reduction: NaN-canonicalising, flag-raising fold in row-major input order (bit d of `reduced_mask` = dimension d reduced).
 wb200_status launch_reduce_formal(int op, int format, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map, const LayoutMap &dst_map,
                                   uint32_t reduced_mask, uint32_t *flags_word, cudaStream_t stream);

@@ -537,6 +537,64 @@ formal_elementwise_kernel(int runtime_op, int runtime_format, int out_format, in
   merge_block_flags(flags_word, flags);
 }
 
+// A chain of formal elementwise commands (see ElementwiseChain): the running value stays in registers, every step's
+// destination is still written, second operands are read where the step names one. A thread owns the same eight
+// elements of every vector, so a step may read what an earlier step of the chain wrote at the same address.
+__global__ void __launch_bounds__(kThreads)
+formal_chain_kernel(const ElementwiseChain chain, int vector, uint32_t *flags_word) {
+  const int format = chain.format, bytes = format_bits(format) / 8;
+  const int64_t total = chain.count, groups = (total + 7) / 8;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  uint32_t flags = 0;
+  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < groups; g += stride) {
+    const int64_t first = g * 8;
+    const int count = total - first < 8 ? static_cast<int>(total - first) : 8;
+    const bool wide = vector && count == 8;
+    uint32_t value[8], b[8];
+    if (wide) {
+      load_group8(chain.lhs, g, bytes, value);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) value[e] = e < count ? load_element_bits(chain.lhs, first + e, format) : 0u;
+    }
+#pragma unroll 1
+    for (int s = 0; s < chain.steps; ++s) {
+      const int op = chain.step[s].op;
+      const uint8_t *rhs = chain.step[s].rhs;
+      uint8_t *dst = chain.step[s].dst;
+      const bool mpfr_family = op == WB200_EW_SQRT || op == WB200_EW_RSQRT || (op >= WB200_EW_LOG2 && op <= WB200_EW_EXP) ||
+                               (op >= WB200_EW_SIN && op <= WB200_EW_SIGMOID) || op == WB200_EW_SOFTPLUS;
+      if (chain.step[s].rhs_mode == WB200_RHS_SAME) {
+        if (wide) {
+          load_group8(rhs, g, bytes, b);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) b[e] = e < count ? load_element_bits(rhs, first + e, format) : 0u;
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) b[e] = chain.step[s].scalar;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (e >= count) break;
+        uint32_t element_flags = 0;
+        value[e] = mpfr_family ? formal_mpfr_scalar(op, format, value[e], &element_flags)
+                               : formal_scalar(op, format, format, value[e], b[e], &element_flags);
+        flags |= element_flags;
+      }
+      if (wide) {
+        store_group8(dst, g, bytes, value);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (e < count) store_element_bits(dst, first + e, format, value[e]);
+      }
+    }
+  }
+  merge_block_flags(flags_word, flags);
+}
+
 // The same fold for rank-4 NCx tensors [n, h, w, c] (every TargetCall-level reduce): coordinates are carried as loop
 // counters, so the only divisions are the three that split the output index.
 template <int kCombine, int kFormat>
@@ -793,6 +851,20 @@ wb200_status launch_elementwise_formal(int op, int in_format, int out_format, in
   }
 #undef WB200_EW_FORMATS
 #undef WB200_EW_LAUNCH
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
+}
+
+wb200_status launch_elementwise_chain(const ElementwiseChain &chain, uint32_t *flags_word, cudaStream_t stream) {
+  if (chain.steps < 1 || chain.steps > kMaxChainSteps || chain.count < 1 || !is_float_format(chain.format))
+    return fail(WB200_ERR_INVALID_ARGUMENT, "malformed elementwise chain");
+  uintptr_t low_bits = reinterpret_cast<uintptr_t>(chain.lhs);
+  for (int s = 0; s < chain.steps; ++s)
+    low_bits |= reinterpret_cast<uintptr_t>(chain.step[s].dst) | (chain.step[s].rhs_mode == WB200_RHS_SAME ? reinterpret_cast<uintptr_t>(chain.step[s].rhs) : 0);
+  const int64_t groups = (chain.count + 7) / 8;
+  int64_t blocks = (groups + kThreads - 1) / kThreads;
+  blocks = blocks < 1 ? 1 : blocks > 148 * 32 ? 148 * 32 : blocks;
+  formal_chain_kernel<<<static_cast<int>(blocks), kThreads, 0, stream>>>(chain, (low_bits & 15) == 0, flags_word);
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }

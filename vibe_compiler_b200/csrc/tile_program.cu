@@ -622,7 +622,19 @@ struct PreparedSend {
   bool issued = false, released = false;
 };
 
+// Elementwise commands of one Tile that are held back while the following command may extend them into one fused launch.
+struct PendingChain {
+  ElementwiseChain chain{};                 // device pointers; chain.steps == 0 when nothing is pending
+  uint64_t bytes = 0, lhs_address = 0;
+  uint64_t rhs_address[kMaxChainSteps] = {0}, dst_address[kMaxChainSteps] = {0};
+  bool rhs_vector[kMaxChainSteps] = {false};
+  uint64_t first_args[8] = {0};             // the first command as issued: a chain that stays one command long runs unfused
+  uint32_t first_operation = 0;
+  int first_command = 0;
+};
+
 struct TileState {
+  PendingChain chain;
   std::vector<uint64_t> regs;
   int block = 0, previous = -1;
   size_t pc = 0;
@@ -662,6 +674,7 @@ struct wb200_tile_program {
   std::vector<PreparedSend> prepared;
   uint64_t next_event = 1;
   bool execute = false;
+  bool fuse_chains = true;   // WB200_REPLAY_FUSE=0 in the environment issues every elementwise command as its own launch
   uint32_t gemm_policy = WB200_GEMM_FORMAL;
   wb200_program_stats stats{};
   std::vector<wb200_program_command> *trace = nullptr;
@@ -921,6 +934,86 @@ wb200_status try_match(wb200_tile_program *program, size_t index) {
 }
 
 // Executes one wafer_tx81_* call of `tile`. Sets *blocked when the call has to wait for another Tile.
+// One elementwise command as issued: unary (source, destination, count, format); binary (lhs, rhs | scalar bits,
+// destination, count, format, rhs unit, scalar flag, numeric | rhs group); logic (lhs, rhs, destination, count, format).
+wb200_status issue_elementwise(wb200_tile_program *program, wb200_spm_image *spm, int command, uint32_t operation, const uint64_t *a, bool execute) {
+  const bool unary = command == kElementwiseUnary, full = command == kElementwiseBinary;
+  const uint64_t rhs = unary ? 0 : a[1], destination = unary ? a[1] : a[2], count = unary ? a[2] : a[3], format = unary ? a[3] : a[4];
+  const uint64_t before = execute ? program->backend->launches : 0;
+  const wb200_status st = enqueue_image_elementwise(spm, operation, a[0], rhs, destination, static_cast<uint32_t>(count), static_cast<uint32_t>(format),
+                                                    full ? static_cast<uint32_t>(a[5]) : 0, full ? static_cast<uint32_t>(a[6]) : 0,
+                                                    full ? static_cast<uint32_t>(a[7]) : 0, program->numeric_words, execute);
+  if (execute) program->stats.gpu_launches += program->backend->launches - before;
+  return st;
+}
+
+// Launches what the Tile holds back: one fused kernel for two or more commands, the ordinary kernel for one.
+wb200_status flush_chain(wb200_tile_program *program, int tile_index) {
+  PendingChain &pending = program->state[tile_index].chain;
+  if (pending.chain.steps == 0) return WB200_OK;
+  wb200_spm_image *spm = &program->spm[tile_index];
+  wb200_status st;
+  if (pending.chain.steps == 1) {
+    st = issue_elementwise(program, spm, pending.first_command, pending.first_operation, pending.first_args, true);
+  } else {
+    DeviceGuard guard(program->backend->device);
+    st = launch_elementwise_chain(pending.chain, program->numeric_words, spm->work_stream());
+    if (st == WB200_OK) { program->backend->launches += 1; program->stats.gpu_launches += 1; }
+  }
+  pending.chain.steps = 0;
+  return st;
+}
+
+// Two equally long byte ranges may both take part in a chain when they coincide or do not touch: a thread of the fused
+// kernel owns the same elements of every vector, so only a shifted overlap would cross threads.
+bool ranges_compatible(uint64_t x, uint64_t y, uint64_t bytes) { return x == y || x + bytes <= y || y + bytes <= x; }
+
+// Holds an arithmetic / function elementwise command back as a chain step, extending the pending chain when the
+// command's first operand is the pending chain's last destination. Validation has already passed.
+wb200_status defer_elementwise(wb200_tile_program *program, int tile_index, int command, uint32_t operation, const uint64_t *a) {
+  PendingChain &pending = program->state[tile_index].chain;
+  wb200_spm_image *spm = &program->spm[tile_index];
+  const bool unary = command == kElementwiseUnary;
+  const bool rhs_vector = !unary && a[6] == 0;
+  const uint64_t lhs = a[0], rhs = unary ? 0 : a[1], destination = unary ? a[1] : a[2], count = unary ? a[2] : a[3], format = unary ? a[3] : a[4];
+  const uint64_t bytes = count * (format_bits(static_cast<int>(format)) / 8);
+  wb200_status st;
+  bool extend = pending.chain.steps > 0 && pending.chain.steps < kMaxChainSteps && pending.chain.format == static_cast<int32_t>(format) &&
+                pending.chain.count == static_cast<int64_t>(count) && lhs == pending.dst_address[pending.chain.steps - 1];
+  if (extend) {
+    extend = ranges_compatible(destination, pending.lhs_address, bytes) && (!rhs_vector || ranges_compatible(destination, rhs, bytes));
+    for (int s = 0; extend && s < pending.chain.steps; ++s)
+      extend = ranges_compatible(destination, pending.dst_address[s], bytes) &&
+               (!pending.rhs_vector[s] || ranges_compatible(destination, pending.rhs_address[s], bytes)) &&
+               (!rhs_vector || ranges_compatible(rhs, pending.dst_address[s], bytes));
+  }
+  if (!extend) {
+    if ((st = flush_chain(program, tile_index)) != WB200_OK) return st;
+    if (!ranges_compatible(destination, lhs, bytes) || (rhs_vector && !ranges_compatible(destination, rhs, bytes)))
+      return issue_elementwise(program, spm, command, operation, a, true);   // shifted in-place command: never part of a chain
+    pending.chain.format = static_cast<int32_t>(format);
+    pending.chain.count = static_cast<int64_t>(count);
+    pending.chain.lhs = spm->device + (lhs - spm->base);
+    pending.bytes = bytes;
+    pending.lhs_address = lhs;
+    pending.first_command = command;
+    pending.first_operation = operation;
+    for (int i = 0; i < 8; ++i) pending.first_args[i] = a[i];
+  }
+  const int s = pending.chain.steps++;
+  ChainStep &step = pending.chain.step[s];
+  step.op = static_cast<int32_t>(operation);
+  step.rhs_mode = rhs_vector ? WB200_RHS_SAME : WB200_RHS_SCALAR;
+  step.scalar = unary ? 0u : static_cast<uint32_t>(rhs);
+  step.reserved = 0;
+  step.rhs = rhs_vector ? spm->device + (rhs - spm->base) : nullptr;
+  step.dst = spm->device + (destination - spm->base);
+  pending.rhs_vector[s] = rhs_vector;
+  pending.rhs_address[s] = rhs_vector ? rhs : 0;
+  pending.dst_address[s] = destination;
+  return WB200_OK;
+}
+
 wb200_status execute_call(wb200_tile_program *program, int tile_index, const Inst &inst, bool *blocked, uint64_t *result) {
   TileState &tile = program->state[tile_index];
   uint64_t a[17] = {0};
@@ -935,6 +1028,8 @@ wb200_status execute_call(wb200_tile_program *program, int tile_index, const Ins
   wb200_status st = WB200_OK;
   *blocked = false;
   *result = 0;
+  const bool elementwise = inst.command == kElementwiseUnary || inst.command == kElementwiseBinary || inst.command == kElementwiseLogic;
+  if (!elementwise && (st = flush_chain(program, tile_index)) != WB200_OK) return st;   // held-back commands precede this one
   switch (inst.command) {
     case kNccJoin:
       if (a[0] == 0 || (a[0] & ~0xFull)) return program_error(program, tile_index, "NCC join mask is empty or outside the worker domain");
@@ -1063,18 +1158,19 @@ wb200_status execute_call(wb200_tile_program *program, int tile_index, const Ins
     case kElementwiseUnary:
     case kElementwiseBinary:
     case kElementwiseLogic: {
-      // unary (source, destination, count, format); binary (lhs, rhs | scalar bits, destination, count, format, rhs unit,
-      // scalar flag, numeric | rhs group); logic (lhs, rhs, destination, count, format)
       const bool unary = inst.command == kElementwiseUnary, full = inst.command == kElementwiseBinary;
-      const uint64_t rhs = unary ? 0 : a[1], destination = unary ? a[1] : a[2], count = unary ? a[2] : a[3], format = unary ? a[3] : a[4];
+      const uint64_t count = unary ? a[2] : a[3], format = unary ? a[3] : a[4];
       record(program, tile_index, inst.command, a, argc, inst.operation);
       program->stats.bytes_moved += count * (format_bits(static_cast<int>(format)) / 8) * (unary ? 2 : 3);
-      const uint64_t before = program->execute ? program->backend->launches : 0;
-      st = enqueue_image_elementwise(spm, inst.operation, a[0], rhs, destination, static_cast<uint32_t>(count), static_cast<uint32_t>(format),
-                                     full ? static_cast<uint32_t>(a[5]) : 0, full ? static_cast<uint32_t>(a[6]) : 0,
-                                     full ? static_cast<uint32_t>(a[7]) : 0, program->numeric_words, program->execute);
-      if (program->execute) program->stats.gpu_launches += program->backend->launches - before;
-      return st;
+      if (!program->execute || !program->fuse_chains) return issue_elementwise(program, spm, inst.command, inst.operation, a, program->execute);
+      if ((st = issue_elementwise(program, spm, inst.command, inst.operation, a, false)) != WB200_OK) return st;   // validation only
+      const uint32_t op = inst.operation;
+      const bool arithmetic = op == WB200_EW_MAX || op == WB200_EW_MIN || op == WB200_EW_ADD || op == WB200_EW_SUB || op == WB200_EW_MUL;
+      // same-index or immediate second operands only; relations, logic and the repeated-unit / grouped forms run unfused
+      const bool chainable = unary ? op != WB200_EW_LOGIC_NOT : (full && arithmetic && (a[6] != 0 || (a[5] == 0 && a[7] == 0)));
+      if (chainable) return defer_elementwise(program, tile_index, inst.command, op, a);
+      if ((st = flush_chain(program, tile_index)) != WB200_OK) return st;
+      return issue_elementwise(program, spm, inst.command, op, a, true);
     }
     case kBit2Fp:
       // (source, destination, count, format)
@@ -1212,6 +1308,7 @@ wb200_status run_tile(wb200_tile_program *program, int tile_index, StepResult *r
       }
       case Op::Ret:
         if (tile.dte_state == 1) return program_error(program, tile_index, "entry returned inside a Direct-DTE session");
+        if (wb200_status st = flush_chain(program, tile_index)) return st;
         tile.done = true;
         *result = StepResult::Done;
         *progressed = true;
@@ -1343,6 +1440,7 @@ wb200_status wb200_tile_program_load(wb200_backend *backend, const char *const *
   std::unique_ptr<wb200_tile_program> program(new wb200_tile_program);
   program->backend = backend;
   program->spm_bytes = spm_bytes ? spm_bytes : kDefaultSpmBytes;
+  { const char *env = getenv("WB200_REPLAY_FUSE"); program->fuse_chains = !(env && env[0] == '0'); }
   program->tiles.resize(tile_count);
   std::vector<bool> seen(tile_count, false);
   for (uint32_t i = 0; i < tile_count; ++i) {
