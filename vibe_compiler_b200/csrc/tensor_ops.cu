@@ -537,12 +537,44 @@ formal_elementwise_kernel(int runtime_op, int runtime_format, int out_format, in
   merge_block_flags(flags_word, flags);
 }
 
+// One step of a chain on a thread's eight values. The switch gives every arithmetic operation its own copy of the scalar
+// evaluator with the operation and format fixed at compile time (a few dozen instructions each); only the cases a chain
+// uses are ever fetched. The correctly rounded function family is one out-of-line call.
+template <int kFormat>
+__device__ __forceinline__ void chain_step(int op, uint32_t (&value)[8], const uint32_t (&b)[8], int count, uint32_t &flags) {
+#define WB200_CHAIN_CASE(OP)                                                             \
+  case OP:                                                                               \
+    _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                      \
+      if (e < count) {                                                                   \
+        uint32_t element_flags = 0;                                                      \
+        value[e] = formal_scalar(OP, kFormat, kFormat, value[e], b[e], &element_flags);  \
+        flags |= element_flags;                                                          \
+      }                                                                                  \
+    }                                                                                    \
+    break;
+  switch (op) {
+    WB200_CHAIN_CASE(WB200_EW_ABS) WB200_CHAIN_CASE(WB200_EW_NEG) WB200_CHAIN_CASE(WB200_EW_RELU) WB200_CHAIN_CASE(WB200_EW_RECIP)
+    WB200_CHAIN_CASE(WB200_EW_SQUARE) WB200_CHAIN_CASE(WB200_EW_MAX) WB200_CHAIN_CASE(WB200_EW_MIN) WB200_CHAIN_CASE(WB200_EW_ADD)
+    WB200_CHAIN_CASE(WB200_EW_SUB) WB200_CHAIN_CASE(WB200_EW_MUL)
+    default:
+#pragma unroll 1
+      for (int e = 0; e < count; ++e) {
+        uint32_t element_flags = 0;
+        value[e] = formal_mpfr_scalar(op, kFormat, value[e], &element_flags);
+        flags |= element_flags;
+      }
+      break;
+  }
+#undef WB200_CHAIN_CASE
+}
+
 // A chain of formal elementwise commands (see ElementwiseChain): the running value stays in registers, every step's
 // destination is still written, second operands are read where the step names one. A thread owns the same eight
 // elements of every vector, so a step may read what an earlier step of the chain wrote at the same address.
+template <int kFormat>
 __global__ void __launch_bounds__(kThreads)
 formal_chain_kernel(const ElementwiseChain chain, int vector, uint32_t *flags_word) {
-  const int format = chain.format, bytes = format_bits(format) / 8;
+  constexpr int format = kFormat, bytes = kFormat == WB200_F32 ? 4 : 2;
   const int64_t total = chain.count, groups = (total + 7) / 8;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   uint32_t flags = 0;
@@ -559,11 +591,8 @@ formal_chain_kernel(const ElementwiseChain chain, int vector, uint32_t *flags_wo
     }
 #pragma unroll 1
     for (int s = 0; s < chain.steps; ++s) {
-      const int op = chain.step[s].op;
       const uint8_t *rhs = chain.step[s].rhs;
       uint8_t *dst = chain.step[s].dst;
-      const bool mpfr_family = op == WB200_EW_SQRT || op == WB200_EW_RSQRT || (op >= WB200_EW_LOG2 && op <= WB200_EW_EXP) ||
-                               (op >= WB200_EW_SIN && op <= WB200_EW_SIGMOID) || op == WB200_EW_SOFTPLUS;
       if (chain.step[s].rhs_mode == WB200_RHS_SAME) {
         if (wide) {
           load_group8(rhs, g, bytes, b);
@@ -575,14 +604,7 @@ formal_chain_kernel(const ElementwiseChain chain, int vector, uint32_t *flags_wo
 #pragma unroll
         for (int e = 0; e < 8; ++e) b[e] = chain.step[s].scalar;
       }
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        if (e >= count) break;
-        uint32_t element_flags = 0;
-        value[e] = mpfr_family ? formal_mpfr_scalar(op, format, value[e], &element_flags)
-                               : formal_scalar(op, format, format, value[e], b[e], &element_flags);
-        flags |= element_flags;
-      }
+      chain_step<kFormat>(chain.step[s].op, value, b, count, flags);
       if (wide) {
         store_group8(dst, g, bytes, value);
       } else {
@@ -864,7 +886,10 @@ wb200_status launch_elementwise_chain(const ElementwiseChain &chain, uint32_t *f
   const int64_t groups = (chain.count + 7) / 8;
   int64_t blocks = (groups + kThreads - 1) / kThreads;
   blocks = blocks < 1 ? 1 : blocks > 148 * 32 ? 148 * 32 : blocks;
-  formal_chain_kernel<<<static_cast<int>(blocks), kThreads, 0, stream>>>(chain, (low_bits & 15) == 0, flags_word);
+  const int grid = static_cast<int>(blocks), vector = (low_bits & 15) == 0;
+  if (chain.format == WB200_F32) formal_chain_kernel<WB200_F32><<<grid, kThreads, 0, stream>>>(chain, vector, flags_word);
+  else if (chain.format == WB200_BF16) formal_chain_kernel<WB200_BF16><<<grid, kThreads, 0, stream>>>(chain, vector, flags_word);
+  else formal_chain_kernel<WB200_F16><<<grid, kThreads, 0, stream>>>(chain, vector, flags_word);
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }
