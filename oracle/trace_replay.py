@@ -143,6 +143,35 @@ def _reduce(image, c):
     return flags
 
 
+def _pool(image, c):
+    """One wafer_tx81_pool record (NCx in and out, no padding) -> flags; the (kh, kw) fold of
+    lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:466-583: max / min start from the first tap, sum from +0."""
+    from . import formal_scalar as F
+    a = c.args
+    source_shape, destination_shape = [int(v) for v in a[3:7]], [int(v) for v in a[7:11]]
+    kernel_w, kernel_h, stride_w, stride_h = (int(v) for v in a[15:19])
+    fmt, op = FORMAT_NAMES[a[19]], {116: "add", 117: "max", 119: "min"}[c.operation]
+    if any(a[11:15]):
+        raise ValueError("plain pooling requires explicit input padding")
+    size = binding.geometry(fmt, "ncx", source_shape)["physical_bytes"]
+    compact = binding.unpack(fmt, "ncx", source_shape, image[a[0]:a[0] + size]).reshape(source_shape)
+    out, flags = np.zeros(destination_shape, dtype=compact.dtype), 0
+    for n, h, w, ch in np.ndindex(*destination_shape):
+        result = 0
+        for kh in range(kernel_h):
+            for kw in range(kernel_w):
+                tap = int(compact[n, h * stride_h + kh, w * stride_w + kw, ch])
+                if kh == 0 and kw == 0 and op != "add":
+                    result = tap
+                else:
+                    result, f = F.evaluate(op, fmt, fmt, result, tap)
+                    flags |= f
+        out[n, h, w, ch] = result
+    out_size = binding.geometry(fmt, "ncx", destination_shape)["physical_bytes"]
+    image[a[1]:a[1] + out_size] = binding.pack(fmt, "ncx", destination_shape, out.reshape(-1), image[a[1]:a[1] + out_size].copy())
+    return flags
+
+
 def replay(commands, ddr: np.ndarray, tile_count: int, spm_bytes: int = 3 << 20, threads: int = 1, report: dict = None):
     """commands: iterable of objects with .tile, .name, .args (the library's trace). `ddr` is the DDR arena (uint8,
     address DDR_BASE at index 0) with the inputs already in place; it is updated in place."""
@@ -156,6 +185,8 @@ def replay(commands, ddr: np.ndarray, tile_count: int, spm_bytes: int = 3 << 20,
             numeric_flags |= _convert(spm[c.tile], c)
         elif name == "wafer_tx81_reduce":
             numeric_flags |= _reduce(spm[c.tile], c)
+        elif name == "wafer_tx81_pool":
+            numeric_flags |= _pool(spm[c.tile], c)
         elif name == "wafer_tx81_bit2fp":      # TargetModelTensorNumeric.cpp:198-236
             one = {2: 0x3c00, 3: 0x3f80, 5: 0x3f800000}[a[3]]
             bits = _read_vector(spm[c.tile], a[0], _BOOL, a[2])

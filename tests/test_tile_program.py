@@ -253,6 +253,53 @@ def test_chain_program_is_replayed_on_the_cpu():
     assert out[:1018].any() and not out[1018:2048].any() and flags & 1   # inf - inf and the NaN operand raise invalid
 
 
+# NCx f32 [1, 4, 4, 64]: 2x2 / stride-2 max pooling, then 2x2 sum pooling of the result (one 64-channel block, so the
+# physical bytes are the row-major ones).
+POOL = _module("""
+  call void @wafer_tx81_rdma(i64 %0, i64 0, i32 4096, i32 4096, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  call void @wafer_tx81_pool_max(i64 0, i64 4096, i32 117, i32 1, i32 4, i32 4, i32 64, i32 1, i32 2, i32 2, i32 64, i32 0, i32 0, i32 0, i32 0, i32 2, i32 2, i32 2, i32 2, i32 5, i32 1)
+  call void @wafer_tx81_pool_sum(i64 4096, i64 8192, i32 116, i32 1, i32 2, i32 2, i32 64, i32 1, i32 1, i32 1, i32 64, i32 0, i32 0, i32 0, i32 0, i32 2, i32 2, i32 2, i32 2, i32 5, i32 1)
+  call void @wafer_tx81_wdma(i64 4096, i64 %1, i32 1024, i32 1024, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  call void @wafer_tx81_wdma(i64 8192, i64 %2, i32 256, i32 256, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  ret void
+""", arguments="i64 %0, i64 %1, i64 %2", rows=[
+    '!{i64 0, !"external-input", i64 0, !"", !"f32", !"tensor", i64 4096, i64 1024, !"read-only", i64 16, i64 64, i64 0}',
+    '!{i64 1, !"external-output", i64 0, !"", !"f32", !"tensor", i64 1024, i64 256, !"write-only", i64 4, i64 64, i64 0}',
+    '!{i64 2, !"external-output", i64 1, !"", !"f32", !"tensor", i64 256, i64 64, !"write-only", i64 64, i64 0}'])
+
+
+def _pool_input():
+    x = np.random.default_rng(41).standard_normal((4, 4, 64)).astype(np.float32)
+    x[0, 0, :3] = [np.float32(3.0e38), np.float32("nan"), -0.0]
+    x[2, 2, 0] = np.float32(3.0e38)    # the sum of the pooled maxima of channel 0 overflows
+    return x
+
+
+def test_pool_calls_are_traced_and_replayed_on_the_cpu():
+    from oracle import binding, trace_replay
+    binding.build()
+    program = TileProgram([POOL], spm_bytes=1 << 16)
+    commands, _ = program.trace()
+    assert [(c.name, c.operation, len(c.args)) for c in commands if "pool" in c.name] == [("wafer_tx81_pool", 117, 20), ("wafer_tx81_pool", 116, 20)]
+    places = [program.placement(False, 0), program.placement(True, 0), program.placement(True, 1)]
+    ddr = np.zeros(places[0]["ddr_bytes"], dtype=np.uint8)
+    x = _pool_input()
+    at = places[0]["address"] - places[0]["ddr_base"]
+    ddr[at:at + 4096] = x.view(np.uint8).reshape(-1)
+    report = {}
+    trace_replay.replay(commands, ddr, 1, spm_bytes=1 << 16, report=report)
+    at = places[1]["address"] - places[1]["ddr_base"]
+    pooled = ddr[at:at + 1024].view(np.float32).reshape(2, 2, 64)
+    finite = np.ones(64, dtype=bool)
+    finite[1] = False
+    assert np.array_equal(pooled[:, :, finite], x.reshape(2, 2, 2, 2, 64).max(axis=(1, 3))[:, :, finite])
+    assert pooled[0, 0, 1].view(np.uint32) == 0x7fc00000 and report["numeric_flags"] & 0x4   # canonical NaN; the sum overflows
+    with pytest.raises(WB200Error, match="pool_avg"):
+        TileProgram([POOL.replace("pool_sum", "pool_avg")], spm_bytes=1 << 16)
+    with pytest.raises(WB200Error, match="kind field"):
+        TileProgram([POOL.replace("i32 117", "i32 119")], spm_bytes=1 << 16).trace()
+
+
 def test_integer_subset_semantics():
     body = """
   %a = add i32 4000000000, 100
@@ -405,6 +452,26 @@ def test_elementwise_chain_is_fused_and_matches_the_unfused_replay_and_the_cpu(b
         assert stats_fused["numeric_flags"] == stats_unfused["numeric_flags"] == expected_flags
         assert stats_fused["commands"] == stats_unfused["commands"] == 12
         assert stats_unfused["gpu_launches"] == 12 and stats_fused["gpu_launches"] == 6   # seven commands in one launch
+
+
+@pytest.mark.gpu
+def test_pool_program_matches_the_cpu_replay_bit_for_bit(backend):
+    from oracle import binding, trace_replay
+    binding.build()
+    program = TileProgram([POOL], backend, spm_bytes=1 << 16)
+    commands, _ = program.trace()
+    places = [program.placement(False, 0), program.placement(True, 0), program.placement(True, 1)]
+    ddr = np.zeros(places[0]["ddr_bytes"], dtype=np.uint8)
+    x = _pool_input()
+    at = places[0]["address"] - places[0]["ddr_base"]
+    ddr[at:at + 4096] = x.view(np.uint8).reshape(-1)
+    report = {}
+    trace_replay.replay(commands, ddr, 1, spm_bytes=1 << 16, report=report)
+    (pooled, summed), stats = program.run([x.reshape(16, 64)])
+    for place, got in zip(places[1:], (pooled, summed)):
+        at = place["address"] - place["ddr_base"]
+        assert np.array_equal(got.reshape(-1).view(np.uint8), ddr[at:at + got.nbytes])
+    assert stats["numeric_flags"] == report["numeric_flags"] and stats["gpu_launches"] == 5
 
 
 @pytest.mark.gpu

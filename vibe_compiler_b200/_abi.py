@@ -135,7 +135,7 @@ class ProgramStats(C.Structure):
 
 
 class ProgramCommand(C.Structure):
-    _fields_ = [("tile", C.c_uint32), ("kind", C.c_uint32), ("argc", C.c_uint32), ("operation", C.c_uint32), ("args", C.c_uint64 * 17)]
+    _fields_ = [("tile", C.c_uint32), ("kind", C.c_uint32), ("argc", C.c_uint32), ("operation", C.c_uint32), ("args", C.c_uint64 * 20)]
 
 
 class Comparison(C.Structure):

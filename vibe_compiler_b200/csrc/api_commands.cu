@@ -649,7 +649,7 @@ wb200_status enqueue_image_reduce(wb200_spm_image *image, uint32_t operation, ui
 // wafer_tx81_pool_{max,min,sum} on a scratch-pad image (NCx [n, h, w, c] in and out, no padding, no index output).
 wb200_status enqueue_image_pool(wb200_spm_image *image, uint32_t kind, uint64_t input, uint64_t dst, const uint32_t source_shape[4],
                                 const uint32_t destination_shape[4], const uint32_t pads[4], const uint32_t kernel_strides[4],
-                                uint32_t format, uint32_t *d_flags) {
+                                uint32_t format, uint32_t *d_flags, bool execute) {
   if (!image || !source_shape || !destination_shape || !pads || !kernel_strides) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
   int combine;
   switch (kind) {
@@ -686,6 +686,7 @@ wb200_status enqueue_image_pool(wb200_spm_image *image, uint32_t kind, uint64_t 
   if ((st = make_layout_map(describe(destination_shape), &dst_map, &dst_geo)) != WB200_OK) return st;
   if ((st = spm_range(image, input, src_geo.physical_bytes, "pooling input")) != WB200_OK) return st;
   if ((st = spm_range(image, dst, dst_geo.physical_bytes, "pooling destination")) != WB200_OK) return st;
+  if (!execute) return WB200_OK;   // validation only (device-free trace)
   wb200_backend *backend = image->backend;
   DeviceGuard guard(backend->device);
   const PoolWindow window{kernel_strides[0], kernel_strides[1], kernel_strides[2], kernel_strides[3]};
@@ -750,7 +751,7 @@ wb200_status wb200_target_call_pool(wb200_spm_image *image, uint32_t kind, uint6
                                     const uint32_t destination_shape[4], const uint32_t pads[4], const uint32_t kernel_strides[4],
                                     uint32_t format, uint32_t *flags) {
   return with_flag_word(image, flags, [&](uint32_t *word) {
-    return enqueue_image_pool(image, kind, input, dst, source_shape, destination_shape, pads, kernel_strides, format, word);
+    return enqueue_image_pool(image, kind, input, dst, source_shape, destination_shape, pads, kernel_strides, format, word, true);
   });
 }
 

@@ -103,7 +103,7 @@ wb200_status enqueue_image_reduce(wb200_spm_image *image, uint32_t operation, ui
                                   const uint32_t nhwc[4], uint32_t format, uint32_t *d_flags, bool execute);
 wb200_status enqueue_image_pool(wb200_spm_image *image, uint32_t kind, uint64_t input, uint64_t dst, const uint32_t source_shape[4],
                                 const uint32_t destination_shape[4], const uint32_t pads[4], const uint32_t kernel_strides[4],
-                                uint32_t format, uint32_t *d_flags);
+                                uint32_t format, uint32_t *d_flags, bool execute);
 
 wb200_status enqueue_image_convert(wb200_spm_image *image, uint32_t opcode, uint64_t source, uint64_t destination, uint32_t count,
                                    uint32_t rounding_mode, bool execute, uint32_t *d_flags, unsigned long long *d_error);

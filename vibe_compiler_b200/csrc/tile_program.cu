@@ -85,7 +85,7 @@ enum Command : int {
   kNccJoin, kDteBegin, kDteBeginAfterPrepare, kDteSendPrepare, kDteSendIssue, kDteRecvPrepare, kDteWait, kDteFinish,
   kRdma, kWdma, kGatherScatter, kMemset, kGemm, kGemmOriented,
   // Families whose symbol carries the operation (wafer_tx81_elementwise_<op>, wafer_tx81_convert_<route>):
-  kElementwiseUnary, kElementwiseBinary, kElementwiseLogic, kConvert, kReduce, kBit2Fp, kMaskMove, kCommandCount
+  kElementwiseUnary, kElementwiseBinary, kElementwiseLogic, kConvert, kReduce, kPool, kBit2Fp, kMaskMove, kCommandCount
 };
 struct CommandInfo {
   const char *symbol;
@@ -114,6 +114,8 @@ const CommandInfo kCommands[kCommandCount] = {
     {"wafer_tx81_elementwise_logic", 6, true, false},     // (lhs, rhs, destination; count, format; worker)
     {"wafer_tx81_convert", 6, true, false},               // (source, destination; count, zero point, rounding mode; worker)
     {"wafer_tx81_reduce", 9, true, false},                // (source, destination; dimension, n, h, w, c, format; worker)
+    // (input, destination; kind, source nhwc[4], destination nhwc[4], pads[4], kernel w, kernel h, stride w, stride h, format; worker)
+    {"wafer_tx81_pool", 21, true, false},
     {"wafer_tx81_bit2fp", 5, true, false},                // (source, destination; count, format; worker)
     {"wafer_tx81_mask_move", 6, true, false},             // (source, mask, destination, count, format; worker)
 };
@@ -138,6 +140,12 @@ int find_command(const std::string &symbol, uint32_t *operation) {
   for (int i = kBit2Fp; i < kCommandCount; ++i)
     if (symbol == kCommands[i].symbol) return i;
   const std::string elementwise = "wafer_tx81_elementwise_", convert = "wafer_tx81_convert_", reduce = "wafer_tx81_reduce_";
+  const std::string pool = "wafer_tx81_pool_";
+  if (symbol.compare(0, pool.size(), pool) == 0) {   // plain pooling only (lib/Wafer/Target/TargetCall.cpp:113-118); *operation = the target opcode
+    const std::string name = symbol.substr(pool.size());
+    *operation = name == "sum" ? 116u : name == "max" ? 117u : name == "min" ? 119u : 0u;
+    return *operation ? kPool : -1;
+  }
   if (symbol.compare(0, reduce.size(), reduce) == 0) {   // lib/Wafer/Target/TargetOperation.cpp stringifyTargetReduceOperation
     const char *const names[4] = {"sum", "max", "min", "avg"};
     for (uint32_t op = 0; op < 4; ++op)
@@ -756,7 +764,7 @@ void record(wb200_tile_program *program, int tile, int kind, const uint64_t *arg
   entry.kind = static_cast<uint32_t>(kind);
   entry.argc = static_cast<uint32_t>(argc);
   entry.operation = operation;
-  for (int i = 0; i < argc && i < 17; ++i) entry.args[i] = args[i];
+  for (int i = 0; i < argc && i < 20; ++i) entry.args[i] = args[i];
   program->trace->push_back(entry);
 }
 
@@ -1016,7 +1024,7 @@ wb200_status defer_elementwise(wb200_tile_program *program, int tile_index, int 
 
 wb200_status execute_call(wb200_tile_program *program, int tile_index, const Inst &inst, bool *blocked, uint64_t *result) {
   TileState &tile = program->state[tile_index];
-  uint64_t a[17] = {0};
+  uint64_t a[20] = {0};
   const CommandInfo &info = kCommands[inst.command];
   const int argc = info.has_worker ? info.argc - 1 : info.argc;   // the trailing NCC worker does not reach the payload
   for (int i = 0; i < argc; ++i) a[i] = value_of(tile, inst.args[i]);
@@ -1171,6 +1179,18 @@ wb200_status execute_call(wb200_tile_program *program, int tile_index, const Ins
       if (chainable) return defer_elementwise(program, tile_index, inst.command, op, a);
       if ((st = flush_chain(program, tile_index)) != WB200_OK) return st;
       return issue_elementwise(program, spm, inst.command, op, a, true);
+    }
+    case kPool: {
+      // (input, destination, kind, source nhwc[4], destination nhwc[4], pads[4], kernel w / h and stride w / h, format)
+      if (a[2] != inst.operation) return program_error(program, tile_index, "pool kind field differs from the symbol's operation");
+      uint32_t fields[16];
+      for (int i = 0; i < 16; ++i) fields[i] = static_cast<uint32_t>(a[3 + i]);
+      record(program, tile_index, inst.command, a, argc, inst.operation);
+      const uint64_t before = program->execute ? program->backend->launches : 0;
+      st = enqueue_image_pool(spm, inst.operation, a[0], a[1], fields, fields + 4, fields + 8, fields + 12, static_cast<uint32_t>(a[19]),
+                              program->numeric_words, program->execute);
+      if (program->execute) program->stats.gpu_launches += program->backend->launches - before;
+      return st;
     }
     case kBit2Fp:
       // (source, destination, count, format)
