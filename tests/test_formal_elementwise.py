@@ -97,6 +97,30 @@ def test_flags_per_element(backend):
 
 
 @pytest.mark.gpu
+def test_f32_products_around_the_residual_and_underflow_thresholds(backend):
+    # one element per request. The kernel takes the product's rounding error from one f32 fused multiply-add when
+    # |product| >= 2^-100 and from f64 arithmetic below; cases sit on both sides of that threshold, around the smallest
+    # normal number, in the subnormal range and at overflow, with full-width and few-bit (exact product) significands.
+    rng = np.random.default_rng(99)
+    cases = []
+    for total in list(range(-153, -143)) + list(range(-130, -122)) + list(range(-104, -96)) + [-60, 0, 60, 125, 126, 127, 128]:
+        for width in (24, 12, 3):
+            e1 = int(rng.integers(max(-126, total - 127), min(127, total + 126) + 1))
+            e2 = total - e1
+            m1 = (int(rng.integers(1 << (width - 1), 1 << width)) | 1) << (24 - width)
+            m2 = (int(rng.integers(1 << (width - 1), 1 << width)) | 1) << (24 - width)
+            x = np.float32(np.ldexp(float(m1), e1 - 23)) * np.float32(rng.choice([-1.0, 1.0]))
+            y = np.float32(np.ldexp(float(m2), e2 - 23))
+            cases.append((int(np.array(x, np.float32).view(np.uint32)), int(np.array(y, np.float32).view(np.uint32))))
+    for x, y in cases:
+        for op in ("mul", "square"):
+            one = np.array([x], dtype=np.uint32)
+            other = None if op == "square" else np.array([y], dtype=np.uint32)
+            storage, evidence = _run(backend, op, "f32", "f32", one, other)
+            assert (int(storage.view(np.uint32)[0]), evidence.flags) == F.evaluate(op, "f32", "f32", x, y), (op, hex(x), hex(y))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("fmt", ["f16", "bf16", "f32"])
 def test_relations_to_bool_and_to_numbers(backend, fmt):
     rng = np.random.default_rng(9)

@@ -269,6 +269,34 @@ __device__ __forceinline__ bool tiny_after_rounding(double value, int precision,
 }
 
 __device__ __forceinline__ uint32_t formal_scalar(int op, int format, int out_format, uint32_t a, uint32_t b, uint32_t *flags_out) {
+  if (format == WB200_F32 && out_format == WB200_F32 && (op == WB200_EW_ADD || op == WB200_EW_SUB || op == WB200_EW_MUL || op == WB200_EW_SQUARE)) {
+    // The common f32 case first: finite operands and a finite result that cannot be tiny. The arithmetic is the general
+    // path's (same sum / product, same error-free residual), with its NaN, infinity, narrowing and underflow decisions
+    // known in advance: a finite sum that is subnormal or zero is exact, and a product of at least 2^-100 is normal and
+    // has a residual that one fused multiply-add yields exactly.
+    const uint32_t second = op == WB200_EW_SQUARE ? a : b;
+    if ((a & 0x7f800000u) != 0x7f800000u && (second & 0x7f800000u) != 0x7f800000u) {
+      const float x = __uint_as_float(a);
+      float r, residual;
+      bool decided;
+      if (op == WB200_EW_MUL || op == WB200_EW_SQUARE) {
+        const float y = __uint_as_float(second);
+        r = __fmul_rn(x, y);
+        residual = __fmaf_rn(x, y, -r);
+        decided = fabsf(r) >= 7.8886090522101181e-31f;
+      } else {
+        const float y = op == WB200_EW_SUB ? -__uint_as_float(second) : __uint_as_float(second);
+        r = __fadd_rn(x, y);
+        const float part = __fsub_rn(r, x);
+        residual = __fadd_rn(__fsub_rn(x, __fsub_rn(r, part)), __fsub_rn(y, part));
+        decided = true;
+      }
+      if (decided && fabsf(r) < __uint_as_float(0x7f800000u)) {
+        *flags_out = residual != 0.f ? kFlagInexact : 0u;
+        return __float_as_uint(r);
+      }
+    }
+  }
   const FormatTraits t = traits_of(format);
   uint32_t flags = 0;
   const bool binary = !(op == WB200_EW_ABS || op == WB200_EW_NEG || op == WB200_EW_RECIP || op == WB200_EW_SQUARE || op == WB200_EW_RELU);
@@ -335,12 +363,19 @@ __device__ __forceinline__ uint32_t formal_scalar(int op, int format, int out_fo
       } else {
         const float yy = op == WB200_EW_SQUARE ? x : y;
         r32 = __fmul_rn(x, yy);
-        if (finite_inputs) inexact32 = static_cast<double>(r32) != static_cast<double>(x) * static_cast<double>(yy);
-        // only a product below twice the smallest normal number can still be tiny after rounding
-        const double product = static_cast<double>(x) * static_cast<double>(yy);
-        if (finite_inputs && inexact32 && fabs(product) < 2.0 * static_cast<double>(t.min_normal) &&
-            tiny_after_rounding(product, t.precision, t.min_normal))
-          flags |= kFlagUnderflow;
+        const float magnitude = fabsf(r32);
+        if (magnitude >= 7.8886090522101181e-31f && magnitude >= 2.0f * t.min_normal) {
+          // |r32| >= 2^-100: the residual x * yy - r32 is a multiple of 2^-149, so one fused multiply-add yields it
+          // exactly; and a product of at least twice the smallest normal number is never tiny after rounding.
+          if (finite_inputs) inexact32 = __fmaf_rn(x, yy, -r32) != 0.f;
+        } else {
+          if (finite_inputs) inexact32 = static_cast<double>(r32) != static_cast<double>(x) * static_cast<double>(yy);
+          // only a product below twice the smallest normal number can still be tiny after rounding
+          const double product = static_cast<double>(x) * static_cast<double>(yy);
+          if (finite_inputs && inexact32 && fabs(product) < 2.0 * static_cast<double>(t.min_normal) &&
+              tiny_after_rounding(product, t.precision, t.min_normal))
+            flags |= kFlagUnderflow;
+        }
       }
       if (r32 != r32) {
         if (!nan) flags |= kFlagInvalid;   // inf - inf, 0 * inf
