@@ -298,6 +298,19 @@ __device__ __forceinline__ uint32_t formal_scalar(int op, int format, int out_fo
     }
   }
   const FormatTraits t = traits_of(format);
+  if (op == WB200_EW_MAX || op == WB200_EW_MIN) {
+    // Maximum / minimum as straight-line selects (no branch, so a fold's independent loads stay ahead of its chain):
+    // a NaN operand gives the canonical NaN (invalid when it signals), two zeros give -0 only when the sign rule says
+    // so, otherwise the operand the comparison picks. No rounding.
+    const uint32_t magnitude_a = a & ~t.sign, magnitude_b = b & ~t.sign;
+    const bool nan_a = magnitude_a > t.exp_mask, nan_b = magnitude_b > t.exp_mask;
+    const bool signalling = (nan_a && !(a & t.quiet_bit)) || (nan_b && !(b & t.quiet_bit));
+    const float x = widen_bits(a, format), y = widen_bits(b, format);
+    const uint32_t picked = (op == WB200_EW_MAX ? x < y : x > y) ? b : a;
+    const uint32_t zero = (op == WB200_EW_MAX ? (a & b) : (a | b)) & t.sign;
+    *flags_out = signalling ? kFlagInvalid : 0u;
+    return (nan_a || nan_b) ? t.canonical_nan : ((magnitude_a | magnitude_b) == 0 ? zero : picked);
+  }
   uint32_t flags = 0;
   const bool binary = !(op == WB200_EW_ABS || op == WB200_EW_NEG || op == WB200_EW_RECIP || op == WB200_EW_SQUARE || op == WB200_EW_RELU);
   auto is_nan = [&](uint32_t v) { return (v & t.exp_mask) == t.exp_mask && (v & t.mant_mask) != 0; };
