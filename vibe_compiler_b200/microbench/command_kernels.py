@@ -80,7 +80,10 @@ def main(argv=None) -> int:
     shape = (n // (64 * 64 * 64), 64, 64, 64)
     count = int(np.prod(shape))
     report("formal_reduce max f32 over w", 4 * count + 4 * count // 64, (lambda: pad.reduce("max", a_at, c_at, "trailing1", shape, abi.F32)))
+    report("formal_reduce sum f32 over w", 4 * count + 4 * count // 64, (lambda: pad.reduce("sum", a_at, c_at, "trailing1", shape, abi.F32)))
     out_shape = (shape[0], 32, 32, 64)
+    report("formal_pool sum f32 2x2 stride 2", 4 * count + 4 * count // 4,
+           (lambda: pad.pool("sum", a_at, c_at, shape, out_shape, (2, 2, 2, 2), abi.F32)))
     report("formal_pool max f32 2x2 stride 2", 4 * count + 4 * count // 4,
            (lambda: pad.pool("max", a_at, c_at, shape, out_shape, (2, 2, 2, 2), abi.F32)))
     # one bit-exact GEMM command of the shipped Tile programs: Cx operands in place, bf16 -> f32 with an f32 partial sum
