@@ -121,6 +121,49 @@ def test_f32_products_around_the_residual_and_underflow_thresholds(backend):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("fmt", ["f16", "bf16"])
+def test_16_bit_arithmetic_values_and_flag_classes(backend, fmt):
+    # values element by element on 6000 operand pairs (random bit patterns and moderate magnitudes); flags class by
+    # class: all pairs the oracle gives one flag set run as one request, whose OR must be exactly that set
+    rng = np.random.default_rng(314)
+    n = 6000
+    def moderate():
+        values = (rng.standard_normal(n // 2) * np.exp(rng.uniform(-6, 6, n // 2))).astype(np.float32)
+        if fmt == "bf16":
+            return (values.view(np.uint32) >> 16).astype(np.uint16)
+        return values.astype(np.float16).view(np.uint16)
+    a = np.concatenate([_patterns(fmt, n // 2, rng), moderate()])
+    b = np.concatenate([_patterns(fmt, n // 2, rng), moderate()])
+    b[n // 2:n // 2 + 500] = a[n // 2:n // 2 + 500] ^ 0x8000            # exact cancellations
+    for op in ("add", "sub", "mul", "square"):
+        unary = op in F.UNARY
+        expected = [F.evaluate(op, fmt, fmt, int(x), int(y)) for x, y in zip(a, b)]
+        storage, _ = _run(backend, op, fmt, fmt, a, None if unary else b)
+        assert np.array_equal(storage.view(np.uint16), np.array([bits for bits, _ in expected], dtype=np.uint16)), op
+        classes = {}
+        for index, (_, flags) in enumerate(expected):
+            classes.setdefault(flags, []).append(index)
+        for flags, members in classes.items():
+            _, evidence = _run(backend, op, fmt, fmt, a[members], None if unary else b[members])
+            assert evidence.flags == flags, (op, flags, evidence.flags, len(members))
+
+
+@pytest.mark.gpu
+def test_16_bit_products_that_round_up_to_the_smallest_normal_number(backend):
+    # A product of two 16-bit operands is exact in f32; it becomes inexact only when it is narrowed. Just below the
+    # smallest normal number such a product can round up to it and is then still tiny after rounding with an unbounded
+    # exponent: underflow and inexact, with a normal result (f16 0x1fff * 0x2000 = 2^-14 - 2^-25 -> 0x0400).
+    assert F.evaluate("mul", "f16", "f16", 0x1fff, 0x2000) == (0x0400, F.UNDERFLOW | F.INEXACT)
+    assert F.evaluate("mul", "bf16", "bf16", 0x3fff, 0x0040) == (0x0080, F.UNDERFLOW | F.INEXACT)
+    sweeps = {"f16": (range(0x1ff0, 0x2010), (0x2000, 0x1fff, 0x2001, 0x1c00)), "bf16": (range(0x3ff0, 0x4010), (0x0040, 0x0041, 0x003f, 0x0080))}
+    for fmt, (lhs, rhs) in sweeps.items():
+        for x in lhs:
+            for y in rhs:
+                storage, evidence = _run(backend, "mul", fmt, fmt, np.array([x], dtype=np.uint16), np.array([y], dtype=np.uint16))
+                assert (int(storage.view(np.uint16)[0]), evidence.flags) == F.evaluate("mul", fmt, fmt, x, y), (fmt, hex(x), hex(y))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("fmt", ["f16", "bf16", "f32"])
 def test_relations_to_bool_and_to_numbers(backend, fmt):
     rng = np.random.default_rng(9)

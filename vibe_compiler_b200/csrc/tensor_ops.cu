@@ -303,6 +303,36 @@ __device__ __forceinline__ uint32_t formal_scalar(int op, int format, int out_fo
     }
   }
   const FormatTraits t = traits_of(format);
+  if (common_case && (format == WB200_F16 || format == WB200_BF16) && out_format == format &&
+      (op == WB200_EW_ADD || op == WB200_EW_SUB || op == WB200_EW_MUL || op == WB200_EW_SQUARE)) {
+    // The 16-bit common case: finite operands and a normal result. Same f32 sum / product, residual and single narrowing
+    // as the general path. A small sum of two 16-bit values is exact, so only a product can be tiny after rounding, and
+    // one of at least twice the smallest normal number (and at least 2^-100, for the exact residual) is not.
+    const uint32_t second = op == WB200_EW_SQUARE ? a : b;
+    if ((a & t.exp_mask) != t.exp_mask && (second & t.exp_mask) != t.exp_mask) {
+      const float x = widen_bits(a, format);
+      float r, residual;
+      bool decided;
+      if (op == WB200_EW_MUL || op == WB200_EW_SQUARE) {
+        const float y = widen_bits(second, format);
+        r = __fmul_rn(x, y);
+        residual = __fmaf_rn(x, y, -r);
+        decided = fabsf(r) >= 7.8886090522101181e-31f && fabsf(r) >= 2.0f * t.min_normal;
+      } else {
+        const float y = op == WB200_EW_SUB ? -widen_bits(second, format) : widen_bits(second, format);
+        r = __fadd_rn(x, y);
+        const float part = __fsub_rn(r, x);
+        residual = __fadd_rn(__fsub_rn(x, __fsub_rn(r, part)), __fsub_rn(y, part));
+        decided = true;
+      }
+      const uint32_t narrowed = narrow_bits(r, format);   // r is not a NaN: the operands are finite
+      const uint32_t exponent = narrowed & t.exp_mask;
+      if (decided && exponent != 0 && exponent != t.exp_mask) {
+        *flags_out = (residual != 0.f || widen_bits(narrowed, format) != r) ? kFlagInexact : 0u;
+        return narrowed;
+      }
+    }
+  }
   if (op == WB200_EW_MAX || op == WB200_EW_MIN) {
     // Maximum / minimum as straight-line selects (no branch, so a fold's independent loads stay ahead of its chain):
     // a NaN operand gives the canonical NaN (invalid when it signals), two zeros give -0 only when the sign rule says
@@ -362,6 +392,8 @@ __device__ __forceinline__ uint32_t formal_scalar(int op, int format, int out_fo
     default: {
       // recip, square, add, sub, mul: one RNE rounding in the operand format
       float r32;
+      double small_product = 0.0;   // the exact product where it is small enough to be tiny after rounding
+      bool maybe_tiny = false;
       bool inexact32 = false, finite_inputs = !is_inf(a) && !(binary && is_inf(b)) && !nan;
       if (op == WB200_EW_RECIP) {
         r32 = __fdiv_rn(1.0f, x);
@@ -388,11 +420,10 @@ __device__ __forceinline__ uint32_t formal_scalar(int op, int format, int out_fo
           if (finite_inputs) inexact32 = __fmaf_rn(x, yy, -r32) != 0.f;
         } else {
           if (finite_inputs) inexact32 = static_cast<double>(r32) != static_cast<double>(x) * static_cast<double>(yy);
-          // only a product below twice the smallest normal number can still be tiny after rounding
-          const double product = static_cast<double>(x) * static_cast<double>(yy);
-          if (finite_inputs && inexact32 && fabs(product) < 2.0 * static_cast<double>(t.min_normal) &&
-              tiny_after_rounding(product, t.precision, t.min_normal))
-            flags |= kFlagUnderflow;
+          // only a product below twice the smallest normal number can still be tiny after rounding; whether it is also
+          // inexact is known once the result is narrowed (a 16-bit product is exact in f32 and inexact only after that)
+          small_product = static_cast<double>(x) * static_cast<double>(yy);
+          maybe_tiny = finite_inputs && fabs(small_product) < 2.0 * static_cast<double>(t.min_normal);
         }
       }
       if (r32 != r32) {
@@ -407,6 +438,7 @@ __device__ __forceinline__ uint32_t formal_scalar(int op, int format, int out_fo
         else if (inexact) {
           flags |= kFlagInexact;
           if ((result & t.exp_mask) == 0) flags |= kFlagUnderflow;   // subnormal or zero after rounding, and inexact
+          else if (maybe_tiny && tiny_after_rounding(small_product, t.precision, t.min_normal)) flags |= kFlagUnderflow;   // rounded up to the smallest normal
         }
       }
       break;

@@ -96,6 +96,14 @@ def main(argv=None) -> int:
     psum_at = dst_at + ((sizes[2] + 0xfff) & ~0xfff)
     report(f"formal GEMM command {gm}x{gk}x{gn} bf16 -> f32 + psum (FMAs as bytes: 2 flop each)", 2 * gm * gk * gn,
            (lambda: pad.gemm(lhs_at, rhs_at, dst_at, gm, gk, gn, in_format=abi.BF16, out_format=abi.F32, psum=psum_at, psum_format=abi.F32)))
+    if "bf16 (vector rhs)" in args.only or not args.only:
+        # bf16 operands: the top halves of the same pseudo-random f32 values, 2 n elements per operand over the a / b regions
+        block16 = (block.view(np.uint32) >> 16).astype(np.uint16)
+        for base in (a_at, b_at):
+            for offset in range(0, 4 * n, block16.nbytes):
+                pad.write(base + offset, block16[: min(block16.size, (4 * n - offset) // 2)])
+        report("formal_elementwise add bf16 (vector rhs)", 6 * 2 * n, (lambda: pad.elementwise("add", a_at, c_at, 2 * n, abi.BF16, rhs=b_at)))
+        report("formal_elementwise mul bf16 (vector rhs)", 6 * 2 * n, (lambda: pad.elementwise("mul", a_at, c_at, 2 * n, abi.BF16, rhs=b_at)))
     # seam-1 commands take host storage (the reference passes std::vector bytes): the kernel time comes from the
     # evidence's device_us, the call time is dominated by the two host <-> device copies
     from ..backend import NumericTensor, PhysicalTensorDescriptor
