@@ -563,6 +563,7 @@ formal_elementwise_kernel(int runtime_op, int runtime_format, int out_format, in
                            (op >= WB200_EW_SIN && op <= WB200_EW_SIGMOID) || op == WB200_EW_SOFTPLUS;
   const int in_bytes = format_bits(in_format) / 8, out_bytes = format_bits(out_format) / 8;   // 0 for Bool
   const bool same_rhs = input_count > 1 && rhs.mode == WB200_RHS_SAME;
+  const bool scalar_rhs = input_count > 1 && rhs.mode == WB200_RHS_SCALAR;   // decided once, not per element
   for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < groups; g += stride) {
     const int64_t first = g * 8;
     const int count = total - first < 8 ? static_cast<int>(total - first) : 8;
@@ -582,14 +583,15 @@ formal_elementwise_kernel(int runtime_op, int runtime_format, int out_format, in
       const int64_t i = first + e;
       if (!wide) a[e] = kLinear ? (in_format == WB200_BOOL ? (in0[i >> 3] >> (i & 7)) & 1u : load_element_bits(in0, i, in_format))
                                 : formal_load(in0, in_format, in_map, i);
-      if (input_count > 1 && !(wide && same_rhs)) {
+      if (scalar_rhs) {
+        b[e] = rhs.parameter;
+      } else if (input_count > 1 && !(wide && same_rhs)) {
         // Second-operand forms of lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:347-372.
         int64_t j = i;
         if (rhs.mode == WB200_RHS_UNIT) j = i % rhs.parameter;
         else if (rhs.mode == WB200_RHS_GROUP) j = i / rhs.parameter * 64 + i % 64;
-        if (rhs.mode == WB200_RHS_SCALAR) b[e] = rhs.parameter;
-        else b[e] = kLinear ? (in_format == WB200_BOOL ? (in1[j >> 3] >> (j & 7)) & 1u : load_element_bits(in1, j, in_format))
-                            : formal_load(in1, in_format, in_map, j);
+        b[e] = kLinear ? (in_format == WB200_BOOL ? (in1[j >> 3] >> (j & 7)) & 1u : load_element_bits(in1, j, in_format))
+                       : formal_load(in1, in_format, in_map, j);
       } else if (input_count <= 1) {
         b[e] = 0u;
       }
