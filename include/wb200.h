@@ -310,15 +310,16 @@ wb200_status wb200_attention_fa(wb200_backend *backend, const wb200_attention_pa
 wb200_status wb200_attention_fd(wb200_backend *backend, const wb200_attention_params *params,
                                 uint32_t kv_splits);
 
-/* Flash-decoding for callers that must not allocate device memory at call time: code that runs while a
- * CUDA stream is being captured, a serving loop whose memory was divided up at start-up and that cannot
- * afford the implicit synchronisation of an allocation, or a process held to a fixed memory budget.
+/* Flash-decoding for callers that must not allocate device memory at call time: a serving loop whose
+ * memory was divided up at start-up and that cannot afford the implicit synchronisation of an allocation,
+ * a process held to a fixed memory budget, or code that runs at a point where the CUDA runtime refuses
+ * allocation calls.
  * It has no counterpart in the reference. Same arithmetic and results as wb200_attention_fd; the split-KV
  * partial records go to a fixed 16 MiB array inside the library image (every GPU that loads the library
  * holds it until exit) instead of a buffer allocated on demand, and the call itself performs no
  * allocation. Limits: device buffers only (memory == WB200_MEM_DEVICE);
  * batch * q_heads * kv_splits * (head_dim + 2) <= 4 194 304 floats, otherwise WB200_ERR_LIMIT
- * (kv_splits == 0 picks the largest split count that fits). The first call on a device looks up the
+ * (kv_splits == 0 takes the split count wb200_attention_fd would choose and halves it until it fits). The first call on a device looks up the
  * array's device address; make that call before any stream capture begins. All calls share the one
  * array: two calls whose kernels overlap on the GPU (different streams) race on it, so serialise them.
  * Nothing in the array has to be cleared between calls (every record read is written first). */

@@ -1,7 +1,7 @@
 """The allocation-free decode entry point (wb200_attention_fd_static) against the regular one.
 
-Callers that cannot allocate at call time (stream capture in progress, a fixed memory plan, a
-latency-critical loop) use this entry; it must give the same result as wb200_attention_fd, call after
+Callers that cannot allocate at call time (a fixed memory plan, a latency-critical loop, a
+process under a memory cap) use this entry; it must give the same result as wb200_attention_fd, call after
 call, although every call reuses the one scratch array inside the library. Collected last on purpose."""
 import numpy as np
 import pytest

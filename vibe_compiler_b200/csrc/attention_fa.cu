@@ -45,18 +45,15 @@ constexpr int kFaThreads = 384;          // warpgroup 0: TMA + MMA warps; warpgr
 #ifndef WB200_FA_POLY_EVERY
 #define WB200_FA_POLY_EVERY 0
 #endif
-#ifndef WB200_FA_SPLIT_P
-#define WB200_FA_SPLIT_P 1
-#endif
 constexpr int kPolyEvery = WB200_FA_POLY_EVERY;  // every kPolyEvery-th pair of exponentials runs on the FMA pipe (0: none)
-constexpr bool kSplitP = WB200_FA_SPLIT_P != 0;  // publish P in four 32-key parts so PV starts while exp still runs
 #ifndef WB200_FA_P_PARTS
 #define WB200_FA_P_PARTS 2
 #endif
 #ifndef WB200_FA_FENCE_EVERY_PART
 #define WB200_FA_FENCE_EVERY_PART 1
 #endif
-constexpr int kPParts = WB200_FA_P_PARTS;        // 1, 2 or 4 publications of P per tile
+constexpr int kPParts = WB200_FA_P_PARTS;        // 1 or 2 publications of P per tile
+static_assert(kPParts == 1 || kPParts == 2, "P is published whole or in two halves");
 constexpr int kChunksPerPart = 4 / kPParts;
 constexpr uint32_t kColS0 = 0, kColO0 = 256;    // S_t at t*128, O_t at 256 + t*128
 
@@ -304,116 +301,135 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc_s = umma_idesc_f16(kTileM, kTileN, kBf16, false, false);
-      const uint32_t idesc_o = umma_idesc_f16(kTileM, kHd, kBf16, false, true);
+    // The whole warp walks this code (waits included) and one elected lane issues: with warp-uniform control flow
+    // the descriptor arithmetic stays on the uniform datapath, so an instruction costs far fewer issue slots than in
+    // a loop run by a single diverged lane (which measured 80-100 clocks per 128 x 128 x 16 product here, against the
+    // 64 clocks the product occupies the tensor pipe).
+    {
+      constexpr uint32_t idesc_s = umma_idesc_f16(kTileM, kTileN, kBf16, false, false);
+      constexpr uint32_t idesc_o = umma_idesc_f16(kTileM, kHd, kBf16, false, true);
       int slot = 0;
       uint32_t phase = 0;
       bool ok = true;
       auto advance = [&]() { if (++slot == L::kSlots) { slot = 0; phase ^= 1u; } };
-      // Descriptors differ only in the 14-bit start-address field, so a tile's descriptor is built once
-      // and each k-step adds a compile-time constant to it.
-      const uint64_t q_desc[2] = {umma_desc_kmajor(smem_base + L::kQOff), umma_desc_kmajor(smem_base + L::kQOff + kTileBytesFa)};
-#if defined(WB200_FA_TRACE) && WB200_FA_TRACE >= 2
-      int s_count[2] = {0, 0};
-#endif
-      auto issue_s = [&](int t, uint32_t k_addr) {
-        const uint64_t k_desc = umma_desc_kmajor(k_addr);
+      // Descriptors differ only in the 14-bit start-address field: one descriptor per buffer, and every ring slot or
+      // k-step adds a constant to it.
+      const uint64_t q_desc0 = umma_desc_kmajor(smem_base + L::kQOff);
+      const uint64_t q_desc1 = umma_desc_kmajor(smem_base + L::kQOff + kTileBytesFa);
+      const uint64_t ring_k_desc = umma_desc_kmajor(smem_base + L::kRingOff);
+      const uint64_t ring_v_desc = umma_desc_mnmajor(smem_base + L::kRingOff, kBlockBytes);
+      constexpr uint32_t kSlotStep = kTileBytesFa >> 4;
+      auto issue_s = [&](auto tile_tag, int k_slot) {
+        constexpr int t = decltype(tile_tag)::value;
+        const uint64_t k_desc = ring_k_desc + static_cast<uint32_t>(k_slot) * kSlotStep;
+        const uint64_t q_desc = t ? q_desc1 : q_desc0;
         const uint32_t d_tmem = tmem_base + kColS0 + t * 128;
+        if (elect_one_sync()) {
 #pragma unroll
-        for (int ks = 0; ks < kHd / 16; ++ks) {
-          const uint64_t off = static_cast<uint64_t>(((ks >> 2) * kBlockBytes + (ks & 3) * 32) >> 4);
-          umma_f16_ss(d_tmem, q_desc[t] + off, k_desc + off, idesc_s, ks != 0 ? 1u : 0u);
+          for (int ks = 0; ks < kHd / 16; ++ks) {
+            constexpr uint32_t kBlockStep = kBlockBytes >> 4;
+            const uint32_t off = (ks >> 2) * kBlockStep + (ks & 3) * 2;
+            umma_f16_ss(d_tmem, q_desc + off, k_desc + off, idesc_s, ks != 0 ? 1u : 0u);
+          }
+          umma_commit(s_full(t));
         }
-        umma_commit(s_full(t));
-#if defined(WB200_FA_TRACE) && WB200_FA_TRACE >= 2
-        FA_TRACE(0 + t, s_count[t]++);
-#endif
+        __syncwarp();
       };
       // PV over the keys of one published part of P.
-      auto issue_pv_part = [&](int t, int part, uint32_t v_addr, bool accumulate) {
-        const uint64_t v_desc = umma_desc_mnmajor(v_addr, kBlockBytes);
+      auto issue_pv_part = [&](auto tile_tag, auto part_tag, int v_slot, bool accumulate) {
+        constexpr int t = decltype(tile_tag)::value;
+        constexpr int part = decltype(part_tag)::value;
+        const uint64_t v_desc = ring_v_desc + static_cast<uint32_t>(v_slot) * kSlotStep;
         const uint32_t d_tmem = tmem_base + kColO0 + t * 128;
+        if (elect_one_sync()) {
 #pragma unroll
-        for (int ks = (8 / kPParts) * part; ks < (8 / kPParts) * (part + 1); ++ks) {
-          const uint64_t bdesc = v_desc + static_cast<uint64_t>((ks * 2048) >> 4);
-          const uint32_t acc = (accumulate || ks != 0) ? 1u : 0u;
-          if constexpr (kPInTmem) {
-            umma_f16_ts(d_tmem, tmem_base + kColS0 + t * 128 + ks * 8, bdesc, idesc_o, acc);
-          } else {
-            const uint32_t p_addr = smem_base + L::kPOff + t * kTileBytesFa + (ks >> 2) * kBlockBytes + (ks & 3) * 32;
-            umma_f16_ss(d_tmem, umma_desc_kmajor(p_addr), bdesc, idesc_o, acc);
+          for (int ks = (8 / kPParts) * part; ks < (8 / kPParts) * (part + 1); ++ks) {
+            const uint64_t bdesc = v_desc + static_cast<uint32_t>((ks * 2048) >> 4);
+            const uint32_t acc = (accumulate || ks != 0) ? 1u : 0u;
+            if constexpr (kPInTmem) {
+              umma_f16_ts(d_tmem, tmem_base + kColS0 + t * 128 + ks * 8, bdesc, idesc_o, acc);
+            } else {
+              const uint32_t p_addr = smem_base + L::kPOff + t * kTileBytesFa + (ks >> 2) * kBlockBytes + (ks & 3) * 32;
+              umma_f16_ss(d_tmem, umma_desc_kmajor(p_addr), bdesc, idesc_o, acc);
+            }
           }
+          if (part == kPParts - 1) umma_commit(o_done(t));
         }
-        if (part == kPParts - 1) umma_commit(o_done(t));
+        __syncwarp();
+      };
+      auto commit = [&](uint32_t bar) {
+        if (elect_one_sync()) umma_commit(bar);
+        __syncwarp();
       };
 
       // Work items follow one another on the same barriers; base[t] counts the tiles Q-tile slot t has consumed in
       // earlier items, q_count the Q loads, so every parity is a running count.
-      uint32_t base[2] = {0, 0};
+      uint32_t base0 = 0, base1 = 0;
       uint32_t q_count = 0;
       int item_cursor = 0;
       FaItem item = fa_next_working_item(p, item_cursor);
       while (ok && item.valid) {
-      const int n_tiles[2] = {item.n0, item.n1};
-      const int n_max = item.n_max;
-      ok = mbar_wait(q_full, q_count & 1u, abort_word);
-      ++q_count;
-      FA_TRACE_ITEM(102, 0);
-      // K_0: first scores of both tiles.
-      if (ok) ok = mbar_wait(kv_full(slot), phase, abort_word);
-      if (ok) {
-        FA_TRACE_ITEM(103, 0);
-        tc_fence_after();
-        const uint32_t k_addr = smem_base + L::kRingOff + slot * kTileBytesFa;
-        for (int t = 0; t < 2; ++t)
-          if (n_tiles[t] > 0) issue_s(t, k_addr);
-        umma_commit(kv_empty(slot));
-        if (n_max == 1) umma_commit(q_empty);   // the only S products of the item are in flight
-        advance();
-      }
-      for (int j = 0; ok && j < n_max; ++j) {
-        // ring now points at V_j; K_{j+1} follows it.
-        const int v_slot = slot;
-        const uint32_t v_phase = phase;
-        advance();
-        const int k_slot = slot;
-        const uint32_t k_phase = phase;
-        const bool has_next = j + 1 < n_max;
-        if (has_next) advance();
-        if (!mbar_wait(kv_full(v_slot), v_phase, abort_word)) { ok = false; break; }
-        const uint32_t v_addr = smem_base + L::kRingOff + v_slot * kTileBytesFa;
-        const uint32_t k_addr = smem_base + L::kRingOff + k_slot * kTileBytesFa;
-        bool k_ready = false;
-        for (int t = 0; ok && t < 2; ++t) {
-          if (j < n_tiles[t]) {
-#pragma unroll
-            for (int part = 0; part < kPParts; ++part) {
-              if (!mbar_wait_spin(p_part(t, part), (base[t] + j) & 1u, abort_word)) { ok = false; break; }
-              if (WB200_FA_FENCE_EVERY_PART || part == 0) tc_fence_after();
-              if (part == 0) FA_TRACE(2 + t, j);
-              issue_pv_part(t, part, v_addr, j > 0);
-            }
-            if (!ok) break;
-            FA_TRACE(4 + t, j);
-          }
-          if (j + 1 < n_tiles[t]) {
-            if (!k_ready) {
-              if (!mbar_wait(kv_full(k_slot), k_phase, abort_word)) { ok = false; break; }
-              tc_fence_after();
-              k_ready = true;
-            }
-            issue_s(t, k_addr);
-          }
+        const int n0 = item.n0, n1 = item.n1;
+        const int n_max = item.n_max;
+        ok = mbar_wait(q_full, q_count & 1u, abort_word);
+        ++q_count;
+        FA_TRACE_ITEM(102, 0);
+        // K_0: first scores of both tiles.
+        if (ok) ok = mbar_wait(kv_full(slot), phase, abort_word);
+        if (ok) {
+          FA_TRACE_ITEM(103, 0);
+          tc_fence_after();
+          if (n0 > 0) issue_s(std::integral_constant<int, 0>{}, slot);
+          if (n1 > 0) issue_s(std::integral_constant<int, 1>{}, slot);
+          commit(kv_empty(slot));
+          if (n_max == 1) commit(q_empty);   // the only S products of the item are in flight
+          advance();
         }
-        if (!ok) break;
-        umma_commit(kv_empty(v_slot));
-        if (has_next) umma_commit(kv_empty(k_slot));
-        if (j + 2 == n_max) umma_commit(q_empty);   // the last S products of the item are in flight: Q may be replaced
-      }
-      base[0] += n_tiles[0];
-      base[1] += n_tiles[1];
-      item = fa_next_working_item(p, item_cursor);
+        for (int j = 0; ok && j < n_max; ++j) {
+          // ring now points at V_j; K_{j+1} follows it.
+          const int v_slot = slot;
+          const uint32_t v_phase = phase;
+          advance();
+          const int k_slot = slot;
+          const uint32_t k_phase = phase;
+          const bool has_next = j + 1 < n_max;
+          if (has_next) advance();
+          if (!mbar_wait(kv_full(v_slot), v_phase, abort_word)) { ok = false; break; }
+          bool k_ready = false;
+          auto tile_step = [&](auto tile_tag, int n_tiles, uint32_t tile_base) {
+            constexpr int t = decltype(tile_tag)::value;
+            if (j < n_tiles) {
+              if (!mbar_wait_spin(p_part(t, 0), (tile_base + j) & 1u, abort_word)) { ok = false; return; }
+              tc_fence_after();
+              FA_TRACE(2 + t, j);
+              issue_pv_part(tile_tag, std::integral_constant<int, 0>{}, v_slot, j > 0);
+              if constexpr (kPParts > 1) {
+                if (!mbar_wait_spin(p_part(t, kPParts - 1), (tile_base + j) & 1u, abort_word)) { ok = false; return; }
+                tc_fence_after();
+                issue_pv_part(tile_tag, std::integral_constant<int, kPParts - 1>{}, v_slot, j > 0);
+              }
+              FA_TRACE(4 + t, j);
+            }
+            if (j + 1 < n_tiles) {
+              if (!k_ready) {
+                if (!mbar_wait(kv_full(k_slot), k_phase, abort_word)) { ok = false; return; }
+                tc_fence_after();
+                k_ready = true;
+              }
+              issue_s(tile_tag, k_slot);
+              FA_TRACE(0 + t, j + 1);
+            }
+          };
+          tile_step(std::integral_constant<int, 0>{}, n0, base0);
+          if (ok) tile_step(std::integral_constant<int, 1>{}, n1, base1);
+          if (!ok) break;
+          commit(kv_empty(v_slot));
+          if (has_next) commit(kv_empty(k_slot));
+          if (j + 2 == n_max) commit(q_empty);   // the last S products of the item are in flight: Q may be replaced
+        }
+        base0 += n0;
+        base1 += n1;
+        item = fa_next_working_item(p, item_cursor);
       }   // items
     }
   }

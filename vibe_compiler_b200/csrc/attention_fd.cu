@@ -392,12 +392,13 @@ wb200_status launch_attention_fd(const AttentionArgs &a, uint32_t splits, float 
   p.v = static_cast<const uint16_t *>(a.v);
   p.partials = partials;
 
-  static bool attribute_set = false;
-  if (!attribute_set) {
+  static PerDeviceOnce attributes;
+  const wb200_status attribute_status = attributes.run([]() -> wb200_status {
     WB200_CUDA_CHECK(cudaFuncSetAttribute(fd_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmemBytes));
     WB200_CUDA_CHECK(cudaFuncSetAttribute(fd_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmemBytes));
-    attribute_set = true;
-  }
+    return WB200_OK;
+  });
+  if (attribute_status != WB200_OK) return attribute_status;
   dim3 grid(splits, a.kv_heads, a.batch);
   if (a.format == WB200_BF16)
     fd_partial_kernel<true><<<grid, kWarps * 32, kFdSmemBytes, stream>>>(p);
@@ -442,10 +443,10 @@ wb200_status launch_attention_fd_merge(const AttentionArgs &a, const float *stat
 }  // namespace wb200
 
 // ------------------------------------------------------------------ allocation-free entry point
-// Some callers may not allocate device memory when they reach this library: code running while a
-// CUDA stream is being captured, or inside a latency-critical serving loop whose memory was carved up
-// at start-up and where a cudaMalloc (an implicit device synchronisation) is not acceptable, or a
-// host that shares the GPU under a fixed memory budget. For them the split-KV partial records live in
+// Some callers may not allocate device memory when they reach this library: a latency-critical
+// serving loop whose memory was carved up at start-up and where a cudaMalloc (an implicit device
+// synchronisation) is not acceptable, a host that shares the GPU under a fixed memory budget, or code
+// that runs at a point where the CUDA runtime refuses allocation calls. For them the split-KV partial records live in
 // a fixed array inside the library image instead of in a buffer the backend allocates on demand.
 #include <mutex>
 

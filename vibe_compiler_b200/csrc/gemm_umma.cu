@@ -48,6 +48,7 @@ __device__ __forceinline__ float gelu_erf(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
 }
 
+template <bool kAMn, bool kBMn, bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmUmmaParams p) {
@@ -109,13 +110,13 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t a_dst = smem_base + stage * kStageBytes;
           const uint32_t b_dst = a_dst + kABytes;
           const int k0 = kb * kBK;
-          if (!p.a_mn_major) {
+          if constexpr (!kAMn) {
             tma_load_2d(a_dst, &tmap_a, full_bar(stage), k0, m0);            // box {64 k, 128 m}
           } else {
             tma_load_2d(a_dst, &tmap_a, full_bar(stage), m0, k0);            // box {64 m, 64 k}
             tma_load_2d(a_dst + 8192, &tmap_a, full_bar(stage), m0 + 64, k0);
           }
-          if (p.b_mn_major) {
+          if constexpr (kBMn) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)                                       // box {64 n, 64 k}
               tma_load_2d(b_dst + i * 8192, &tmap_b, full_bar(stage), n0 + 64 * i, k0);
@@ -127,38 +128,44 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(kBM, kBN, p.bf16 != 0, p.a_mn_major != 0, p.b_mn_major != 0);
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
-        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_word)) { ok = false; break; }
+    // The whole warp walks the loop (waits included) and one elected lane issues: with warp-uniform control flow the
+    // descriptor arithmetic stays on the uniform datapath, which keeps the issue cost per instruction well below the
+    // 128 clocks a 128 x 256 x 16 product occupies the tensor pipe (a loop run by a single diverged lane measured
+    // 171 clocks per instruction, the converged form 128).
+    constexpr uint32_t idesc = umma_idesc_f16(kBM, kBN, kBf16, kAMn, kBMn);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+      if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_word)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + acc * kBN;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (!mbar_wait(full_bar(stage), phase, abort_word)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * kBN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_word)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_src = smem_base + stage * kStageBytes;
-          const uint32_t b_src = a_src + kABytes;
+        const uint32_t a_src = smem_base + stage * kStageBytes;
+        const uint32_t b_src = a_src + kABytes;
+        const uint64_t adesc = kAMn ? umma_desc_mnmajor(a_src, 8192) : umma_desc_kmajor(a_src);
+        const uint64_t bdesc = kBMn ? umma_desc_mnmajor(b_src, 8192) : umma_desc_kmajor(b_src);
+        if (elect_one_sync()) {
 #pragma unroll
           for (int ks = 0; ks < kBK / 16; ++ks) {
-            const uint64_t adesc = p.a_mn_major ? umma_desc_mnmajor(a_src + ks * 2048, 8192)
-                                                : umma_desc_kmajor(a_src + ks * 32);
-            const uint64_t bdesc = p.b_mn_major ? umma_desc_mnmajor(b_src + ks * 2048, 8192)
-                                                : umma_desc_kmajor(b_src + ks * 32);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | ks) != 0 ? 1u : 0u);
+            // a k-step of 16 advances the start address by 32 B in a K-major tile and by 2 KiB in an MN-major one
+            constexpr uint64_t a_step = (kAMn ? 2048 : 32) >> 4, b_step = (kBMn ? 2048 : 32) >> 4;
+            umma_f16_ss(d_tmem, adesc + ks * a_step, bdesc + ks * b_step, idesc, (kb | ks) != 0 ? 1u : 0u);
           }
           umma_commit(empty_bar(stage));
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        if (!ok) break;
-        umma_commit(tmem_full_bar(acc));
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
+        __syncwarp();
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
+      if (!ok) break;
+      if (elect_one_sync()) umma_commit(tmem_full_bar(acc));
+      __syncwarp();
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
     }
   } else {
     const int quarter = warp & 3;
@@ -305,15 +312,22 @@ wb200_status launch_gemm_umma(const GemmUmmaArgs &a, int sm_count, int *device_s
   p.num_m_tiles = (a.m + kBM - 1) / kBM;
   p.num_n_tiles = (a.n + kBN - 1) / kBN;
 
-  static bool attribute_set = false;
-  if (!attribute_set) {
-    WB200_CUDA_CHECK(cudaFuncSetAttribute(gemm_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(kSmemBytes)));
-    attribute_set = true;
-  }
+  using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const GemmUmmaParams);
+  static const Kernel kernels[8] = {
+      gemm_umma_kernel<false, false, false>, gemm_umma_kernel<false, false, true>, gemm_umma_kernel<false, true, false>,
+      gemm_umma_kernel<false, true, true>,   gemm_umma_kernel<true, false, false>, gemm_umma_kernel<true, false, true>,
+      gemm_umma_kernel<true, true, false>,   gemm_umma_kernel<true, true, true>};
+  static PerDeviceOnce attributes;
+  st = attributes.run([]() -> wb200_status {
+    for (Kernel kernel : kernels)
+      WB200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes)));
+    return WB200_OK;
+  });
+  if (st != WB200_OK) return st;
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  gemm_umma_kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, p);
+  const Kernel kernel = kernels[(p.a_mn_major ? 4 : 0) | (p.b_mn_major ? 2 : 0) | (p.bf16 ? 1 : 0)];
+  kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, p);
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }

@@ -6,9 +6,40 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace wb200 {
+
+// Function attributes (the opt-in to more than 48 KiB of dynamic shared memory) belong to a device, not to the
+// process: a launcher keeps one of these per kernel family and runs its set-up the first time each device is used.
+class PerDeviceOnce {
+ public:
+  static constexpr int kMaxDevices = 64;
+  // Returns the table slot of `device`, or -1 when the index lies outside the table (the set-up then runs on every call).
+  static int slot_of(int device) { return (device >= 0 && device < kMaxDevices) ? device : -1; }
+  template <typename Setup>
+  wb200_status run(Setup &&setup) {
+    int device = -1;
+    WB200_CUDA_CHECK(cudaGetDevice(&device));
+    const int slot = slot_of(device);
+    std::lock_guard<std::mutex> lock(mutex_);
+    if (slot >= 0 && done_[slot]) return WB200_OK;
+    const wb200_status st = setup();
+    if (st == WB200_OK && slot >= 0) done_[slot] = true;
+    return st;
+  }
+  bool done_for(int device) {
+    std::lock_guard<std::mutex> lock(mutex_);
+    const int slot = slot_of(device);
+    return slot >= 0 && done_[slot];
+  }
+
+ private:
+  std::mutex mutex_;
+  bool done_[kMaxDevices] = {};
+};
 
 // ---- TMA descriptor encoding (driver entry point fetched at run time; libcuda is not linked)
 // `inner`/`outer`(/`batch`) are extents in elements, innermost first; the box is {box_inner,
