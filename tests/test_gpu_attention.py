@@ -64,41 +64,26 @@ def test_fa_persistent_grid_walks_many_items(backend, oracle, shape):
     check_against_oracle(oracle, "bf16", out, lse, want)
 
 
-def test_fa_persistent_and_plain_grid_agree():
-    # WB200_FA_PERSISTENT=0 launches one CTA per item; the arithmetic per item is the same, so the bits must agree.
-    import subprocess, sys
-    code = ("import sys, torch; sys.path.insert(0, %r);"
-            "from vibe_compiler_b200.backend import B200TargetModelBackend as B;"
-            "from tests.test_gpu_attention import make_qkv;"
-            "q, k, v = make_qkv(2, 48, 8, 1100, 1100, 128, torch.bfloat16);"
-            "be = B(0); lse = torch.empty(2, 48, 1100);"
-            "out = be.attention_fa(q, k, v, 128 ** -0.5, True, lse=lse);"
-            "torch.save((out, lse), sys.argv[1])") % str(helpers.ROOT)
-    outs = []
-    for mode in ("0", "1"):
-        path = f"/tmp/wb200_fa_persistent{mode}.pt"
-        subprocess.run([sys.executable, "-c", code, path], check=True, env=dict(os.environ, WB200_FA_PERSISTENT=mode), timeout=300)
-        outs.append(torch.load(path))
-    assert torch.equal(outs[0][0].view(torch.int16), outs[1][0].view(torch.int16))
-    assert torch.equal(outs[0][1], outs[1][1])
-
-
-def test_fa_both_p_placements_agree(oracle):
-    # The kernel keeps the rounded P either in TMEM or in shared memory (WB200_FA_P_IN_TMEM); both are the same
-    # arithmetic, so the outputs must be identical bit for bit. Run each in a fresh process (the mode is read once).
-    import subprocess, sys
-    code = ("import sys, torch; sys.path.insert(0, %r);"
-            "from vibe_compiler_b200.backend import B200TargetModelBackend as B;"
-            "from tests.test_gpu_attention import make_qkv;"
-            "q, k, v = make_qkv(1, 4, 2, 384, 384, 128, torch.bfloat16);"
-            "out = B(0).attention_fa(q, k, v, 128 ** -0.5, True);"
-            "torch.save(out, sys.argv[1])") % str(helpers.ROOT)
-    outs = []
-    for mode in ("0", "1"):
-        path = f"/tmp/wb200_fa_mode{mode}.pt"
-        subprocess.run([sys.executable, "-c", code, path], check=True, env=dict(os.environ, WB200_FA_P_IN_TMEM=mode), timeout=300)
-        outs.append(torch.load(path))
-    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+def test_fa_persistent_and_plain_grid_agree(backend):
+    # More 256-row items than SMs: a persistent grid walks a plan. The same heads in slices of at most 148 items run one CTA
+    # per item. The arithmetic per item is the same, so the bits must agree, and a second launch must repeat them.
+    q, k, v = make_qkv(2, 48, 8, 1100, 1100, 128, torch.bfloat16)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    scale = 128 ** -0.5
+    lse = torch.empty(2, 48, 1100, device="cuda")
+    out = backend.attention_fa(q, k, v, scale, True, lse=lse)
+    again = backend.attention_fa(q, k, v, scale, True)
+    assert torch.equal(out.view(torch.int16), again.view(torch.int16))
+    for b in range(2):
+        for h0 in range(0, 48, 24):        # 24 heads x 5 items = 120 CTAs, 4 KV heads
+            sl = slice(h0, h0 + 24)
+            kv = slice(h0 // 6, h0 // 6 + 4)
+            part_lse = torch.empty(1, 24, 1100, device="cuda")
+            part = backend.attention_fa(q[b:b + 1, sl].contiguous(), k[b:b + 1, kv].contiguous(), v[b:b + 1, kv].contiguous(), scale, True, lse=part_lse)
+            assert torch.equal(part.view(torch.int16), out[b:b + 1, sl].view(torch.int16))
+            assert torch.equal(part_lse, lse[b:b + 1, sl])
+    torch.cuda.synchronize()
+    backend.poll()
 
 
 @pytest.mark.parametrize("shape", [(1, 8, 8, 512, 512, 64, False), (1, 2, 1, 100, 333, 96, True), (2, 2, 2, 65, 65, 32, True)])

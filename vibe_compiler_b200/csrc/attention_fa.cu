@@ -12,15 +12,16 @@
 // One work item is 256 query rows of one (batch, head): two 128-row Q tiles, each with its own S and O
 // accumulators in TMEM (S0 S1 O0 O1 = 4 x 128 columns) and its own softmax warpgroup, so the tensor
 // pipe works on one tile while the other tile's softmax runs. A persistent grid of one CTA per SM walks
-// a host-made plan of items (longest-processing-time assignment, heaviest first), so the loads and first
-// scores of an item overlap the softmax tail and write-out of the previous one and every CTA ends at
-// nearly the same time. Warp 0 = TMA producer (per item: Q, then K0 V0 K1 V1 ... through a ring of
-// 32 KiB slots that runs on across items), warp 1 = MMA issuer and TMEM owner, warps 4-7 / 8-11 =
+// a host-made plan of items, so the loads and first scores of an item overlap the softmax tail and
+// write-out of the previous one and every CTA ends at nearly the same time. Warp 0 = TMA producer (per
+// item: Q, then K0 V0 K1 V1 ... through a ring of five 32 KiB slots that runs on across items), warp 1 =
+// MMA issuer and TMEM owner (the whole warp walks the loop, one elected lane issues), warps 4-7 / 8-11 =
 // softmax + rescale + epilogue for Q tile 0 / 1 (thread = query row, so row max and row sum need no
 // shuffles; setmaxnreg moves registers from warpgroup 0 to the softmax warpgroups). All mbarriers are
-// reused across items with running completion counts as parities. kPInTmem selects where the rounded
-// P lives: in TMEM, aliasing the first 64 columns of S (A operand read from TMEM, 5 ring slots), or in
-// shared memory (3 ring slots).
+// reused across items with running completion counts as parities. The rounded P lives in TMEM over the
+// first 64 columns of its scores and is the A operand of the PV product: with P in shared memory instead
+// every product would read both operands from shared memory, whose bandwidth (128 B per clock) a
+// 128 x 128 x 16 product with two shared-memory operands already uses in full.
 // Roofline: tensor pipe; algorithmic work is 4 * head_dim flop per visible (query, key) pair.
 #include <algorithm>
 #include <map>
@@ -42,50 +43,17 @@ constexpr int kTileN = 128;       // keys per KV tile
 constexpr int kTileBytesFa = kTileN * kHd * 2;  // 32 KiB: two 64-element column blocks of 128 rows
 constexpr int kBlockBytes = 128 * 128;          // one [128 rows][128 B] swizzled block
 constexpr int kFaThreads = 384;          // warpgroup 0: TMA + MMA warps; warpgroups 1, 2: softmax of Q tile 0, 1
-#ifndef WB200_FA_POLY_EVERY
-#define WB200_FA_POLY_EVERY 0
-#endif
-constexpr int kPolyEvery = WB200_FA_POLY_EVERY;  // every kPolyEvery-th pair of exponentials runs on the FMA pipe (0: none)
-#ifndef WB200_FA_P_PARTS
-#define WB200_FA_P_PARTS 2
-#endif
-#ifndef WB200_FA_FENCE_EVERY_PART
-#define WB200_FA_FENCE_EVERY_PART 1
-#endif
-constexpr int kPParts = WB200_FA_P_PARTS;        // 1 or 2 publications of P per tile
-static_assert(kPParts == 1 || kPParts == 2, "P is published whole or in two halves");
-constexpr int kChunksPerPart = 4 / kPParts;
+constexpr int kPParts = 2;               // P of a tile is published in two halves so PV starts on the first
+constexpr int kChunksPerPart = 2;        // 32-key chunks per half
 constexpr uint32_t kColS0 = 0, kColO0 = 256;    // S_t at t*128, O_t at 256 + t*128
 
-template <bool kPInTmem>
 struct FaSmem {
-  static constexpr int kSlots = kPInTmem ? 5 : 3;
+  static constexpr int kSlots = 5;         // K / V ring
   static constexpr int kQOff = 0;
   static constexpr int kRingOff = 2 * kTileBytesFa;
-  static constexpr int kPOff = kRingOff + kSlots * kTileBytesFa;
-  static constexpr int kBarOff = kPOff + (kPInTmem ? 0 : 2 * kTileBytesFa);
+  static constexpr int kBarOff = kRingOff + kSlots * kTileBytesFa;
   static constexpr size_t kBytes = kBarOff + 256 + 1024;
 };
-
-#ifdef WB200_FA_TRACE
-// Debug builds only: clock64 time stamps of CTA 0, read back through wb200_debug_fa_trace. -DWB200_FA_TRACE=1 keeps
-// the per-item stamps (a few per work item), -DWB200_FA_TRACE=2 adds the per-tile stamps (which perturb the loop).
-__device__ long long g_fa_trace[8192];
-#define FA_TRACE_ITEM(slot, index) do { if (blockIdx.x == 0) g_fa_trace[(slot) * 64 + ((index) & 63)] = clock64(); } while (0)
-__device__ __forceinline__ long long fa_global_ns() { long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-#define FA_TRACE_NS(slot, index) do { if (blockIdx.x == 0) g_fa_trace[(slot) * 64 + ((index) & 63)] = fa_global_ns(); } while (0)
-#define FA_TRACE_CTA(which) do { if (blockIdx.x < 256) g_fa_trace[2560 + blockIdx.x * 2 + (which)] = fa_global_ns(); } while (0)
-#if WB200_FA_TRACE >= 2
-#define FA_TRACE(slot, index) FA_TRACE_ITEM(slot, index)
-#else
-#define FA_TRACE(slot, index) do { } while (0)
-#endif
-#else
-#define FA_TRACE(slot, index) do { } while (0)
-#define FA_TRACE_ITEM(slot, index) do { } while (0)
-#define FA_TRACE_NS(slot, index) do { } while (0)
-#define FA_TRACE_CTA(which) do { } while (0)
-#endif
 
 struct FaParams {
   int batch, q_heads, kv_heads, group;
@@ -98,7 +66,7 @@ struct FaParams {
   int bf16;
   int num_pairs;           // ceil(q_len / 256)
   int out_token_major;     // out is [batch, q_len, q_heads, head_dim] instead of [batch, q_heads, q_len, head_dim]
-  const int *plan;         // [grid][plan_stride] item ids of each CTA in execution order, -1 terminated
+  const int *plan;         // [grid][plan_stride] item ids of each CTA in execution order, -1 terminated; null: CTA b runs item b
   int plan_stride;
   float scale_log2;        // scale * log2(e)
   void *out;
@@ -119,17 +87,36 @@ template <int kRegs>
 __device__ __forceinline__ void setmaxnreg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
 }
-// 2^x on the FMA pipe: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-4 polynomial
-// (max relative error 2.7e-6), 2^n by adding n to the exponent field. x is clamped at -126.
+// 2^x on the FMA pipe for x <= 0: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3 polynomial (maximum
+// relative error 7.5e-5, far below the rounding of P to 16 bits), 2^n by adding n to the exponent field. x is clamped at
+// -126, so the result is never exactly zero: tiles that hold masked (-inf) scores use the hardware ex2 throughout.
 __device__ __forceinline__ float ex2_poly(float x) {
   x = fmaxf(x, -126.0f);
   const float shifted = x + 12582912.0f;                 // 1.5 * 2^23: the low mantissa bits now hold n
   const float f = x - (shifted - 12582912.0f);
-  float p = fmaf(0.00957008171826601f, f, 0.05591784045100212f);
-  p = fmaf(p, f, 0.240247443318367f);
-  p = fmaf(p, f, 0.6931217908859253f);
-  p = fmaf(p, f, 0.9999992847442627f);
+  float p = fmaf(0.0551716685295105f, f, 0.2426111251115799f);
+  p = fmaf(p, f, 0.6932609677314758f);
+  p = fmaf(p, f, 0.9999280571937561f);
   return __int_as_float(__float_as_int(p) + (__float_as_int(shifted) << 23));
+}
+// Packed pairs of f32 (sm_100 has two-wide f32 fma / add): halves the issue slots of the scaling and of the row sums.
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
 }
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
@@ -183,7 +170,9 @@ __device__ __forceinline__ FaItem fa_item(const FaParams &p, int k) {
   FaItem item;
   // 32-bit arithmetic only: a 64-bit division is an out-of-line call, and a call inside the MMA warp's code costs
   // about 8 % per KV step of its issue loop.
-  const int id = p.plan[static_cast<size_t>(blockIdx.x) * p.plan_stride + k];
+  int id;
+  if (p.plan) id = p.plan[static_cast<size_t>(blockIdx.x) * p.plan_stride + k];
+  else id = k == 0 ? static_cast<int>(blockIdx.x) : -1;   // no plan: CTA b runs item b only
   const unsigned g = static_cast<unsigned>(id);
   const unsigned bh_count = static_cast<unsigned>(p.batch * p.q_heads);
   item.valid = id >= 0;
@@ -210,11 +199,11 @@ __device__ __forceinline__ FaItem fa_next_working_item(const FaParams &p, int &k
   }
 }
 
-template <bool kPInTmem, bool kBf16>
+template <bool kBf16>
 __global__ void __launch_bounds__(kFaThreads, 1)
 fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                const __grid_constant__ CUtensorMap tmap_v, const FaParams p) {
-  using L = FaSmem<kPInTmem>;
+  using L = FaSmem;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   uint8_t *smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
@@ -235,7 +224,6 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   // All barriers are reused across work items; every role keeps running completion counts for the parities.
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) { FA_TRACE_ITEM(100, 0); FA_TRACE_NS(120, 0); FA_TRACE_CTA(0); }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < L::kSlots; ++s) {
@@ -263,7 +251,6 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) FA_TRACE_ITEM(101, 0);
 
   // setmaxnreg.inc blocks until the CTA's own register pool can supply the request, so the totals after
   // reallocation (128 * 104 + 256 * 200) must not exceed what the CTA was launched with (384 * 168).
@@ -346,12 +333,7 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           for (int ks = (8 / kPParts) * part; ks < (8 / kPParts) * (part + 1); ++ks) {
             const uint64_t bdesc = v_desc + static_cast<uint32_t>((ks * 2048) >> 4);
             const uint32_t acc = (accumulate || ks != 0) ? 1u : 0u;
-            if constexpr (kPInTmem) {
-              umma_f16_ts(d_tmem, tmem_base + kColS0 + t * 128 + ks * 8, bdesc, idesc_o, acc);
-            } else {
-              const uint32_t p_addr = smem_base + L::kPOff + t * kTileBytesFa + (ks >> 2) * kBlockBytes + (ks & 3) * 32;
-              umma_f16_ss(d_tmem, umma_desc_kmajor(p_addr), bdesc, idesc_o, acc);
-            }
+            umma_f16_ts(d_tmem, tmem_base + kColS0 + t * 128 + ks * 8, bdesc, idesc_o, acc);
           }
           if (part == kPParts - 1) umma_commit(o_done(t));
         }
@@ -373,11 +355,9 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         const int n_max = item.n_max;
         ok = mbar_wait(q_full, q_count & 1u, abort_word);
         ++q_count;
-        FA_TRACE_ITEM(102, 0);
         // K_0: first scores of both tiles.
         if (ok) ok = mbar_wait(kv_full(slot), phase, abort_word);
         if (ok) {
-          FA_TRACE_ITEM(103, 0);
           tc_fence_after();
           if (n0 > 0) issue_s(std::integral_constant<int, 0>{}, slot);
           if (n1 > 0) issue_s(std::integral_constant<int, 1>{}, slot);
@@ -401,14 +381,12 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             if (j < n_tiles) {
               if (!mbar_wait_spin(p_part(t, 0), (tile_base + j) & 1u, abort_word)) { ok = false; return; }
               tc_fence_after();
-              FA_TRACE(2 + t, j);
               issue_pv_part(tile_tag, std::integral_constant<int, 0>{}, v_slot, j > 0);
               if constexpr (kPParts > 1) {
                 if (!mbar_wait_spin(p_part(t, kPParts - 1), (tile_base + j) & 1u, abort_word)) { ok = false; return; }
                 tc_fence_after();
                 issue_pv_part(tile_tag, std::integral_constant<int, kPParts - 1>{}, v_slot, j > 0);
               }
-              FA_TRACE(4 + t, j);
             }
             if (j + 1 < n_tiles) {
               if (!k_ready) {
@@ -417,7 +395,6 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
                 k_ready = true;
               }
               issue_s(tile_tag, k_slot);
-              FA_TRACE(0 + t, j + 1);
             }
           };
           tile_step(std::integral_constant<int, 0>{}, n0, base0);
@@ -469,9 +446,6 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
     for (int j = 0; ok && j < my_tiles; ++j, ++tiles_done) {
       if (!mbar_wait(s_full(t), tiles_done & 1u, abort_word, 110 + t)) { ok = false; break; }
       tc_fence_after();
-      const bool tracer = lane == 0;
-      if (tracer) FA_TRACE(8 + 16 * t + quarter, j);
-      if (tracer && j == 0 && quarter == 0) FA_TRACE_ITEM(110 + t, item_index);
       const int key0 = j * kTileN;
       uint32_t r[128];
 #pragma unroll
@@ -498,7 +472,6 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
 #pragma unroll
       for (int a = 0; a < 4; ++a) mx[a] = fmaxf(mx[a], __uint_as_float(r[32 * a + 31]));
       const float raw_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      if (tracer) FA_TRACE(12 + 16 * t + quarter, j);
       m_true = fmaxf(m_true, raw_max * p.scale_log2);     // scale > 0, so max commutes with the scaling
       float alpha = 1.0f;
       if (m_true - m_ref > kRescaleThreshold) {           // also taken when m_ref is still -inf
@@ -506,24 +479,11 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         m_ref = m_true;
       }
       const float m_exp = (m_ref == -INFINITY) ? 0.f : m_ref;
-      // acc' = acc * alpha (rare): needs PV of the previous tile to have landed in TMEM, and must be done
-      // before any PV of this tile is issued, i.e. before the first half of P is published.
-      if (j > 0) {
-        if (!mbar_wait(o_done(t), (tiles_done - 1) & 1u, abort_word, 112 + t)) { ok = false; break; }
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-#pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
-            uint32_t o[32];
-            tmem_ld_32x32(o_addr + c * 32, o);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st_32x32(o_addr + c * 32, o);
-          }
-        }
-      }
-      float sum[4] = {0.f, 0.f, 0.f, 0.f};
+      // acc' = acc * alpha (rare) needs the PV product of the previous tile in TMEM and has to land before any PV of
+      // this tile is issued, i.e. before the first half of P is published; the wait for that product sits there, behind
+      // the first 64 exponentials, where it costs nothing.
+      const unsigned long long scale2 = pack_f32x2(p.scale_log2, p.scale_log2), neg_m2 = pack_f32x2(-m_exp, -m_exp);
+      unsigned long long sum2[4] = {0ull, 0ull, 0ull, 0ull};
       auto exp_phase = [&](auto masked_tag) {
       constexpr bool kMasked = decltype(masked_tag)::value;
 #pragma unroll
@@ -531,14 +491,15 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float x0 = fmaf(__uint_as_float(r[32 * c + i]), p.scale_log2, -m_exp);
-          const float x1 = fmaf(__uint_as_float(r[32 * c + i + 1]), p.scale_log2, -m_exp);
-          // Masked tiles keep the hardware ex2 for every element: exp2(-inf) must be exactly 0 there.
-          constexpr int kEvery = kPolyEvery > 0 ? kPolyEvery : 1;
-          const bool poly = !kMasked && kPolyEvery > 0 && ((i >> 1) % kEvery) == 0;
+          const unsigned long long x2 = fma_f32x2(pack_f32x2(__uint_as_float(r[32 * c + i]), __uint_as_float(r[32 * c + i + 1])), scale2, neg_m2);
+          float x0, x1;
+          unpack_f32x2(x2, x0, x1);
+          // Every fourth pair of exponentials runs on the FMA pipe: the special-function pipe (ex2 and the 16-bit
+          // conversions) is the busiest unit of the softmax warps.
+          const bool poly = !kMasked && ((i >> 1) & 3) == 3;
           const float e0 = poly ? ex2_poly(x0) : ex2_approx(x0);
           const float e1 = poly ? ex2_poly(x1) : ex2_approx(x1);
-          sum[(i >> 1) & 3] += e0 + e1;
+          sum2[(i >> 1) & 3] = add_f32x2(sum2[(i >> 1) & 3], pack_f32x2(e0, e1));
           if constexpr (kBf16) {
             __nv_bfloat162 v = __floats2bfloat162_rn(e0, e1);
             packed[i >> 1] = *reinterpret_cast<uint32_t *>(&v);
@@ -547,36 +508,39 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
             packed[i >> 1] = *reinterpret_cast<uint32_t *>(&v);
           }
         }
-        if constexpr (kPInTmem) {
-          tmem_st_32x16(s_addr + c * 16, packed);   // P aliases the first 64 columns of S
-        } else {
-          uint8_t *p_row = smem + L::kPOff + t * kTileBytesFa + (c >> 1) * kBlockBytes + row_in_tile * 128;
+        tmem_st_32x16(s_addr + c * 16, packed);   // P aliases the first 64 columns of S
+        if (c == kChunksPerPart - 1 && j > 0) {
+          if (!mbar_wait(o_done(t), (tiles_done - 1) & 1u, abort_word, 112 + t)) { ok = false; return; }
+          if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+            tc_fence_after();
+#pragma unroll 1
+            for (int oc = 0; oc < 4; ++oc) {
+              uint32_t o[32];
+              tmem_ld_32x32(o_addr + oc * 32, o);
+              tmem_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int chunk = ((c & 1) * 4 + i) ^ (row_in_tile & 7);
-            *reinterpret_cast<uint4 *>(p_row + chunk * 16) =
-                make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+              tmem_st_32x32(o_addr + oc * 32, o);
+            }
           }
         }
-        if ((c + 1) % kChunksPerPart == 0) {   // a part of P is complete: publish it
+        if ((c + 1) % kChunksPerPart == 0) {   // a half of P is complete: publish it
           tmem_wait_st();
-          if constexpr (!kPInTmem) fence_proxy_async_smem();
           tc_fence_before();
           mbar_arrive(p_part(t, c / kChunksPerPart));
-          if (tracer && c == 3) FA_TRACE(16 + 16 * t + quarter, j);
-          if (tracer && c == kChunksPerPart - 1) FA_TRACE(20 + 16 * t + quarter, j);
         }
       }
       };
       if (need_mask) exp_phase(std::true_type{});
       else exp_phase(std::false_type{});
-      l_run = l_run * alpha + ((sum[0] + sum[1]) + (sum[2] + sum[3]));
+      if (!ok) break;
+      float s0, s1, s2, s3, s4, s5, s6, s7;
+      unpack_f32x2(sum2[0], s0, s1); unpack_f32x2(sum2[1], s2, s3); unpack_f32x2(sum2[2], s4, s5); unpack_f32x2(sum2[3], s6, s7);
+      l_run = l_run * alpha + (((s0 + s1) + (s2 + s3)) + ((s4 + s5) + (s6 + s7)));
     }
 
     // Finalize: out = acc * (1 / l), rounded once to the storage type.
-    if (threadIdx.x == 256) FA_TRACE_ITEM(104, item_index);
     if (ok && my_tiles > 0) ok = mbar_wait(o_done(t), (tiles_done - 1) & 1u, abort_word, 114 + t);
-    if (threadIdx.x == 256) FA_TRACE_ITEM(105, item_index);
     if (ok && row_base + t * kTileM < p.q_len) {
       tc_fence_after();
       float coefficient = 1.0f / l_run;
@@ -627,13 +591,11 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
         if (p.row_sum) p.row_sum[stat] = (l_run == 0.f) ? 0.f : l_run * exp2f(m_ref - m_true);
       }
     }
-    if (threadIdx.x == 256) { FA_TRACE_ITEM(106, item_index); FA_TRACE_NS(121, item_index); }
     }   // items
   }
 
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) { FA_TRACE(107, 0); FA_TRACE_CTA(1); }
   if (*abort_word != 0) {
     for (int i = 0; i < 64; ++i) __nanosleep(10000);
     if (threadIdx.x == 0) atomicExch(p.status, *abort_word);
@@ -653,9 +615,43 @@ int host_kv_tiles(const FaParams &p, long long row0) {
   return static_cast<int>(last / kTileN) + 1;
 }
 
-// The plan of a launch shape: longest-processing-time assignment of the items to `grid` CTAs (weight = KV steps of
-// the longer Q tile plus a constant for the hand-over), each CTA's items in descending weight. Plans are cached per
-// device and shape in device memory; a plan is a few KiB and is built once.
+// The plan of a launch shape: which items each of the `grid` CTAs runs, in order. Items are dealt head by head
+// (all 256-row items of one (batch, head), heaviest first, each to the CTA with the least work so far), so the CTAs
+// that share a head's K and V run at about the same time and find them in L2; the last heads' items are dealt in one
+// pool by descending weight (longest-processing-time order), which evens out the finish times. The weight of an item
+// is the KV steps of its longer Q tile plus a constant for the hand-over.
+std::vector<std::vector<int>> build_plan_rows(const FaParams &p, int grid) {
+  const int bh_count = p.batch * p.q_heads;
+  std::vector<int> weight(p.num_pairs);
+  for (int pair = 0; pair < p.num_pairs; ++pair) {
+    const long long row0 = static_cast<long long>(pair) * 2 * kTileM;
+    weight[pair] = std::max(host_kv_tiles(p, row0), host_kv_tiles(p, row0 + kTileM)) * 4 + 2;   // quarter steps; hand-over = half a step
+  }
+  auto weight_of = [&](int g) { return weight[p.num_pairs - 1 - g / bh_count]; };   // item g = pair rank * bh_count + bh
+  std::vector<std::vector<int>> rows(grid);
+  using Load = std::pair<long long, int>;   // (load, CTA): the least loaded CTA takes the next item
+  std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
+  for (int c = 0; c < grid; ++c) heap.push({0, c});
+  auto deal = [&](int g) {
+    Load least = heap.top();
+    heap.pop();
+    rows[least.second].push_back(g);
+    heap.push({least.first + weight_of(g), least.second});
+  };
+  // The pooled tail holds about three items per CTA.
+  const int tail_heads = std::min(bh_count, (3 * grid + p.num_pairs - 1) / p.num_pairs);
+  const int head_major = bh_count - tail_heads;
+  for (int bh = 0; bh < head_major; ++bh)
+    for (int rank = 0; rank < p.num_pairs; ++rank) deal(rank * bh_count + bh);
+  for (int rank = 0; rank < p.num_pairs; ++rank)
+    for (int bh = head_major; bh < bh_count; ++bh) deal(rank * bh_count + bh);
+  return rows;
+}
+
+// Plans live in device memory for the lifetime of the library (a few KiB each, at most kMaxPlansPerDevice per
+// device; nothing is ever freed, so neither a launch in flight nor a captured graph can hold a stale pointer).
+// Building one allocates and copies, so a shape's first launch should come outside stream capture; when that is not
+// possible (a capture is in progress, or the device's cap is reached) the launch gets no plan and runs one CTA per item.
 struct PlanKey {
   int device, num_pairs, bh_count, q_len, kv_visible, causal, grid;
   long long causal_offset;
@@ -665,104 +661,41 @@ struct PlanKey {
   }
 };
 struct PlanEntry { int *device_plan; int stride; };
+constexpr int kMaxPlansPerDevice = 1024;
 
-wb200_status get_plan(const FaParams &p, int grid, const int **plan, int *stride) {
+wb200_status get_plan(const FaParams &p, int grid, cudaStream_t stream, const int **plan, int *stride) {
   static std::mutex mutex;
   static std::map<PlanKey, PlanEntry> cache;
+  static int plans_on_device[PerDeviceOnce::kMaxDevices] = {};
   PlanKey key{0, p.num_pairs, p.batch * p.q_heads, p.q_len, p.kv_visible, p.causal, grid, p.causal_offset};
   WB200_CUDA_CHECK(cudaGetDevice(&key.device));
   std::lock_guard<std::mutex> lock(mutex);
   auto found = cache.find(key);
   if (found != cache.end()) { *plan = found->second.device_plan; *stride = found->second.stride; return WB200_OK; }
-  const int bh_count = key.bh_count, items = p.num_pairs * bh_count;
-  std::vector<int> weight(p.num_pairs);
-  for (int pair = 0; pair < p.num_pairs; ++pair) {
-    const long long row0 = static_cast<long long>(pair) * 2 * kTileM;
-    weight[pair] = std::max(host_kv_tiles(p, row0), host_kv_tiles(p, row0 + kTileM)) * 4 + 2;   // quarter steps; hand-over = half a step
-  }
-  std::vector<int> order(items);
-  for (int g = 0; g < items; ++g) order[g] = g;
-  auto weight_of = [&](int g) { return weight[p.num_pairs - 1 - g / bh_count]; };
-  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return weight_of(a) > weight_of(b); });
-  std::vector<std::vector<int>> rows(grid);
-  using Load = std::pair<long long, int>;   // (load, CTA): the least loaded CTA takes the next item
-  std::priority_queue<Load, std::vector<Load>, std::greater<Load>> heap;
-  for (int c = 0; c < grid; ++c) heap.push({0, c});
-  for (int g : order) {
-    Load least = heap.top();
-    heap.pop();
-    rows[least.second].push_back(g);
-    heap.push({least.first + weight_of(g), least.second});
-  }
+  *plan = nullptr;
+  *stride = 0;
+  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+  WB200_CUDA_CHECK(cudaStreamIsCapturing(stream, &capture));
+  const int slot = PerDeviceOnce::slot_of(key.device);
+  if (capture != cudaStreamCaptureStatusNone || slot < 0 || plans_on_device[slot] >= kMaxPlansPerDevice) return WB200_OK;
+  const std::vector<std::vector<int>> rows = build_plan_rows(p, grid);
   size_t longest = 0;
   for (const auto &row : rows) longest = std::max(longest, row.size());
   const int row_stride = static_cast<int>(longest) + 1;
   std::vector<int> flat(static_cast<size_t>(grid) * row_stride, -1);
   for (int c = 0; c < grid; ++c) std::copy(rows[c].begin(), rows[c].end(), flat.begin() + static_cast<size_t>(c) * row_stride);
-  if (cache.size() >= 256) {   // bound the cache: drop everything once no kernel can still be reading a plan
-    WB200_CUDA_CHECK(cudaDeviceSynchronize());
-    for (auto &entry : cache) cudaFree(entry.second.device_plan);
-    cache.clear();
-  }
   PlanEntry entry{nullptr, row_stride};
   WB200_CUDA_CHECK(cudaMalloc(&entry.device_plan, flat.size() * sizeof(int)));
-  WB200_CUDA_CHECK(cudaMemcpy(entry.device_plan, flat.data(), flat.size() * sizeof(int), cudaMemcpyHostToDevice));
+  // Pageable source: the copy is staged before the call returns, and it is ordered before the launch on `stream`.
+  WB200_CUDA_CHECK(cudaMemcpyAsync(entry.device_plan, flat.data(), flat.size() * sizeof(int), cudaMemcpyHostToDevice, stream));
   cache[key] = entry;
+  plans_on_device[slot] += 1;
   *plan = entry.device_plan;
   *stride = row_stride;
   return WB200_OK;
 }
 
-template <bool kPInTmem>
-wb200_status launch_variant(const AttentionArgs &a, FaParams p, const CUtensorMap &tq,
-                            const CUtensorMap &tk, const CUtensorMap &tv, int sm_count, cudaStream_t stream) {
-  using L = FaSmem<kPInTmem>;
-  auto kernel_bf16 = fa_umma_kernel<kPInTmem, true>;
-  auto kernel_f16 = fa_umma_kernel<kPInTmem, false>;
-  static bool attribute_set = false;
-  if (!attribute_set) {
-    WB200_CUDA_CHECK(cudaFuncSetAttribute(kernel_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(L::kBytes)));
-    WB200_CUDA_CHECK(cudaFuncSetAttribute(kernel_f16, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(L::kBytes)));
-    attribute_set = true;
-  }
-  // Persistent grid: one CTA per SM walks its share of the items, so the first loads and scores of an item overlap
-  // the softmax tail and write-out of the previous one. WB200_FA_PERSISTENT=0 launches one CTA per item instead.
-  const int items = p.num_pairs * a.batch * a.q_heads;
-  static int persistent = -1;
-  if (persistent < 0) {
-    const char *env = getenv("WB200_FA_PERSISTENT");
-    persistent = (env && env[0] == '0') ? 0 : 1;
-  }
-  const int grid = (persistent && items > sm_count) ? sm_count : items;
-  wb200_status st = get_plan(p, grid, &p.plan, &p.plan_stride);
-  if (st != WB200_OK) return st;
-  if (a.format == WB200_BF16)
-    kernel_bf16<<<grid, kFaThreads, L::kBytes, stream>>>(tq, tk, tv, p);
-  else
-    kernel_f16<<<grid, kFaThreads, L::kBytes, stream>>>(tq, tk, tv, p);
-  WB200_CUDA_CHECK(cudaGetLastError());
-  return WB200_OK;
-}
-
-// 0 = P in shared memory, 1 = P in TMEM. Chosen once per process from WB200_FA_P_IN_TMEM (default 1).
-int p_in_tmem_mode() {
-  static int mode = -1;
-  if (mode < 0) {
-    const char *env = getenv("WB200_FA_P_IN_TMEM");
-    mode = (env && env[0] == '0') ? 0 : 1;
-  }
-  return mode;
-}
-
 }  // namespace
-
-#ifdef WB200_FA_TRACE
-extern "C" int wb200_debug_fa_trace(long long *out, int count) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_fa_trace, sizeof(long long) * count));
-}
-#endif
 
 bool attention_fa_umma_supports(const AttentionArgs &a) {
   if (a.format != WB200_BF16 && a.format != WB200_F16) return false;
@@ -809,8 +742,34 @@ wb200_status launch_attention_fa_umma(const AttentionArgs &a, int sm_count, int 
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.out = a.out; p.lse = a.lse; p.row_max = a.row_max; p.row_sum = a.row_sum;
   p.status = device_status;
-  if (p_in_tmem_mode()) return launch_variant<true>(a, p, tq, tk, tv, sm_count, stream);
-  return launch_variant<false>(a, p, tq, tk, tv, sm_count, stream);
+  p.plan = nullptr;
+  p.plan_stride = 0;
+
+  static PerDeviceOnce attributes;
+  st = attributes.run([]() -> wb200_status {
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(fa_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(FaSmem::kBytes)));
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(fa_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(FaSmem::kBytes)));
+    return WB200_OK;
+  });
+  if (st != WB200_OK) return st;
+  // Persistent grid: one CTA per SM walks its share of the items, so the first loads and scores of an item overlap the
+  // softmax tail and write-out of the previous one. With no more items than SMs, or when no plan can be had (see
+  // get_plan), one CTA per item.
+  const int items = p.num_pairs * a.batch * a.q_heads;
+  int grid = items;
+  if (items > sm_count) {
+    st = get_plan(p, sm_count, stream, &p.plan, &p.plan_stride);
+    if (st != WB200_OK) return st;
+    if (p.plan) grid = sm_count;
+  }
+  if (a.format == WB200_BF16)
+    fa_umma_kernel<true><<<grid, kFaThreads, FaSmem::kBytes, stream>>>(tq, tk, tv, p);
+  else
+    fa_umma_kernel<false><<<grid, kFaThreads, FaSmem::kBytes, stream>>>(tq, tk, tv, p);
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
 }
 
 }  // namespace wb200
