@@ -4,9 +4,10 @@ flash-decoding (HBM bound) and the GEMM + bias + GELU region reported beside it 
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (N = 1): FA prefill bf16, batch 4, 32 heads, seq 4096, head_dim 128, causal, synthetic
-N(0,1) inputs from a seed. One step = one pass of the kernel over that batch. At N > 1 every rank
-runs the same-size batch of independent (batch, head) units (weak scaling, no data-path collective).
+Workload: FA prefill bf16, batch 4, 32 heads, seq 4096, head_dim 128, causal, synthetic N(0,1) inputs
+from a seed. One step = one pass of the kernel over that batch. At N > 1 the 128 independent
+(batch, head) units of that fixed problem are dealt out in contiguous blocks, 128 / N per rank, with no
+data-path collective (strong scaling: value = the whole problem's flop / the slowest rank's time).
 `value` is device-timed with inputs resident in HBM; `e2e` goes through the public host-buffer call
 (pinned host memory, copies inside the timed region). `--impl reference` times the CPU restatement
 of the reference's numeric path (the reference itself needs LLVM/MLIR/SystemC and cannot be built
@@ -135,10 +136,12 @@ class ClockSampler:
                            "source": "nvidia-smi"}
 
 
-def timed_steps(fn, steps, warmup, torch, dist=None, check=None):
+def timed_steps(fn, steps, warmup, torch, dist=None, check=None, flush=None):
     """Warm-up, then `steps` launches bracketed by barrier + synchronize; per-launch CUDA events on the
     launching stream. Returns (total ms over the bracket, mean per-launch ms). `check` runs after the
-    first warm-up launch and raises if the device reported a failure, before any time is spent."""
+    first warm-up launch and raises if the device reported a failure, before any time is spent.
+    `flush`: a buffer larger than the L2, rewritten before every timed launch (for inputs that would fit the
+    L2); the flush writes are then taken out of the total, which becomes the sum of the per-launch times."""
     for i in range(warmup):
         fn()
         if i == 0 and check is not None:
@@ -151,7 +154,9 @@ def timed_steps(fn, steps, warmup, torch, dist=None, check=None):
     events = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for begin, end in events:
+    for index, (begin, end) in enumerate(events):
+        if flush is not None:
+            flush.fill_(index & 0xff)
         begin.record()
         fn()
         end.record()
@@ -159,8 +164,8 @@ def timed_steps(fn, steps, warmup, torch, dist=None, check=None):
     torch.cuda.synchronize()
     if dist is not None:
         dist.barrier()
-    total = start.elapsed_time(stop)
     per_launch = sum(b.elapsed_time(e) for b, e in events) / steps
+    total = start.elapsed_time(stop) if flush is None else per_launch * steps
     return total, per_launch
 
 
@@ -186,12 +191,13 @@ def cpu_sample(threads: int, units: int = CPU_SAMPLE_UNITS):
                                                f"{threads} threads")
 
 
-def layer_extra(backend, args, torch, dist, rank, world, device, peak):
+def layer_extra(backend, args, torch, dist, rank, world, device, peak, failures):
     """Llama-style decoder layer forward (batch 8 x seq 2048), tensor-parallel over the ranks: heads and FFN columns are
     sharded, the two partial sums are NCCL all-reduces. Strong scaling: total work is fixed as the world grows."""
     from vibe_compiler_b200.decoder_layer import LayerConfig, ShardedDecoderLayer, layer_flops, random_weights
     cfg = LayerConfig()
-    layer = ShardedDecoderLayer(backend, cfg, random_weights(cfg, seed=SEED), rank=rank, world_size=world, device=device)
+    weights = random_weights(cfg, seed=SEED)
+    layer = ShardedDecoderLayer(backend, cfg, weights, rank=rank, world_size=world, device=device)
     gen = torch.Generator(device="cpu").manual_seed(SEED + 5)
     x = torch.randn(LAYER["batch"], LAYER["seq"], cfg.d_model, generator=gen).bfloat16().to(device)
     parts = int(os.environ.get("WB200_LAYER_MICRO_BATCHES", "0")) or None   # default: 2 when tensor parallel
@@ -203,9 +209,25 @@ def layer_extra(backend, args, torch, dist, rank, world, device, peak):
     ms = elapsed.item() / args.steps
     flops = layer_flops(cfg, LAYER["batch"], LAYER["seq"])
     tflops = flops / (ms * 1e-3) / 1e12
+    # Check what was timed (the tensor-parallel output, all-reduces included): sampled token rows of rank 0's copy against
+    # a float64 recomputation from the full weights, as the reference judges its transformer block against eager PyTorch.
+    from vibe_compiler_b200 import selfcheck
+    out = layer.forward_fused(x, micro_batches=parts)
+    torch.cuda.synchronize()
+    backend.poll()
+    layer_err = 0.0
+    if rank == 0:
+        for batch_index, rows in ((0, [0, 1, 127, 1000, 2047]), (LAYER["batch"] - 1, [255, 256, 1531])):
+            want = selfcheck.layer_rows_f64(cfg, weights, x, batch_index, rows, device)
+            layer_err = max(layer_err, selfcheck.max_rel_err(out[batch_index, rows], want))
+        if not layer_err <= 1e-2:
+            failures.append(f"decoder_layer TP{world}: max rel err {layer_err:.3e} on sampled rows")
+    del weights
     return {"workload": f"decoder layer forward bf16 d4096 32/8 heads hd128 FFN14336, batch 8 x seq 2048, TP{world} (NCCL all-reduce after o-proj and down-proj)",
             "value": tflops, "unit": "TFLOP/s", "ms_per_step": ms, "scaling": "strong", "tokens_per_s": LAYER["batch"] * LAYER["seq"] / (ms * 1e-3),
             "kernels_per_step": 10, "collectives_per_step": 0 if world == 1 else 2,
+            "verified": bool(layer_err <= 1e-2), "max_rel_err": layer_err,
+            "verified_against": "float64 torch recomputation of 8 sampled token rows from the full weights",
             "roofline": {"bound": "tensor", "achieved": tflops / world, "peak": peak["bf16_tflops_sustained"], "unit": "TFLOP/s per GPU",
                          "frac": tflops / world / peak["bf16_tflops_sustained"], "traffic": None, "peak_source": peak["source"] + " (sustained)"}}
 
@@ -314,24 +336,35 @@ def main():
     device = torch.device("cuda", local_rank)
     backend = B200TargetModelBackend(local_rank)
     peak = peaks()
+    failures = []      # outputs that disagree with their recomputation: reported in the line, and the exit code is 1
 
     # ---------------------------------------------------------------- FA prefill (headline)
+    # The fixed problem is 128 independent (batch, head) units; this rank owns a contiguous block of them, laid out as
+    # the heads of one batch entry (each unit has its own K and V).
+    from vibe_compiler_b200.sharding import unit_range
     gen = torch.Generator(device=device).manual_seed(SEED + rank)
-    shape = (FA["batch"], FA["heads"], FA["seq"], FA["head_dim"])
+    unit_begin, unit_end = unit_range(FA["batch"] * FA["heads"], world, rank)
+    units = unit_end - unit_begin
+    shape = (1, units, FA["seq"], FA["head_dim"]) if world > 1 else (FA["batch"], FA["heads"], FA["seq"], FA["head_dim"])
     q = torch.randn(shape, device=device, generator=gen).bfloat16()
     k = torch.randn(shape, device=device, generator=gen).bfloat16()
     v = torch.randn(shape, device=device, generator=gen).bfloat16()
     out = torch.empty_like(q)
     lse = torch.empty(shape[:3], device=device)
     scale = FA["head_dim"] ** -0.5
-    flops = fa_flops(FA["batch"], FA["heads"], FA["seq"], FA["head_dim"])
+    flops = fa_flops(FA["batch"], FA["heads"], FA["seq"], FA["head_dim"])      # the whole problem
+    rank_flops = fa_flops(1, units, FA["seq"], FA["head_dim"])                  # this rank's units
+
+    q_bytes = q.numel() * 2
+    # At 8 ranks a rank's Q + K + V (50 MB) fit the L2: write a buffer larger than the L2 between timed launches there.
+    flush = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=device) if 3 * q_bytes <= 126e6 else None
 
     def fa_step():
         backend.attention_fa(q, k, v, scale, True, out=out, lse=lse)
 
     launches_before = backend.launch_count
     with ClockSampler(local_rank) as sampler:
-        total_ms, launch_ms = timed_steps(fa_step, args.steps, args.warmup, torch, dist, check=backend.poll)
+        total_ms, launch_ms = timed_steps(fa_step, args.steps, args.warmup, torch, dist, check=backend.poll, flush=flush)
     backend.poll()
     launches = backend.launch_count - launches_before - args.warmup
     times = torch.tensor([total_ms, launch_ms], device=device, dtype=torch.float64)
@@ -339,8 +372,8 @@ def main():
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     total_ms, launch_ms = times.tolist()
     ms_per_step = total_ms / args.steps
-    value = world * flops / (ms_per_step * 1e-3) / 1e12
-    achieved = flops / (launch_ms * 1e-3) / 1e12
+    value = flops / (ms_per_step * 1e-3) / 1e12
+    achieved = rank_flops / (launch_ms * 1e-3) / 1e12    # per GPU (ranks own equal shares)
 
     # ---------------------------------------------------------------- e2e through host buffers
     e2e_steps = max(1, min(args.steps, 5))
@@ -358,24 +391,27 @@ def main():
     e2e_seconds = torch.tensor([(time.perf_counter() - t0) / e2e_steps], device=device, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(e2e_seconds, op=dist.ReduceOp.MAX)
-    e2e_value = world * flops / e2e_seconds.item() / 1e12
-    h2d = 3 * q.numel() * 2
-    d2h = out.numel() * 2 + lse.numel() * 4
+    e2e_value = flops / e2e_seconds.item() / 1e12
+    h2d = world * 3 * q.numel() * 2
+    d2h = world * (out.numel() * 2 + lse.numel() * 4)
     assert torch.equal(hout.view(torch.int16), out.cpu().view(torch.int16)), "host-buffer path disagrees with device path"
-    del hq, hk, hv, hout, hlse
+    del hq, hk, hv, hout, hlse, flush
 
     extras = {}
     if not args.skip_extras:
         q = k = v = out = None
         torch.cuda.empty_cache()
     if not args.skip_extras:
-        # ------------------------------------------------------------ FD decode (HBM bound); every rank runs the same-size batch
-        fq = torch.randn(FD["batch"], FD["q_heads"], 1, FD["head_dim"], device=device, generator=gen).bfloat16()
-        fk = torch.randn(FD["batch"], FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
-        fv = torch.randn(FD["batch"], FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
+        # ------------------------------------------------------------ FD decode (HBM bound): the fixed batch of 64 sequences is
+        # dealt out in contiguous blocks (64 / N sequences = 512 / N (batch, kv-head) units per rank), no collective
+        seq_begin, seq_end = unit_range(FD["batch"], world, rank)
+        fd_batch = seq_end - seq_begin
+        fq = torch.randn(fd_batch, FD["q_heads"], 1, FD["head_dim"], device=device, generator=gen).bfloat16()
+        fk = torch.randn(fd_batch, FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
+        fv = torch.randn(fd_batch, FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
         fout = torch.empty_like(fq)
-        flse = torch.empty(FD["batch"], FD["q_heads"], 1, device=device)
-        fd_bytes = 2 * fk.numel() * 2
+        flse = torch.empty(fd_batch, FD["q_heads"], 1, device=device)
+        fd_bytes = 2 * fk.numel() * 2                 # this rank's K + V
         fd_total, fd_launch = timed_steps(lambda: backend.attention_fd(fq, fk, fv, scale, out=fout, lse=flse), args.steps, args.warmup, torch, dist, check=backend.poll)
         backend.poll()
         fd_times = torch.tensor([fd_total, fd_launch], device=device, dtype=torch.float64)
@@ -383,10 +419,11 @@ def main():
             dist.all_reduce(fd_times, op=dist.ReduceOp.MAX)
         fd_ms, fd_launch_ms = fd_times[0].item() / args.steps, fd_times[1].item()
         fd_gbs = fd_bytes / (fd_launch_ms * 1e-3) / 1e9
-        extras["fd_decode"] = {"workload": "FD decode bf16 B64 Hq32 Hkv8 KV32768 D128 per GPU, inputs (8.6 GB) larger than L2", "value": world * fd_bytes / (fd_ms * 1e-3) / 1e9,
-                               "unit": "GB/s", "ms_per_step": fd_ms, "scaling": "weak", "n_gpus": world,
-                               "roofline": {"bound": "hbm", "achieved": fd_gbs, "peak": peak["hbm_gbs"], "unit": "GB/s",
-                                            "frac": fd_gbs / peak["hbm_gbs"], "traffic": TRAFFIC["fd"], "peak_source": peak["source"], "launch_ms": fd_launch_ms}}
+        extras["fd_decode"] = {"workload": f"FD decode bf16 B64 Hq32 Hkv8 KV32768 D128, 64 sequences dealt over {world} rank(s); per-rank K + V ({fd_bytes / 1e9:.1f} GB) larger than L2",
+                               "value": world * fd_bytes / (fd_ms * 1e-3) / 1e9,
+                               "unit": "GB/s", "ms_per_step": fd_ms, "scaling": "strong", "n_gpus": world,
+                               "roofline": {"bound": "hbm", "achieved": fd_gbs, "peak": peak["hbm_gbs"], "unit": "GB/s per GPU",
+                                            "frac": fd_gbs / peak["hbm_gbs"], "traffic": TRAFFIC["fd"] * fd_batch / FD["batch"], "peak_source": peak["source"], "launch_ms": fd_launch_ms}}
         del fq, fk, fv
         torch.cuda.empty_cache()
         # ------------------------------------------------------------ long-context decode: the KV sequence is sharded over the ranks
@@ -429,9 +466,32 @@ def main():
         long_ms = long_t.item() / args.steps
         long_bytes = 2 * FD_LONG["kv_heads"] * FD_LONG["kv_len"] * FD_LONG["head_dim"] * 2
         long_gbs = long_bytes / (long_ms * 1e-3) / 1e9
+        # Check what was timed: every rank recomputes the state of its own KV shard in float64 with torch operators, the
+        # states are gathered and merged in float64, and the library's output (this rank's copy) is compared with that.
+        from vibe_compiler_b200 import selfcheck
+        long_lse = torch.empty(1, FD_LONG["q_heads"], 1, device=device)
+        sharded_decode(lambda b, e: backend.attention_fd_partial(lq, lk, lv, scale, state=lstate),
+                       lambda st: backend.attention_fd_merge(st, lq, out=lout, lse=long_lse), FD_LONG["kv_len"], group, lgathered)
+        torch.cuda.synchronize()
+        backend.poll()
+        m64, l64, acc64 = selfcheck.decode_state_f64(lq, lk, lv, scale)
+        packed = torch.cat([m64[..., None], l64[..., None], acc64], -1).contiguous()          # [1, Hq, D + 2] float64
+        all_packed = [torch.empty_like(packed) for _ in range(world)]
+        if dist is not None:
+            dist.all_gather(all_packed, packed)
+        else:
+            all_packed = [packed]
+        want_out, want_lse = selfcheck.merge_states_f64([(t[..., 0], t[..., 1], t[..., 2:]) for t in all_packed])
+        long_err = selfcheck.max_rel_err(lout.view(1, FD_LONG["q_heads"], FD_LONG["head_dim"]), want_out)
+        long_lse_err = float((long_lse.view(1, -1).double() - want_lse).abs().max())
+        long_ok = long_err <= 1e-2 and long_lse_err <= 1e-3
+        if not long_ok:
+            failures.append(f"fd_long_context: max rel err {long_err:.3e}, lse abs err {long_lse_err:.3e} on rank {rank}")
         extras["fd_long_context"] = {"workload": f"FD decode bf16 B1 Hq32 Hkv8 KV1048576 D128, KV sequence sharded over {world} rank(s); exchange = all-gather of (acc, m, l) states" + ("; the step replays as one CUDA graph" if world == 1 else ""),
                                      "value": long_gbs, "unit": "GB/s", "ms_per_step": long_ms, "scaling": "strong", "n_gpus": world,
                                      "exchange_bytes_per_rank": FD_LONG["q_heads"] * (FD_LONG["head_dim"] + 2) * 4,
+                                     "verified": long_ok, "max_rel_err": long_err, "lse_abs_err": long_lse_err,
+                                     "verified_against": "float64 torch recomputation of every rank's shard, merged in float64",
                                      "roofline": {"bound": "hbm", "achieved": long_gbs / world, "peak": peak["hbm_gbs"], "unit": "GB/s per GPU",
                                                   "frac": long_gbs / world / peak["hbm_gbs"], "traffic": None, "peak_source": peak["source"]}}
         del lk, lv
@@ -453,7 +513,7 @@ def main():
     if not args.skip_extras:
         ga = gb = gout = fk = fv = None
         torch.cuda.empty_cache()
-        extras["decoder_layer"] = layer_extra(backend, args, torch, dist, rank, world, device, peak)
+        extras["decoder_layer"] = layer_extra(backend, args, torch, dist, rank, world, device, peak, failures)
 
     if rank == 0:
         cpu_threads = os.cpu_count() or 1
@@ -462,14 +522,15 @@ def main():
         one_seconds, one_flops, one_desc = cpu_sample(1, units=1) if world == 1 else (None, None, None)
         line = {
             "metric": "fa_prefill_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "FA prefill bf16 B4 H32 S4096 D128 causal (+f32 LSE), per GPU", "batch": FA["batch"], "heads": FA["heads"],
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "FA prefill bf16 B4 H32 S4096 D128 causal (+f32 LSE)", "batch": FA["batch"], "heads": FA["heads"],
                        "seq_len": FA["seq"], "head_dim": FA["head_dim"], "causal": True,
-                       "flops_per_step_per_gpu": flops, "flops_counting": "visible (query,key) pairs only",
-                       "l2": "inputs (Q+K+V 403 MB) larger than the 126 MB L2",
-                       "parallelism": f"independent (batch, head) units, {world} rank(s), no collective"},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peak["bf16_tflops"], "traffic": TRAFFIC["fa"], "peak_source": peak["source"],
+                       "flops_per_step": flops, "units_per_rank": units, "flops_counting": "visible (query,key) pairs only",
+                       "l2": f"per-rank inputs (Q+K+V {3 * q_bytes / 1e6:.0f} MB)" + (" larger than the 126 MB L2" if 3 * q_bytes > 126e6 else
+                                                                                     " fit the 126 MB L2: a buffer larger than L2 is written between timed launches"),
+                       "parallelism": f"the 128 independent (batch, head) units dealt over {world} rank(s), no collective"},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak["bf16_tflops"], "unit": "TFLOP/s per GPU",
+                         "frac": achieved / peak["bf16_tflops"], "traffic": TRAFFIC["fa"] * units / (FA["batch"] * FA["heads"]), "peak_source": peak["source"],
                          "frac_of_sustained": achieved / peak["bf16_tflops_sustained"], "launch_ms": launch_ms},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
             "gpu_launches": launches,
@@ -481,11 +542,17 @@ def main():
                                     "single_thread": {"value": one_flops / one_seconds / 1e12, "unit": "TFLOP/s", "cores": 1, "sample": one_desc,
                                                       "seconds": one_seconds}}
         line.update(extras)
+        if failures:
+            line["failures"] = failures
         emit(line)
+    bad = torch.tensor([1 if failures else 0], device=device)
     if dist is not None:
+        dist.all_reduce(bad, op=dist.ReduceOp.MAX)
         dist.barrier()
         dist.destroy_process_group()
-    return 0
+    if failures:
+        print("\n".join(failures), file=sys.stderr)
+    return 1 if bad.item() else 0
 
 
 if __name__ == "__main__":

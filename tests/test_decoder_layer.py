@@ -55,6 +55,17 @@ def test_f32_restatement_matches_hugging_face_layer():
     assert helpers.max_rel_err(got.astype(np.float64), expected.astype(np.float64)) <= 1e-5
 
 
+def test_sampled_row_recomputation_matches_the_f32_restatement():
+    # The float64 sampled-row checker used on full-size outputs, against the whole-layer restatement above.
+    from vibe_compiler_b200 import selfcheck
+    cfg = fixture.CFG
+    w, x = random_weights(cfg), fixture.layer_input()
+    want = reference_layer(cfg, w, x)
+    rows = [0, 1, 77, x.shape[1] - 1]
+    got = selfcheck.layer_rows_f64(cfg, w, x, 1, rows, torch.device("cpu"))
+    assert selfcheck.max_rel_err(got, want[1, rows]) <= 1e-5
+
+
 def _gate(oracle, got: torch.Tensor, expected: np.ndarray):
     want_bits = helpers.bits(torch.from_numpy(expected).bfloat16())
     err = helpers.max_rel_err(got.double().cpu().numpy(), expected.astype(np.float64))
@@ -206,3 +217,25 @@ def test_micro_batched_layer_equals_one_pass(backend):
     part_streams = [s for s, _ in seen[2:]]
     assert all(s != main for s in part_streams) and part_streams[0] != part_streams[1]
     assert part_streams[:2] == part_streams[2:]          # attention phase of both parts, then FFN phase of both parts
+
+
+@pytest.mark.gpu
+def test_full_size_layer_properties(backend):
+    """The benchmark's shape (d_model 4096, 32 / 8 heads, FFN 14336, batch 8 x seq 2048) on one GPU: sampled token rows
+    against a float64 recomputation from the same bf16 weights and inputs, bound 1e-2 (16-bit storage path)."""
+    from vibe_compiler_b200 import selfcheck
+    from vibe_compiler_b200.decoder_layer import ShardedDecoderLayer
+    cfg = LayerConfig()
+    weights = random_weights(cfg)
+    g = torch.Generator(device="cpu").manual_seed(20260808)
+    x = torch.randn(8, 2048, cfg.d_model, generator=g).bfloat16()
+    layer = ShardedDecoderLayer(backend, cfg, weights)
+    out = layer.forward_fused(x.cuda())
+    torch.cuda.synchronize()
+    backend.poll()
+    assert torch.isfinite(out.float()).all()
+    device = torch.device("cuda", backend.device)
+    for batch_index, rows in ((0, [0, 1, 127, 128, 1000, 2047]), (5, [255, 256, 1531, 2046])):
+        want = selfcheck.layer_rows_f64(cfg, weights, x, batch_index, rows, device)
+        err = selfcheck.max_rel_err(out[batch_index, rows], want)
+        assert err <= 1e-2, (batch_index, err)

@@ -101,6 +101,14 @@ def test_fa_f32_kernel(backend, oracle, shape):
     mask = torch.ones(sq, skv, dtype=torch.bool).tril(skv - sq) if causal else None
     ref = torch.nn.functional.scaled_dot_product_attention(q, k.repeat_interleave(g, 1), v.repeat_interleave(g, 1), attn_mask=mask)
     assert helpers.max_rel_err(out.double().numpy(), ref.double().numpy()) <= 1e-5
+    # and element by element: |a - e| <= atol + rtol * |e| for every element (the reference's elementwise policy,
+    # ProgramTensorComparison.cpp:276-403), with the ULP distance of the bulk bounded, against a float64 SDPA
+    from vibe_compiler_b200.gate import ComparisonPolicy, ProgramTensor, compute_statistics
+    ref64 = torch.nn.functional.scaled_dot_product_attention(q.double(), k.double().repeat_interleave(g, 1), v.double().repeat_interleave(g, 1),
+                                                            attn_mask=mask).float()
+    as_tensor = lambda t: ProgramTensor("f32", tuple(t.shape), np.frombuffer(t.contiguous().numpy().tobytes(), np.uint8))
+    stats = compute_statistics(backend, as_tensor(out.cpu()), as_tensor(ref64), ComparisonPolicy(atol=5e-6, rtol=1e-5))
+    assert stats.mismatch_count == 0 and stats.p99_ulp <= 1024, stats   # outputs near zero carry large ULP distances at tiny absolute error
 
 
 @pytest.mark.parametrize("name", ["fa_bf16_gqa", "fa_f16_decode_tail", "fa_f32_cfg1_small"])
@@ -227,3 +235,30 @@ def test_full_size_decode_properties(backend):
     torch.cuda.synchronize()
     backend.poll()
     assert ((other.float() - out.float()).abs().max() / out.float().abs().max()).item() <= 2 ** -6
+
+
+def test_full_size_long_context(backend):
+    """cfg 3L at its real size: one sequence of 1 048 576 keys, 32 query heads over 8 KV heads, against a float64
+    recomputation (output and log-sum-exp), through the single-GPU entry and through four sequence shards merged in
+    ascending order."""
+    from vibe_compiler_b200 import selfcheck
+    from vibe_compiler_b200.sharding import sequence_range
+    gen = torch.Generator(device="cuda").manual_seed(20260804)
+    kv_len, scale = 1 << 20, 128 ** -0.5
+    q = torch.randn(1, 32, 1, 128, device="cuda", generator=gen).bfloat16()
+    k = torch.randn(1, 8, kv_len, 128, device="cuda", generator=gen).bfloat16()
+    v = torch.randn(1, 8, kv_len, 128, device="cuda", generator=gen).bfloat16()
+    want_out, want_lse = selfcheck.merge_states_f64([selfcheck.decode_state_f64(q, k, v, scale)])
+    lse = torch.empty(1, 32, 1, device="cuda")
+    out = backend.attention_fd(q, k, v, scale, lse=lse)
+    states = []
+    for rank in range(4):
+        lo, hi = sequence_range(kv_len, 4, rank)
+        states.append(backend.attention_fd_partial(q, k[:, :, lo:hi].contiguous(), v[:, :, lo:hi].contiguous(), scale))
+    lse_sharded = torch.empty(1, 32, 1, device="cuda")
+    out_sharded = backend.attention_fd_merge(torch.stack(states), q, lse=lse_sharded)
+    torch.cuda.synchronize()
+    backend.poll()
+    for got, got_lse in ((out, lse), (out_sharded, lse_sharded)):
+        assert selfcheck.max_rel_err(got.view(1, 32, 128), want_out) <= 1e-2
+        assert (got_lse.view(1, 32).double() - want_lse).abs().max().item() <= 1e-3
