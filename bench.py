@@ -223,9 +223,25 @@ def layer_extra(backend, args, torch, dist, rank, world, device, peak, failures)
         if not layer_err <= 1e-2:
             failures.append(f"decoder_layer TP{world}: max rel err {layer_err:.3e} on sampled rows")
     del weights
+    breakdown = None
+    if world > 1:
+        # Where the step's time goes: the same layer with the sums left out (compute only; its output is meaningless), and
+        # one all-reduce of a whole [tokens, d_model] partial sum on its own.
+        layer._all_reduce_enabled = False
+        compute_ms, _ = timed_steps(lambda: layer.forward_fused(x, micro_batches=parts), max(3, args.steps // 2), 2, torch, dist=dist)
+        layer._all_reduce_enabled = True
+        message = torch.empty(LAYER["batch"] * LAYER["seq"], cfg.d_model, dtype=torch.bfloat16, device=device)
+        reduce_ms, _ = timed_steps(lambda: dist.all_reduce(message), max(3, args.steps // 2), 2, torch, dist=dist)
+        steps_half = max(3, args.steps // 2)
+        both = torch.tensor([compute_ms / steps_half, reduce_ms / steps_half], device=device)
+        dist.all_reduce(both, op=dist.ReduceOp.MAX)
+        breakdown = {"compute_only_ms": both[0].item(), "allreduce_128MiB_ms": both[1].item(), "allreduces_per_step": 2,
+                     "exposed_ms": ms - both[0].item(), "micro_batches": parts or layer.default_micro_batches(LAYER["batch"]), "reserved_sms": 16}
+        del message
     return {"workload": f"decoder layer forward bf16 d4096 32/8 heads hd128 FFN14336, batch 8 x seq 2048, TP{world} (NCCL all-reduce after o-proj and down-proj)",
             "value": tflops, "unit": "TFLOP/s", "ms_per_step": ms, "scaling": "strong", "tokens_per_s": LAYER["batch"] * LAYER["seq"] / (ms * 1e-3),
             "kernels_per_step": 10, "collectives_per_step": 0 if world == 1 else 2,
+            "breakdown": breakdown,
             "verified": bool(layer_err <= 1e-2), "max_rel_err": layer_err,
             "verified_against": "float64 torch recomputation of 8 sampled token rows from the full weights",
             "roofline": {"bound": "tensor", "achieved": tflops / world, "peak": peak["bf16_tflops_sustained"], "unit": "TFLOP/s per GPU",
@@ -329,6 +345,10 @@ def main():
     if world > 1:
         import torch.distributed as dist_mod
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # The decoder layer leaves 16 SMs to the collectives that run beside its persistent kernels: keep NCCL within them.
+        os.environ.setdefault("NCCL_MAX_CTAS", "16")
+        # The decode exchange uses plain peer loads and stores only: no NVLink multicast binding for its buffers.
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         torch.cuda.set_device(local_rank)
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         dist = dist_mod
@@ -427,7 +447,7 @@ def main():
         del fq, fk, fv
         torch.cuda.empty_cache()
         # ------------------------------------------------------------ long-context decode: the KV sequence is sharded over the ranks
-        from vibe_compiler_b200.sharding import sequence_range, sharded_decode
+        from vibe_compiler_b200.sharding import sequence_range
         lo, hi = sequence_range(FD_LONG["kv_len"], world, rank)
         shared_gen = torch.Generator(device=device).manual_seed(SEED + 77)   # the query is the same on every rank
         lq = torch.randn(1, FD_LONG["q_heads"], 1, FD_LONG["head_dim"], device=device, generator=shared_gen).bfloat16()
@@ -435,30 +455,36 @@ def main():
         lv = torch.randn(1, FD_LONG["kv_heads"], hi - lo, FD_LONG["head_dim"], device=device, generator=gen).bfloat16()
         lout = torch.empty_like(lq)
         group = None
-
-        lstate = torch.empty(1, FD_LONG["q_heads"], FD_LONG["head_dim"] + 2, device=device)
-        lgathered = torch.empty(world, 1, FD_LONG["q_heads"], FD_LONG["head_dim"] + 2, device=device)
+        # One step = stage 1 over this rank's KV shard + one kernel that folds the splits, exchanges the per-head states
+        # with plain peer stores over NVLink and merges them in ascending shard order. No collective library call, so
+        # the two launches replay as one CUDA graph at every world size.
+        from vibe_compiler_b200.sharding import PeerExchange
+        exchange = PeerExchange(backend, 1, FD_LONG["q_heads"], group, device)
+        long_lse = torch.empty(1, FD_LONG["q_heads"], 1, device=device)
 
         def long_step():
-            sharded_decode(lambda b, e: backend.attention_fd_partial(lq, lk, lv, scale, state=lstate), lambda st: backend.attention_fd_merge(st, lq, out=lout),
-                           FD_LONG["kv_len"], group, lgathered)
-        long_step()
+            backend.attention_fd_exchange(lq, lk, lv, scale, rank=exchange.rank, peer_pointers=exchange.pointers, epoch=exchange.epoch,
+                                          out=lout, lse=long_lse)
+        for _ in range(2):      # sizes the library's scratch before the capture
+            long_step()
         torch.cuda.synchronize()
         backend.poll()
-        step, graphed = long_step, None
-        if world == 1:
-            # One rank: the step has no collective, and its three launches replay as one CUDA graph. With several ranks the
-            # step stays eager (a captured NCCL all-gather has to be released before the process group is torn down).
-            from vibe_compiler_b200.sharding import GraphedDecodeStep
-            eager_out = lout.clone()
-            graphed = GraphedDecodeStep(lambda b, e: backend.attention_fd_partial(lq, lk, lv, scale, state=lstate),
-                                        lambda st: backend.attention_fd_merge(st, lq, out=lout), FD_LONG["kv_len"], lgathered, group)
-            graphed()
-            torch.cuda.synchronize()
-            assert torch.equal(eager_out, lout), "graph replay of the decode step disagrees with the eager step"
-            step = graphed
+        eager_out = lout.clone()
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                long_step()
+        torch.cuda.current_stream().wait_stream(side)
+        if dist is not None:
+            dist.barrier()          # every rank has captured before anyone replays (a replay waits for the peers' kernels)
+        graph.replay()
+        torch.cuda.synchronize()
+        backend.poll()
+        assert torch.equal(eager_out, lout), "graph replay of the decode step disagrees with the eager step"
+        step = graph.replay
         long_total, _ = timed_steps(step, args.steps, args.warmup, torch, dist, check=backend.poll)
-        del step, graphed
         backend.poll()
         long_t = torch.tensor([long_total], device=device, dtype=torch.float64)
         if dist is not None:
@@ -469,9 +495,7 @@ def main():
         # Check what was timed: every rank recomputes the state of its own KV shard in float64 with torch operators, the
         # states are gathered and merged in float64, and the library's output (this rank's copy) is compared with that.
         from vibe_compiler_b200 import selfcheck
-        long_lse = torch.empty(1, FD_LONG["q_heads"], 1, device=device)
-        sharded_decode(lambda b, e: backend.attention_fd_partial(lq, lk, lv, scale, state=lstate),
-                       lambda st: backend.attention_fd_merge(st, lq, out=lout, lse=long_lse), FD_LONG["kv_len"], group, lgathered)
+        graph.replay()
         torch.cuda.synchronize()
         backend.poll()
         m64, l64, acc64 = selfcheck.decode_state_f64(lq, lk, lv, scale)
@@ -487,14 +511,17 @@ def main():
         long_ok = long_err <= 1e-2 and long_lse_err <= 1e-3
         if not long_ok:
             failures.append(f"fd_long_context: max rel err {long_err:.3e}, lse abs err {long_lse_err:.3e} on rank {rank}")
-        extras["fd_long_context"] = {"workload": f"FD decode bf16 B1 Hq32 Hkv8 KV1048576 D128, KV sequence sharded over {world} rank(s); exchange = all-gather of (acc, m, l) states" + ("; the step replays as one CUDA graph" if world == 1 else ""),
+        extras["fd_long_context"] = {"workload": f"FD decode bf16 B1 Hq32 Hkv8 KV1048576 D128, KV sequence sharded over {world} rank(s); exchange of (acc, m, l) states by peer stores inside the merge kernel; the step replays as one CUDA graph",
                                      "value": long_gbs, "unit": "GB/s", "ms_per_step": long_ms, "scaling": "strong", "n_gpus": world,
                                      "exchange_bytes_per_rank": FD_LONG["q_heads"] * (FD_LONG["head_dim"] + 2) * 4,
                                      "verified": long_ok, "max_rel_err": long_err, "lse_abs_err": long_lse_err,
                                      "verified_against": "float64 torch recomputation of every rank's shard, merged in float64",
                                      "roofline": {"bound": "hbm", "achieved": long_gbs / world, "peak": peak["hbm_gbs"], "unit": "GB/s per GPU",
                                                   "frac": long_gbs / world / peak["hbm_gbs"], "traffic": None, "peak_source": peak["source"]}}
-        del lk, lv
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()          # no rank releases its exchange buffer while a peer may still write to it
+        del lk, lv, graph, step, exchange
         torch.cuda.empty_cache()
     if not args.skip_extras and world == 1:
         # ------------------------------------------------------------ GEMM + bias + GELU (tensor bound)

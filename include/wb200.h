@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define WB200_ABI_VERSION 2
+#define WB200_ABI_VERSION 3
 #define WB200_MAX_RANK 8
 
 typedef struct wb200_backend wb200_backend;
@@ -336,6 +336,26 @@ wb200_status wb200_attention_fd_partial(wb200_backend *backend, const wb200_atte
 wb200_status wb200_attention_fd_merge(wb200_backend *backend, const wb200_attention_params *params,
                                       const float *states, uint32_t shard_count);
 
+/* Sequence-sharded flash-decoding with the exchange inside the kernel (one shard of the KV sequence per GPU, one
+ * process per GPU). Stage 1 as in wb200_attention_fd_partial; then one kernel folds this rank's splits, stores the
+ * per-head state (head_dim + 2 floats) into every rank's exchange buffer with plain peer stores over NVLink, waits
+ * (bounded: WB200_ERR_DEVICE_TIMEOUT at the next wb200_backend_poll) for the states of all ranks and merges them in
+ * ascending rank order, the fold order of lib/Wafer/Transforms/Linalg/SpatialRegionMaterialization.cpp:2420-2433.
+ * No collective library call is involved, so the step can be captured into a CUDA graph.
+ *   peer_buffers[r]  rank r's exchange buffer as addressable from this GPU (peer-mapped / symmetric memory; entry
+ *                    [rank] is this rank's own), wb200_fd_exchange_bytes() bytes each, zero-filled before first use
+ *   epoch            two zero-filled 32-bit words in this rank's memory; the kernel keeps the call count there
+ * Every rank must make the same sequence of calls with the same batch and q_heads. Device buffers only. */
+#define WB200_MAX_EXCHANGE_RANKS 16
+typedef struct wb200_fd_exchange {
+  uint32_t rank, world;
+  void *peer_buffers[WB200_MAX_EXCHANGE_RANKS];
+  uint32_t *epoch;
+} wb200_fd_exchange;
+uint64_t wb200_fd_exchange_bytes(uint32_t batch, uint32_t q_heads, uint32_t world);
+wb200_status wb200_attention_fd_exchange(wb200_backend *backend, const wb200_attention_params *params, uint32_t kv_splits,
+                                         const wb200_fd_exchange *exchange);
+
 typedef enum wb200_epilogue {
   WB200_EPI_NONE = 0,      /* out = round(acc)                                   */
   WB200_EPI_BIAS = 1,      /* out = round(acc + bias[n])                         */
@@ -392,10 +412,10 @@ wb200_status wb200_residual_add(wb200_backend *backend, uint32_t format, const v
  *   wgu   [d_model, 2 ffn]   gate and up columns interleaved: (gate_0, up_0, gate_1, up_1, ...)
  *   wdown [ffn, d_model]
  * `allreduce` (may be null for a single shard) is called twice per part, after the kernels producing the partial sum
- * have been enqueued, with a buffer inside `workspace` holding `elements` values of `format` and the stream those
- * kernels were enqueued on; it must enqueue an in-place sum over the shards ordered after the work already on that
- * stream and before work enqueued on it later (an NCCL all-reduce on that stream, or on another stream with event
- * edges), and return 0. */
+ * have been enqueued, with a buffer inside `workspace` holding `elements` values of `format` and a stream that is
+ * already ordered after those kernels; it must enqueue an in-place sum over the shards ordered after the work already
+ * on that stream and before work enqueued on it later (an NCCL all-reduce on that stream, or on another stream with
+ * event edges), and return 0. */
 typedef int32_t (*wb200_allreduce_fn)(void *user, void *device_buffer, uint64_t elements, uint32_t format, void *stream);
 typedef struct wb200_decoder_layer_params {
   uint32_t batch, seq, d_model, head_dim;
@@ -403,9 +423,12 @@ typedef struct wb200_decoder_layer_params {
   uint32_t format;             /* WB200_BF16 or WB200_F16 */
   float eps, rope_theta;
   uint32_t position_offset;
-  uint32_t micro_batches;      /* > 1 with an allreduce callback: the batch runs as that many equal parts on two
-                                  internal streams, phase by phase, so that the all-reduce of one part overlaps the
-                                  kernels of the other; the callback then receives the part's stream. 0 / 1: one pass */
+  uint32_t micro_batches;      /* > 1 with an allreduce callback: the batch flows through the layer as that many equal
+                                  parts (whole sequences) on `stream`, and the sum of each part is enqueued on a second,
+                                  internal stream (which the callback then receives), so that it travels while the
+                                  following parts compute. 0 / 1: one pass, sums on `stream` */
+  uint32_t reserved_sms;       /* with micro_batches > 1: SMs the persistent compute kernels leave free for the
+                                  collective's kernels (0: none) */
   const void *x;               /* [batch * seq, d_model] */
   void *out;                   /* [batch * seq, d_model] */
   const void *norm1, *wqkv, *wo, *norm2, *wgu, *wdown;
@@ -421,6 +444,12 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
 /* Reads and clears the device status word of asynchronous (WB200_MEM_DEVICE) calls after
  * synchronising `stream`. Returns WB200_ERR_DEVICE_TIMEOUT if a kernel gave up a bounded wait. */
 wb200_status wb200_backend_poll(wb200_backend *backend, void *stream);
+
+/* Self-test of the bounded device-side waits: launches a kernel that waits, for at most `cycle_limit` SM clocks, on a
+ * barrier nothing arrives on. The kernel gives up, records the timeout and returns; the call reports the cycles it
+ * waited, and the next wb200_backend_poll(backend, NULL) returns WB200_ERR_DEVICE_TIMEOUT (and clears it). Replaces
+ * nothing in the reference: its commands run synchronously on the host and cannot time out. */
+wb200_status wb200_selftest_bounded_wait(wb200_backend *backend, uint64_t cycle_limit, uint64_t *waited_cycles);
 
 /* Number of kernels this backend has launched since creation (for bench accounting). */
 uint64_t wb200_backend_launch_count(const wb200_backend *backend);

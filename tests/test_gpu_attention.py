@@ -262,3 +262,25 @@ def test_full_size_long_context(backend):
     for got, got_lse in ((out, lse), (out_sharded, lse_sharded)):
         assert selfcheck.max_rel_err(got.view(1, 32, 128), want_out) <= 1e-2
         assert (got_lse.view(1, 32).double() - want_lse).abs().max().item() <= 1e-3
+
+
+def test_in_kernel_exchange_single_rank_matches_the_two_call_path(backend):
+    """The decode step whose fold, exchange and merge run in one kernel, with a world of one rank (the buffer is ordinary
+    device memory): same split records, same fold order, so the same bits as partial + merge, call after call (the
+    epoch parity alternates)."""
+    from vibe_compiler_b200.sharding import PeerExchange
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    q = torch.randn(2, 32, 1, 128, device="cuda", generator=gen).bfloat16()
+    k = torch.randn(2, 8, 5000, 128, device="cuda", generator=gen).bfloat16()
+    v = torch.randn(2, 8, 5000, 128, device="cuda", generator=gen).bfloat16()
+    scale = 128 ** -0.5
+    exchange = PeerExchange(backend, 2, 32)
+    want_lse = torch.empty(2, 32, 1, device="cuda")
+    want = backend.attention_fd_merge(backend.attention_fd_partial(q, k, v, scale, kv_splits=6).unsqueeze(0), q, lse=want_lse)
+    for call in range(3):
+        lse = torch.empty(2, 32, 1, device="cuda")
+        out = backend.attention_fd_exchange(q, k, v, scale, rank=0, peer_pointers=exchange.pointers, epoch=exchange.epoch, kv_splits=6, lse=lse)
+        torch.cuda.synchronize()
+        backend.poll()
+        assert torch.equal(out.view(torch.int16), want.view(torch.int16)) and torch.equal(lse, want_lse)
+        assert exchange.epoch.tolist() == [call + 1, 0]

@@ -3,6 +3,7 @@ elementwise, convert, reduce and the codec against the CPU oracle and the refere
 Bit-exact for everything except the libm transcendentals (tolerance stated per test)."""
 import numpy as np
 import pytest
+import torch
 
 from tests import helpers
 from vibe_compiler_b200 import _abi as abi
@@ -300,3 +301,48 @@ def test_device_codec_equals_oracle(backend, oracle, fmt, layout, shape):
     packed = backend.pack(k, compact, tmpl)
     assert np.array_equal(packed, oracle.pack(fmt, layout, shape, compact, tmpl))
     assert np.array_equal(backend.unpack(NumericTensor(k, packed)).view(DT[fmt]), compact)
+
+
+def test_bounded_wait_runs_out_and_the_backend_stays_usable(backend):
+    """A device-side wait that nothing satisfies gives up at its limit, the status word carries the timeout to the host, and
+    the context is intact afterwards (no trap, no hang)."""
+    from vibe_compiler_b200 import _abi as abi
+    from vibe_compiler_b200.backend import WB200Error
+    waited = backend.selftest_bounded_wait(200_000)
+    assert 200_000 <= waited < 20_000_000
+    with pytest.raises(WB200Error) as err:
+        backend.poll()
+    assert err.value.status == abi.ERR_DEVICE_TIMEOUT
+    backend.poll()                                   # the status was cleared
+    a = torch.ones(64, 64, dtype=torch.bfloat16, device="cuda")
+    out = backend.gemm_epilogue(a, a)
+    torch.cuda.synchronize()
+    backend.poll()
+    assert torch.equal(out.float().cpu(), torch.full((64, 64), 64.0))
+
+
+def test_two_backends_on_two_devices_in_one_process(oracle):
+    """Kernel attributes (the opt-in to large dynamic shared memory) belong to a device: a second backend on another GPU of
+    the same process must launch the tcgen05 GEMM, the prefill and the decode kernels too. Needs two visible devices."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("one visible device")
+    from vibe_compiler_b200.backend import B200TargetModelBackend
+    g = torch.Generator(device="cpu").manual_seed(11)
+    a = (torch.rand(256, 128, generator=g) * 2 - 1).bfloat16()
+    q = torch.randn(1, 4, 300, 128, generator=g).bfloat16()
+    k = torch.randn(1, 2, 300, 128, generator=g).bfloat16()
+    q1 = torch.randn(1, 8, 1, 128, generator=g).bfloat16()
+    results = []
+    for index in (0, 1):
+        be = B200TargetModelBackend(index)
+        device = torch.device("cuda", index)
+        with torch.cuda.device(device):
+            c = be.gemm_epilogue(a.to(device), a.t().contiguous().to(device))
+            o = be.attention_fa(q.to(device), k.to(device), k.to(device), 128 ** -0.5, True)
+            d = be.attention_fd(q1.to(device), k.to(device), k.to(device), 128 ** -0.5)
+            torch.cuda.synchronize(device)
+            be.poll()
+        results.append((c.cpu(), o.cpu(), d.cpu()))
+        be.close()
+    for first, second in zip(*results):
+        assert torch.equal(first.view(torch.int16), second.view(torch.int16))

@@ -120,11 +120,15 @@ ALLREDUCE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_void_p, C.c_uint64, C.c_ui
 class DecoderLayerParams(C.Structure):
     _fields_ = [("batch", C.c_uint32), ("seq", C.c_uint32), ("d_model", C.c_uint32), ("head_dim", C.c_uint32),
                 ("q_heads", C.c_uint32), ("kv_heads", C.c_uint32), ("ffn", C.c_uint32), ("format", C.c_uint32),
-                ("eps", C.c_float), ("rope_theta", C.c_float), ("position_offset", C.c_uint32), ("micro_batches", C.c_uint32),
+                ("eps", C.c_float), ("rope_theta", C.c_float), ("position_offset", C.c_uint32), ("micro_batches", C.c_uint32), ("reserved_sms", C.c_uint32),
                 ("x", C.c_void_p), ("out", C.c_void_p),
                 ("norm1", C.c_void_p), ("wqkv", C.c_void_p), ("wo", C.c_void_p), ("norm2", C.c_void_p), ("wgu", C.c_void_p), ("wdown", C.c_void_p),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
                 ("allreduce", ALLREDUCE_FN), ("allreduce_user", C.c_void_p), ("stream", C.c_void_p)]
+
+
+class FdExchange(C.Structure):
+    _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("peer_buffers", C.c_void_p * 16), ("epoch", C.c_void_p)]
 
 
 class ProgramStats(C.Structure):
@@ -180,6 +184,9 @@ SIGNATURES = {
     "wb200_rmsnorm": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_float, C.c_void_p]),
     "wb200_rope_split": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_uint32] * 5 + [C.c_float, C.c_uint32, C.c_void_p]),
     "wb200_residual_add": (C.c_int, [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64, C.c_void_p]),
+    "wb200_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint64)]),
+    "wb200_fd_exchange_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32, C.c_uint32]),
+    "wb200_attention_fd_exchange": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams), C.c_uint32, C.POINTER(FdExchange)]),
     "wb200_decoder_layer_workspace_bytes": (C.c_uint64, [C.POINTER(DecoderLayerParams)]),
     "wb200_decoder_layer": (C.c_int, [C.c_void_p, C.POINTER(DecoderLayerParams)]),
     "wb200_target_call_rdma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, _U32x3, _U32x3]),

@@ -141,6 +141,13 @@ class B200TargetModelBackend:
     def set_budget(self, max_total_bytes: int = 0, max_scratch_bytes: int = 0):
         self._check(self._lib.wb200_backend_set_budget(self._handle, max_total_bytes, max_scratch_bytes))
 
+    def selftest_bounded_wait(self, cycle_limit: int) -> int:
+        """Runs a kernel whose wait can never be satisfied, with a limit of `cycle_limit` SM clocks; returns the clocks it
+        waited. The next poll() raises WB200Error(ERR_DEVICE_TIMEOUT)."""
+        waited = C.c_uint64()
+        self._check(self._lib.wb200_selftest_bounded_wait(self._handle, cycle_limit, C.byref(waited)))
+        return waited.value
+
     def poll(self, stream: int = 0):
         self._check(self._lib.wb200_backend_poll(self._handle, C.c_void_p(stream)))
 
@@ -354,6 +361,26 @@ class B200TargetModelBackend:
         self._check(self._lib.wb200_attention_fd_partial(self._handle, C.byref(p), kv_splits, state.data_ptr()))
         return state
 
+    def fd_exchange_bytes(self, batch: int, q_heads: int, world: int) -> int:
+        return int(self._lib.wb200_fd_exchange_bytes(batch, q_heads, world))
+
+    def attention_fd_exchange(self, q, k, v, scale: float, *, rank: int, peer_pointers: Sequence[int], epoch: torch.Tensor,
+                              kv_splits: int = 0, out=None, lse=None, stream: Optional[int] = None):
+        """Sequence-sharded decode step of this rank (its KV shard in k, v) with the state exchange and the merge inside the
+        kernel. `peer_pointers[r]` is rank r's exchange buffer as addressable from this GPU; `epoch` a zeroed int32[2]."""
+        if out is None:
+            out = torch.empty_like(q)
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream
+        p = self._attention_params(q, k, v, out, scale, False, False, 0, 0, 0, lse, None, None, stream)
+        x = abi.FdExchange()
+        x.rank, x.world = rank, len(peer_pointers)
+        for r, pointer in enumerate(peer_pointers):
+            x.peer_buffers[r] = pointer
+        x.epoch = epoch.data_ptr()
+        self._check(self._lib.wb200_attention_fd_exchange(self._handle, C.byref(p), kv_splits, C.byref(x)))
+        return out
+
     def attention_fd_merge(self, states, like_q, *, out=None, lse=None, zero_fully_masked: bool = False,
                            stream: Optional[int] = None):
         """Left-folds [shards, batch, q_heads, D + 2] states in ascending shard order and finalizes."""
@@ -433,7 +460,7 @@ class B200TargetModelBackend:
 
     def decoder_layer(self, x, *, norm1, wqkv, wo, norm2, wgu, wdown, q_heads: int, kv_heads: int, head_dim: int, eps: float,
                       rope_theta: float, position_offset: int = 0, allreduce=None, workspace=None, out=None,
-                      micro_batches: int = 1, stream: Optional[int] = None):
+                      micro_batches: int = 1, reserved_sms: int = 0, stream: Optional[int] = None):
         """One shard of a Llama-style decoder layer forward through the single C-ABI call wb200_decoder_layer.
         x: [batch, seq, d_model] CUDA tensor. `allreduce(tensor)` must enqueue an in-place sum over the shards
         (torch.distributed.all_reduce); `workspace` is a uint8 CUDA tensor that is reused if large enough.
@@ -445,6 +472,7 @@ class B200TargetModelBackend:
         p.format = _TORCH_FORMATS[x.dtype]
         p.eps, p.rope_theta, p.position_offset = eps, rope_theta, position_offset
         p.micro_batches = micro_batches if allreduce is not None else 1
+        p.reserved_sms = reserved_sms
         needed = self._lib.wb200_decoder_layer_workspace_bytes(C.byref(p))
         if needed == 0:
             raise WB200Error(abi.ERR_UNSUPPORTED, self._lib.wb200_last_error().decode())

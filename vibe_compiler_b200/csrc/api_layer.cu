@@ -64,19 +64,29 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
   if (st != WB200_OK) return st;
   if (p->workspace_bytes < plan.total) return fail(WB200_ERR_LIMIT, "workspace smaller than wb200_decoder_layer_workspace_bytes()");
   if (reinterpret_cast<uintptr_t>(p->workspace) % kAlign) return fail(WB200_ERR_INVALID_ARGUMENT, "workspace must be 256-byte aligned");
-  // Micro-batches: the batch is cut into `micro_batches` equal parts that run on the backend's two auxiliary streams,
-  // phase by phase, so that the all-reduce of one part overlaps the kernels of the other.
+  // Micro-batches: the batch is cut into `micro_batches` equal parts (whole sequences) that flow through the layer one
+  // after the other on the caller's stream, while the all-reduce of each part runs on a second stream: the sum of part i
+  // travels over NVLink while the kernels of parts i + 1 ... compute. The compute kernels are persistent (one CTA per
+  // SM); `reserved_sms` of the SMs are left to the collective's kernels, which could otherwise not start before a
+  // compute kernel ends, or would hold back that kernel's CTAs.
   const uint32_t parts = (p->micro_batches > 1 && p->allreduce) ? p->micro_batches : 1;
   if (parts > 1 && (p->batch % parts != 0 || ((static_cast<uint64_t>(p->batch / parts) * p->seq) % 8) != 0))
     return fail(WB200_ERR_INVALID_ARGUMENT, "micro_batches must divide the batch into parts of a multiple of 8 tokens");
+  if (parts > 64) return fail(WB200_ERR_INVALID_ARGUMENT, "at most 64 micro-batches");
   DeviceGuard guard(backend->device);
   cudaStream_t user_stream = static_cast<cudaStream_t>(p->stream);
   if (parts > 1 && (st = backend->auxiliary_streams()) != WB200_OK) return st;
+  if (parts > 1 && (st = backend->pipeline_events(4 * parts)) != WB200_OK) return st;
+  cudaStream_t comm_stream = parts > 1 ? backend->aux_stream[0] : user_stream;
+  int compute_sms = backend->sm_count;
+  if (parts > 1 && p->reserved_sms > 0 && static_cast<int>(p->reserved_sms) < backend->sm_count / 2)
+    compute_sms = backend->sm_count - static_cast<int>(p->reserved_sms);
   const int fmt = p->format, d = p->d_model;
   const size_t part_tokens = plan.tokens / parts;
   const size_t e = 2;
 
   struct Part {
+    uint32_t index;
     cudaStream_t stream;
     const uint8_t *x;
     uint8_t *out, *h, *qkv, *q, *k, *v, *attn, *partial, *x1, *act;
@@ -87,7 +97,8 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
     uint8_t *ws = static_cast<uint8_t *>(p->workspace);
     const size_t t0 = index * part_tokens;
     Part part;
-    part.stream = parts > 1 ? backend->aux_stream[index & 1] : user_stream;
+    part.index = index;
+    part.stream = user_stream;
     part.x = static_cast<const uint8_t *>(p->x) + t0 * d * e;
     part.out = static_cast<uint8_t *>(p->out) + t0 * d * e;
     part.h = ws + plan.off_h + t0 * d * e;
@@ -110,14 +121,27 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
     g.in_format = fmt; g.out_format = fmt;
     g.epilogue = epilogue;
     g.a = a; g.b = b; g.out = out;
-    wb200_status s = launch_gemm_umma(g, backend->sm_count, backend->d_status, stream);
+    wb200_status s = launch_gemm_umma(g, compute_sms, backend->d_status, stream);
     if (s == WB200_OK) backend->launches += 1;
     return s;
   };
-  auto reduce = [&](const Part &part) -> wb200_status {
+  // The sum over shards of a part's partial output: ordered after the part's kernels by an event, enqueued on the
+  // communication stream; `done` is recorded behind it for the kernels that consume the sum.
+  auto reduce = [&](const Part &part, int phase) -> wb200_status {
     if (!p->allreduce) return WB200_OK;
-    if (p->allreduce(p->allreduce_user, part.partial, static_cast<uint64_t>(tokens) * d, p->format, part.stream) != 0)
+    if (parts > 1) {
+      cudaEvent_t ready = backend->pipeline_event[4 * part.index + 2 * phase];
+      WB200_CUDA_CHECK(cudaEventRecord(ready, part.stream));
+      WB200_CUDA_CHECK(cudaStreamWaitEvent(comm_stream, ready, 0));
+    }
+    if (p->allreduce(p->allreduce_user, part.partial, static_cast<uint64_t>(tokens) * d, p->format, comm_stream) != 0)
       return fail(WB200_ERR_CALLBACK, "the all-reduce callback reported a failure");
+    if (parts > 1) WB200_CUDA_CHECK(cudaEventRecord(backend->pipeline_event[4 * part.index + 2 * phase + 1], comm_stream));
+    return WB200_OK;
+  };
+  auto await_sum = [&](const Part &part, int phase) -> wb200_status {
+    if (parts > 1 && p->allreduce)
+      WB200_CUDA_CHECK(cudaStreamWaitEvent(part.stream, backend->pipeline_event[4 * part.index + 2 * phase + 1], 0));
     return WB200_OK;
   };
   // RMSNorm -> QKV -> rotary split -> attention -> output projection -> [sum over shards]
@@ -136,44 +160,46 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
     a.causal_offset = 0; a.kv_valid = p->seq;
     a.q = part.q; a.k = part.k; a.v = part.v; a.out = part.attn;
     a.out_token_major = 1;
-    s = attention_fa_umma_supports(a) ? launch_attention_fa_umma(a, backend->sm_count, backend->d_status, part.stream)
+    s = attention_fa_umma_supports(a) ? launch_attention_fa_umma(a, compute_sms, backend->d_status, part.stream)
                                       : launch_attention_fa_simt(a, part.stream);
     if (s != WB200_OK) return s;
     backend->launches += 1;
     if ((s = gemm(part.stream, part.attn, p->wo, part.partial, tokens, d, static_cast<int>(plan.attn_cols), WB200_EPI_NONE)) != WB200_OK) return s;
-    return reduce(part);
+    return reduce(part, 0);
   };
   // residual -> RMSNorm -> gate/up with SwiGLU epilogue -> down projection -> [sum over shards] -> residual
   auto ffn_phase = [&](const Part &part) -> wb200_status {
     wb200_status s;
+    if ((s = await_sum(part, 0)) != WB200_OK) return s;
     if ((s = launch_residual_add(fmt, part.x, part.partial, part.x1, static_cast<size_t>(tokens) * d, part.stream)) != WB200_OK) return s;
     backend->launches += 1;
     if ((s = launch_rmsnorm(fmt, part.x1, p->norm2, part.h, tokens, d, p->eps, part.stream)) != WB200_OK) return s;
     backend->launches += 1;
     if ((s = gemm(part.stream, part.h, p->wgu, part.act, tokens, 2 * static_cast<int>(p->ffn), d, WB200_EPI_SWIGLU)) != WB200_OK) return s;
     if ((s = gemm(part.stream, part.act, p->wdown, part.partial, tokens, d, static_cast<int>(p->ffn), WB200_EPI_NONE)) != WB200_OK) return s;
-    if ((s = reduce(part)) != WB200_OK) return s;
+    return reduce(part, 1);
+  };
+  auto final_residual = [&](const Part &part) -> wb200_status {
+    wb200_status s;
+    if ((s = await_sum(part, 1)) != WB200_OK) return s;
     if ((s = launch_residual_add(fmt, part.x1, part.partial, part.out, static_cast<size_t>(tokens) * d, part.stream)) != WB200_OK) return s;
     backend->launches += 1;
     return WB200_OK;
   };
 
-  if (parts > 1) {   // fork: the auxiliary streams start after the work already on the caller's stream
-    WB200_CUDA_CHECK(cudaEventRecord(backend->aux_event[0], user_stream));
-    for (int i = 0; i < 2; ++i) WB200_CUDA_CHECK(cudaStreamWaitEvent(backend->aux_stream[i], backend->aux_event[0], 0));
-  }
-  // Phase by phase over the parts, so that the all-reduces are issued in the order their inputs become ready.
+  // Phase by phase over the parts, so that the all-reduces are issued in the order their inputs become ready. Every
+  // kernel is on the caller's stream and every sum's `done` event is waited for there, so the call leaves no work
+  // behind that the caller's stream is not ordered after; on a failure the enqueued part is simply left to finish.
   for (uint32_t i = 0; i < parts; ++i)
-    if ((st = attention_phase(part_of(i))) != WB200_OK) return st;
-  for (uint32_t i = 0; i < parts; ++i)
-    if ((st = ffn_phase(part_of(i))) != WB200_OK) return st;
-  if (parts > 1) {   // join
-    for (int i = 0; i < 2; ++i) {
-      WB200_CUDA_CHECK(cudaEventRecord(backend->aux_event[1 + i], backend->aux_stream[i]));
-      WB200_CUDA_CHECK(cudaStreamWaitEvent(user_stream, backend->aux_event[1 + i], 0));
-    }
+    if ((st = attention_phase(part_of(i))) != WB200_OK) break;
+  for (uint32_t i = 0; st == WB200_OK && i < parts; ++i) st = ffn_phase(part_of(i));
+  for (uint32_t i = 0; st == WB200_OK && i < parts; ++i) st = final_residual(part_of(i));
+  if (st != WB200_OK && parts > 1) {
+    // join: later work on the caller's stream must not overtake a collective that is still running on the other stream
+    cudaEventRecord(backend->aux_event[0], comm_stream);
+    cudaStreamWaitEvent(user_stream, backend->aux_event[0], 0);
   }
-  return WB200_OK;
+  return st;
 }
 
 }  // extern "C"

@@ -221,6 +221,33 @@ wb200_status wb200_attention_fd_partial(wb200_backend *backend, const wb200_atte
   return read_device_status(backend, backend->stream, nullptr);
 }
 
+uint64_t wb200_fd_exchange_bytes(uint32_t batch, uint32_t q_heads, uint32_t world) {
+  return fd_exchange_floats(static_cast<int>(batch * q_heads), static_cast<int>(world)) * sizeof(float);
+}
+
+wb200_status wb200_attention_fd_exchange(wb200_backend *backend, const wb200_attention_params *p, uint32_t kv_splits,
+                                         const wb200_fd_exchange *x) {
+  if (!backend || !p || !x || !p->out || !x->epoch) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  if (p->q_len != 1) return fail(WB200_ERR_INVALID_ARGUMENT, "flash-decoding takes query length 1");
+  if (p->memory != WB200_MEM_DEVICE) return fail(WB200_ERR_UNSUPPORTED, "the in-kernel exchange takes device buffers only");
+  if (x->world < 1 || x->world > WB200_MAX_EXCHANGE_RANKS || x->rank >= x->world)
+    return fail(WB200_ERR_INVALID_ARGUMENT, "exchange takes 1 to 16 ranks and a rank inside the world");
+  for (uint32_t r = 0; r < x->world; ++r)
+    if (!x->peer_buffers[r] || (reinterpret_cast<uintptr_t>(x->peer_buffers[r]) & 15u))
+      return fail(WB200_ERR_INVALID_ARGUMENT, "every rank's exchange buffer must be given, 16-byte aligned");
+  AttentionArgs a;
+  wb200_status st = make_attention_args(p, &a);
+  if (st != WB200_OK) return st;
+  DeviceGuard guard(backend->device);
+  const uint32_t splits = kv_splits ? kv_splits : fd_choose_splits(a, backend->sm_count);
+  void *partials;
+  if ((st = backend->buffer(7, fd_partial_floats(a, splits) * sizeof(float), &partials)) != WB200_OK) return st;
+  st = launch_attention_fd_exchange(a, splits, static_cast<float *>(partials), static_cast<int>(x->rank), static_cast<int>(x->world),
+                                    x->peer_buffers, x->epoch, backend->d_status, static_cast<cudaStream_t>(p->stream));
+  if (st == WB200_OK) backend->launches += 2;
+  return st;
+}
+
 wb200_status wb200_attention_fd_merge(wb200_backend *backend, const wb200_attention_params *p, const float *states, uint32_t shard_count) {
   if (!backend || !p || !states || !p->out) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
   if (p->q_len != 1) return fail(WB200_ERR_INVALID_ARGUMENT, "flash-decoding takes query length 1");

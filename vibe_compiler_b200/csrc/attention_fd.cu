@@ -340,6 +340,117 @@ __global__ void __launch_bounds__(kD) fd_combine_kernel(const FdCombineParams p)
   }
 }
 
+// Sequence-sharded decode, one shard per GPU: the fold over this GPU's splits, the exchange of the per-head states
+// between the GPUs and the final merge in one kernel (one CTA per (batch, query head) row, thread = head dimension).
+// Every rank owns an exchange buffer that all ranks can address (peer-mapped memory):
+//   states [2][world][rows][kRecord] floats, then flags [2][world][rows] words, both indexed by the parity of an epoch
+// that advances by one per call on every rank. A CTA writes its row's state into slot [parity][rank][row] of every
+// rank's buffer with plain stores over NVLink, publishes it with a release store of the epoch tag to the matching
+// flag, waits (bounded) until the flags of all ranks for its row carry the tag in its own buffer, and folds the world's
+// states in ascending rank order - the shard order of the reference's spatial flash-decoding fold
+// (lib/Wafer/Transforms/Linalg/SpatialRegionMaterialization.cpp:2420-2433). A rank can run at most one epoch ahead of
+// another (its next exchange cannot complete before the other has entered it), so two parities suffice.
+constexpr int kMaxExchangeRanks = 16;
+struct FdExchangeParams {
+  FdCombineParams fold;              // this rank's split records and the outputs
+  int rank, world;
+  float *peer[kMaxExchangeRanks];    // exchange buffers of all ranks, [rank] = this rank's own
+  unsigned int *epoch;               // this rank's {epoch, finished CTAs}, zero-initialised
+  int *status;
+};
+__device__ __forceinline__ void st_release_sys(unsigned int *address, unsigned int value) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(address), "r"(value) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *address) {
+  unsigned int value;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(value) : "l"(address) : "memory");
+  return value;
+}
+
+__global__ void __launch_bounds__(kD) fd_exchange_kernel(const FdExchangeParams p) {
+  const int row = blockIdx.x, d = threadIdx.x, rows = p.fold.rows;
+  // fold this rank's splits in ascending order
+  const float *rec = p.fold.records_ptr + row * p.fold.row_stride;
+  float m = rec[kD], l = rec[kD + 1], a = rec[d];
+  for (int i = 1; i < p.fold.records; ++i) {
+    const float *right = rec + i * p.fold.record_stride;
+    const float m_right = right[kD], l_right = right[kD + 1], a_right = right[d];
+    const float m_new = fmaxf(m, m_right);
+    const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;
+    const float scale_left = exp_lp(m - m_exp), scale_right = exp_lp(m_right - m_exp);
+    l = l * scale_left + l_right * scale_right;
+    a = a * scale_left + a_right * scale_right;
+    m = m_new;
+  }
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int *>(p.epoch);
+  const unsigned int parity = epoch & 1u, tag = epoch + 1u;
+  const size_t state_floats = static_cast<size_t>(2) * p.world * rows * kRecord;
+  const size_t my_slot = (static_cast<size_t>(parity) * p.world + p.rank) * rows + row;
+  for (int r = 0; r < p.world; ++r) {
+    float *dst = p.peer[r] + my_slot * kRecord;
+    dst[d] = a;
+    if (d == 0) {
+      dst[kD] = m;
+      dst[kD + 1] = l;
+    }
+  }
+  __syncthreads();   // the whole row is written before it is published
+  if (d == 0) {
+    __threadfence_system();
+    for (int r = 0; r < p.world; ++r)
+      st_release_sys(reinterpret_cast<unsigned int *>(p.peer[r] + state_floats) + my_slot, tag);
+  }
+  // bounded wait for every rank's row
+  float *own = p.peer[p.rank];
+  if (d < p.world) {
+    const unsigned int *flag = reinterpret_cast<const unsigned int *>(own + state_floats) + (static_cast<size_t>(parity) * p.world + d) * rows + row;
+    const long long start = clock64();
+    unsigned int polls = 0;
+    while (ld_acquire_sys(flag) != tag) {
+      if ((++polls & 63u) == 0u && clock64() - start > 2000000000LL) {   // about a second: give up, report, carry on
+        atomicExch(p.status, 2);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  // merge the world's states in ascending shard order (L1 is bypassed: peers wrote these lines)
+  {
+    const float *first = own + (static_cast<size_t>(parity) * p.world * rows + row) * kRecord;
+    m = __ldcg(first + kD); l = __ldcg(first + kD + 1); a = __ldcg(first + d);
+    for (int r = 1; r < p.world; ++r) {
+      const float *right = own + ((static_cast<size_t>(parity) * p.world + r) * rows + row) * kRecord;
+      const float m_right = __ldcg(right + kD), l_right = __ldcg(right + kD + 1), a_right = __ldcg(right + d);
+      const float m_new = fmaxf(m, m_right);
+      const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;
+      const float scale_left = exp_lp(m - m_exp), scale_right = exp_lp(m_right - m_exp);
+      l = l * scale_left + l_right * scale_right;
+      a = a * scale_left + a_right * scale_right;
+      m = m_new;
+    }
+  }
+  float coefficient = 1.0f / l;
+  if (p.fold.zero_fully_masked && l == 0.f) coefficient = 0.f;
+  const float value = a * coefficient;
+  if (p.fold.out_format == WB200_F32)
+    reinterpret_cast<float *>(p.fold.out)[static_cast<size_t>(row) * kD + d] = value;
+  else
+    reinterpret_cast<uint16_t *>(p.fold.out)[static_cast<size_t>(row) * kD + d] =
+        static_cast<uint16_t>(narrow_bits(value, p.fold.out_format));
+  if (d == 0) {
+    if (p.fold.lse) p.fold.lse[row] = (l == 0.f) ? -INFINITY : m + logf(l);
+    if (p.fold.row_max) p.fold.row_max[row] = m;
+    if (p.fold.row_sum) p.fold.row_sum[row] = l;
+    // the last CTA of the launch advances the epoch for the next call
+    __threadfence();
+    if (atomicAdd(p.epoch + 1, 1u) == static_cast<unsigned int>(rows) - 1u) {
+      p.epoch[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile unsigned int *>(p.epoch) = epoch + 1u;
+    }
+  }
+}
+
 int visible_keys(const AttentionArgs &a) {
   int64_t visible = a.kv_valid < a.kv_len ? a.kv_valid : a.kv_len;
   if (a.causal && a.causal_offset + 1 < visible) visible = a.causal_offset + 1;
@@ -359,21 +470,85 @@ bool attention_fd_supports(const AttentionArgs &a) {
 
 uint32_t fd_choose_splits(const AttentionArgs &a, int sm_count) {
   const int64_t visible = visible_keys(a);
-  int64_t splits = (visible + 2047) / 2048;
   const int64_t units = static_cast<int64_t>(a.batch) * a.kv_heads;
-  // Enough CTAs for four resident waves when the KV axis allows it (>= 256 rows per split).
-  while (units * splits < 4LL * sm_count && (visible + splits * 2 - 1) / (splits * 2) >= 256) splits *= 2;
-  if (splits < 2) splits = 2;  // flash-decoding splits K2 into at least two intervals
-  if (splits > 4096) splits = 4096;
-  return static_cast<uint32_t>(splits);
+  const int64_t slots = 2LL * sm_count;                 // two CTAs are resident per SM
+  const int64_t base = (visible + 2047) / 2048;         // 2048-key splits
+  // Many more CTAs than slots: the hardware deals them out as slots free up and the tail is one short CTA.
+  if (units * base >= 8 * slots) return static_cast<uint32_t>(base < 2 ? 2 : (base > 4096 ? 4096 : base));
+  // Otherwise pick the split count with the least estimated time, in units of one key streamed by one CTA:
+  // waves x (keys per split + the CTA's fixed cost) + the serial fold over the splits (one record costs about as much
+  // as six keys). A long sequence with few (batch, kv head) units ends up with exactly one resident wave.
+  int64_t limit = visible / 256;                        // at least 256 keys per split
+  if (limit > 4096) limit = 4096;
+  int64_t best_splits = 2, best_cost = -1;
+  for (int64_t splits = 2; splits <= (limit < 2 ? 2 : limit); ++splits) {
+    const int64_t rows = ((visible + splits - 1) / splits + 63) / 64 * 64;
+    const int64_t waves = (units * splits + slots - 1) / slots;
+    const int64_t cost = waves * (rows + 130) + 6 * splits;
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_splits = splits; }
+  }
+  return static_cast<uint32_t>(best_splits);            // flash-decoding splits K2 into at least two intervals
 }
 
 size_t fd_partial_floats(const AttentionArgs &a, uint32_t splits) {
   return static_cast<size_t>(a.batch) * a.q_heads * splits * kRecord;
 }
 
+namespace {
+wb200_status launch_fd_stage1(const AttentionArgs &a, uint32_t splits, float *partials, cudaStream_t stream);
+}
+
+size_t fd_exchange_floats(int rows, int world) {
+  // states [2][world][rows][kRecord] floats followed by flags [2][world][rows] words
+  return static_cast<size_t>(2) * world * rows * (kRecord + 1);
+}
+
+wb200_status launch_attention_fd_exchange(const AttentionArgs &a, uint32_t splits, float *partials, int rank, int world,
+                                          void *const *peer_buffers, unsigned int *epoch, int *device_status, cudaStream_t stream) {
+  if (world < 1 || world > kMaxExchangeRanks || rank < 0 || rank >= world)
+    return fail(WB200_ERR_INVALID_ARGUMENT, "exchange takes 1 to 16 ranks and a rank inside the world");
+  wb200_status st = launch_fd_stage1(a, splits, partials, stream);
+  if (st != WB200_OK) return st;
+  FdExchangeParams p;
+  p.fold.rows = a.batch * a.q_heads;
+  p.fold.records = static_cast<int>(splits);
+  p.fold.row_stride = static_cast<size_t>(splits) * kRecord;
+  p.fold.record_stride = kRecord;
+  p.fold.records_ptr = partials;
+  p.fold.out_format = a.format;
+  p.fold.zero_fully_masked = a.zero_fully_masked;
+  p.fold.finalize = 1;
+  p.fold.out = a.out; p.fold.lse = a.lse; p.fold.row_max = a.row_max; p.fold.row_sum = a.row_sum; p.fold.state_out = nullptr;
+  p.rank = rank; p.world = world;
+  for (int r = 0; r < kMaxExchangeRanks; ++r) p.peer[r] = r < world ? static_cast<float *>(peer_buffers[r]) : nullptr;
+  p.epoch = epoch;
+  p.status = device_status;
+  fd_exchange_kernel<<<p.fold.rows, kD, 0, stream>>>(p);
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
+}
+
 wb200_status launch_attention_fd(const AttentionArgs &a, uint32_t splits, float *partials, int finalize,
                                  float *state_out, cudaStream_t stream) {
+  wb200_status st = launch_fd_stage1(a, splits, partials, stream);
+  if (st != WB200_OK) return st;
+  FdCombineParams c;
+  c.rows = a.batch * a.q_heads;
+  c.records = static_cast<int>(splits);
+  c.row_stride = static_cast<size_t>(splits) * kRecord;
+  c.record_stride = kRecord;
+  c.records_ptr = partials;
+  c.out_format = a.format;
+  c.zero_fully_masked = a.zero_fully_masked;
+  c.finalize = finalize;
+  c.out = a.out; c.lse = a.lse; c.row_max = a.row_max; c.row_sum = a.row_sum; c.state_out = state_out;
+  fd_combine_kernel<<<c.rows, kD, 0, stream>>>(c);
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
+}
+
+namespace {
+wb200_status launch_fd_stage1(const AttentionArgs &a, uint32_t splits, float *partials, cudaStream_t stream) {
   if (!attention_fd_supports(a)) return fail(WB200_ERR_UNSUPPORTED, "flash-decoding request outside the kernel's domain");
   if (splits < 1) return fail(WB200_ERR_INVALID_ARGUMENT, "kv_splits must be positive");
   FdParams p;
@@ -405,21 +580,9 @@ wb200_status launch_attention_fd(const AttentionArgs &a, uint32_t splits, float 
   else
     fd_partial_kernel<false><<<grid, kWarps * 32, kFdSmemBytes, stream>>>(p);
   WB200_CUDA_CHECK(cudaGetLastError());
-
-  FdCombineParams c;
-  c.rows = a.batch * a.q_heads;
-  c.records = static_cast<int>(splits);
-  c.row_stride = static_cast<size_t>(splits) * kRecord;
-  c.record_stride = kRecord;
-  c.records_ptr = partials;
-  c.out_format = a.format;
-  c.zero_fully_masked = a.zero_fully_masked;
-  c.finalize = finalize;
-  c.out = a.out; c.lse = a.lse; c.row_max = a.row_max; c.row_sum = a.row_sum; c.state_out = state_out;
-  fd_combine_kernel<<<c.rows, kD, 0, stream>>>(c);
-  WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }
+}  // namespace
 
 wb200_status launch_attention_fd_merge(const AttentionArgs &a, const float *states, uint32_t shard_count,
                                        cudaStream_t stream) {

@@ -162,6 +162,13 @@ wb200_status launch_attention_fd(const AttentionArgs &args, uint32_t splits, flo
                                  int finalize, float *state_out, cudaStream_t stream);
 wb200_status launch_attention_fd_merge(const AttentionArgs &args, const float *states,
                                        uint32_t shard_count, cudaStream_t stream);
+// Sequence-sharded decode with the exchange inside the kernel: stage 1, then one kernel that folds this rank's splits,
+// writes the state into every rank's exchange buffer (peer-mapped memory), waits for the world's states and merges
+// them in ascending rank order. `peer_buffers` holds `world` buffers of fd_exchange_floats() floats, zero-initialised;
+// `epoch` is this rank's pair of zero-initialised words.
+size_t fd_exchange_floats(int rows, int world);
+wb200_status launch_attention_fd_exchange(const AttentionArgs &args, uint32_t splits, float *partials, int rank, int world,
+                                          void *const *peer_buffers, unsigned int *epoch, int *device_status, cudaStream_t stream);
 
 
 // ---- decoder-layer pieces (layer_ops.cu); device pointers, bf16 / f16 storage

@@ -62,7 +62,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait. `abort_word` lives in shared memory; any role that gives up sets it and every other
 // spinning role sees it within a few hundred polls and gives up too.
 // `site` identifies the wait in the status word when it gives up (1 if not given).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_word, int site = kDeviceWaitTimeout) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_word, int site = kDeviceWaitTimeout,
+                                          long long cycle_limit = kSpinCycleLimit) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long start = clock64();
   uint32_t polls = 0;
@@ -70,7 +71,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 255u) == 0u) {
       if (*abort_word != 0) return false;
-      if (clock64() - start > kSpinCycleLimit) {
+      if (clock64() - start > cycle_limit) {
         *abort_word = site;
         return false;
       }

@@ -117,18 +117,33 @@ class ShardedDecoderLayer:
         return self.backend.residual_add(x1, partial2).reshape(batch, seq, d)
 
 
-    def forward_fused(self, x: torch.Tensor, position_offset: int = 0, micro_batches: Optional[int] = None) -> torch.Tensor:
-        """Same computation through the single C-ABI call (wb200_decoder_layer): ten kernels enqueued by one call, the
-        two sums through a callback into torch.distributed, intermediates in one reused workspace."""
+    def default_micro_batches(self, batch: int) -> int:
+        if self.world == 1:
+            return 1
+        for parts in (4, 2):
+            if batch % parts == 0:
+                return parts
+        return 1
+
+    def forward_fused(self, x: torch.Tensor, position_offset: int = 0, micro_batches: Optional[int] = None,
+                      reserved_sms: Optional[int] = None) -> torch.Tensor:
+        """Same computation through the single C-ABI call (wb200_decoder_layer): ten kernels per part enqueued by one call,
+        the two sums through a callback into torch.distributed, intermediates in one reused workspace. With several
+        shards the batch is cut into `micro_batches` parts (default: 4 when the batch allows) whose all-reduces run on a
+        second stream while the following parts compute; `reserved_sms` SMs (default 16) stay free for NCCL's kernels."""
         reduce = None
         if self.world > 1:
             import torch.distributed as dist
-            reduce = lambda t: dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)   # noqa: E731
+            if getattr(self, "_all_reduce_enabled", True):
+                reduce = lambda t: dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)   # noqa: E731
+            else:                                      # timing aid: the layer's kernels without the sums (wrong values)
+                reduce = lambda t: None                # noqa: E731
         out, self._workspace = self.backend.decoder_layer(
             x, norm1=self.norm1, wqkv=self.wqkv, wo=self.wo, norm2=self.norm2, wgu=self.wgu, wdown=self.wdown, q_heads=self.hq,
             kv_heads=self.hkv, head_dim=self.cfg.head_dim, eps=self.cfg.eps, rope_theta=self.cfg.rope_theta,
             position_offset=position_offset, allreduce=reduce, workspace=getattr(self, "_workspace", None),
-            micro_batches=(micro_batches if micro_batches is not None else (2 if (self.world > 1 and x.shape[0] % 2 == 0) else 1)))
+            micro_batches=(micro_batches if micro_batches is not None else self.default_micro_batches(x.shape[0])),
+            reserved_sms=(reserved_sms if reserved_sms is not None else (16 if self.world > 1 else 0)))
         return out
 
 

@@ -84,3 +84,37 @@ class GraphedDecodeStep:
 
     def __call__(self):
         self._graph.replay()
+
+
+class PeerExchange:
+    """Exchange buffers for the sequence-sharded decode whose state exchange runs inside the kernel
+    (B200TargetModelBackend.attention_fd_exchange): one buffer per rank that every rank's GPU can address, plus this
+    rank's epoch words. With one rank the buffer is ordinary device memory; with several it is torch symmetric memory
+    (peer-mapped over NVLink), and the constructor is a collective call of the group.
+
+        exchange = PeerExchange(backend, batch, q_heads, group)
+        backend.attention_fd_exchange(q, k_shard, v_shard, scale, rank=exchange.rank, peer_pointers=exchange.pointers,
+                                      epoch=exchange.epoch, out=out)
+
+    The step involves no collective library call, so it may be captured into a CUDA graph. Release the object only after
+    every rank has finished its last step (synchronise, then barrier)."""
+
+    def __init__(self, backend, batch: int, q_heads: int, group=None, device: Optional[torch.device] = None):
+        import torch.distributed as dist
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        device = device or torch.device("cuda", backend.device)
+        nbytes = backend.fd_exchange_bytes(batch, q_heads, self.world)
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=device)
+        if self.world == 1:
+            self.buffer = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+            self.pointers = [self.buffer.data_ptr()]
+            self._handle = None
+        else:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+            self.buffer.zero_()
+            self._handle = symm_mem.rendezvous(self.buffer, group if group is not None else dist.group.WORLD)
+            self.pointers = [int(pointer) for pointer in self._handle.buffer_ptrs]
+            torch.cuda.synchronize(device)
+            dist.barrier(group)          # every rank's buffer is zeroed before anyone's first step
