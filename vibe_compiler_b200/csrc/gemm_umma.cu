@@ -48,6 +48,69 @@ __device__ __forceinline__ float gelu_erf(float x) {
   return 0.5f * x * (1.0f + erff(x * 0.70710678118654752440f));
 }
 
+// Epilogue of 32 accumulator columns [col0, col0 + 32) of output row `row`: bias / GELU / SwiGLU in f32, one
+// round-to-nearest-even narrowing, 16-byte stores.
+__device__ __forceinline__ void epilogue_chunk(const GemmUmmaParams &p, uint32_t (&r)[32], int row, int col0) {
+  if (p.epilogue == WB200_EPI_SWIGLU) {
+    // Columns (2j, 2j+1) hold (gate_j, up_j): out[row, j] = silu(gate) * up, 16 outputs per 32 columns.
+    if (row < p.m && col0 + 32 <= p.n) {
+      uint32_t w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float o[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float gate = __uint_as_float(r[4 * j + 2 * h]), up = __uint_as_float(r[4 * j + 2 * h + 1]);
+          o[h] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
+        }
+        w[j] = narrow_bits(o[0], p.out_format) | (narrow_bits(o[1], p.out_format) << 16);
+      }
+      uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + static_cast<size_t>(row) * (p.n / 2) + col0 / 2;
+      *reinterpret_cast<uint4 *>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4 *>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    return;
+  }
+  if (p.epilogue != WB200_EPI_NONE) {
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+      float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (col0 + i + 4 <= p.n) b = __ldg(reinterpret_cast<const float4 *>(p.bias + col0 + i));
+      float v0 = __uint_as_float(r[i]) + b.x, v1 = __uint_as_float(r[i + 1]) + b.y;
+      float v2 = __uint_as_float(r[i + 2]) + b.z, v3 = __uint_as_float(r[i + 3]) + b.w;
+      if (p.epilogue == WB200_EPI_BIAS_GELU) {
+        v0 = gelu_erf(v0); v1 = gelu_erf(v1); v2 = gelu_erf(v2); v3 = gelu_erf(v3);
+      }
+      r[i] = __float_as_uint(v0); r[i + 1] = __float_as_uint(v1);
+      r[i + 2] = __float_as_uint(v2); r[i + 3] = __float_as_uint(v3);
+    }
+  }
+  if (row < p.m) {
+    if (p.out_format == WB200_F32) {
+      float *dst = reinterpret_cast<float *>(p.out) + static_cast<size_t>(row) * p.n + col0;
+#pragma unroll
+      for (int i = 0; i < 32; i += 4)
+        if (col0 + i + 4 <= p.n)
+          *reinterpret_cast<uint4 *>(dst + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+    } else {
+      uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + static_cast<size_t>(row) * p.n + col0;
+#pragma unroll
+      for (int i = 0; i < 32; i += 8) {
+        if (col0 + i + 8 <= p.n) {
+          uint32_t w[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t lo = narrow_bits(__uint_as_float(r[i + 2 * j]), p.out_format);
+            const uint32_t hi = narrow_bits(__uint_as_float(r[i + 2 * j + 1]), p.out_format);
+            w[j] = lo | (hi << 16);
+          }
+          *reinterpret_cast<uint4 *>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      }
+    }
+  }
+}
+
 template <bool kAMn, bool kBMn, bool kBf16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -185,65 +248,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_wait_ld();
-        const int col0 = n0 + c * 32;
-        if (p.epilogue == WB200_EPI_SWIGLU) {
-          // Columns (2j, 2j+1) hold (gate_j, up_j): out[row, j] = silu(gate) * up, 16 outputs per 32 columns.
-          if (row < p.m && col0 + 32 <= p.n) {
-            uint32_t w[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float o[2];
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const float gate = __uint_as_float(r[4 * j + 2 * h]), up = __uint_as_float(r[4 * j + 2 * h + 1]);
-                o[h] = __fdividef(gate, 1.0f + __expf(-gate)) * up;
-              }
-              w[j] = narrow_bits(o[0], p.out_format) | (narrow_bits(o[1], p.out_format) << 16);
-            }
-            uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + static_cast<size_t>(row) * (p.n / 2) + col0 / 2;
-            *reinterpret_cast<uint4 *>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
-            *reinterpret_cast<uint4 *>(dst + 8) = make_uint4(w[4], w[5], w[6], w[7]);
-          }
-          continue;
-        }
-        if (p.epilogue != WB200_EPI_NONE) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (col0 + i + 4 <= p.n) b = __ldg(reinterpret_cast<const float4 *>(p.bias + col0 + i));
-            float v0 = __uint_as_float(r[i]) + b.x, v1 = __uint_as_float(r[i + 1]) + b.y;
-            float v2 = __uint_as_float(r[i + 2]) + b.z, v3 = __uint_as_float(r[i + 3]) + b.w;
-            if (p.epilogue == WB200_EPI_BIAS_GELU) {
-              v0 = gelu_erf(v0); v1 = gelu_erf(v1); v2 = gelu_erf(v2); v3 = gelu_erf(v3);
-            }
-            r[i] = __float_as_uint(v0); r[i + 1] = __float_as_uint(v1);
-            r[i + 2] = __float_as_uint(v2); r[i + 3] = __float_as_uint(v3);
-          }
-        }
-        if (row < p.m) {
-          if (p.out_format == WB200_F32) {
-            float *dst = reinterpret_cast<float *>(p.out) + static_cast<size_t>(row) * p.n + col0;
-#pragma unroll
-            for (int i = 0; i < 32; i += 4)
-              if (col0 + i + 4 <= p.n)
-                *reinterpret_cast<uint4 *>(dst + i) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
-          } else {
-            uint16_t *dst = reinterpret_cast<uint16_t *>(p.out) + static_cast<size_t>(row) * p.n + col0;
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              if (col0 + i + 8 <= p.n) {
-                uint32_t w[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const uint32_t lo = narrow_bits(__uint_as_float(r[i + 2 * j]), p.out_format);
-                  const uint32_t hi = narrow_bits(__uint_as_float(r[i + 2 * j + 1]), p.out_format);
-                  w[j] = lo | (hi << 16);
-                }
-                *reinterpret_cast<uint4 *>(dst + i) = make_uint4(w[0], w[1], w[2], w[3]);
-              }
-            }
-          }
-        }
+        epilogue_chunk(p, r, row, n0 + c * 32);
       }
       tc_fence_before();
       mbar_arrive(tmem_empty_bar(acc));
@@ -262,6 +267,189 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+
+// ---------------------------------------------------------------- CTA-pair kernel: 256 x 256 x 64 tiles
+// Two CTAs of a cluster share one output tile: CTA r of the pair owns rows [128 r, 128 r + 128) of it (A rows,
+// accumulator lanes, epilogue) and loads half of the tile's B columns; the even CTA issues cta_group::2 instructions of
+// M = 256, N = 256 that read both halves. Against the single-CTA tile that halves the B bytes each SM pulls from L2 and
+// shared memory per flop, and the 32 KiB stage leaves room for six stages instead of four. Loads carry no multicast
+// qualifier: every CTA fetches its own bytes.
+constexpr int kPairStages = 6;
+constexpr int kPairBHalf = (kBN / 2) * kBK * 2;            // 16 KiB: this CTA's 128 B columns of a k-block
+constexpr int kPairStageBytes = kABytes + kPairBHalf;      // 32 KiB
+constexpr size_t kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256;
+
+template <bool kAMn, bool kBMn, bool kBf16>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const GemmUmmaParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t *smem = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  const uint32_t smem_base = smem_u32(smem);
+
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kPairStages * kPairStageBytes);
+  const uint32_t bar_base = smem_base + kPairStages * kPairStageBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };                              // used in the issuing CTA only
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kPairStages + s); };             // one per CTA
+  auto tmem_full_bar = [&](int a) { return bar_base + 8u * (2 * kPairStages + a); };     // one per CTA
+  auto tmem_empty_bar = [&](int a) { return bar_base + 8u * (2 * kPairStages + 2 + a); };// issuing CTA: 256 arrivals
+  volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(bars + 2 * kPairStages + 4);
+  volatile int *abort_word = reinterpret_cast<volatile int *>(bars + 2 * kPairStages + 5);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_cta_rank();
+  const bool issuer = cta_rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tmem_full_bar(a), 1);
+      mbar_init(tmem_empty_bar(a), 256);
+    }
+    *abort_word = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(const_cast<uint32_t *>(tmem_slot)), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();     // both CTAs' barriers exist before either touches the partner's
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_pair_m = (p.m + 2 * kBM - 1) / (2 * kBM);
+  const int num_tiles = num_pair_m * p.num_n_tiles;
+  const int k_blocks = (p.k + kBK - 1) / kBK;
+  const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+        int m_blk, n_blk;
+        tile_coords(tile, num_pair_m, p.num_n_tiles, m_blk, n_blk);
+        const int m0 = m_blk * 2 * kBM + static_cast<int>(cta_rank) * kBM;         // this CTA's 128 rows
+        const int n0 = n_blk * kBN + static_cast<int>(cta_rank) * (kBN / 2);       // this CTA's 128 B columns
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word)) { ok = false; break; }
+          // Both CTAs' bytes are counted on the issuing CTA's barrier, which expects the two stages together.
+          const uint32_t full = cluster_map_shared(full_bar(stage), 0);
+          if (issuer) mbar_arrive_expect_tx(full_bar(stage), 2 * kPairStageBytes);
+          const uint32_t a_dst = smem_base + stage * kPairStageBytes;
+          const uint32_t b_dst = a_dst + kABytes;
+          const int k0 = kb * kBK;
+          if constexpr (!kAMn) {
+            tma_load_2d_pair(a_dst, &tmap_a, full, k0, m0);                   // box {64 k, 128 m}
+          } else {
+            tma_load_2d_pair(a_dst, &tmap_a, full, m0, k0);                   // box {64 m, 64 k}
+            tma_load_2d_pair(a_dst + 8192, &tmap_a, full, m0 + 64, k0);
+          }
+          if constexpr (kBMn) {
+            tma_load_2d_pair(b_dst, &tmap_b, full, n0, k0);                   // box {64 n, 64 k}
+            tma_load_2d_pair(b_dst + 8192, &tmap_b, full, n0 + 64, k0);
+          } else {
+            tma_load_2d_pair(b_dst, &tmap_b, full, k0, n0);                   // box {64 k, 128 n}
+          }
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (issuer) {
+      // The whole warp walks the loop and one elected lane issues (warp-uniform control flow keeps the descriptor
+      // arithmetic on the uniform datapath).
+      constexpr uint32_t idesc = umma_idesc_f16(2 * kBM, kBN, kBf16, kAMn, kBMn);
+      const uint32_t peer_bar_base = cluster_map_shared(bar_base, 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+        if (!mbar_wait(tmem_empty_bar(acc), acc_phase ^ 1u, abort_word)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kBN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_word)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_src = smem_base + stage * kPairStageBytes;
+          const uint32_t b_src = a_src + kABytes;
+          const uint64_t adesc = kAMn ? umma_desc_mnmajor(a_src, 8192) : umma_desc_kmajor(a_src);
+          const uint64_t bdesc = kBMn ? umma_desc_mnmajor(b_src, 8192) : umma_desc_kmajor(b_src);
+          if (elect_one_sync()) {
+#pragma unroll
+            for (int ks = 0; ks < kBK / 16; ++ks) {
+              constexpr uint64_t a_step = (kAMn ? 2048 : 32) >> 4, b_step = (kBMn ? 2048 : 32) >> 4;
+              umma_f16_ss_pair(d_tmem, adesc + ks * a_step, bdesc + ks * b_step, idesc, (kb | ks) != 0 ? 1u : 0u);
+            }
+            // the stage is free in both CTAs once these instructions have read it
+            umma_commit_pair(empty_bar(stage));
+            umma_commit_pair(peer_bar_base + 8u * (kPairStages + stage));
+          }
+          __syncwarp();
+          if (++stage == kPairStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        if (elect_one_sync()) {
+          umma_commit_pair(tmem_full_bar(acc));
+          umma_commit_pair(peer_bar_base + 8u * (2 * kPairStages + acc));
+        }
+        __syncwarp();
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    const uint32_t issuer_bar_base = cluster_map_shared(bar_base, 0);
+    for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
+      int m_blk, n_blk;
+      tile_coords(tile, num_pair_m, p.num_n_tiles, m_blk, n_blk);
+      const int row = m_blk * 2 * kBM + static_cast<int>(cta_rank) * kBM + quarter * 32 + lane;
+      const int n0 = n_blk * kBN;
+      if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_word)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBN;
+#pragma unroll 1
+      for (int c = 0; c < kBN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_wait_ld();
+        epilogue_chunk(p, r, row, n0 + c * 32);
+      }
+      tc_fence_before();
+      mbar_arrive_cluster(issuer_bar_base + 8u * (2 * kPairStages + 2 + acc));   // both CTAs' epilogues free the accumulator
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_word != 0) {
+    for (int i = 0; i < 64; ++i) __nanosleep(10000);
+    if (threadIdx.x == 0) atomicExch(p.status, *abort_word);
+  }
+  cluster_sync_all();     // neither CTA leaves while the partner may still read its shared memory or signal its barriers
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
@@ -286,6 +474,11 @@ bool gemm_umma_supports(const GemmUmmaArgs &a) {
 wb200_status launch_gemm_umma(const GemmUmmaArgs &a, int sm_count, int *device_status,
                               cudaStream_t stream) {
   if (!gemm_umma_supports(a)) return fail(WB200_ERR_UNSUPPORTED, "GEMM outside the tcgen05 kernel's domain");
+  // CTA pairs when the problem has at least one full 256 x 256 tile per pair of SMs to amortise the pairing; the
+  // single-CTA kernel otherwise (small or narrow problems, WB200_GEMM_PAIR=0).
+  static const bool pair_enabled = []() { const char *env = getenv("WB200_GEMM_PAIR"); return !(env && env[0] == '0'); }();
+  const int pair_tiles = ((a.m + 2 * kBM - 1) / (2 * kBM)) * ((a.n + kBN - 1) / kBN);
+  const bool use_pairs = pair_enabled && a.m >= 2 * kBM && a.n >= kBN && pair_tiles * 4 >= sm_count;
   CUtensorMap tmap_a, tmap_b;
   wb200_status st;
   if (!a.lhs_transposed)  // A[m,k], k contiguous: K-major
@@ -296,7 +489,7 @@ wb200_status launch_gemm_umma(const GemmUmmaArgs &a, int sm_count, int *device_s
   if (!a.rhs_transposed)  // B[k,n], n contiguous: MN-major
     st = encode_tmap_2d(&tmap_b, a.b, a.in_format, a.n, a.k, static_cast<uint64_t>(a.n) * 2, 64, 64);
   else                    // B[n,k], k contiguous: K-major
-    st = encode_tmap_2d(&tmap_b, a.b, a.in_format, a.k, a.n, static_cast<uint64_t>(a.k) * 2, 64, kBN);
+    st = encode_tmap_2d(&tmap_b, a.b, a.in_format, a.k, a.n, static_cast<uint64_t>(a.k) * 2, 64, use_pairs ? kBN / 2 : kBN);
   if (st != WB200_OK) return st;
 
   GemmUmmaParams p;
@@ -317,17 +510,30 @@ wb200_status launch_gemm_umma(const GemmUmmaArgs &a, int sm_count, int *device_s
       gemm_umma_kernel<false, false, false>, gemm_umma_kernel<false, false, true>, gemm_umma_kernel<false, true, false>,
       gemm_umma_kernel<false, true, true>,   gemm_umma_kernel<true, false, false>, gemm_umma_kernel<true, false, true>,
       gemm_umma_kernel<true, true, false>,   gemm_umma_kernel<true, true, true>};
+  static const Kernel pair_kernels[8] = {
+      gemm_umma_pair_kernel<false, false, false>, gemm_umma_pair_kernel<false, false, true>, gemm_umma_pair_kernel<false, true, false>,
+      gemm_umma_pair_kernel<false, true, true>,   gemm_umma_pair_kernel<true, false, false>, gemm_umma_pair_kernel<true, false, true>,
+      gemm_umma_pair_kernel<true, true, false>,   gemm_umma_pair_kernel<true, true, true>};
   static PerDeviceOnce attributes;
   st = attributes.run([]() -> wb200_status {
     for (Kernel kernel : kernels)
       WB200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes)));
+    for (Kernel kernel : pair_kernels)
+      WB200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPairSmemBytes)));
     return WB200_OK;
   });
   if (st != WB200_OK) return st;
+  const int variant = (p.a_mn_major ? 4 : 0) | (p.b_mn_major ? 2 : 0) | (p.bf16 ? 1 : 0);
+  if (use_pairs) {
+    int clusters = sm_count / 2;
+    if (pair_tiles < clusters) clusters = pair_tiles;
+    pair_kernels[variant]<<<2 * clusters, kThreads, kPairSmemBytes, stream>>>(tmap_a, tmap_b, p);
+    WB200_CUDA_CHECK(cudaGetLastError());
+    return WB200_OK;
+  }
   const int tiles = p.num_m_tiles * p.num_n_tiles;
   const int grid = tiles < sm_count ? tiles : sm_count;
-  const Kernel kernel = kernels[(p.a_mn_major ? 4 : 0) | (p.b_mn_major ? 2 : 0) | (p.bf16 ? 1 : 0)];
-  kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, p);
+  kernels[variant]<<<grid, kThreads, kSmemBytes, stream>>>(tmap_a, tmap_b, p);
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }
