@@ -358,8 +358,8 @@ struct FdExchangeParams {
   unsigned int *epoch;               // this rank's {epoch, finished CTAs}, zero-initialised
   int *status;
 };
-__device__ __forceinline__ void st_release_sys(unsigned int *address, unsigned int value) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(address), "r"(value) : "memory");
+__device__ __forceinline__ void st_relaxed_sys(unsigned int *address, unsigned int value) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(address), "r"(value) : "memory");
 }
 __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *address) {
   unsigned int value;
@@ -395,10 +395,12 @@ __global__ void __launch_bounds__(kD) fd_exchange_kernel(const FdExchangeParams 
     }
   }
   __syncthreads();   // the whole row is written before it is published
-  if (d == 0) {
+  // One thread per peer: a system-scope fence (cumulative over the row's stores, which the barrier ordered before it)
+  // and then the flag. The fences of the peers run side by side; a single thread publishing to every peer in turn would
+  // pay one NVLink round trip per peer.
+  if (d < p.world) {
     __threadfence_system();
-    for (int r = 0; r < p.world; ++r)
-      st_release_sys(reinterpret_cast<unsigned int *>(p.peer[r] + state_floats) + my_slot, tag);
+    st_relaxed_sys(reinterpret_cast<unsigned int *>(p.peer[d] + state_floats) + my_slot, tag);
   }
   // bounded wait for every rank's row
   float *own = p.peer[p.rank];
