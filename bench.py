@@ -191,6 +191,67 @@ def cpu_sample(threads: int, units: int = CPU_SAMPLE_UNITS):
                                                f"{threads} threads")
 
 
+def cpu_baselines(threads: int):
+    """CPU numbers beside the other configurations, each on a stated fraction of the workload (rank 0, N = 1 only).
+    Decode: the oracle (the reference's online update restated, `kind: port`) on 2 of the 64 sequences, all threads.
+    GEMM: the reference's oneDNN profile (OneDNNGemmAdapter.cpp:94-126, 351-357): operands widened to f32 once, a
+    sequential f32 matmul on ONE thread (torch's bundled oneDNN stands in for the pinned build), 512 of the 8192 rows.
+    Decoder layer: eager f32 torch on all threads, one sequence of 256 tokens, scaled by flop."""
+    import numpy as np
+    import torch
+    from oracle import binding
+    binding.build()
+    rng = np.random.default_rng(SEED)
+
+    def bf16(shape):
+        x = rng.standard_normal(shape, dtype=np.float32)
+        return binding.convert("f32", "bf16", x.view(np.uint32).reshape(-1))[1].reshape(shape)
+    out = {}
+    sequences = 2
+    q = bf16((sequences, FD["q_heads"], 1, FD["head_dim"]))
+    k = bf16((sequences, FD["kv_heads"], FD["kv_len"], FD["head_dim"]))
+    v = bf16((sequences, FD["kv_heads"], FD["kv_len"], FD["head_dim"]))
+    t0 = time.perf_counter()
+    binding.attention("bf16", q, k, v, FD["head_dim"] ** -0.5, splits=16, tile_n=16, threads=threads)
+    seconds = time.perf_counter() - t0
+    out["fd_decode"] = {"value": 2 * k.size * 2 / seconds / 1e9, "unit": "GB/s", "cores": threads, "kind": "port", "seconds": seconds,
+                        "sample": f"{sequences} of {FD['batch']} sequences (KV {FD['kv_len']}, 32 / 8 heads), {threads} threads"}
+    previous = torch.get_num_threads()
+    torch.set_num_threads(1)
+    rows = 512
+    a = (torch.rand(rows, GEMM["k"]) * 2 - 1).bfloat16().float()      # widened once, as the adapter does
+    b = (torch.rand(GEMM["k"], GEMM["n"]) * 2 - 1).bfloat16().float()
+    bias = torch.randn(GEMM["n"]) * 0.02
+    t0 = time.perf_counter()
+    torch.nn.functional.gelu(a @ b + bias).bfloat16()
+    seconds = time.perf_counter() - t0
+    out["gemm_bias_gelu"] = {"value": 2 * rows * GEMM["n"] * GEMM["k"] / seconds / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "port", "seconds": seconds,
+                             "sample": f"{rows} of {GEMM['m']} rows, operands widened to f32, sequential f32 matmul on one thread (the reference's oneDNN profile)"}
+    torch.set_num_threads(previous)
+    from vibe_compiler_b200.decoder_layer import LayerConfig, layer_flops
+    cfg = LayerConfig()
+    tokens = 256
+    g = torch.Generator().manual_seed(SEED)
+    w = lambda *shape: torch.randn(*shape, generator=g) * 0.02   # noqa: E731
+    wq, wk, wv, wo = w(cfg.d_model, cfg.q_heads * cfg.head_dim), w(cfg.d_model, cfg.kv_heads * cfg.head_dim), w(cfg.d_model, cfg.kv_heads * cfg.head_dim), w(cfg.q_heads * cfg.head_dim, cfg.d_model)
+    wg, wu, wd = w(cfg.d_model, cfg.ffn), w(cfg.d_model, cfg.ffn), w(cfg.ffn, cfg.d_model)
+    x = torch.randn(tokens, cfg.d_model, generator=g)
+    t0 = time.perf_counter()
+    rms = lambda t: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + cfg.eps)   # noqa: E731
+    h = rms(x)
+    qh = (h @ wq).view(tokens, cfg.q_heads, cfg.head_dim).transpose(0, 1)
+    kh = (h @ wk).view(tokens, cfg.kv_heads, cfg.head_dim).transpose(0, 1).repeat_interleave(cfg.q_heads // cfg.kv_heads, 0)
+    vh = (h @ wv).view(tokens, cfg.kv_heads, cfg.head_dim).transpose(0, 1).repeat_interleave(cfg.q_heads // cfg.kv_heads, 0)
+    attn = torch.nn.functional.scaled_dot_product_attention(qh[None], kh[None], vh[None], is_causal=True)[0].transpose(0, 1).reshape(tokens, -1)
+    x1 = x + attn @ wo
+    h2 = rms(x1)
+    (x1 + (torch.nn.functional.silu(h2 @ wg) * (h2 @ wu)) @ wd).sum().item()
+    seconds = time.perf_counter() - t0
+    out["decoder_layer"] = {"value": layer_flops(cfg, 1, tokens) / seconds / 1e12, "unit": "TFLOP/s", "cores": previous, "kind": "port", "seconds": seconds,
+                            "sample": f"one sequence of {tokens} tokens of the 8 x 2048 (rotary omitted), eager f32 torch on {previous} threads"}
+    return out
+
+
 def layer_extra(backend, args, torch, dist, rank, world, device, peak, failures):
     """Llama-style decoder layer forward (batch 8 x seq 2048), tensor-parallel over the ranks: heads and FFN columns are
     sharded, the two partial sums are NCCL all-reduces. Strong scaling: total work is fixed as the world grows."""
@@ -538,6 +599,23 @@ def main():
                                     "roofline": {"bound": "tensor", "achieved": g_tflops, "peak": peak["bf16_tflops"], "unit": "TFLOP/s",
                                                  "frac": g_tflops / peak["bf16_tflops"], "traffic": None, "peak_source": peak["source"]}}
 
+    if not args.skip_extras and world == 1:
+        # ------------------------------------------------------------ cfg 1: the reference's own CPU-runnable attention case
+        # (f32, batch 1, 8 heads, seq 512, head_dim 64, non-causal): latency bound, half a GFLOP; reported with its parity error.
+        c1 = torch.Generator(device=device).manual_seed(SEED + 1)
+        q1, k1, v1 = (torch.randn(1, 8, 512, 64, device=device, generator=c1) for _ in range(3))
+        o1 = torch.empty_like(q1)
+        flush1 = torch.empty(192 * 1024 * 1024, dtype=torch.uint8, device=device)
+        _, c1_ms = timed_steps(lambda: backend.attention_fa(q1, k1, v1, 0.125, False, out=o1), args.steps, args.warmup, torch, check=backend.poll, flush=flush1)
+        backend.poll()
+        ref1 = torch.nn.functional.scaled_dot_product_attention(q1.double(), k1.double(), v1.double())
+        c1_flops = 4 * 8 * 512 * 512 * 64
+        extras["fa_f32_cfg1"] = {"workload": "attention f32 B1 H8 S512 D64 non-causal (the reference's CPU-runnable case); L2 flushed between launches",
+                                 "value": c1_flops / (c1_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": c1_ms,
+                                 "max_rel_err_vs_f64": float((o1.double() - ref1).abs().max() / ref1.abs().max()),
+                                 "roofline": {"bound": "latency", "achieved": c1_flops / (c1_ms * 1e-3) / 1e12, "peak": None, "unit": "TFLOP/s", "frac": None,
+                                              "traffic": None, "note": "0.5 GFLOP on 1024 warps: launch and dependency latency, not a pipe, bound it"}}
+        del flush1
     if not args.skip_extras:
         ga = gb = gout = fk = fv = None
         torch.cuda.empty_cache()
@@ -569,6 +647,10 @@ def main():
                                     "sample": cpu_desc, "seconds": cpu_seconds,
                                     "single_thread": {"value": one_flops / one_seconds / 1e12, "unit": "TFLOP/s", "cores": 1, "sample": one_desc,
                                                       "seconds": one_seconds}}
+        if cpu_seconds is not None and not args.skip_extras:
+            for name, baseline in cpu_baselines(cpu_threads).items():
+                if name in extras:
+                    extras[name]["cpu_baseline"] = baseline
         line.update(extras)
         if failures:
             line["failures"] = failures

@@ -306,7 +306,11 @@ wb200_status wb200_attention_fa(wb200_backend *backend, const wb200_attention_pa
 /* Flash-decoding: KV axis split into `kv_splits` >= 2 contiguous intervals (0 = choose), each
  * producing a partial (m, l, acc); partials are left-folded in ascending interval order and then
  * finalized. replaces OnlineAttentionMaterialization.cpp:264-373 and the fold order of
- * lib/Wafer/Transforms/Linalg/SpatialRegionMaterialization.cpp:2420-2433. q_len must be 1. */
+ * lib/Wafer/Transforms/Linalg/SpatialRegionMaterialization.cpp:2420-2433. q_len must be 1.
+ * The split-KV partial records of this entry and of wb200_attention_fd_partial / _exchange live in a grow-only scratch
+ * buffer of the backend: a call that needs more than every call before it frees and reallocates that buffer (after the
+ * work enqueued on it earlier, in stream order of the legacy default stream), so a CUDA graph that captured an earlier
+ * decode call replays with a dangling address. Capture only after the largest shape has run once. */
 wb200_status wb200_attention_fd(wb200_backend *backend, const wb200_attention_params *params,
                                 uint32_t kv_splits);
 

@@ -115,6 +115,9 @@ wb200_status run_fa_host_pipelined(wb200_backend *backend, const wb200_attention
   WB200_CUDA_CHECK(cudaStreamWaitEvent(copy_out, backend->aux_event[0], 0));
   auto at = [](const void *base, size_t offset) { return static_cast<const uint8_t *>(base) + offset; };
   auto at_mut = [](void *base, size_t offset) { return static_cast<uint8_t *>(base) + offset; };
+  // The pipeline proper; any failure inside leaves copies in flight that write the caller's buffers, so whatever it
+  // returns, the three streams are drained before this call does.
+  auto enqueue = [&]() -> wb200_status {
   uint32_t first = 0;
   for (uint32_t c = 0; c < chunks; ++c) {
     const uint32_t count = units / chunks + (c < units % chunks ? 1 : 0);
@@ -139,8 +142,15 @@ wb200_status run_fa_host_pipelined(wb200_backend *backend, const wb200_attention
     if (p->row_sum) WB200_CUDA_CHECK(cudaMemcpyAsync(at_mut(p->row_sum, stat_at), at(ds, stat_at), count * stat_unit, cudaMemcpyDeviceToHost, copy_out));
     first += count;
   }
-  WB200_CUDA_CHECK(cudaStreamSynchronize(copy_in));
-  WB200_CUDA_CHECK(cudaStreamSynchronize(copy_out));
+  return WB200_OK;
+  };
+  st = enqueue();
+  const cudaError_t drained_in = cudaStreamSynchronize(copy_in), drained_out = cudaStreamSynchronize(copy_out);
+  const cudaError_t drained_compute = st != WB200_OK ? cudaStreamSynchronize(compute) : cudaSuccess;
+  if (st != WB200_OK) return st;
+  WB200_CUDA_CHECK(drained_in);
+  WB200_CUDA_CHECK(drained_out);
+  WB200_CUDA_CHECK(drained_compute);
   return read_device_status(backend, compute, nullptr);
 }
 

@@ -885,6 +885,8 @@ enum class StepResult { Progress, Blocked, Done, Failed };
 
 // Matches endpoint `index` against the live endpoints of the opposite kind; on a match the payload is copied from
 // the sender's scratch-pad to the receiver's and both sides complete.
+wb200_status flush_chain(wb200_tile_program *program, int tile_index);
+
 wb200_status try_match(wb200_tile_program *program, size_t index) {
   Endpoint &endpoint = program->endpoints[index];
   for (size_t other_index = 0; other_index < program->endpoints.size(); ++other_index) {
@@ -906,6 +908,10 @@ wb200_status try_match(wb200_tile_program *program, size_t index) {
     if (send.source + send.bytes > program->spm_bytes || receive.destination + receive.bytes > program->spm_bytes)
       return program_error(program, send.owner, "Direct-DTE transfer lies outside the scratch-pad");
     if (program->execute) {
+      // Elementwise commands either Tile issued before this point may still be held back for fusion: they precede the
+      // transfer in the command order (and may produce the payload or touch its destination), so they are launched first.
+      wb200_status flushed;
+      if ((flushed = flush_chain(program, send.owner)) != WB200_OK || (flushed = flush_chain(program, receive.owner)) != WB200_OK) return flushed;
       cudaStream_t sender = from->work_stream(), receiver = to->work_stream();
       if (sender != receiver) {
         // The payload is read after everything the sender has issued so far and lands after everything the receiver

@@ -62,7 +62,9 @@ def sharded_decode(state_fn: Callable[[int, int], torch.Tensor], merge_fn: Calla
 class GraphedDecodeStep:
     """One sequence-sharded decode step (local state, all-gather, merge) captured once into a CUDA graph and replayed:
     a decode step is four small launches plus one collective, so at small per-rank KV lengths the launch path, not the
-    HBM stream, sets its time. The callables must use preallocated tensors only (captured addresses are replayed).
+    HBM stream, sets its time. The callables must use preallocated tensors only (captured addresses are replayed); the
+    library's own split-KV scratch is grow-only, so a later decode call with a larger batch x heads x splits reallocates it
+    and invalidates this graph: build the step after the largest shape has run once.
     With more than one rank the graph holds an NCCL all-gather: release the step object (and synchronise) before the
     process group is destroyed - a process that tore the group down while the graph was alive did not exit.
 
