@@ -10,7 +10,7 @@ and tests/test_formal_elementwise.py). Pure Python on purpose: small cases only.
 """
 from fractions import Fraction
 
-FORMATS = {"f16": (5, 10), "bf16": (8, 7), "f32": (8, 23)}   # exponent bits, stored mantissa bits
+FORMATS = {"f16": (5, 10), "bf16": (8, 7), "f32": (8, 23), "tf32": (8, 10)}   # exponent bits, stored mantissa bits (tf32: the 19-bit encoding, storage bits 31..13)
 INVALID, DIV_BY_ZERO, OVERFLOW, UNDERFLOW, INEXACT = 1, 2, 4, 8, 16
 RELATIONS = {"eq", "ne", "ge", "gt", "le", "lt"}
 LOGIC = {"logic_not", "logic_and", "logic_or", "logic_xor"}

@@ -8,8 +8,8 @@ from oracle import formal_scalar as F
 from vibe_compiler_b200 import _abi as abi
 from vibe_compiler_b200.backend import NumericTensor, PhysicalTensorDescriptor
 
-FMT = {"f16": abi.F16, "bf16": abi.BF16, "f32": abi.F32}
-DTYPE = {"f16": np.uint16, "bf16": np.uint16, "f32": np.uint32}
+FMT = {"f16": abi.F16, "bf16": abi.BF16, "f32": abi.F32, "tf32": abi.TF32}
+DTYPE = {"f16": np.uint16, "bf16": np.uint16, "f32": np.uint32, "tf32": np.uint32}
 ARITHMETIC = ["abs", "neg", "recip", "square", "max", "min", "add", "sub", "mul", "relu"]
 RELATIONS = ["eq", "ne", "ge", "gt", "le", "lt"]
 BOOL = 7
@@ -203,8 +203,8 @@ def test_formal_entry_rejects_what_it_does_not_cover(backend):
     a = np.zeros(8, dtype=np.uint16)
     with pytest.raises(WB200Error, match="outside the formal"):
         _run(backend, "exp_lp", "f16", "f16", a)
-    with pytest.raises(WB200Error, match="F16 and BF16"):
-        _run(backend, "exp", "f32", "f32", np.zeros(8, dtype=np.uint32))
+    with pytest.raises(WB200Error, match="TF32 for the function family"):
+        _run(backend, "add", "tf32", "tf32", np.zeros(8, dtype=np.uint32), np.zeros(8, dtype=np.uint32))
     with pytest.raises(WB200Error, match="arity"):
         _run(backend, "add", "f16", "f16", a)
     with pytest.raises(WB200Error, match="result format"):
@@ -261,3 +261,79 @@ def test_function_family_flags_per_element(backend):
         for bits, (result, flags) in list(entry["samples"].items())[::3]:
             storage, evidence = _run(backend, op, fmt, fmt, np.array([int(bits)], dtype=np.uint16))
             assert (int(storage.view(np.uint16)[0]), evidence.flags) == (result, flags), (key, hex(int(bits)))
+
+
+# ------------------------------------------------------------------------------------------------ binary32 / TF32 operands
+def _f32_expected():
+    from pathlib import Path
+    return np.load(Path(__file__).resolve().parent / "golden" / "formal_function_f32_expected.npz")
+
+
+def _f32_generator():
+    import importlib.util
+    from pathlib import Path
+    spec = importlib.util.spec_from_file_location("make_f32", Path(__file__).resolve().parent / "golden" / "make_formal_function_f32_expected.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+
+
+def test_f32_function_oracle_and_host_evaluator_agree_with_the_vectors():
+    """CPU: the 200-bit oracle reproduces a sample of the committed vectors, and the library's evaluator compiled for the host
+    reproduces all of them (listed hard cases and specials element by element, 2^20 random operands and the complete TF32
+    space by hash)."""
+    import hashlib
+    data, gen = _f32_expected(), _f32_generator()
+    assert F.evaluate_function("exp", "f32", 0x00000000) == (0x3f800000, 0)
+    assert F.evaluate_function("log2", "f32", 0x41000000) == (0x40400000, 0)                   # log2(8) = 3
+    assert F.evaluate_function("sqrt", "f32", 0x40800000) == (0x40000000, 0)
+    assert F.evaluate_function("exp", "f32", 0x42b20000) == (0x7f800000, F.OVERFLOW | F.INEXACT)   # e^89
+    assert F.evaluate_function("pow2", "f32", 0xc3160000) == (0x00000000, F.UNDERFLOW | F.INEXACT) # 2^-150: ties to zero
+    assert F.evaluate_function("pow2", "tf32", 0x3f800000 >> 13) == (0x40000000 >> 13, 0)
+    tool = gen.build_tool()
+    for function, op in enumerate(F.FUNCTIONS):
+        listed, want, flags = data[f"f32_{op}_operands"], data[f"f32_{op}_results"], data[f"f32_{op}_flags"]
+        for i in range(0, len(listed), 97):
+            assert F.evaluate_function(op, "f32", int(listed[i])) == (int(want[i]), int(flags[i])), (op, hex(int(listed[i])))
+        got, got_flags = gen.host_eval(tool, function, False, listed)
+        assert np.array_equal(got, want) and np.array_equal(got_flags.astype(np.uint8), flags), op
+        got, got_flags = gen.host_eval(tool, function, False, gen.random_operands(function))
+        assert hashlib.sha256(got.astype("<u4").tobytes()).hexdigest() == str(data[f"f32_{op}_random_sha256"]), op
+        assert int(np.bitwise_or.reduce(got_flags)) == int(data[f"f32_{op}_random_flags_or"]), op
+        got, got_flags = gen.host_eval(tool, function, True, np.arange(1 << 19, dtype=np.uint32) << 13)
+        assert hashlib.sha256(got.astype("<u4").tobytes()).hexdigest() == str(data[f"tf32_{op}_sha256"]), op
+        assert int(np.bitwise_or.reduce(got_flags)) == int(data[f"tf32_{op}_flags_or"]), op
+
+
+@pytest.mark.gpu
+def test_function_family_f32_hard_cases_specials_and_random_operands(backend):
+    """binary32 operands: every operand of the complete space that needs more than binary64 to round (found by a host scan
+    with the same evaluator), the special operands, and 2^20 seeded random operands, against the 200-bit evaluation."""
+    import hashlib
+    data, gen = _f32_expected(), _f32_generator()
+    for function, op in enumerate(F.FUNCTIONS):
+        listed, want, flags = data[f"f32_{op}_operands"], data[f"f32_{op}_results"], data[f"f32_{op}_flags"]
+        for value in np.unique(flags):                      # operands with equal expected flags share a call: OR of the call == that value
+            pick = flags == value
+            storage, evidence = _run(backend, op, "f32", "f32", listed[pick])
+            got = storage.view(np.uint32)
+            wrong = np.nonzero(got != want[pick])[0]
+            assert len(wrong) == 0, (op, [(hex(int(listed[pick][i])), hex(int(got[i])), hex(int(want[pick][i]))) for i in wrong[:6]])
+            assert evidence.flags == int(value), (op, evidence.flags, int(value))
+        for i in range(0, len(listed), 61):                 # and a sample one by one, so a missing flag cannot hide in an OR
+            storage, evidence = _run(backend, op, "f32", "f32", listed[i:i + 1])
+            assert (int(storage.view(np.uint32)[0]), evidence.flags) == (int(want[i]), int(flags[i])), (op, hex(int(listed[i])))
+        storage, evidence = _run(backend, op, "f32", "f32", gen.random_operands(function))
+        assert hashlib.sha256(storage.view(np.uint32).astype("<u4").tobytes()).hexdigest() == str(data[f"f32_{op}_random_sha256"]), op
+        assert evidence.flags == int(data[f"f32_{op}_random_flags_or"]), op
+
+
+@pytest.mark.gpu
+def test_function_family_tf32_over_the_complete_operand_space(backend):
+    import hashlib
+    data = _f32_expected()
+    everything = np.arange(1 << 19, dtype=np.uint32) << 13
+    for op in F.FUNCTIONS:
+        storage, evidence = _run(backend, op, "tf32", "tf32", everything)
+        assert hashlib.sha256(storage.view(np.uint32).astype("<u4").tobytes()).hexdigest() == str(data[f"tf32_{op}_sha256"]), op
+        assert evidence.flags == int(data[f"tf32_{op}_flags_or"]), op

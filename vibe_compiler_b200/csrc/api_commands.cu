@@ -207,7 +207,7 @@ wb200_status wb200_elementwise(wb200_backend *backend, const wb200_elementwise_r
 wb200_status wb200_elementwise_formal(wb200_backend *backend, const wb200_elementwise_request *r, wb200_evidence *evidence) {
   if (!backend || !r) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
   int arity;
-  bool relation = false, logic = false;
+  bool relation = false, logic = false, function_family = false;
   switch (r->operation) {
     case WB200_EW_MAX: case WB200_EW_MIN: case WB200_EW_ADD: case WB200_EW_SUB: case WB200_EW_MUL: arity = 2; break;
     case WB200_EW_EQ: case WB200_EW_NE: case WB200_EW_GE: case WB200_EW_GT: case WB200_EW_LE: case WB200_EW_LT: arity = 2; relation = true; break;
@@ -217,16 +217,17 @@ wb200_status wb200_elementwise_formal(wb200_backend *backend, const wb200_elemen
     case WB200_EW_SQRT: case WB200_EW_RSQRT: case WB200_EW_LOG2: case WB200_EW_LN: case WB200_EW_POW2: case WB200_EW_EXP:
     case WB200_EW_SIN: case WB200_EW_COS: case WB200_EW_TANH: case WB200_EW_SIGMOID: case WB200_EW_SOFTPLUS:
       arity = 1;
-      if (r->inputs[0].format != WB200_F16 && r->inputs[0].format != WB200_BF16)
-        return fail(WB200_ERR_UNSUPPORTED, "the correctly rounded function family takes F16 and BF16 operands (F32 needs more than f64 evaluation)");
+      function_family = true;
       break;
     default: return fail(WB200_ERR_UNSUPPORTED, "elementwise operation is outside the formal arithmetic, relation, logic and function families");
   }
   if (static_cast<int>(r->input_count) != arity) return fail(WB200_ERR_INVALID_ARGUMENT, "elementwise input arity does not match semantics");
   const wb200_tensor_desc &dst = r->destination, &first = r->inputs[0];
   const bool bool_out = dst.format == WB200_BOOL, bool_in = first.format == WB200_BOOL;
-  if (logic ? !(bool_out && (bool_in || is_float_format(first.format))) : !is_float_format(first.format))
-    return fail(WB200_ERR_UNSUPPORTED, "formal elementwise operands must be F16, BF16 or F32 (Bool for logic)");
+  // TF32 (19 significant bits in storage bits 31..13) is an operand format of the correctly rounded function family only.
+  const bool tf32_function = function_family && first.format == WB200_TF32;
+  if (logic ? !(bool_out && (bool_in || is_float_format(first.format))) : !(is_float_format(first.format) || tf32_function))
+    return fail(WB200_ERR_UNSUPPORTED, "formal elementwise operands must be F16, BF16 or F32 (Bool for logic, TF32 for the function family)");
   if (!logic && !(relation ? (bool_out || is_float_format(dst.format)) : dst.format == first.format))
     return fail(WB200_ERR_UNSUPPORTED, "formal elementwise result format does not fit the operation");
   auto packed_ok = [](const wb200_tensor_desc &d) { return d.format != WB200_BOOL || d.layout == WB200_LAYOUT_TENSOR || d.layout == WB200_LAYOUT_NTENSOR; };
@@ -541,7 +542,7 @@ wb200_status enqueue_image_elementwise(wb200_spm_image *image, uint32_t operatio
                                        uint32_t scalar_flag, uint32_t relation_numeric_or_rhs_group, uint32_t *d_flags, bool execute) {
   if (!image) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
   int arity;
-  bool relation = false, logic = false;
+  bool relation = false, logic = false, function_family = false;
   switch (operation) {
     case WB200_EW_MAX: case WB200_EW_MIN: case WB200_EW_ADD: case WB200_EW_SUB: case WB200_EW_MUL: arity = 2; break;
     case WB200_EW_EQ: case WB200_EW_NE: case WB200_EW_GE: case WB200_EW_GT: case WB200_EW_LE: case WB200_EW_LT: arity = 2; relation = true; break;
@@ -551,14 +552,13 @@ wb200_status enqueue_image_elementwise(wb200_spm_image *image, uint32_t operatio
     case WB200_EW_SQRT: case WB200_EW_RSQRT: case WB200_EW_LOG2: case WB200_EW_LN: case WB200_EW_POW2: case WB200_EW_EXP:
     case WB200_EW_SIN: case WB200_EW_COS: case WB200_EW_TANH: case WB200_EW_SIGMOID: case WB200_EW_SOFTPLUS:
       arity = 1;
-      if (format != WB200_F16 && format != WB200_BF16)
-        return fail(WB200_ERR_UNSUPPORTED, "the correctly rounded function family takes F16 and BF16 operands");
+      function_family = true;
       break;
     default: return fail(WB200_ERR_UNSUPPORTED, "elementwise operation has no formal evaluation");
   }
   if (count == 0) return fail(WB200_ERR_INVALID_ARGUMENT, "elementwise element count must be positive");
-  if (logic ? !(format == WB200_BOOL || is_float_format(format)) : !is_float_format(format))
-    return fail(WB200_ERR_UNSUPPORTED, "elementwise operand format must be F16, BF16 or F32 (Bool for logic)");
+  if (logic ? !(format == WB200_BOOL || is_float_format(format)) : !(is_float_format(format) || (function_family && format == WB200_TF32)))
+    return fail(WB200_ERR_UNSUPPORTED, "elementwise operand format must be F16, BF16 or F32 (Bool for logic, TF32 for the function family)");
   const bool extras = arity == 2 && !logic;   // only arithmetic and relation calls carry the three extra fields
   if (!extras) rhs_unit_elements = scalar_flag = relation_numeric_or_rhs_group = 0;
   if (scalar_flag > 1) return fail(WB200_ERR_INVALID_ARGUMENT, "elementwise scalar flag must be 0 or 1");

@@ -61,12 +61,12 @@ __device__ __forceinline__ uint32_t narrow_bits(float value, int format) {
 }
 
 __device__ __forceinline__ uint32_t load_element_bits(const uint8_t *base, int64_t index, int format) {
-  if (format == WB200_F32) return reinterpret_cast<const uint32_t *>(base)[index];
+  if (format == WB200_F32 || format == WB200_TF32) return reinterpret_cast<const uint32_t *>(base)[index];
   return reinterpret_cast<const uint16_t *>(base)[index];
 }
 __device__ __forceinline__ void store_element_bits(uint8_t *base, int64_t index, int format,
                                                    uint32_t bits) {
-  if (format == WB200_F32)
+  if (format == WB200_F32 || format == WB200_TF32)
     reinterpret_cast<uint32_t *>(base)[index] = bits;
   else
     reinterpret_cast<uint16_t *>(base)[index] = static_cast<uint16_t>(bits);

@@ -4,6 +4,7 @@
 // round-to-nearest-even (:157-185); NaN inputs or results are reported, not produced. Arithmetic
 // uses the explicitly rounded intrinsics so the compiler cannot contract or reassociate.
 #include "kernels.h"
+#include "formal_functions_f32.cuh"
 
 namespace wb200 {
 namespace {
@@ -453,8 +454,8 @@ __device__ __forceinline__ uint32_t formal_scalar(int op, int format, int out_fo
 // nearest-even with gradual underflow; sigmoid and softplus as whole functions, :372-470). The value is computed in
 // f64 (a few ulp of f64) and narrowed with a single rounding (f64 -> f32 with round-to-odd, then RNE to 11 or 8 bits);
 // a misrounding needs the true value within 2^-50 of a rounding boundary of a 16-bit format, and the complete input
-// space (65 536 operands per function and format) is checked against a 200-bit evaluation. f32 operands are not
-// taken: f64 evaluation cannot guarantee their rounding.
+// space (65 536 operands per function and format) is checked against a 200-bit evaluation. binary32 and TF32 operands
+// take the two-step evaluation of formal_functions_f32.cuh.
 __device__ __forceinline__ uint32_t narrow_from_double(double value, int format) {
   float f = __double2float_rz(value);
   if (static_cast<double>(f) != value && isfinite(f)) f = __uint_as_float(__float_as_uint(f) | 1u);   // sticky bit: round to odd
@@ -462,6 +463,26 @@ __device__ __forceinline__ uint32_t narrow_from_double(double value, int format)
 }
 
 __device__ uint32_t formal_mpfr_scalar(int op, int format, uint32_t a, uint32_t *flags_out) {
+  if (format == WB200_F32 || format == WB200_TF32) {
+    // binary32 and TF32 operands: binary64 evaluation with a rounding test and a double-double second step
+    // (formal_functions_f32.cuh). TF32 keeps its 19 significant bits in storage bits 31..13; the low bits are ignored.
+    int function;
+    switch (op) {
+      case WB200_EW_SQRT: function = ff32::kSqrt; break;
+      case WB200_EW_RSQRT: function = ff32::kRsqrt; break;
+      case WB200_EW_LOG2: function = ff32::kLog2; break;
+      case WB200_EW_LN: function = ff32::kLn; break;
+      case WB200_EW_POW2: function = ff32::kPow2; break;
+      case WB200_EW_EXP: function = ff32::kExp; break;
+      case WB200_EW_SIN: function = ff32::kSin; break;
+      case WB200_EW_COS: function = ff32::kCos; break;
+      case WB200_EW_TANH: function = ff32::kTanh; break;
+      case WB200_EW_SIGMOID: function = ff32::kSigmoid; break;
+      default: function = ff32::kSoftplus; break;
+    }
+    const bool tf32 = format == WB200_TF32;
+    return ff32::correctly_rounded(function, tf32, tf32 ? (a & 0xffffe000u) : a, flags_out, nullptr);
+  }
   const FormatTraits t = traits_of(format);
   uint32_t flags = 0;
   const bool nan = (a & t.exp_mask) == t.exp_mask && (a & t.mant_mask) != 0;
