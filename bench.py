@@ -354,10 +354,17 @@ def run_profile_case(name: str):
         k = torch.randn(8, FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
         v = torch.randn(8, FD["kv_heads"], FD["kv_len"], FD["head_dim"], device=device, generator=gen).bfloat16()
         fn = lambda: backend.attention_fd(q, k, v, FD["head_dim"] ** -0.5)
-    else:                  # 4096^3 of the benchmark's 8192^3: A + B + out = 100 MB
-        a = (torch.rand(4096, 4096, device=device, generator=gen) * 2 - 1).bfloat16()
-        b = (torch.rand(4096, 4096, device=device, generator=gen) * 2 - 1).bfloat16()
-        bias = torch.randn(4096, device=device, generator=gen) * 0.02
+    elif name == "layer":  # the decoder layer at the benchmark's shape, for single-pass captures (DRAM bytes) only
+        from vibe_compiler_b200.decoder_layer import LayerConfig, ShardedDecoderLayer, random_weights
+        cfg = LayerConfig()
+        layer = ShardedDecoderLayer(backend, cfg, random_weights(cfg, seed=SEED), device=device)
+        x = torch.randn(LAYER["batch"], LAYER["seq"], cfg.d_model, device=device, generator=gen).bfloat16()
+        fn = lambda: layer.forward_fused(x)
+    else:                  # 4096^3 of the benchmark's 8192^3: A + B + out = 100 MB; "gemm_full": 8192^3, single-pass captures only
+        size = GEMM["m"] if name == "gemm_full" else 4096
+        a = (torch.rand(size, size, device=device, generator=gen) * 2 - 1).bfloat16()
+        b = (torch.rand(size, size, device=device, generator=gen) * 2 - 1).bfloat16()
+        bias = torch.randn(size, device=device, generator=gen) * 0.02
         fn = lambda: backend.gemm_epilogue(a, b, bias, epilogue=abi.EPI_BIAS_GELU)
     for _ in range(3):
         fn()
@@ -387,7 +394,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-extras", action="store_true", help="only the headline FA workload")
-    parser.add_argument("--profile-case", choices=["fa", "fd", "gemm"],
+    parser.add_argument("--profile-case", choices=["fa", "fd", "gemm", "gemm_full", "layer"],
                         help="run three launches of a reduced-size case of one kernel and exit (for ncu captures)")
     args = parser.parse_args()
     if args.profile_case:

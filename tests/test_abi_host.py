@@ -84,3 +84,14 @@ def test_invalid_descriptors_are_rejected():
     bad = abi.make_desc(abi.F32, abi.LAYOUT_CX, [])
     assert lib.wb200_physical_bytes(C.byref(bad), C.byref(out)) == abi.ERR_INVALID_ARGUMENT
     assert lib.wb200_physical_bytes(None, C.byref(out)) == abi.ERR_INVALID_ARGUMENT
+
+
+def test_microbenchmarks_import_and_parse_their_arguments():
+    """The benchmarking tools that ship in the package import without a device and insist on their inputs."""
+    import importlib
+    for name in ("replay", "chain_replay", "command_kernels"):
+        module = importlib.import_module(f"vibe_compiler_b200.microbench.{name}")
+        assert callable(module.main)
+    replay = importlib.import_module("vibe_compiler_b200.microbench.replay")
+    with pytest.raises(SystemExit):
+        replay.main([])            # --fixture is required: no default into the test tree

@@ -123,8 +123,8 @@ def test_malformed_elementwise_calls_are_rejected(backend):
         pad.elementwise("add", 0, 0x2000, 1 << 15, abi.F32, rhs=0x1000)
     with pytest.raises(WB200Error, match="no formal evaluation"):
         pad.elementwise("exp_lp", 0, 0x2000, 16, abi.F32)
-    with pytest.raises(WB200Error, match="F16 and BF16"):
-        pad.elementwise("tanh", 0, 0x2000, 16, abi.F32)
+    with pytest.raises(WB200Error, match="TF32 for the function family"):
+        pad.elementwise("add", 0, 0x2000, 16, abi.TF32, rhs=0x1000)
     lib = abi.load()
     assert lib.wb200_target_call_elementwise(pad._handle, abi.ELEMENTWISE_OPS["add"], 0, 0, 0x2000, 16, abi.F32, 0, 2, 0, None) == abi.ERR_INVALID_ARGUMENT
     assert lib.wb200_target_call_elementwise(pad._handle, abi.ELEMENTWISE_OPS["eq"], 0, 0, 0x2000, 16, abi.F32, 0, 0, 2, None) == abi.ERR_INVALID_ARGUMENT

@@ -475,8 +475,9 @@ uint32_t fd_choose_splits(const AttentionArgs &a, int sm_count) {
   const int64_t units = static_cast<int64_t>(a.batch) * a.kv_heads;
   const int64_t slots = 2LL * sm_count;                 // two CTAs are resident per SM
   const int64_t base = (visible + 2047) / 2048;         // 2048-key splits
-  // Many more CTAs than slots: the hardware deals them out as slots free up and the tail is one short CTA.
-  if (units * base >= 8 * slots) return static_cast<uint32_t>(base < 2 ? 2 : (base > 4096 ? 4096 : base));
+  // More (batch, kv head) units than resident slots: 2048-key splits give many short CTAs, which the hardware deals out
+  // as slots free up (the tail is one short CTA), and the fold over a unit's few splits is short.
+  if (units >= slots) return static_cast<uint32_t>(base < 2 ? 2 : (base > 4096 ? 4096 : base));
   // Otherwise pick the split count with the least estimated time, in units of one key streamed by one CTA:
   // waves x (keys per split + the CTA's fixed cost) + the serial fold over the splits (one record costs about as much
   // as six keys). A long sequence with few (batch, kv head) units ends up with exactly one resident wave.

@@ -6,7 +6,7 @@
 // plus the full physical storage bytes of every operand. This header offers the same four calls with the same
 // names, argument meaning and error behaviour, with std:: types in place of LLVM's (llvm::Expected<T> becomes
 // wafer_b200::Expected<T>, llvm::ArrayRef becomes std::vector), so that a reference-side adapter is a field-by-field
-// copy (see INTEGRATION.md). Header only; link with -lwb200.
+// copy. Header only; link with -lwb200.
 #pragma once
 
 #include <cstdint>

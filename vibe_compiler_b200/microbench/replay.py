@@ -1,6 +1,6 @@
 """Replay time of the shipped GEMM Tile programs (16 Tiles x 7 plans, out[4096,4096] = arg1[4096,1024] . arg0[1024,4096], bf16).
 
-    python -m vibe_compiler_b200.microbench.replay [--plan NAME] [--runs N] [--fixture tests/golden/gemm_tile_modules.json.xz]
+    python -m vibe_compiler_b200.microbench.replay --fixture tests/golden/gemm_tile_modules.json.xz [--plan NAME] [--runs N]
 
 Prints one JSON line per plan: commands, kernel launches and the device time of the command stream (CUDA events inside
 wb200_tile_program_run; host <-> device tensor copies excluded). WB200_REPLAY_GRAPH=0 in the environment replays the
@@ -22,11 +22,12 @@ from ..tile_program import TileProgram
 
 
 def main(argv=None) -> int:
-    root = Path(__file__).resolve().parents[2]
     parser = argparse.ArgumentParser()
     parser.add_argument("--plan", default="", help="only the plans whose name contains this text")
     parser.add_argument("--runs", type=int, default=5)
-    parser.add_argument("--fixture", default=str(root / "tests" / "golden" / "gemm_tile_modules.json.xz"))
+    parser.add_argument("--fixture", required=True,
+                        help="packed per-Tile modules (JSON, xz): {plan: {tile name: .ll text}}; the reference's seven GEMM plans are "
+                             "packed in tests/golden/gemm_tile_modules.json.xz of the source tree")
     args = parser.parse_args(argv)
     fixture = json.loads(lzma.decompress(Path(args.fixture).read_bytes()))
     backend = B200TargetModelBackend(0)

@@ -1,6 +1,8 @@
 // Microbenchmark: back-to-back tcgen05.mma (K = 16, bf16) issue and completion rate per operand mode,
 // for single-CTA instructions (cta_group::1, M = 128) and for CTA pairs (cta_group::2, M = 256: each CTA of
 // a two-CTA cluster holds 128 rows of A and half of the N rows of B).
+// Three issue-loop forms are timed: runtime operand mode (a branch per instruction, `bench`), two issuing warps
+// (`bench_dual`), and compile-time shapes with the loop walked by one lane or by the whole warp (`issue`).
 // Build: nvcc -gencode arch=compute_100a,code=sm_100a -O3 -std=c++17 -o umma_rate umma_rate.cu ; run: ./umma_rate
 #include <cstdio>
 #include <cuda_runtime.h>
@@ -21,15 +23,6 @@ __device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a, uint64_t b, uint3
   else
     asm volatile("{\n\t.reg .pred P;\n\tsetp.ne.b32 P, %4, 0;\n\ttcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, P;\n\t}" ::"r"(d), "r"(a), "l"(b), "r"(idesc), "r"(acc) : "memory");
 }
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ uint32_t cluster_cta_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return r;
-}
-
 // mode 0: SS A K-major, B K-major (S = Q K^T); 1: TS, B MN-major (PV); 2: SS A K-major, B MN-major; 3: TS, B K-major.
 // accumulators: 1 = every instruction adds into one TMEM tile; 2 = alternate between two tiles every 8 instructions.
 template <int kGroup>
@@ -159,6 +152,100 @@ static void run_dual(int grid, int n, int ts, int issuers, int collector, long l
          issuers, collector, h[1] / (iters * 8.0), h[3] / (iters * 8.0), cudaGetErrorString(e));
 }
 
+
+// ---- How the shape of the issuing code affects the rate: compile-time instruction shape, and who walks the loop.
+// kShape 0: if (threadIdx.x == 0) { loop }   1: warp-wide loop, elect_one_sync() around each MMA   2: warp-wide loop, lane == 0 around each MMA
+// 3: warp-wide loop, one elect_one_sync() per group of 8 MMAs
+template <int kShape, int kTs, int kN>
+__global__ void __launch_bounds__(128, 1) issue(int iters, int issuers, long long *out) {
+  extern __shared__ uint8_t raw[];
+  uint8_t *smem = raw + ((1024u - (smem_u32(raw) & 1023u)) & 1023u);
+  const uint32_t base = smem_u32(smem);
+  __shared__ uint64_t bar[4];
+  __shared__ uint32_t slot;
+  __shared__ int abortw;
+  for (int i = threadIdx.x; i < 200 * 1024 / 4; i += blockDim.x) reinterpret_cast<uint32_t *>(smem)[i] = 0x3c003c00u;
+  if (threadIdx.x == 0) { for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&bar[i]), 1); abortw = 0; fence_mbar_init(); }
+  if (threadIdx.x < 32) { tmem_alloc(smem_u32(&slot), 512); tmem_relinquish(); }
+  fence_proxy_async_smem();
+  tc_fence_before(); __syncthreads(); tc_fence_after();
+  const uint32_t tm = slot;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp < issuers) {
+    const uint32_t idesc = umma_idesc_f16(128, kN, true, false, false);
+    const uint64_t a_desc = umma_desc_kmajor(base + warp * 98304);
+    const uint64_t b_desc = umma_desc_kmajor(base + warp * 98304 + 32768);
+    const uint32_t d = tm + 128 + warp * 128;
+    const uint32_t a_tm = tm + warp * 64;
+    long long t0 = 0, t2 = 0;
+    if (kShape == 0) {
+      if (lane == 0) {
+        t0 = clock64();
+        for (int it = 0; it < iters; ++it) {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t off = ((ks >> 2) * 16384 + (ks & 3) * 32) >> 4;
+            if (kTs) mma_ts<1>(d, a_tm + ks * 8, b_desc + off, idesc, 1);
+            else mma_ss<1>(d, a_desc + off, b_desc + off, idesc, 1);
+          }
+        }
+        umma_commit(smem_u32(&bar[warp]));
+        mbar_wait(smem_u32(&bar[warp]), 0, &abortw);
+        t2 = clock64();
+      }
+    } else {
+      t0 = clock64();
+      for (int it = 0; it < iters; ++it) {
+        if (kShape == 3) {
+          if (elect_one_sync()) {
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint64_t off = ((ks >> 2) * 16384 + (ks & 3) * 32) >> 4;
+              if (kTs) mma_ts<1>(d, a_tm + ks * 8, b_desc + off, idesc, 1);
+              else mma_ss<1>(d, a_desc + off, b_desc + off, idesc, 1);
+            }
+          }
+          __syncwarp();
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint64_t off = ((ks >> 2) * 16384 + (ks & 3) * 32) >> 4;
+            const bool mine = kShape == 1 ? elect_one_sync() : (lane == 0);
+            if (mine) {
+              if (kTs) mma_ts<1>(d, a_tm + ks * 8, b_desc + off, idesc, 1);
+              else mma_ss<1>(d, a_desc + off, b_desc + off, idesc, 1);
+            }
+          }
+        }
+      }
+      if (elect_one_sync()) umma_commit(smem_u32(&bar[warp]));
+      __syncwarp();
+      mbar_wait(smem_u32(&bar[warp]), 0, &abortw);
+      t2 = clock64();
+    }
+    if (blockIdx.x == 0 && lane == 0) { out[warp] = t2 - t0; }
+  }
+  tc_fence_before(); __syncthreads();
+  if (threadIdx.x < 32) { tc_fence_after(); tmem_dealloc(tm, 512); }
+}
+template <int kShape, int kTs, int kN>
+void run_issue(long long *d) {
+  const int iters = 200;
+  cudaFuncSetAttribute(issue<kShape, kTs, kN>, cudaFuncAttributeMaxDynamicSharedMemorySize, 204 * 1024);
+  for (int issuers = 1; issuers <= 2; ++issuers) {
+    cudaMemset(d, 0, 32);
+    issue<kShape, kTs, kN><<<148, 128, 204 * 1024>>>(iters, issuers, d);
+    cudaError_t e = cudaDeviceSynchronize();
+    long long h[2]; cudaMemcpy(h, d, 16, cudaMemcpyDeviceToHost);
+    printf("shape %d %s N=%3d issuers %d: warp0 %.1f clk/MMA  warp1 %.1f clk/MMA (%s)\n", kShape, kTs ? "TS" : "SS", kN, issuers, h[0] / (iters * 8.0), h[1] / (iters * 8.0), cudaGetErrorString(e));
+  }
+}
+template <int kShape>
+void run_shape(long long *d) {
+  run_issue<kShape, 0, 64>(d); run_issue<kShape, 0, 128>(d);
+  run_issue<kShape, 1, 64>(d); run_issue<kShape, 1, 128>(d);
+}
+
 template <int kGroup>
 static void run(int grid, int n, int mode, int accumulators, long long *d) {
   const char *names[] = {"SS  A:K  B:K ", "TS  A:tm B:MN", "SS  A:K  B:MN", "TS  A:tm B:K "};
@@ -192,7 +279,9 @@ int main(int argc, char **argv) {
     for (int ts = 0; ts < 2; ++ts)
       for (int issuers = 1; issuers <= 2; ++issuers) run_dual(148, n, ts, issuers, 0, d);
   for (int n : {64, 128}) run_dual(148, n, 0, 1, 1, d);
-  if (argc > 1) return 0;   // any argument: only the two-issuer and collector cases
+  run_shape<0>(d); run_shape<1>(d); run_shape<2>(d); run_shape<3>(d);
+  run_issue<1, 0, 256>(d); run_issue<1, 1, 256>(d); run_issue<0, 0, 256>(d); run_issue<0, 1, 256>(d);
+  if (argc > 1) return 0;   // any argument: skip the table of runtime-mode issue loops below
   for (int grid : {2, 148})
     for (int n : {32, 64, 128, 256})
       for (int mode = 0; mode < 4; ++mode) {
