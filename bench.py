@@ -36,8 +36,9 @@ SEED = 20260803
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised under profiles/,
 # taken on reduced cases (bench.py --profile-case) and scaled to a full launch by the units processed.
 TRAFFIC = {
-    "fa": 2 * (533.9e6 + 45.0e6),      # profiles/fa_umma_kernel_cfg2.md: batch 2 of 4 captured
+    "fa": 2 * (214.2e6 + 46.1e6),      # profiles/fa_umma_kernel_cfg2.md: batch 2 of 4 captured
     "fd": 8 * (1.073832e9 + 6.2e6),    # profiles/fd_partial_kernel_cfg3.md: batch 8 of 64 captured
+    "gemm": 1.118e9 + 0.124e9,         # profiles/gemm_umma_pair_kernel_cfg4.md: the full 8192^3 launch, one-pass capture
 }
 
 
@@ -586,7 +587,10 @@ def main():
                                      "verified": long_ok, "max_rel_err": long_err, "lse_abs_err": long_lse_err,
                                      "verified_against": "float64 torch recomputation of every rank's shard, merged in float64",
                                      "roofline": {"bound": "hbm", "achieved": long_gbs / world, "peak": peak["hbm_gbs"], "unit": "GB/s per GPU",
-                                                  "frac": long_gbs / world / peak["hbm_gbs"], "traffic": None, "peak_source": peak["source"]}}
+                                                  "frac": long_gbs / world / peak["hbm_gbs"],
+                                                  "traffic": long_bytes / world * TRAFFIC["fd"] / (FD["batch"] * 2 * FD["kv_heads"] * FD["kv_len"] * FD["head_dim"] * 2),
+                                                  "traffic_note": "the same stage-1 kernel as the decode configuration: its captured DRAM bytes per algorithmic byte, times this rank's K and V bytes",
+                                                  "peak_source": peak["source"]}}
         torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()          # no rank releases its exchange buffer while a peer may still write to it
@@ -604,7 +608,7 @@ def main():
         extras["gemm_bias_gelu"] = {"workload": "GEMM 8192^3 bf16 + f32 bias + GELU(erf) -> bf16", "value": g_tflops, "unit": "TFLOP/s",
                                     "ms_per_step": g_ms,
                                     "roofline": {"bound": "tensor", "achieved": g_tflops, "peak": peak["bf16_tflops"], "unit": "TFLOP/s",
-                                                 "frac": g_tflops / peak["bf16_tflops"], "traffic": None, "peak_source": peak["source"]}}
+                                                 "frac": g_tflops / peak["bf16_tflops"], "traffic": TRAFFIC["gemm"], "peak_source": peak["source"]}}
 
     if not args.skip_extras and world == 1:
         # ------------------------------------------------------------ cfg 1: the reference's own CPU-runnable attention case

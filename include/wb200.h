@@ -445,6 +445,35 @@ typedef struct wb200_decoder_layer_params {
 uint64_t wb200_decoder_layer_workspace_bytes(const wb200_decoder_layer_params *params);
 wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_layer_params *params);
 
+/* Sum over the shards of a tensor-parallel region (the `allreduce` of wb200_decoder_layer, or any buffer) as one kernel
+ * per GPU that lets the NVSwitch add and broadcast: the reference's Tile collectives realise such a sum as reduce-scatter
+ * followed by all-gather over the dies (lib/Wafer/Transforms/Tile/DistributedCollectiveMovement.cpp:675-735); here rank
+ * r reads the r-th slice of the buffer through an NVLink multicast address with multimem.ld_reduce (one sum of all
+ * ranks' values comes back, accumulated in f32) and stores it through the same address with multimem.st (it lands in
+ * every rank's buffer). In place; all ranks end with bit-identical values.
+ *   multicast   the multicast address of this call's buffer: the buffer must lie at the same offset of a symmetric
+ *               allocation on every rank, and that allocation must be bound to a multicast object (torch symmetric
+ *               memory: handle.multicast_ptr + offset). 16-byte aligned, elements * size a multiple of 16 bytes.
+ *   signals     every rank's signal words (peer-mapped device memory, wb200_switch_sum_signal_bytes(world) bytes each,
+ *               zero-initialised), [rank] this rank's own
+ *   epoch       two zero-initialised 32-bit words in this rank's device memory; the kernel advances them
+ *   blocks      thread blocks of the kernel (0: 32). Beside persistent compute kernels, give it the SMs they leave free.
+ * Every rank must make the same sequence of calls per signal area; calls that may overlap in time need areas of their
+ * own. The waits on the other ranks are bounded (about a second): a rank that never arrives leaves
+ * WB200_ERR_DEVICE_TIMEOUT for the next wb200_backend_poll, not a hung GPU. */
+typedef struct wb200_switch_sum_params {
+  uint32_t rank, world;
+  void *multicast;
+  uint64_t elements;
+  uint32_t format;             /* WB200_BF16, WB200_F16 or WB200_F32 */
+  uint32_t blocks;
+  void *signals[WB200_MAX_EXCHANGE_RANKS];
+  uint32_t *epoch;
+  void *stream;
+} wb200_switch_sum_params;
+uint64_t wb200_switch_sum_signal_bytes(uint32_t world);
+wb200_status wb200_switch_sum(wb200_backend *backend, const wb200_switch_sum_params *params);
+
 /* Reads and clears the device status word of asynchronous (WB200_MEM_DEVICE) calls after
  * synchronising `stream`. Returns WB200_ERR_DEVICE_TIMEOUT if a kernel gave up a bounded wait. */
 wb200_status wb200_backend_poll(wb200_backend *backend, void *stream);

@@ -131,6 +131,12 @@ class FdExchange(C.Structure):
     _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("peer_buffers", C.c_void_p * 16), ("epoch", C.c_void_p)]
 
 
+class SwitchSumParams(C.Structure):
+    _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("multicast", C.c_void_p), ("elements", C.c_uint64),
+                ("format", C.c_uint32), ("blocks", C.c_uint32), ("signals", C.c_void_p * 16), ("epoch", C.c_void_p),
+                ("stream", C.c_void_p)]
+
+
 class ProgramStats(C.Structure):
     _fields_ = [("instructions", C.c_uint64), ("commands", C.c_uint64), ("gemm_commands", C.c_uint64), ("movement_commands", C.c_uint64),
                 ("fill_commands", C.c_uint64), ("transfer_commands", C.c_uint64), ("sync_commands", C.c_uint64),
@@ -187,6 +193,8 @@ SIGNATURES = {
     "wb200_selftest_bounded_wait": (C.c_int, [C.c_void_p, C.c_uint64, C.POINTER(C.c_uint64)]),
     "wb200_fd_exchange_bytes": (C.c_uint64, [C.c_uint32, C.c_uint32, C.c_uint32]),
     "wb200_attention_fd_exchange": (C.c_int, [C.c_void_p, C.POINTER(AttentionParams), C.c_uint32, C.POINTER(FdExchange)]),
+    "wb200_switch_sum_signal_bytes": (C.c_uint64, [C.c_uint32]),
+    "wb200_switch_sum": (C.c_int, [C.c_void_p, C.POINTER(SwitchSumParams)]),
     "wb200_decoder_layer_workspace_bytes": (C.c_uint64, [C.POINTER(DecoderLayerParams)]),
     "wb200_decoder_layer": (C.c_int, [C.c_void_p, C.POINTER(DecoderLayerParams)]),
     "wb200_target_call_rdma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, _U32x3, _U32x3]),

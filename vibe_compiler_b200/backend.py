@@ -381,6 +381,24 @@ class B200TargetModelBackend:
         self._check(self._lib.wb200_attention_fd_exchange(self._handle, C.byref(p), kv_splits, C.byref(x)))
         return out
 
+    def switch_sum_signal_bytes(self, world: int) -> int:
+        return int(self._lib.wb200_switch_sum_signal_bytes(world))
+
+    def switch_sum(self, multicast_pointer: int, elements: int, dtype, *, rank: int, signal_pointers: Sequence[int],
+                   epoch: torch.Tensor, blocks: int = 0, stream: Optional[int] = None) -> None:
+        """In-place sum over the ranks of the buffer at `multicast_pointer` (an NVLink multicast address of a symmetric
+        allocation) by one kernel per GPU: the switch adds and broadcasts (wb200_switch_sum). `signal_pointers[r]` are
+        rank r's signal words as addressable from this GPU; `epoch` a zeroed int32[2] of this rank."""
+        if stream is None:
+            stream = torch.cuda.current_stream().cuda_stream
+        x = abi.SwitchSumParams()
+        x.rank, x.world = rank, len(signal_pointers)
+        x.multicast, x.elements, x.format, x.blocks = multicast_pointer, elements, _TORCH_FORMATS[dtype], blocks
+        for r, pointer in enumerate(signal_pointers):
+            x.signals[r] = pointer
+        x.epoch, x.stream = epoch.data_ptr(), stream
+        self._check(self._lib.wb200_switch_sum(self._handle, C.byref(x)))
+
     def attention_fd_merge(self, states, like_q, *, out=None, lse=None, zero_fully_masked: bool = False,
                            stream: Optional[int] = None):
         """Left-folds [shards, batch, q_heads, D + 2] states in ascending shard order and finalizes."""
@@ -460,11 +478,11 @@ class B200TargetModelBackend:
 
     def decoder_layer(self, x, *, norm1, wqkv, wo, norm2, wgu, wdown, q_heads: int, kv_heads: int, head_dim: int, eps: float,
                       rope_theta: float, position_offset: int = 0, allreduce=None, workspace=None, out=None,
-                      micro_batches: int = 1, reserved_sms: int = 0, stream: Optional[int] = None):
+                      micro_batches: int = 1, reserved_sms: int = 0, stream: Optional[int] = None, workspace_factory=None):
         """One shard of a Llama-style decoder layer forward through the single C-ABI call wb200_decoder_layer.
         x: [batch, seq, d_model] CUDA tensor. `allreduce(tensor)` must enqueue an in-place sum over the shards
-        (torch.distributed.all_reduce); `workspace` is a uint8 CUDA tensor that is reused if large enough.
-        Returns (out, workspace)."""
+        (torch.distributed.all_reduce); `workspace` is a uint8 CUDA tensor that is reused if large enough, else
+        `workspace_factory(bytes)` (default: torch.empty) makes one. Returns (out, workspace)."""
         batch, seq, d_model = x.shape
         p = abi.DecoderLayerParams()
         p.batch, p.seq, p.d_model, p.head_dim = batch, seq, d_model, head_dim
@@ -477,7 +495,10 @@ class B200TargetModelBackend:
         if needed == 0:
             raise WB200Error(abi.ERR_UNSUPPORTED, self._lib.wb200_last_error().decode())
         if workspace is None or workspace.numel() < needed:
-            workspace = torch.empty(needed, dtype=torch.uint8, device=x.device)
+            if workspace_factory is not None:
+                workspace = workspace_factory(needed)
+            else:
+                workspace = torch.empty(needed, dtype=torch.uint8, device=x.device)
         if out is None:
             out = torch.empty_like(x)
         if stream is None:

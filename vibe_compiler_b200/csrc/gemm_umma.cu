@@ -32,13 +32,14 @@ struct GemmUmmaParams {
   void *out;
   int *status;
   int num_m_tiles, num_n_tiles;
+  int group_m;   // tile rows walked together (see tile_coords)
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int &m_blk, int &n_blk) {
-  const int per_group = kGroupM * num_n;
+__device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int group_m, int &m_blk, int &n_blk) {
+  const int per_group = group_m * num_n;
   const int group = tile / per_group;
-  const int first_m = group * kGroupM;
-  const int group_size = min(num_m - first_m, kGroupM);
+  const int first_m = group * group_m;
+  const int group_size = min(num_m - first_m, group_m);
   const int in_group = tile - group * per_group;
   m_blk = first_m + in_group % group_size;
   n_blk = in_group / group_size;
@@ -165,7 +166,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         int m_blk, n_blk;
-        tile_coords(tile, p.num_m_tiles, p.num_n_tiles, m_blk, n_blk);
+        tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, m_blk, n_blk);
         const int m0 = m_blk * kBM, n0 = n_blk * kBN;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_word)) { ok = false; break; }
@@ -237,7 +238,7 @@ gemm_umma_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     bool ok = true;
     for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
       int m_blk, n_blk;
-      tile_coords(tile, p.num_m_tiles, p.num_n_tiles, m_blk, n_blk);
+      tile_coords(tile, p.num_m_tiles, p.num_n_tiles, p.group_m, m_blk, n_blk);
       const int row = m_blk * kBM + quarter * 32 + lane;
       const int n0 = n_blk * kBN;
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_word)) { ok = false; break; }
@@ -340,7 +341,7 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
       bool ok = true;
       for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
         int m_blk, n_blk;
-        tile_coords(tile, num_pair_m, p.num_n_tiles, m_blk, n_blk);
+        tile_coords(tile, num_pair_m, p.num_n_tiles, p.group_m, m_blk, n_blk);
         const int m0 = m_blk * 2 * kBM + static_cast<int>(cta_rank) * kBM;         // this CTA's 128 rows
         const int n0 = n_blk * kBN + static_cast<int>(cta_rank) * (kBN / 2);       // this CTA's 128 B columns
         for (int kb = 0; kb < k_blocks; ++kb) {
@@ -420,7 +421,7 @@ gemm_umma_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const uint32_t issuer_bar_base = cluster_map_shared(bar_base, 0);
     for (int tile = cluster_id; ok && tile < num_tiles; tile += num_clusters) {
       int m_blk, n_blk;
-      tile_coords(tile, num_pair_m, p.num_n_tiles, m_blk, n_blk);
+      tile_coords(tile, num_pair_m, p.num_n_tiles, p.group_m, m_blk, n_blk);
       const int row = m_blk * 2 * kBM + static_cast<int>(cta_rank) * kBM + quarter * 32 + lane;
       const int n0 = n_blk * kBN;
       if (!mbar_wait(tmem_full_bar(acc), acc_phase, abort_word)) { ok = false; break; }
@@ -504,6 +505,8 @@ wb200_status launch_gemm_umma(const GemmUmmaArgs &a, int sm_count, int *device_s
   p.status = device_status;
   p.num_m_tiles = (a.m + kBM - 1) / kBM;
   p.num_n_tiles = (a.n + kBN - 1) / kBN;
+  static const int group_override = []() { const char *env = getenv("WB200_GEMM_GROUP_M"); return env ? atoi(env) : 0; }();
+  p.group_m = group_override > 0 ? group_override : kGroupM;
 
   using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const GemmUmmaParams);
   static const Kernel kernels[8] = {

@@ -170,6 +170,13 @@ size_t fd_exchange_floats(int rows, int world);
 wb200_status launch_attention_fd_exchange(const AttentionArgs &args, uint32_t splits, float *partials, int rank, int world,
                                           void *const *peer_buffers, unsigned int *epoch, int *device_status, cudaStream_t stream);
 
+// Sum over the ranks of a buffer that lies at `multicast` in an NVLink multicast mapping of a symmetric allocation
+// (switch_sum.cu): in place, every rank ends with the same sums. `signals` holds every rank's 2 * world zero-initialised
+// signal words (peer-mapped), `epoch` this rank's pair of zero-initialised words.
+constexpr int kMaxSwitchRanks = 16;
+wb200_status launch_switch_sum(void *multicast, uint64_t elements, int format, int rank, int world, void *const *signals,
+                               unsigned int *epoch, int blocks, int *device_status, cudaStream_t stream);
+
 
 // ---- decoder-layer pieces (layer_ops.cu); device pointers, bf16 / f16 storage
 wb200_status launch_rmsnorm(int format, const void *x, const void *gamma, void *y, int rows, int dim, float eps,

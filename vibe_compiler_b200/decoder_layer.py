@@ -136,22 +136,45 @@ class ShardedDecoderLayer:
                       reserved_sms: Optional[int] = None) -> torch.Tensor:
         """Same computation through the single C-ABI call (wb200_decoder_layer): ten kernels per part enqueued by one call,
         the two sums through a callback into torch.distributed, intermediates in one reused workspace. With several
-        shards the batch is cut into `micro_batches` parts whose all-reduces run on a
-        second stream while the following parts compute; `reserved_sms` SMs stay free for NCCL's kernels."""
-        reduce = None
+        shards the batch is cut into `micro_batches` parts whose sums run on a second stream while the following parts
+        compute; `reserved_sms` SMs stay free for the sum's kernel. The sums are done by the NVSwitch through the
+        library's own kernel (switch_sums()) where the GPUs offer NVLink multicast, else by torch.distributed."""
+        reduce, factory = None, None
+        reserved = reserved_sms if reserved_sms is not None else self.default_reserved_sms()
         if self.world > 1:
             import torch.distributed as dist
-            if getattr(self, "_all_reduce_enabled", True):
-                reduce = lambda t: dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)   # noqa: E731
-            else:                                      # timing aid: the layer's kernels without the sums (wrong values)
+            sums = self.switch_sums(blocks=reserved)
+            if not getattr(self, "_all_reduce_enabled", True):   # timing aid: the layer's kernels without the sums (wrong values)
                 reduce = lambda t: None                # noqa: E731
+            elif sums is not None:
+                reduce, factory = sums, sums.allocate
+            else:
+                reduce = lambda t: dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)   # noqa: E731
         out, self._workspace = self.backend.decoder_layer(
             x, norm1=self.norm1, wqkv=self.wqkv, wo=self.wo, norm2=self.norm2, wgu=self.wgu, wdown=self.wdown, q_heads=self.hq,
             kv_heads=self.hkv, head_dim=self.cfg.head_dim, eps=self.cfg.eps, rope_theta=self.cfg.rope_theta,
             position_offset=position_offset, allreduce=reduce, workspace=getattr(self, "_workspace", None),
             micro_batches=(micro_batches if micro_batches is not None else self.default_micro_batches(x.shape[0])),
-            reserved_sms=(reserved_sms if reserved_sms is not None else self.default_reserved_sms()))
+            reserved_sms=reserved, workspace_factory=factory)
         return out
+
+    def switch_sums(self, blocks: int = 0):
+        """The NVSwitch sum of this layer's group (sharding.SwitchSum), made on first use by a collective call, or None:
+        one shard, no multicast on these GPUs, or WB200_LAYER_SUM=nccl in the environment (the library all-reduce)."""
+        import os
+        if self.world == 1 or os.environ.get("WB200_LAYER_SUM", "switch") == "nccl":
+            return None
+        if not hasattr(self, "_switch_sums"):
+            from .sharding import SwitchSum
+            try:
+                sums = SwitchSum(self.backend, self.group, blocks=blocks)
+                self._switch_sums = sums if sums.available else None
+            except (RuntimeError, AttributeError):      # symmetric memory or multicast unavailable in this process
+                self._switch_sums = None
+            self._workspace = None                      # the workspace has to be symmetric from now on
+        if self._switch_sums is not None:
+            self._switch_sums.blocks = blocks
+        return self._switch_sums
 
 
 def layer_flops(cfg: LayerConfig, batch: int, seq: int) -> int:

@@ -120,3 +120,57 @@ class PeerExchange:
             self.pointers = [int(pointer) for pointer in self._handle.buffer_ptrs]
             torch.cuda.synchronize(device)
             dist.barrier(group)          # every rank's buffer is zeroed before anyone's first step
+
+
+class SwitchSum:
+    """Sums over the ranks done by the NVSwitch (B200TargetModelBackend.switch_sum): symmetric buffers bound to an NVLink
+    multicast object, this rank's signal words and epoch. The constructor and `allocate` are collective calls of the
+    group; `available` is False where the GPUs offer no multicast (then use a library all-reduce instead).
+
+        sums = SwitchSum(backend, group)
+        workspace = sums.allocate(nbytes)        # uint8 tensor; the same offsets mean the same data on every rank
+        ...                                      # kernels write this rank's partial sums into a region of workspace
+        sums(region)                             # in place, on the current stream: every rank now holds the sums
+
+    One object serialises its sums (they share the signal words): give sums that may overlap in time objects of their own.
+    Release the object only after every rank has finished its last sum (synchronise, then barrier)."""
+
+    def __init__(self, backend, group=None, device: Optional[torch.device] = None, blocks: int = 0):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.backend, self.blocks = backend, blocks
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.device = device or torch.device("cuda", backend.device)
+        self._buffers = []        # (tensor, handle, multicast pointer)
+        self.epoch = torch.zeros(2, dtype=torch.int32, device=self.device)
+        self._signals = symm_mem.empty(backend.switch_sum_signal_bytes(self.world), dtype=torch.uint8, device=self.device)
+        self._signals.zero_()
+        self._signal_handle = symm_mem.rendezvous(self._signals, self.group)
+        self.signal_pointers = [int(pointer) for pointer in self._signal_handle.buffer_ptrs]
+        self.available = self.world > 1 and int(getattr(self._signal_handle, "multicast_ptr", 0) or 0) != 0
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)              # every rank's signal words are zero before anyone's first sum
+
+    def allocate(self, nbytes: int) -> torch.Tensor:
+        import torch.distributed._symmetric_memory as symm_mem
+        buffer = symm_mem.empty(int(nbytes), dtype=torch.uint8, device=self.device)
+        handle = symm_mem.rendezvous(buffer, self.group)
+        multicast = int(handle.multicast_ptr or 0)
+        if multicast == 0:
+            raise RuntimeError("this allocation has no NVLink multicast mapping")
+        self._buffers.append((buffer, handle, multicast))
+        return buffer
+
+    def __call__(self, region: torch.Tensor) -> torch.Tensor:
+        begin = region.data_ptr()
+        for buffer, _handle, multicast in self._buffers:
+            offset = begin - buffer.data_ptr()
+            if 0 <= offset and offset + region.numel() * region.element_size() <= buffer.numel():
+                if not region.is_contiguous():
+                    raise ValueError("the region must be contiguous")
+                self.backend.switch_sum(multicast + offset, region.numel(), region.dtype, rank=self.rank,
+                                        signal_pointers=self.signal_pointers, epoch=self.epoch, blocks=self.blocks)
+                return region
+        raise ValueError("the region does not lie in a buffer made by allocate()")
+
