@@ -255,7 +255,8 @@ def cpu_baselines(threads: int):
 
 def layer_extra(backend, args, torch, dist, rank, world, device, peak, failures):
     """Llama-style decoder layer forward (batch 8 x seq 2048), tensor-parallel over the ranks: heads and FFN columns are
-    sharded, the two partial sums are NCCL all-reduces. Strong scaling: total work is fixed as the world grows."""
+    sharded, the two partial sums are done by the NVSwitch through the library's multimem kernel (torch.distributed's
+    all-reduce where the GPUs have no NVLink multicast). Strong scaling: total work is fixed as the world grows."""
     from vibe_compiler_b200.decoder_layer import LayerConfig, ShardedDecoderLayer, layer_flops, random_weights
     cfg = LayerConfig()
     weights = random_weights(cfg, seed=SEED)
@@ -294,14 +295,22 @@ def layer_extra(backend, args, torch, dist, rank, world, device, peak, failures)
         compute_ms, _ = timed_steps(lambda: layer.forward_fused(x, micro_batches=parts, reserved_sms=reserved), max(3, args.steps // 2), 2, torch, dist=dist)
         layer._all_reduce_enabled = True
         message = torch.empty(LAYER["batch"] * LAYER["seq"], cfg.d_model, dtype=torch.bfloat16, device=device)
-        reduce_ms, _ = timed_steps(lambda: dist.all_reduce(message), max(3, args.steps // 2), 2, torch, dist=dist)
         steps_half = max(3, args.steps // 2)
-        both = torch.tensor([compute_ms / steps_half, reduce_ms / steps_half], device=device)
+        reduce_ms, _ = timed_steps(lambda: dist.all_reduce(message), steps_half, 2, torch, dist=dist)
+        switch_ms = float("nan")
+        sums = layer.switch_sums(blocks=reserved)
+        if sums is not None:      # the same whole-partial-sum message through the switch kernel, inside the layer's workspace
+            region = layer._workspace[:message.numel() * 2].view(torch.bfloat16)
+            switch_ms, _ = timed_steps(lambda: sums(region), steps_half, 2, torch, dist=dist, check=backend.poll)
+        both = torch.tensor([compute_ms / steps_half, reduce_ms / steps_half, switch_ms / steps_half], device=device)
         dist.all_reduce(both, op=dist.ReduceOp.MAX)
-        breakdown = {"compute_only_ms": both[0].item(), "allreduce_128MiB_ms": both[1].item(), "allreduces_per_step": 2,
+        breakdown = {"compute_only_ms": both[0].item(), "nccl_allreduce_128MiB_ms": both[1].item(),
+                     "switch_sum_128MiB_ms": both[2].item() if sums is not None else None, "sums_per_step": 2,
                      "exposed_ms": ms - both[0].item(), "micro_batches": parts or layer.default_micro_batches(LAYER["batch"]), "reserved_sms": reserved}
         del message
-    return {"workload": f"decoder layer forward bf16 d4096 32/8 heads hd128 FFN14336, batch 8 x seq 2048, TP{world} (NCCL all-reduce after o-proj and down-proj)",
+    sum_kind = "one shard" if world == 1 else ("NVSwitch multimem kernel of the library" if layer.switch_sums(blocks=reserved) is not None else "NCCL all-reduce")
+    return {"workload": f"decoder layer forward bf16 d4096 32/8 heads hd128 FFN14336, batch 8 x seq 2048, TP{world} (sum over shards after o-proj and down-proj: {sum_kind})",
+            "sum_over_shards": sum_kind,
             "value": tflops, "unit": "TFLOP/s", "ms_per_step": ms, "scaling": "strong", "tokens_per_s": LAYER["batch"] * LAYER["seq"] / (ms * 1e-3),
             "kernels_per_step": 10, "collectives_per_step": 0 if world == 1 else 2,
             "breakdown": breakdown,
@@ -415,10 +424,8 @@ def main():
     if world > 1:
         import torch.distributed as dist_mod
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # The decoder layer leaves 16 to 24 SMs to the collectives that run beside its persistent kernels: keep NCCL within them.
+        # Where the decoder layer falls back to NCCL for its sums, NCCL has to fit in the SMs the persistent kernels leave free.
         os.environ.setdefault("NCCL_MAX_CTAS", "16")
-        # The decode exchange uses plain peer loads and stores only: no NVLink multicast binding for its buffers.
-        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         torch.cuda.set_device(local_rank)
         dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
         dist = dist_mod

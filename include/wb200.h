@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define WB200_ABI_VERSION 3
+#define WB200_ABI_VERSION 4
 #define WB200_MAX_RANK 8
 
 typedef struct wb200_backend wb200_backend;
@@ -308,9 +308,9 @@ wb200_status wb200_attention_fa(wb200_backend *backend, const wb200_attention_pa
  * finalized. replaces OnlineAttentionMaterialization.cpp:264-373 and the fold order of
  * lib/Wafer/Transforms/Linalg/SpatialRegionMaterialization.cpp:2420-2433. q_len must be 1.
  * The split-KV partial records of this entry and of wb200_attention_fd_partial / _exchange live in a grow-only scratch
- * buffer of the backend: a call that needs more than every call before it frees and reallocates that buffer (after the
- * work enqueued on it earlier, in stream order of the legacy default stream), so a CUDA graph that captured an earlier
- * decode call replays with a dangling address. Capture only after the largest shape has run once. */
+ * buffer of the backend: a call that needs more than every call before it frees and reallocates that buffer (cudaFree
+ * waits for the device's outstanding work first), so a CUDA graph that captured an earlier decode call would replay
+ * with a dangling address. Run the largest shape once before capturing. */
 wb200_status wb200_attention_fd(wb200_backend *backend, const wb200_attention_params *params,
                                 uint32_t kv_splits);
 
@@ -441,9 +441,19 @@ typedef struct wb200_decoder_layer_params {
   wb200_allreduce_fn allreduce;
   void *allreduce_user;
   void *stream;
+  const struct wb200_switch_sum_params *switch_sum; /* optional, instead of `allreduce`: the sums are done by the library's
+                                  NVSwitch kernel (wb200_switch_sum, below) without leaving the call. `multicast` is the
+                                  multicast address of `workspace`, which must then be a symmetric allocation bound to a
+                                  multicast object; rank, world, signals and epoch as for wb200_switch_sum; blocks 0 means
+                                  reserved_sms; elements, format and stream are ignored */
 } wb200_decoder_layer_params;
 uint64_t wb200_decoder_layer_workspace_bytes(const wb200_decoder_layer_params *params);
 wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_layer_params *params);
+/* Device timeline of the last wb200_decoder_layer call that ran with micro_batches > 1 (waits for that call to finish):
+ * milliseconds from the call's first kernel to, for part i and phase f (0 attention, 1 FFN), ms[4 i + 2 f] = the part's
+ * partial sum is ready (its kernels are done) and ms[4 i + 2 f + 1] = the sum over shards is done; ms[4 parts] = the
+ * layer's last kernel is done. *count = 4 parts + 1 (0 if there was no such call); ms may be null to ask for the count. */
+wb200_status wb200_decoder_layer_timeline(wb200_backend *backend, float *ms, uint32_t capacity, uint32_t *count);
 
 /* Sum over the shards of a tensor-parallel region (the `allreduce` of wb200_decoder_layer, or any buffer) as one kernel
  * per GPU that lets the NVSwitch add and broadcast: the reference's Tile collectives realise such a sum as reduce-scatter

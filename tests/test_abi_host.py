@@ -25,7 +25,7 @@ def test_library_exports_every_declared_symbol():
     for name in names:
         assert hasattr(lib, name), f"{name} is declared in include/wb200.h but not exported"
         assert name in abi.SIGNATURES, f"{name} has no ctypes signature"
-    assert lib.wb200_abi_version() == 3
+    assert lib.wb200_abi_version() == 4
 
 
 def test_struct_layouts_match_the_header():

@@ -117,6 +117,12 @@ class GemmEpilogueParams(C.Structure):
 ALLREDUCE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p)
 
 
+class SwitchSumParams(C.Structure):
+    _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("multicast", C.c_void_p), ("elements", C.c_uint64),
+                ("format", C.c_uint32), ("blocks", C.c_uint32), ("signals", C.c_void_p * 16), ("epoch", C.c_void_p),
+                ("stream", C.c_void_p)]
+
+
 class DecoderLayerParams(C.Structure):
     _fields_ = [("batch", C.c_uint32), ("seq", C.c_uint32), ("d_model", C.c_uint32), ("head_dim", C.c_uint32),
                 ("q_heads", C.c_uint32), ("kv_heads", C.c_uint32), ("ffn", C.c_uint32), ("format", C.c_uint32),
@@ -124,17 +130,12 @@ class DecoderLayerParams(C.Structure):
                 ("x", C.c_void_p), ("out", C.c_void_p),
                 ("norm1", C.c_void_p), ("wqkv", C.c_void_p), ("wo", C.c_void_p), ("norm2", C.c_void_p), ("wgu", C.c_void_p), ("wdown", C.c_void_p),
                 ("workspace", C.c_void_p), ("workspace_bytes", C.c_uint64),
-                ("allreduce", ALLREDUCE_FN), ("allreduce_user", C.c_void_p), ("stream", C.c_void_p)]
+                ("allreduce", ALLREDUCE_FN), ("allreduce_user", C.c_void_p), ("stream", C.c_void_p),
+                ("switch_sum", C.POINTER(SwitchSumParams))]
 
 
 class FdExchange(C.Structure):
     _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("peer_buffers", C.c_void_p * 16), ("epoch", C.c_void_p)]
-
-
-class SwitchSumParams(C.Structure):
-    _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("multicast", C.c_void_p), ("elements", C.c_uint64),
-                ("format", C.c_uint32), ("blocks", C.c_uint32), ("signals", C.c_void_p * 16), ("epoch", C.c_void_p),
-                ("stream", C.c_void_p)]
 
 
 class ProgramStats(C.Structure):
@@ -197,6 +198,7 @@ SIGNATURES = {
     "wb200_switch_sum": (C.c_int, [C.c_void_p, C.POINTER(SwitchSumParams)]),
     "wb200_decoder_layer_workspace_bytes": (C.c_uint64, [C.POINTER(DecoderLayerParams)]),
     "wb200_decoder_layer": (C.c_int, [C.c_void_p, C.POINTER(DecoderLayerParams)]),
+    "wb200_decoder_layer_timeline": (C.c_int, [C.c_void_p, C.POINTER(C.c_float), C.c_uint32, C.POINTER(C.c_uint32)]),
     "wb200_target_call_rdma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, _U32x3, _U32x3]),
     "wb200_target_call_wdma": (C.c_int, [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, _U32x3, _U32x3]),
     "wb200_target_call_gather_scatter": (C.c_int, [C.c_void_p, C.c_uint64, C.c_uint64, C.c_uint32, C.c_uint32, _U32x3, _U32x3, _U32x3, _U32x3]),

@@ -381,6 +381,19 @@ class B200TargetModelBackend:
         self._check(self._lib.wb200_attention_fd_exchange(self._handle, C.byref(p), kv_splits, C.byref(x)))
         return out
 
+    def decoder_layer_timeline(self):
+        """Device timeline of the last micro-batched decoder_layer call: a dict with, per part, the milliseconds (from the
+        call's first kernel) at which each phase's partial sum was ready and its sum over shards was done, and `end`."""
+        count = C.c_uint32(0)
+        self._check(self._lib.wb200_decoder_layer_timeline(self._handle, None, 0, C.byref(count)))
+        if count.value == 0:
+            return None
+        ms = (C.c_float * count.value)()
+        self._check(self._lib.wb200_decoder_layer_timeline(self._handle, ms, count.value, C.byref(count)))
+        parts = (count.value - 1) // 4
+        return {"parts": [{"attention_ready": ms[4 * i], "attention_sum_done": ms[4 * i + 1], "ffn_ready": ms[4 * i + 2],
+                           "ffn_sum_done": ms[4 * i + 3]} for i in range(parts)], "end": ms[4 * parts]}
+
     def switch_sum_signal_bytes(self, world: int) -> int:
         return int(self._lib.wb200_switch_sum_signal_bytes(world))
 
@@ -478,18 +491,21 @@ class B200TargetModelBackend:
 
     def decoder_layer(self, x, *, norm1, wqkv, wo, norm2, wgu, wdown, q_heads: int, kv_heads: int, head_dim: int, eps: float,
                       rope_theta: float, position_offset: int = 0, allreduce=None, workspace=None, out=None,
-                      micro_batches: int = 1, reserved_sms: int = 0, stream: Optional[int] = None, workspace_factory=None):
+                      micro_batches: int = 1, reserved_sms: int = 0, stream: Optional[int] = None, workspace_factory=None,
+                      switch_sum=None):
         """One shard of a Llama-style decoder layer forward through the single C-ABI call wb200_decoder_layer.
         x: [batch, seq, d_model] CUDA tensor. `allreduce(tensor)` must enqueue an in-place sum over the shards
         (torch.distributed.all_reduce); `workspace` is a uint8 CUDA tensor that is reused if large enough, else
-        `workspace_factory(bytes)` (default: torch.empty) makes one. Returns (out, workspace)."""
+        `workspace_factory(bytes)` (default: torch.empty) makes one. `switch_sum` (a sharding.SwitchSum whose allocate() is
+        the workspace factory) instead of `allreduce`: the sums are done by the library's NVSwitch kernel inside the call.
+        Returns (out, workspace)."""
         batch, seq, d_model = x.shape
         p = abi.DecoderLayerParams()
         p.batch, p.seq, p.d_model, p.head_dim = batch, seq, d_model, head_dim
         p.q_heads, p.kv_heads, p.ffn = q_heads, kv_heads, wdown.shape[0]
         p.format = _TORCH_FORMATS[x.dtype]
         p.eps, p.rope_theta, p.position_offset = eps, rope_theta, position_offset
-        p.micro_batches = micro_batches if allreduce is not None else 1
+        p.micro_batches = micro_batches if (allreduce is not None or switch_sum is not None) else 1
         p.reserved_sms = reserved_sms
         needed = self._lib.wb200_decoder_layer_workspace_bytes(C.byref(p))
         if needed == 0:
@@ -523,6 +539,15 @@ class B200TargetModelBackend:
                 return 1
         callback = abi.ALLREDUCE_FN(reduce_callback) if allreduce is not None else abi.ALLREDUCE_FN()
         p.allreduce = callback
+        if switch_sum is not None:
+            native = abi.SwitchSumParams()
+            native.rank, native.world = switch_sum.rank, switch_sum.world
+            native.multicast = switch_sum.multicast_of(workspace)
+            native.blocks = switch_sum.blocks
+            for r, pointer in enumerate(switch_sum.signal_pointers):
+                native.signals[r] = pointer
+            native.epoch = switch_sum.epoch.data_ptr()
+            p.switch_sum = C.pointer(native)
         status = self._lib.wb200_decoder_layer(self._handle, C.byref(p))
         if failure:
             raise failure[0]

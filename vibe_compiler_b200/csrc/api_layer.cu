@@ -69,14 +69,25 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
   // travels over NVLink while the kernels of parts i + 1 ... compute. The compute kernels are persistent (one CTA per
   // SM); `reserved_sms` of the SMs are left to the collective's kernels, which could otherwise not start before a
   // compute kernel ends, or would hold back that kernel's CTAs.
-  const uint32_t parts = (p->micro_batches > 1 && p->allreduce) ? p->micro_batches : 1;
+  const wb200_switch_sum_params *switch_sum = p->switch_sum;
+  if (switch_sum) {
+    if (!switch_sum->multicast || !switch_sum->epoch || switch_sum->world < 2 || switch_sum->world > WB200_MAX_EXCHANGE_RANKS ||
+        switch_sum->rank >= switch_sum->world)
+      return fail(WB200_ERR_INVALID_ARGUMENT, "switch_sum needs the workspace's multicast address, epoch words and 2 to 16 ranks");
+    for (uint32_t r = 0; r < switch_sum->world; ++r)
+      if (!switch_sum->signals[r]) return fail(WB200_ERR_INVALID_ARGUMENT, "switch_sum needs every rank's signal words");
+  }
+  const bool has_sum = p->allreduce || switch_sum;
+  const uint32_t parts = (p->micro_batches > 1 && has_sum) ? p->micro_batches : 1;
   if (parts > 1 && (p->batch % parts != 0 || ((static_cast<uint64_t>(p->batch / parts) * p->seq) % 8) != 0))
     return fail(WB200_ERR_INVALID_ARGUMENT, "micro_batches must divide the batch into parts of a multiple of 8 tokens");
   if (parts > 64) return fail(WB200_ERR_INVALID_ARGUMENT, "at most 64 micro-batches");
   DeviceGuard guard(backend->device);
   cudaStream_t user_stream = static_cast<cudaStream_t>(p->stream);
   if (parts > 1 && (st = backend->auxiliary_streams()) != WB200_OK) return st;
-  if (parts > 1 && (st = backend->pipeline_events(4 * parts)) != WB200_OK) return st;
+  if (parts > 1 && (st = backend->pipeline_events(4 * parts + 2)) != WB200_OK) return st;
+  backend->layer_timeline_parts = 0;
+  if (parts > 1) WB200_CUDA_CHECK(cudaEventRecord(backend->pipeline_event[4 * parts], user_stream));   // timeline origin
   cudaStream_t comm_stream = parts > 1 ? backend->aux_stream[0] : user_stream;
   int compute_sms = backend->sm_count;
   if (parts > 1 && p->reserved_sms > 0 && static_cast<int>(p->reserved_sms) < backend->sm_count / 2)
@@ -128,19 +139,29 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
   // The sum over shards of a part's partial output: ordered after the part's kernels by an event, enqueued on the
   // communication stream; `done` is recorded behind it for the kernels that consume the sum.
   auto reduce = [&](const Part &part, int phase) -> wb200_status {
-    if (!p->allreduce) return WB200_OK;
+    if (!has_sum) return WB200_OK;
     if (parts > 1) {
       cudaEvent_t ready = backend->pipeline_event[4 * part.index + 2 * phase];
       WB200_CUDA_CHECK(cudaEventRecord(ready, part.stream));
       WB200_CUDA_CHECK(cudaStreamWaitEvent(comm_stream, ready, 0));
     }
-    if (p->allreduce(p->allreduce_user, part.partial, static_cast<uint64_t>(tokens) * d, p->format, comm_stream) != 0)
+    if (switch_sum) {
+      // the library's own sum: the switch adds and broadcasts the part's region of the (symmetric) workspace
+      uint8_t *multicast = static_cast<uint8_t *>(switch_sum->multicast) + (part.partial - static_cast<uint8_t *>(p->workspace));
+      const int blocks = switch_sum->blocks ? static_cast<int>(switch_sum->blocks) : (p->reserved_sms ? static_cast<int>(p->reserved_sms) : 32);
+      wb200_status s = launch_switch_sum(multicast, static_cast<uint64_t>(tokens) * d, p->format, static_cast<int>(switch_sum->rank),
+                                         static_cast<int>(switch_sum->world), switch_sum->signals, switch_sum->epoch, blocks,
+                                         backend->d_status, comm_stream);
+      if (s != WB200_OK) return s;
+      backend->launches += 1;
+    } else if (p->allreduce(p->allreduce_user, part.partial, static_cast<uint64_t>(tokens) * d, p->format, comm_stream) != 0) {
       return fail(WB200_ERR_CALLBACK, "the all-reduce callback reported a failure");
+    }
     if (parts > 1) WB200_CUDA_CHECK(cudaEventRecord(backend->pipeline_event[4 * part.index + 2 * phase + 1], comm_stream));
     return WB200_OK;
   };
   auto await_sum = [&](const Part &part, int phase) -> wb200_status {
-    if (parts > 1 && p->allreduce)
+    if (parts > 1 && has_sum)
       WB200_CUDA_CHECK(cudaStreamWaitEvent(part.stream, backend->pipeline_event[4 * part.index + 2 * phase + 1], 0));
     return WB200_OK;
   };
@@ -194,12 +215,30 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
     if ((st = attention_phase(part_of(i))) != WB200_OK) break;
   for (uint32_t i = 0; st == WB200_OK && i < parts; ++i) st = ffn_phase(part_of(i));
   for (uint32_t i = 0; st == WB200_OK && i < parts; ++i) st = final_residual(part_of(i));
+  if (st == WB200_OK && parts > 1) {
+    cudaEventRecord(backend->pipeline_event[4 * parts + 1], user_stream);   // timeline end
+    backend->layer_timeline_parts = parts;
+  }
   if (st != WB200_OK && parts > 1) {
     // join: later work on the caller's stream must not overtake a collective that is still running on the other stream
     cudaEventRecord(backend->aux_event[0], comm_stream);
     cudaStreamWaitEvent(user_stream, backend->aux_event[0], 0);
   }
   return st;
+}
+
+wb200_status wb200_decoder_layer_timeline(wb200_backend *backend, float *ms, uint32_t capacity, uint32_t *count) {
+  if (!backend || !count) return fail(WB200_ERR_INVALID_ARGUMENT, "null argument");
+  const uint32_t parts = backend->layer_timeline_parts;
+  *count = parts ? 4 * parts + 1 : 0;
+  if (parts == 0 || !ms) return WB200_OK;
+  if (capacity < *count) return fail(WB200_ERR_LIMIT, "timeline buffer too small");
+  DeviceGuard guard(backend->device);
+  cudaEvent_t origin = backend->pipeline_event[4 * parts];
+  WB200_CUDA_CHECK(cudaEventSynchronize(backend->pipeline_event[4 * parts + 1]));
+  for (uint32_t i = 0; i < 4 * parts; ++i) WB200_CUDA_CHECK(cudaEventElapsedTime(&ms[i], origin, backend->pipeline_event[i]));
+  WB200_CUDA_CHECK(cudaEventElapsedTime(&ms[4 * parts], origin, backend->pipeline_event[4 * parts + 1]));
+  return WB200_OK;
 }
 
 }  // extern "C"

@@ -764,11 +764,26 @@ wb200_status launch_attention_fa_umma(const AttentionArgs &a, int sm_count, int 
     if (st != WB200_OK) return st;
     if (p.plan) grid = sm_count;
   }
+  // The persistent grid is launched as clusters of two CTAs. The kernel makes no use of the cluster; the point is the
+  // placement: a pair takes both SMs of a TPC, so the SMs a persistent grid leaves free are whole TPCs, where the CTA
+  // pairs of a kernel that runs beside it (the sum over shards of a decoder layer, whose neighbours are CTA-pair GEMMs)
+  // still fit. With single CTAs the free SMs are scattered and such pairs wait for the whole grid to end.
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(kFaThreads);
+  config.dynamicSmemBytes = FaSmem::kBytes;
+  config.stream = stream;
+  cudaLaunchAttribute cluster;
+  cluster.id = cudaLaunchAttributeClusterDimension;
+  cluster.val.clusterDim.x = 2; cluster.val.clusterDim.y = 1; cluster.val.clusterDim.z = 1;
+  if (p.plan && grid % 2 == 0) {
+    config.attrs = &cluster;
+    config.numAttrs = 1;
+  }
   if (a.format == WB200_BF16)
-    fa_umma_kernel<true><<<grid, kFaThreads, FaSmem::kBytes, stream>>>(tq, tk, tv, p);
+    WB200_CUDA_CHECK(cudaLaunchKernelEx(&config, fa_umma_kernel<true>, tq, tk, tv, p));
   else
-    fa_umma_kernel<false><<<grid, kFaThreads, FaSmem::kBytes, stream>>>(tq, tk, tv, p);
-  WB200_CUDA_CHECK(cudaGetLastError());
+    WB200_CUDA_CHECK(cudaLaunchKernelEx(&config, fa_umma_kernel<false>, tq, tk, tv, p));
   return WB200_OK;
 }
 

@@ -44,17 +44,22 @@ struct wb200_backend {
     return static_cast<uint32_t>(ms * 1000.f + 0.5f);
   }
   std::vector<cudaEvent_t> pipeline_event;   // edges of host-buffer pipelines, grown on demand
+  uint32_t layer_timeline_parts = 0;         // parts of the last micro-batched decoder layer call (its events are still there)
   wb200_status pipeline_events(size_t count) {
     while (pipeline_event.size() < count) {
       cudaEvent_t event;
-      WB200_CUDA_CHECK(cudaEventCreateWithFlags(&event, cudaEventDisableTiming));
+      WB200_CUDA_CHECK(cudaEventCreate(&event));   // with timing: wb200_decoder_layer_timeline reads them
       pipeline_event.push_back(event);
     }
     return WB200_OK;
   }
   wb200_status auxiliary_streams() {
     if (aux_stream[0]) return WB200_OK;
-    for (int i = 0; i < 2; ++i) WB200_CUDA_CHECK(cudaStreamCreateWithFlags(&aux_stream[i], cudaStreamNonBlocking));
+    // highest priority: the blocks of a sum or a copy enqueued here are placed before the queued blocks of the compute
+    // kernels they run beside
+    int least = 0, greatest = 0;
+    WB200_CUDA_CHECK(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+    for (int i = 0; i < 2; ++i) WB200_CUDA_CHECK(cudaStreamCreateWithPriority(&aux_stream[i], cudaStreamNonBlocking, greatest));
     for (int i = 0; i < 3; ++i) WB200_CUDA_CHECK(cudaEventCreateWithFlags(&aux_event[i], cudaEventDisableTiming));
     return WB200_OK;
   }

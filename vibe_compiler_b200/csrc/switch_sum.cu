@@ -31,8 +31,13 @@ namespace wb200 {
 namespace {
 
 constexpr int kSwitchThreads = 512;
-constexpr int kSwitchUnroll = 4;            // 16-byte requests in flight per thread
+constexpr int kSwitchUnroll = 8;            // 16-byte requests in flight per thread
 constexpr long long kSwitchWaitCycles = 2000000000LL;
+// The kernel is launched as pairs of blocks (clusters of two) that each ask for more than half of an SM's shared memory:
+// a pair then takes both SMs of a TPC and nothing else shares them. Beside persistent compute kernels that are launched
+// as CTA pairs themselves and leave whole TPCs free, the sum neither waits for an SM nor breaks up a TPC that a compute
+// pair needs (a pair that finds no whole TPC waits for the end of the kernel's first wave).
+constexpr int kSwitchSmemBytes = 120 * 1024;
 
 struct SwitchSumParams {
   uint8_t *multicast;                        // multicast address of the buffer
@@ -82,7 +87,7 @@ __device__ __forceinline__ void switch_store(uint8_t *address, const uint4 &v) {
 }
 
 template <int kFormat>
-__global__ void __launch_bounds__(kSwitchThreads) switch_sum_kernel(const SwitchSumParams p) {
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSwitchThreads) switch_sum_kernel(const SwitchSumParams p) {
   const unsigned int epoch = *reinterpret_cast<volatile unsigned int *>(p.epoch);
   const unsigned int tag = epoch + 1u;
   unsigned int *own = p.signals[p.rank];
@@ -155,11 +160,19 @@ wb200_status launch_switch_sum(void *multicast, uint64_t elements, int format, i
   // No more blocks than the slice has rounds of work for.
   const uint64_t per_rank = (p.chunks + world - 1) / world;
   const uint64_t useful = (per_rank + kSwitchThreads * kSwitchUnroll - 1) / (kSwitchThreads * kSwitchUnroll);
-  if (blocks < 1) blocks = 1;
   if (static_cast<uint64_t>(blocks) > useful) blocks = static_cast<int>(useful);
-  if (format == WB200_BF16) switch_sum_kernel<WB200_BF16><<<blocks, kSwitchThreads, 0, stream>>>(p);
-  else if (format == WB200_F16) switch_sum_kernel<WB200_F16><<<blocks, kSwitchThreads, 0, stream>>>(p);
-  else switch_sum_kernel<WB200_F32><<<blocks, kSwitchThreads, 0, stream>>>(p);
+  blocks = blocks < 2 ? 2 : blocks - blocks % 2;      // whole pairs
+  static PerDeviceOnce attributes;
+  const wb200_status attribute_status = attributes.run([]() -> wb200_status {
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(switch_sum_kernel<WB200_BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSwitchSmemBytes));
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(switch_sum_kernel<WB200_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSwitchSmemBytes));
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(switch_sum_kernel<WB200_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSwitchSmemBytes));
+    return WB200_OK;
+  });
+  if (attribute_status != WB200_OK) return attribute_status;
+  if (format == WB200_BF16) switch_sum_kernel<WB200_BF16><<<blocks, kSwitchThreads, kSwitchSmemBytes, stream>>>(p);
+  else if (format == WB200_F16) switch_sum_kernel<WB200_F16><<<blocks, kSwitchThreads, kSwitchSmemBytes, stream>>>(p);
+  else switch_sum_kernel<WB200_F32><<<blocks, kSwitchThreads, kSwitchSmemBytes, stream>>>(p);
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }

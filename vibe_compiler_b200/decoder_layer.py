@@ -120,17 +120,20 @@ class ShardedDecoderLayer:
     def default_micro_batches(self, batch: int) -> int:
         """Parts the batch is cut into so that the sums of one part travel while the next computes. More parts hide more of
         the communication but shrink the per-part GEMMs, which costs more the narrower the shard (measured on 8 GPUs: the
-        kernels alone take 0.93 / 1.04 / 1.25 / 1.66 ms with 1 / 2 / 4 / 8 parts): 2 parts from 8 shards on, else 4."""
+        kernels alone take 0.93 / 1.05 / 1.3 ms with 1 / 2 / 4 parts): 2 parts."""
         if self.world == 1:
             return 1
-        for parts in ((2,) if self.world >= 8 else (4, 2)):
-            if batch % parts == 0:
-                return parts
-        return 1
+        return 2 if batch % 2 == 0 else 1
 
     def default_reserved_sms(self) -> int:
-        """SMs the persistent kernels leave to NCCL (measured best: 24 of 148 on 8 GPUs, 16 on 2)."""
-        return 0 if self.world == 1 else (24 if self.world >= 8 else 16)
+        """SMs the persistent kernels leave to the sums. The library's switch kernel moves a rank's slice (1 / world of the
+        buffer) at the link's rate from two or four SMs (measured: 4 SMs on 8 GPUs, 8 on 2 - fewer halve its rate, more
+        only take SMs from the GEMMs); NCCL wants more (measured best: 24 on 8 GPUs, 16 on 2)."""
+        if self.world == 1:
+            return 0
+        if self.switch_sums() is not None:
+            return 4 if self.world >= 8 else 8
+        return 24 if self.world >= 8 else 16
 
     def forward_fused(self, x: torch.Tensor, position_offset: int = 0, micro_batches: Optional[int] = None,
                       reserved_sms: Optional[int] = None) -> torch.Tensor:
@@ -139,15 +142,17 @@ class ShardedDecoderLayer:
         shards the batch is cut into `micro_batches` parts whose sums run on a second stream while the following parts
         compute; `reserved_sms` SMs stay free for the sum's kernel. The sums are done by the NVSwitch through the
         library's own kernel (switch_sums()) where the GPUs offer NVLink multicast, else by torch.distributed."""
-        reduce, factory = None, None
+        reduce, factory, native = None, None, None
         reserved = reserved_sms if reserved_sms is not None else self.default_reserved_sms()
         if self.world > 1:
             import torch.distributed as dist
             sums = self.switch_sums(blocks=reserved)
+            if sums is not None:
+                factory = sums.allocate
             if not getattr(self, "_all_reduce_enabled", True):   # timing aid: the layer's kernels without the sums (wrong values)
                 reduce = lambda t: None                # noqa: E731
             elif sums is not None:
-                reduce, factory = sums, sums.allocate
+                native = sums                          # the library launches its own sum kernel: no callback into Python
             else:
                 reduce = lambda t: dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)   # noqa: E731
         out, self._workspace = self.backend.decoder_layer(
@@ -155,7 +160,7 @@ class ShardedDecoderLayer:
             kv_heads=self.hkv, head_dim=self.cfg.head_dim, eps=self.cfg.eps, rope_theta=self.cfg.rope_theta,
             position_offset=position_offset, allreduce=reduce, workspace=getattr(self, "_workspace", None),
             micro_batches=(micro_batches if micro_batches is not None else self.default_micro_batches(x.shape[0])),
-            reserved_sms=reserved, workspace_factory=factory)
+            reserved_sms=reserved, workspace_factory=factory, switch_sum=native)
         return out
 
     def switch_sums(self, blocks: int = 0):

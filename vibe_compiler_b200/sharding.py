@@ -162,15 +162,19 @@ class SwitchSum:
         self._buffers.append((buffer, handle, multicast))
         return buffer
 
-    def __call__(self, region: torch.Tensor) -> torch.Tensor:
+    def multicast_of(self, region: torch.Tensor) -> int:
+        """The multicast address of a tensor that lies inside a buffer made by allocate()."""
         begin = region.data_ptr()
         for buffer, _handle, multicast in self._buffers:
             offset = begin - buffer.data_ptr()
             if 0 <= offset and offset + region.numel() * region.element_size() <= buffer.numel():
-                if not region.is_contiguous():
-                    raise ValueError("the region must be contiguous")
-                self.backend.switch_sum(multicast + offset, region.numel(), region.dtype, rank=self.rank,
-                                        signal_pointers=self.signal_pointers, epoch=self.epoch, blocks=self.blocks)
-                return region
+                return multicast + offset
         raise ValueError("the region does not lie in a buffer made by allocate()")
+
+    def __call__(self, region: torch.Tensor) -> torch.Tensor:
+        if not region.is_contiguous():
+            raise ValueError("the region must be contiguous")
+        self.backend.switch_sum(self.multicast_of(region), region.numel(), region.dtype, rank=self.rank,
+                                signal_pointers=self.signal_pointers, epoch=self.epoch, blocks=self.blocks)
+        return region
 
