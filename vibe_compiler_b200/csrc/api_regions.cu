@@ -252,9 +252,15 @@ wb200_status wb200_attention_fd_exchange(wb200_backend *backend, const wb200_att
   const uint32_t splits = kv_splits ? kv_splits : fd_choose_splits(a, backend->sm_count);
   void *partials;
   if ((st = backend->buffer(7, fd_partial_floats(a, splits) * sizeof(float), &partials)) != WB200_OK) return st;
+  // One launch: the last stage-1 CTA of every (batch, kv head) folds, exchanges and merges. WB200_FD_EXCHANGE_FUSED=0 in
+  // the environment keeps the tail as a second launch.
+  static const bool fused = []() { const char *env = getenv("WB200_FD_EXCHANGE_FUSED"); return !(env && env[0] == '0'); }();
+  void *arrivals = nullptr;
+  if (fused && (st = backend->zeroed_buffer(11, static_cast<size_t>(a.batch) * a.kv_heads * sizeof(unsigned int), &arrivals)) != WB200_OK) return st;
   st = launch_attention_fd_exchange(a, splits, static_cast<float *>(partials), static_cast<int>(x->rank), static_cast<int>(x->world),
-                                    x->peer_buffers, x->epoch, backend->d_status, static_cast<cudaStream_t>(p->stream));
-  if (st == WB200_OK) backend->launches += 2;
+                                    x->peer_buffers, x->epoch, static_cast<unsigned int *>(arrivals), backend->d_status,
+                                    static_cast<cudaStream_t>(p->stream));
+  if (st == WB200_OK) backend->launches += fused ? 1 : 2;
   return st;
 }
 

@@ -88,13 +88,29 @@ struct FdParams {
   float *partials;    // [batch, q_heads, splits, kRecord]
 };
 
+// Tail of the sequence-sharded decode step, run by the last CTA of a (batch, kv head) to finish stage 1 (see
+// fd_exchange_rows): the exchange buffers of all ranks and this rank's epoch words.
+constexpr int kMaxExchangeRanks = 16;
+struct FdTailParams {
+  int rank, world;
+  float *peer[kMaxExchangeRanks];    // exchange buffers of all ranks, [rank] = this rank's own
+  unsigned int *epoch;               // this rank's {epoch, finished rows}, zero-initialised
+  unsigned int *arrivals;            // [batch * kv_heads] finished stage-1 CTAs, zero-initialised, reset by the last one
+  int out_format, zero_fully_masked;
+  void *out;
+  float *lse, *row_max, *row_sum;
+  int *status;
+};
+template <int kRowsAtOnce>
+__device__ void fd_exchange_rows(const FdTailParams &x, const float *records, int splits, int first_row, int row_count, int rows_total);
+
 // Swizzled byte offset of 16-byte chunk `c` of row `r` inside a 16 x 256-byte tile.
 __device__ __forceinline__ uint32_t tile_offset(int r, int c) {
   return static_cast<uint32_t>(r * 256 + ((c ^ (r & 7)) << 4));
 }
 
-template <bool kBf16>
-__global__ void __launch_bounds__(kWarps * 32, 2) fd_partial_kernel(const FdParams p) {
+template <bool kBf16, bool kTail>
+__global__ void __launch_bounds__(kWarps * 32, 2) fd_partial_kernel(const FdParams p, const FdTailParams tail) {
   extern __shared__ __align__(128) uint8_t smem[];
   const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -287,6 +303,24 @@ __global__ void __launch_bounds__(kWarps * 32, 2) fd_partial_kernel(const FdPara
       out[kD + 1] = l;
     }
   }
+  if constexpr (kTail) {
+    // The CTA that finishes last among the splits of this (batch, kv head) folds the splits of the group's query heads,
+    // exchanges the states with the other ranks and writes the outputs: the decode step is this one launch.
+    __shared__ bool last_of_head;
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      unsigned int *arrivals = tail.arrivals + b * p.kv_heads + hk;
+      last_of_head = atomicAdd(arrivals, 1u) == static_cast<unsigned int>(p.splits) - 1u;
+      if (last_of_head) *arrivals = 0u;     // ready for the next launch
+    }
+    __syncthreads();
+    if (last_of_head) {
+      __threadfence();
+      const int first_row = b * p.q_heads + hk * p.group;
+      fd_exchange_rows<kD / 32>(tail, p.partials, p.splits, first_row, p.group, p.batch * p.q_heads);
+    }
+  }
 }
 
 struct FdCombineParams {
@@ -350,14 +384,6 @@ __global__ void __launch_bounds__(kD) fd_combine_kernel(const FdCombineParams p)
 // states in ascending rank order - the shard order of the reference's spatial flash-decoding fold
 // (lib/Wafer/Transforms/Linalg/SpatialRegionMaterialization.cpp:2420-2433). A rank can run at most one epoch ahead of
 // another (its next exchange cannot complete before the other has entered it), so two parities suffice.
-constexpr int kMaxExchangeRanks = 16;
-struct FdExchangeParams {
-  FdCombineParams fold;              // this rank's split records and the outputs
-  int rank, world;
-  float *peer[kMaxExchangeRanks];    // exchange buffers of all ranks, [rank] = this rank's own
-  unsigned int *epoch;               // this rank's {epoch, finished CTAs}, zero-initialised
-  int *status;
-};
 __device__ __forceinline__ void st_relaxed_sys(unsigned int *address, unsigned int value) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(address), "r"(value) : "memory");
 }
@@ -367,90 +393,143 @@ __device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int *addre
   return value;
 }
 
-__global__ void __launch_bounds__(kD) fd_exchange_kernel(const FdExchangeParams p) {
-  const int row = blockIdx.x, d = threadIdx.x, rows = p.fold.rows;
-  // fold this rank's splits in ascending order
-  const float *rec = p.fold.records_ptr + row * p.fold.row_stride;
-  float m = rec[kD], l = rec[kD + 1], a = rec[d];
-  for (int i = 1; i < p.fold.records; ++i) {
-    const float *right = rec + i * p.fold.record_stride;
-    const float m_right = right[kD], l_right = right[kD + 1], a_right = right[d];
-    const float m_new = fmaxf(m, m_right);
-    const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;
-    const float scale_left = exp_lp(m - m_exp), scale_right = exp_lp(m_right - m_exp);
-    l = l * scale_left + l_right * scale_right;
-    a = a * scale_left + a_right * scale_right;
-    m = m_new;
-  }
-  const unsigned int epoch = *reinterpret_cast<volatile unsigned int *>(p.epoch);
+// Rows [first_row, first_row + row_count) of the (batch, query head) rows, by one CTA of kD threads = four warps: a warp
+// takes a row, a lane four consecutive head dimensions. Per batch of four rows: fold of the rows' split records in
+// ascending order, stores of the states into every rank's buffer, flags, bounded wait for the world's flags, merge in
+// ascending rank order, outputs. The rows of a batch travel together, so the NVLink round trip is paid once per batch.
+__device__ __forceinline__ void fd_merge_right(float &m, float &l, float4 &a, float m_right, float l_right, const float4 &a_right) {
+  const float m_new = fmaxf(m, m_right);
+  const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;
+  const float scale_left = exp_lp(m - m_exp), scale_right = exp_lp(m_right - m_exp);
+  l = l * scale_left + l_right * scale_right;
+  a.x = a.x * scale_left + a_right.x * scale_right;
+  a.y = a.y * scale_left + a_right.y * scale_right;
+  a.z = a.z * scale_left + a_right.z * scale_right;
+  a.w = a.w * scale_left + a_right.w * scale_right;
+  m = m_new;
+}
+// Four consecutive floats of a record (records are 130 floats long: 8-byte, not 16-byte, aligned), read past L1.
+__device__ __forceinline__ float4 ldcg_quad(const float *address) {
+  const float2 lo = __ldcg(reinterpret_cast<const float2 *>(address)), hi = __ldcg(reinterpret_cast<const float2 *>(address + 2));
+  return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+template <int kRowsAtOnce>
+__device__ void fd_exchange_rows(const FdTailParams &x, const float *records, int splits, int first_row, int row_count, int rows_total) {
+  static_assert(kRowsAtOnce == kD / 32, "one warp per row");
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int *>(x.epoch);
   const unsigned int parity = epoch & 1u, tag = epoch + 1u;
-  const size_t state_floats = static_cast<size_t>(2) * p.world * rows * kRecord;
-  const size_t my_slot = (static_cast<size_t>(parity) * p.world + p.rank) * rows + row;
-  for (int r = 0; r < p.world; ++r) {
-    float *dst = p.peer[r] + my_slot * kRecord;
-    dst[d] = a;
-    if (d == 0) {
-      dst[kD] = m;
-      dst[kD + 1] = l;
+  const size_t state_floats = static_cast<size_t>(2) * x.world * rows_total * kRecord;
+  float *own = x.peer[x.rank];
+  for (int base = 0; base < row_count; base += kRowsAtOnce) {
+    const int count = row_count - base < kRowsAtOnce ? row_count - base : kRowsAtOnce;
+    const int row = first_row + base + warp;
+    const bool active = warp < count;
+    if (active) {
+      // fold this rank's splits (records of other CTAs: read past L1), four records in flight
+      const float *rec = records + static_cast<size_t>(row) * splits * kRecord;
+      float m = __ldcg(rec + kD), l = __ldcg(rec + kD + 1);
+      float4 a = ldcg_quad(rec + 4 * lane);
+      int s = 1;
+      for (; s + 4 <= splits; s += 4) {
+        float mr[4], lr[4];
+        float4 ar[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float *right = rec + static_cast<size_t>(s + u) * kRecord;
+          mr[u] = __ldcg(right + kD); lr[u] = __ldcg(right + kD + 1);
+          ar[u] = ldcg_quad(right + 4 * lane);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) fd_merge_right(m, l, a, mr[u], lr[u], ar[u]);
+      }
+      for (; s < splits; ++s) {
+        const float *right = rec + static_cast<size_t>(s) * kRecord;
+        const float4 ar = ldcg_quad(right + 4 * lane);
+        fd_merge_right(m, l, a, __ldcg(right + kD), __ldcg(right + kD + 1), ar);
+      }
+      // the state into slot [parity][rank][row] of every rank's buffer (records are 130 floats: 8-byte aligned rows)
+      const size_t my_slot = (static_cast<size_t>(parity) * x.world + x.rank) * rows_total + row;
+      for (int r = 0; r < x.world; ++r) {
+        float *dst = x.peer[r] + my_slot * kRecord;
+        *reinterpret_cast<float2 *>(dst + 4 * lane) = make_float2(a.x, a.y);
+        *reinterpret_cast<float2 *>(dst + 4 * lane + 2) = make_float2(a.z, a.w);
+        if (lane == 0) *reinterpret_cast<float2 *>(dst + kD) = make_float2(m, l);
+      }
     }
-  }
-  __syncthreads();   // the whole row is written before it is published
-  // One thread per peer: a system-scope fence (cumulative over the row's stores, which the barrier ordered before it)
-  // and then the flag. The fences of the peers run side by side; a single thread publishing to every peer in turn would
-  // pay one NVLink round trip per peer.
-  if (d < p.world) {
-    __threadfence_system();
-    st_relaxed_sys(reinterpret_cast<unsigned int *>(p.peer[d] + state_floats) + my_slot, tag);
-  }
-  // bounded wait for every rank's row
-  float *own = p.peer[p.rank];
-  if (d < p.world) {
-    const unsigned int *flag = reinterpret_cast<const unsigned int *>(own + state_floats) + (static_cast<size_t>(parity) * p.world + d) * rows + row;
-    const long long start = clock64();
-    unsigned int polls = 0;
-    while (ld_acquire_sys(flag) != tag) {
-      if ((++polls & 63u) == 0u && clock64() - start > 2000000000LL) {   // about a second: give up, report, carry on
-        atomicExch(p.status, 2);
-        break;
+    __syncthreads();   // the rows are written before they are published
+    // One thread per (row, peer): a system-scope fence (cumulative over the rows' stores, which the barrier ordered
+    // before it) and then the flag; the fences of the peers run side by side. Then the bounded wait for every rank's
+    // flag of every row, again one thread per (row, rank).
+    for (int j = tid; j < count * x.world; j += kD) {
+      const int flag_row = first_row + base + j / x.world, peer = j % x.world;
+      const size_t my_slot = (static_cast<size_t>(parity) * x.world + x.rank) * rows_total + flag_row;
+      __threadfence_system();
+      st_relaxed_sys(reinterpret_cast<unsigned int *>(x.peer[peer] + state_floats) + my_slot, tag);
+    }
+    for (int j = tid; j < count * x.world; j += kD) {
+      const int flag_row = first_row + base + j / x.world, source = j % x.world;
+      const unsigned int *flag = reinterpret_cast<const unsigned int *>(own + state_floats) + (static_cast<size_t>(parity) * x.world + source) * rows_total + flag_row;
+      const long long start = clock64();
+      unsigned int polls = 0;
+      while (ld_acquire_sys(flag) != tag) {
+        if ((++polls & 63u) == 0u && clock64() - start > 2000000000LL) {   // about a second: give up, report, carry on
+          atomicExch(x.status, 2);
+          break;
+        }
+      }
+    }
+    __syncthreads();
+    if (active) {
+      // merge the world's states in ascending shard order (L1 is bypassed: peers wrote these lines)
+      auto load_state = [&](int r, float &m, float &l, float4 &a) {
+        const float *state = own + ((static_cast<size_t>(parity) * x.world + r) * rows_total + row) * kRecord;
+        const float2 ml = __ldcg(reinterpret_cast<const float2 *>(state + kD));
+        a = ldcg_quad(state + 4 * lane);
+        m = ml.x; l = ml.y;
+      };
+      float m, l;
+      float4 a;
+      load_state(0, m, l, a);
+      for (int r = 1; r < x.world; ++r) {
+        float m_right, l_right;
+        float4 a_right;
+        load_state(r, m_right, l_right, a_right);
+        fd_merge_right(m, l, a, m_right, l_right, a_right);
+      }
+      float coefficient = 1.0f / l;
+      if (x.zero_fully_masked && l == 0.f) coefficient = 0.f;
+      const float value[4] = {a.x * coefficient, a.y * coefficient, a.z * coefficient, a.w * coefficient};
+      if (x.out_format == WB200_F32) {
+        *(reinterpret_cast<float4 *>(x.out) + static_cast<size_t>(row) * (kD / 4) + lane) = make_float4(value[0], value[1], value[2], value[3]);
+      } else {
+        const uint32_t lo = narrow_bits(value[0], x.out_format) | (static_cast<uint32_t>(narrow_bits(value[1], x.out_format)) << 16);
+        const uint32_t hi = narrow_bits(value[2], x.out_format) | (static_cast<uint32_t>(narrow_bits(value[3], x.out_format)) << 16);
+        *(reinterpret_cast<uint2 *>(x.out) + static_cast<size_t>(row) * (kD / 4) + lane) = make_uint2(lo, hi);
+      }
+      if (lane == 0) {
+        if (x.lse) x.lse[row] = (l == 0.f) ? -INFINITY : m + logf(l);
+        if (x.row_max) x.row_max[row] = m;
+        if (x.row_sum) x.row_sum[row] = l;
       }
     }
   }
-  __syncthreads();
-  // merge the world's states in ascending shard order (L1 is bypassed: peers wrote these lines)
-  {
-    const float *first = own + (static_cast<size_t>(parity) * p.world * rows + row) * kRecord;
-    m = __ldcg(first + kD); l = __ldcg(first + kD + 1); a = __ldcg(first + d);
-    for (int r = 1; r < p.world; ++r) {
-      const float *right = own + ((static_cast<size_t>(parity) * p.world + r) * rows + row) * kRecord;
-      const float m_right = __ldcg(right + kD), l_right = __ldcg(right + kD + 1), a_right = __ldcg(right + d);
-      const float m_new = fmaxf(m, m_right);
-      const float m_exp = (m_new == -INFINITY) ? 0.f : m_new;
-      const float scale_left = exp_lp(m - m_exp), scale_right = exp_lp(m_right - m_exp);
-      l = l * scale_left + l_right * scale_right;
-      a = a * scale_left + a_right * scale_right;
-      m = m_new;
-    }
-  }
-  float coefficient = 1.0f / l;
-  if (p.fold.zero_fully_masked && l == 0.f) coefficient = 0.f;
-  const float value = a * coefficient;
-  if (p.fold.out_format == WB200_F32)
-    reinterpret_cast<float *>(p.fold.out)[static_cast<size_t>(row) * kD + d] = value;
-  else
-    reinterpret_cast<uint16_t *>(p.fold.out)[static_cast<size_t>(row) * kD + d] =
-        static_cast<uint16_t>(narrow_bits(value, p.fold.out_format));
-  if (d == 0) {
-    if (p.fold.lse) p.fold.lse[row] = (l == 0.f) ? -INFINITY : m + logf(l);
-    if (p.fold.row_max) p.fold.row_max[row] = m;
-    if (p.fold.row_sum) p.fold.row_sum[row] = l;
-    // the last CTA of the launch advances the epoch for the next call
+  // the CTA that completes the last rows of the launch advances the epoch for the next call
+  if (tid == 0) {
     __threadfence();
-    if (atomicAdd(p.epoch + 1, 1u) == static_cast<unsigned int>(rows) - 1u) {
-      p.epoch[1] = 0u;
+    if (atomicAdd(x.epoch + 1, static_cast<unsigned int>(row_count)) + row_count == static_cast<unsigned int>(rows_total)) {
+      x.epoch[1] = 0u;
       __threadfence();
-      *reinterpret_cast<volatile unsigned int *>(p.epoch) = epoch + 1u;
+      *reinterpret_cast<volatile unsigned int *>(x.epoch) = epoch + 1u;
     }
   }
+}
+
+// The same tail as a launch of its own (four rows per CTA), behind a stage 1 without it.
+__global__ void __launch_bounds__(kD) fd_exchange_kernel(const FdTailParams x, const float *records, int splits, int rows_total) {
+  const int first_row = blockIdx.x * (kD / 32);
+  const int row_count = rows_total - first_row < kD / 32 ? rows_total - first_row : kD / 32;
+  fd_exchange_rows<kD / 32>(x, records, splits, first_row, row_count, rows_total);
 }
 
 int visible_keys(const AttentionArgs &a) {
@@ -498,7 +577,8 @@ size_t fd_partial_floats(const AttentionArgs &a, uint32_t splits) {
 }
 
 namespace {
-wb200_status launch_fd_stage1(const AttentionArgs &a, uint32_t splits, float *partials, cudaStream_t stream);
+wb200_status launch_fd_stage1(const AttentionArgs &a, uint32_t splits, float *partials, cudaStream_t stream,
+                              const FdTailParams *tail = nullptr);
 }
 
 size_t fd_exchange_floats(int rows, int world) {
@@ -507,27 +587,28 @@ size_t fd_exchange_floats(int rows, int world) {
 }
 
 wb200_status launch_attention_fd_exchange(const AttentionArgs &a, uint32_t splits, float *partials, int rank, int world,
-                                          void *const *peer_buffers, unsigned int *epoch, int *device_status, cudaStream_t stream) {
+                                          void *const *peer_buffers, unsigned int *epoch, unsigned int *arrivals,
+                                          int *device_status, cudaStream_t stream) {
   if (world < 1 || world > kMaxExchangeRanks || rank < 0 || rank >= world)
     return fail(WB200_ERR_INVALID_ARGUMENT, "exchange takes 1 to 16 ranks and a rank inside the world");
-  wb200_status st = launch_fd_stage1(a, splits, partials, stream);
+  FdTailParams x;
+  x.rank = rank; x.world = world;
+  for (int r = 0; r < kMaxExchangeRanks; ++r) x.peer[r] = r < world ? static_cast<float *>(peer_buffers[r]) : nullptr;
+  x.epoch = epoch;
+  x.arrivals = arrivals;
+  x.out_format = a.format;
+  x.zero_fully_masked = a.zero_fully_masked;
+  x.out = a.out; x.lse = a.lse; x.row_max = a.row_max; x.row_sum = a.row_sum;
+  x.status = device_status;
+  // With arrival counters the tail runs inside stage 1 (its last CTA per (batch, kv head)): one launch per step.
+  // Without them it is a launch of its own behind stage 1.
+  wb200_status st = launch_fd_stage1(a, splits, partials, stream, arrivals ? &x : nullptr);
   if (st != WB200_OK) return st;
-  FdExchangeParams p;
-  p.fold.rows = a.batch * a.q_heads;
-  p.fold.records = static_cast<int>(splits);
-  p.fold.row_stride = static_cast<size_t>(splits) * kRecord;
-  p.fold.record_stride = kRecord;
-  p.fold.records_ptr = partials;
-  p.fold.out_format = a.format;
-  p.fold.zero_fully_masked = a.zero_fully_masked;
-  p.fold.finalize = 1;
-  p.fold.out = a.out; p.fold.lse = a.lse; p.fold.row_max = a.row_max; p.fold.row_sum = a.row_sum; p.fold.state_out = nullptr;
-  p.rank = rank; p.world = world;
-  for (int r = 0; r < kMaxExchangeRanks; ++r) p.peer[r] = r < world ? static_cast<float *>(peer_buffers[r]) : nullptr;
-  p.epoch = epoch;
-  p.status = device_status;
-  fd_exchange_kernel<<<p.fold.rows, kD, 0, stream>>>(p);
-  WB200_CUDA_CHECK(cudaGetLastError());
+  if (!arrivals) {
+    const int rows = a.batch * a.q_heads;
+    fd_exchange_kernel<<<(rows + kD / 32 - 1) / (kD / 32), kD, 0, stream>>>(x, partials, static_cast<int>(splits), rows);
+    WB200_CUDA_CHECK(cudaGetLastError());
+  }
   return WB200_OK;
 }
 
@@ -551,7 +632,7 @@ wb200_status launch_attention_fd(const AttentionArgs &a, uint32_t splits, float 
 }
 
 namespace {
-wb200_status launch_fd_stage1(const AttentionArgs &a, uint32_t splits, float *partials, cudaStream_t stream) {
+wb200_status launch_fd_stage1(const AttentionArgs &a, uint32_t splits, float *partials, cudaStream_t stream, const FdTailParams *tail) {
   if (!attention_fd_supports(a)) return fail(WB200_ERR_UNSUPPORTED, "flash-decoding request outside the kernel's domain");
   if (splits < 1) return fail(WB200_ERR_INVALID_ARGUMENT, "kv_splits must be positive");
   FdParams p;
@@ -572,16 +653,23 @@ wb200_status launch_fd_stage1(const AttentionArgs &a, uint32_t splits, float *pa
 
   static PerDeviceOnce attributes;
   const wb200_status attribute_status = attributes.run([]() -> wb200_status {
-    WB200_CUDA_CHECK(cudaFuncSetAttribute(fd_partial_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmemBytes));
-    WB200_CUDA_CHECK(cudaFuncSetAttribute(fd_partial_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmemBytes));
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(fd_partial_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmemBytes));
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(fd_partial_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmemBytes));
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(fd_partial_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmemBytes));
+    WB200_CUDA_CHECK(cudaFuncSetAttribute(fd_partial_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kFdSmemBytes));
     return WB200_OK;
   });
   if (attribute_status != WB200_OK) return attribute_status;
   dim3 grid(splits, a.kv_heads, a.batch);
-  if (a.format == WB200_BF16)
-    fd_partial_kernel<true><<<grid, kWarps * 32, kFdSmemBytes, stream>>>(p);
-  else
-    fd_partial_kernel<false><<<grid, kWarps * 32, kFdSmemBytes, stream>>>(p);
+  static_assert(kWarps * 32 == kD, "the tail of the sharded decode runs with one thread per head dimension");
+  const FdTailParams none{};
+  if (tail) {
+    if (a.format == WB200_BF16) fd_partial_kernel<true, true><<<grid, kWarps * 32, kFdSmemBytes, stream>>>(p, *tail);
+    else fd_partial_kernel<false, true><<<grid, kWarps * 32, kFdSmemBytes, stream>>>(p, *tail);
+  } else {
+    if (a.format == WB200_BF16) fd_partial_kernel<true, false><<<grid, kWarps * 32, kFdSmemBytes, stream>>>(p, none);
+    else fd_partial_kernel<false, false><<<grid, kWarps * 32, kFdSmemBytes, stream>>>(p, none);
+  }
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }

@@ -79,6 +79,14 @@ struct wb200_backend {
     *out = slot.ptr;
     return WB200_OK;
   }
+  // The same, zero-filled whenever it is (re)allocated: for counters that the kernels using them leave at zero.
+  wb200_status zeroed_buffer(size_t index, size_t bytes, void **out) {
+    const size_t before = slots.size() > index ? slots[index].bytes : 0;
+    wb200_status st = buffer(index, bytes, out);
+    if (st != WB200_OK) return st;
+    if (slots[index].bytes != before) WB200_CUDA_CHECK(cudaMemset(*out, 0, slots[index].bytes));
+    return WB200_OK;
+  }
 };
 
 // One flat device-resident memory image (a Tile's scratch-pad, or a DDR arena) addressed by the byte

@@ -165,10 +165,12 @@ wb200_status launch_attention_fd_merge(const AttentionArgs &args, const float *s
 // Sequence-sharded decode with the exchange inside the kernel: stage 1, then one kernel that folds this rank's splits,
 // writes the state into every rank's exchange buffer (peer-mapped memory), waits for the world's states and merges
 // them in ascending rank order. `peer_buffers` holds `world` buffers of fd_exchange_floats() floats, zero-initialised;
-// `epoch` is this rank's pair of zero-initialised words.
+// `epoch` is this rank's pair of zero-initialised words. With `arrivals` (batch * kv_heads zero-initialised words that the
+// kernel leaves zeroed) the fold, exchange and merge run in the last stage-1 CTA of every (batch, kv head): one launch.
 size_t fd_exchange_floats(int rows, int world);
 wb200_status launch_attention_fd_exchange(const AttentionArgs &args, uint32_t splits, float *partials, int rank, int world,
-                                          void *const *peer_buffers, unsigned int *epoch, int *device_status, cudaStream_t stream);
+                                          void *const *peer_buffers, unsigned int *epoch, unsigned int *arrivals,
+                                          int *device_status, cudaStream_t stream);
 
 // Sum over the ranks of a buffer that lies at `multicast` in an NVLink multicast mapping of a symmetric allocation
 // (switch_sum.cu): in place, every rank ends with the same sums. `signals` holds every rank's 2 * world zero-initialised
