@@ -38,6 +38,7 @@ SEED = 20260803
 TRAFFIC = {
     "fa": 2 * (214.2e6 + 46.1e6),      # profiles/fa_umma_kernel_cfg2.md: batch 2 of 4 captured
     "fd": 8 * (1.073832e9 + 6.2e6),    # profiles/fd_partial_kernel_cfg3.md: batch 8 of 64 captured
+    "layer": 8.259e9 + 1.472e9,        # profiles/decoder_layer_tp1_dram.md: the ten kernels of one full-size forward on one GPU
     "gemm": 1.118e9 + 0.124e9,         # profiles/gemm_umma_pair_kernel_cfg4.md: the full 8192^3 launch, one-pass capture
 }
 
@@ -317,7 +318,8 @@ def layer_extra(backend, args, torch, dist, rank, world, device, peak, failures)
             "verified": bool(layer_err <= 1e-2), "max_rel_err": layer_err,
             "verified_against": "float64 torch recomputation of 8 sampled token rows from the full weights",
             "roofline": {"bound": "tensor", "achieved": tflops / world, "peak": peak["bf16_tflops_sustained"], "unit": "TFLOP/s per GPU",
-                         "frac": tflops / world / peak["bf16_tflops_sustained"], "traffic": None, "peak_source": peak["source"] + " (sustained)"}}
+                         "frac": tflops / world / peak["bf16_tflops_sustained"], "traffic": TRAFFIC["layer"] if world == 1 else None,
+                         "peak_source": peak["source"] + " (sustained)"}}
 
 
 def run_reference(args):
