@@ -224,6 +224,98 @@ CHAIN = _module("""
     '!{i64 2, !"external-output", i64 0, !"", !"u8", !"tensor", i64 12288, i64 12288, !"write-only", i64 12288, i64 0}'])
 
 
+# Online attention over two blocks of 64 keys for 64 queries, head dimension 64, all f32, one Tile: the command run the
+# reference's decomposition of an online-attention step lowers to (lib/Wafer/Transforms/Linalg/OnlineAttentionDecomposition.cpp:
+# 568-594: scores, score region, new maximum, norm, rescaled sum, probabilities, new sum, rescaled accumulator, PV with the
+# accumulator as partial sum) in the transposed form (keys x queries: the queries are the 64 channels, so the per-query
+# vectors broadcast with the repeated-unit form and the reductions run over w of NCx [1, 1, keys, queries]). exp is the
+# formal (correctly rounded) exp: the reference's ExpLp has no formal evaluation (FormalNumericElementwise.cpp:216-224).
+# Scratch-pad: Q 0x0000, K 0x4000, V 0x8000, S^T 0xC000, P^T 0x10000, vectors from 0x14000 (m_old, m_tile, m_new, diff,
+# norm, l, l_scaled, p_sum, 1/l), acc^T 0x18000, scaled acc^T 0x1C000 (16 KiB matrices, 256-byte vectors).
+ATTENTION = _module("""
+  call void @wafer_tx81_rdma(i64 %0, i64 0, i32 16384, i32 16384, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  call void @wafer_tx81_memset(i64 81920, i32 -8388608, i32 64, i32 5, i32 0)
+  call void @wafer_tx81_memset(i64 83200, i32 0, i32 64, i32 5, i32 0)
+  call void @wafer_tx81_memset(i64 98304, i32 0, i32 4096, i32 5, i32 0)
+  br label %7
+7:
+  %8 = phi i64 [ 0, %6 ], [ %13, %9 ]
+  %cond = icmp ult i64 %8, 2
+  br i1 %cond, label %9, label %14
+9:
+  %off = mul i64 %8, 16384
+  %ksrc = add i64 %1, %off
+  %vsrc = add i64 %2, %off
+  call void @wafer_tx81_rdma(i64 %ksrc, i64 16384, i32 16384, i32 16384, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  call void @wafer_tx81_rdma(i64 %vsrc, i64 32768, i32 16384, i32 16384, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  call void @wafer_tx81_gemm_oriented(i64 16384, i64 0, i64 49152, i64 0, i32 64, i32 64, i32 64, i32 1, i32 5, i32 5, i32 13, i32 0, i32 1, i32 0)
+  call void @wafer_tx81_elementwise_mul(i64 49152, i64 1040187392, i64 49152, i32 4096, i32 5, i32 0, i32 1, i32 0, i32 1)
+  call void @wafer_tx81_reduce_max(i64 49152, i64 82176, i32 1, i32 1, i32 1, i32 64, i32 64, i32 5, i32 1)
+  call void @wafer_tx81_elementwise_max(i64 81920, i64 82176, i64 82432, i32 64, i32 5, i32 0, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_elementwise_sub(i64 81920, i64 82432, i64 82688, i32 64, i32 5, i32 0, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_elementwise_exp(i64 82688, i64 82944, i32 64, i32 5, i32 1)
+  call void @wafer_tx81_elementwise_mul(i64 83200, i64 82944, i64 83456, i32 64, i32 5, i32 0, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_elementwise_sub(i64 49152, i64 82432, i64 65536, i32 4096, i32 5, i32 64, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_elementwise_exp(i64 65536, i64 65536, i32 4096, i32 5, i32 1)
+  call void @wafer_tx81_reduce_sum(i64 65536, i64 83712, i32 1, i32 1, i32 1, i32 64, i32 64, i32 5, i32 1)
+  call void @wafer_tx81_elementwise_add(i64 83456, i64 83712, i64 83200, i32 64, i32 5, i32 0, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_elementwise_mul(i64 98304, i64 82944, i64 114688, i32 4096, i32 5, i32 64, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_gemm_oriented(i64 32768, i64 65536, i64 98304, i64 114688, i32 64, i32 64, i32 64, i32 1, i32 5, i32 5, i32 5, i32 1, i32 0, i32 0)
+  call void @wafer_tx81_elementwise_max(i64 82432, i64 82432, i64 81920, i32 64, i32 5, i32 0, i32 0, i32 0, i32 1)
+  %13 = add nuw i64 %8, 1
+  br label %7
+14:
+  call void @wafer_tx81_elementwise_recip(i64 83200, i64 83968, i32 64, i32 5, i32 1)
+  call void @wafer_tx81_elementwise_mul(i64 98304, i64 83968, i64 114688, i32 4096, i32 5, i32 64, i32 0, i32 0, i32 1)
+  call void @wafer_tx81_wdma(i64 114688, i64 %3, i32 16384, i32 16384, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  call void @wafer_tx81_wdma(i64 81920, i64 %4, i32 256, i32 256, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  call void @wafer_tx81_wdma(i64 83200, i64 %5, i32 256, i32 256, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 5, i32 0)
+  ret void
+""", arguments="i64 %0, i64 %1, i64 %2, i64 %3, i64 %4, i64 %5", rows=[
+    '!{i64 0, !"external-input", i64 0, !"", !"f32", !"tensor", i64 16384, i64 4096, !"read-only", i64 64, i64 64, i64 0}',
+    '!{i64 1, !"external-input", i64 1, !"", !"f32", !"tensor", i64 32768, i64 8192, !"read-only", i64 128, i64 64, i64 0}',
+    '!{i64 2, !"external-input", i64 2, !"", !"f32", !"tensor", i64 32768, i64 8192, !"read-only", i64 128, i64 64, i64 0}',
+    '!{i64 3, !"external-output", i64 0, !"", !"f32", !"tensor", i64 16384, i64 4096, !"write-only", i64 64, i64 64, i64 0}',
+    '!{i64 4, !"external-output", i64 1, !"", !"f32", !"tensor", i64 256, i64 64, !"write-only", i64 64, i64 0}',
+    '!{i64 5, !"external-output", i64 2, !"", !"f32", !"tensor", i64 256, i64 64, !"write-only", i64 64, i64 0}'])
+
+
+def _attention_inputs():
+    rng = np.random.default_rng(20260803)
+    q, k, v = (rng.standard_normal(shape).astype(np.float32) for shape in ((64, 64), (128, 64), (128, 64)))
+    return q, k, v
+
+
+def _attention_cpu_replay(program):
+    from oracle import binding, trace_replay
+    binding.build()
+    commands, stats = program.trace()
+    ddr = np.zeros(program.placement(False, 0)["ddr_bytes"], dtype=np.uint8)
+    for index, array in enumerate(_attention_inputs()):
+        place = program.placement(False, index)
+        at = place["address"] - place["ddr_base"]
+        ddr[at:at + array.nbytes] = array.view(np.uint8).reshape(-1)
+    report = {}
+    trace_replay.replay(commands, ddr, 1, spm_bytes=1 << 17, report=report)
+    outs = []
+    for index, nbytes in enumerate((16384, 256, 256)):
+        place = program.placement(True, index)
+        at = place["address"] - place["ddr_base"]
+        outs.append(ddr[at:at + nbytes].copy().view(np.float32))
+    return outs, report["numeric_flags"], stats
+
+
+def test_attention_step_program_is_replayed_on_the_cpu():
+    (out_t, m, l), _, stats = _attention_cpu_replay(TileProgram([ATTENTION], spm_bytes=1 << 17))
+    assert stats["commands"] == 41 and stats["gemm_commands"] == 4
+    q, k, v = (a.astype(np.float64) for a in _attention_inputs())
+    scores = q @ k.T * 0.125
+    p = np.exp(scores - scores.max(-1, keepdims=True))
+    want = (p / p.sum(-1, keepdims=True)) @ v                           # [queries, D]
+    assert np.abs(out_t.reshape(64, 64).T - want).max() <= 1e-5           # the program keeps the accumulator transposed
+    assert np.allclose(m, scores.max(-1), rtol=1e-6) and np.allclose(l, p.sum(-1), rtol=1e-5)
+
+
 def _chain_inputs():
     rng = np.random.default_rng(77)
     x = (rng.standard_normal(512).astype(np.float32) * 3).view(np.uint32) >> 16
@@ -452,6 +544,25 @@ def test_elementwise_chain_is_fused_and_matches_the_unfused_replay_and_the_cpu(b
         assert stats_fused["numeric_flags"] == stats_unfused["numeric_flags"] == expected_flags
         assert stats_fused["commands"] == stats_unfused["commands"] == 12
         assert stats_unfused["gpu_launches"] == 12 and stats_fused["gpu_launches"] == 6   # seven commands in one launch
+
+
+@pytest.mark.gpu
+def test_attention_step_run_is_one_launch_and_matches_the_unfused_replay_and_the_cpu(backend, monkeypatch):
+    (want_out, want_m, want_l), want_flags, _ = _attention_cpu_replay(TileProgram([ATTENTION], spm_bytes=1 << 17))
+    fused = TileProgram([ATTENTION], backend, spm_bytes=1 << 17)
+    monkeypatch.setenv("WB200_REPLAY_FUSE", "0")
+    unfused = TileProgram([ATTENTION], backend, spm_bytes=1 << 17)
+    monkeypatch.delenv("WB200_REPLAY_FUSE")
+    inputs = list(_attention_inputs())
+    for _ in range(2):   # the first run captures the graph, the second relaunches it
+        for program, launches in ((fused, 13), (unfused, 41)):
+            (out, m, l), stats = program.run(inputs)
+            assert np.array_equal(out.reshape(-1).view(np.uint32), want_out.view(np.uint32))
+            assert np.array_equal(m.reshape(-1).view(np.uint32), want_m.view(np.uint32))
+            assert np.array_equal(l.reshape(-1).view(np.uint32), want_l.view(np.uint32))
+            assert stats["numeric_flags"] == want_flags and stats["commands"] == 41
+            # fused: the 14 commands of a step between its loads are one launch, and the two closing commands join the last one
+            assert stats["gpu_launches"] == launches
 
 
 @pytest.mark.gpu

@@ -104,16 +104,21 @@ namespace wb200 {
 
 wb200_status image_range(const wb200_spm_image *image, uint64_t address, uint64_t bytes, const char *what);
 // wafer_tx81_gemm on a scratch-pad image, enqueued on the backend stream without synchronising.
+// `defer` (here and in the elementwise and reduce forms): when given, nothing is launched: the validated command is
+// described there and *deferred says whether it fits a command run (formal_run_admits); the caller launches the run, or,
+// when the command does not fit, calls again without `defer`.
 wb200_status enqueue_image_gemm(wb200_spm_image *image, uint64_t lhs, uint64_t rhs, uint64_t dst, uint64_t psum,
                                 uint32_t m, uint32_t k, uint32_t n, uint32_t batch, uint32_t in_format,
                                 uint32_t out_format, uint32_t psum_format, uint32_t lhs_orientation,
-                                uint32_t rhs_orientation, uint32_t policy);
+                                uint32_t rhs_orientation, uint32_t policy, RunCommand *defer = nullptr, bool *deferred = nullptr);
 
 wb200_status enqueue_image_elementwise(wb200_spm_image *image, uint32_t operation, uint64_t lhs, uint64_t rhs_or_scalar_bits,
                                        uint64_t dst, uint32_t count, uint32_t format, uint32_t rhs_unit_elements,
-                                       uint32_t scalar_flag, uint32_t relation_numeric_or_rhs_group, uint32_t *d_flags, bool execute);
+                                       uint32_t scalar_flag, uint32_t relation_numeric_or_rhs_group, uint32_t *d_flags, bool execute,
+                                       RunCommand *defer = nullptr, bool *deferred = nullptr);
 wb200_status enqueue_image_reduce(wb200_spm_image *image, uint32_t operation, uint64_t source, uint64_t destination, uint32_t dimension,
-                                  const uint32_t nhwc[4], uint32_t format, uint32_t *d_flags, bool execute);
+                                  const uint32_t nhwc[4], uint32_t format, uint32_t *d_flags, bool execute, RunCommand *defer = nullptr,
+                                  bool *deferred = nullptr);
 wb200_status enqueue_image_pool(wb200_spm_image *image, uint32_t kind, uint64_t input, uint64_t dst, const uint32_t source_shape[4],
                                 const uint32_t destination_shape[4], const uint32_t pads[4], const uint32_t kernel_strides[4],
                                 uint32_t format, uint32_t *d_flags, bool execute);

@@ -115,6 +115,44 @@ struct ElementwiseChain {
   ChainStep step[kMaxChainSteps];
 };
 wb200_status launch_elementwise_chain(const ElementwiseChain &chain, uint32_t *flags_word, cudaStream_t stream);
+// A run of formal commands of one Tile - GEMMs (one matrix, formal policy), elementwise commands over 1-D vectors and
+// NCx [n, h, w, c] reductions in any order, e.g. the scores, running maximum, probabilities, running sum and PV product
+// of an online-attention step - executed by ONE launch: a single thread block walks the commands in issue order with a
+// block barrier between them, so a command sees what the commands before it wrote, every destination the commands
+// name is written, and every element goes through the same arithmetic as in the command's own kernel (bit-identical).
+// Only small commands qualify (formal_run_admits): one block is a fraction of the machine.
+constexpr int kMaxRunCommands = 16;
+enum { WB200_RUN_ELEMENTWISE = 0, WB200_RUN_REDUCE = 1, WB200_RUN_GEMM = 2 };
+struct RunElementwise {
+  int32_t op, in_format, out_format, input_count;
+  const uint8_t *in0, *in1;
+  uint8_t *dst;
+  LayoutMap in_map, out_map;
+  RhsBroadcast rhs;
+};
+struct RunReduce {
+  int32_t op, format;
+  const uint8_t *src;
+  uint8_t *dst;
+  LayoutMap src_map, dst_map;
+  uint32_t reduced_mask;
+};
+struct RunCommand {
+  int32_t kind;
+  union Payload {
+    RunElementwise elementwise;
+    RunReduce reduce;
+    GemmFormalArgs gemm;
+    __host__ __device__ Payload() {}
+  } u;
+  __host__ __device__ RunCommand() : kind(0) {}
+};
+struct FormalRun {
+  int32_t count = 0;
+  RunCommand command[kMaxRunCommands];
+};
+bool formal_run_admits(const RunCommand &command);
+wb200_status launch_formal_run(const FormalRun &run, uint32_t *flags_word, cudaStream_t stream);
 // Formal reduction: NaN-canonicalising, flag-raising fold in row-major input order (bit d of `reduced_mask` = dimension d reduced).
 wb200_status launch_reduce_formal(int op, int format, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map, const LayoutMap &dst_map,
                                   uint32_t reduced_mask, uint32_t *flags_word, cudaStream_t stream);

@@ -570,14 +570,17 @@ __device__ __forceinline__ uint32_t formal_load(const uint8_t *base, int format,
 // pointers 16-byte aligned) full groups then move with 128-bit accesses and no layout arithmetic at all.
 // kOp >= 0 fixes the operation and the operand format at compile time (the arithmetic and relation families in linear
 // layout): the generic evaluator then folds to a few dozen instructions instead of its whole decision tree.
+// The groups first_group, first_group + group_stride, ... of one command; returns the OR of the elements' flags. The
+// command's own kernel walks the groups with its whole grid, a command run (formal_run_kernel) with one block.
 template <bool kLinear, int kOp, int kFormat>
-__global__ void __launch_bounds__(kThreads)
-formal_elementwise_kernel(int runtime_op, int runtime_format, int out_format, int input_count, const uint8_t *in0, const uint8_t *in1, uint8_t *dst,
-                          const LayoutMap in_map, const LayoutMap out_map, const RhsBroadcast rhs, int vector, uint32_t *flags_word) {
+__device__ __forceinline__ uint32_t
+formal_elementwise_groups(int runtime_op, int runtime_format, int out_format, int input_count, const uint8_t *in0, const uint8_t *in1, uint8_t *dst,
+                          const LayoutMap &in_map, const LayoutMap &out_map, const RhsBroadcast rhs, int vector, int64_t first_group,
+                          int64_t group_stride) {
   const int op = kOp >= 0 ? kOp : runtime_op, in_format = kOp >= 0 ? kFormat : runtime_format;
   const int64_t total = out_map.element_count;
   const int64_t groups = (total + 7) / 8;
-  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t stride = group_stride;
   uint32_t flags = 0;
   const bool logic = op >= WB200_EW_LOGIC_NOT && op <= WB200_EW_LOGIC_XOR;
   const bool mpfr_family = op == WB200_EW_SQRT || op == WB200_EW_RSQRT || (op >= WB200_EW_LOG2 && op <= WB200_EW_EXP) ||
@@ -585,7 +588,7 @@ formal_elementwise_kernel(int runtime_op, int runtime_format, int out_format, in
   const int in_bytes = format_bits(in_format) / 8, out_bytes = format_bits(out_format) / 8;   // 0 for Bool
   const bool same_rhs = input_count > 1 && rhs.mode == WB200_RHS_SAME;
   const bool scalar_rhs = input_count > 1 && rhs.mode == WB200_RHS_SCALAR;   // decided once, not per element
-  for (int64_t g = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; g < groups; g += stride) {
+  for (int64_t g = first_group; g < groups; g += stride) {
     const int64_t first = g * 8;
     const int count = total - first < 8 ? static_cast<int>(total - first) : 8;
     const bool wide = kLinear && vector && count == 8;
@@ -642,6 +645,16 @@ formal_elementwise_kernel(int runtime_op, int runtime_format, int out_format, in
         if (e < count) store_element_bits(dst, kLinear ? first + e : physical_index(out_map, first + e), out_format, value[e]);
     }
   }
+  return flags;
+}
+
+template <bool kLinear, int kOp, int kFormat>
+__global__ void __launch_bounds__(kThreads)
+formal_elementwise_kernel(int runtime_op, int runtime_format, int out_format, int input_count, const uint8_t *in0, const uint8_t *in1, uint8_t *dst,
+                          const LayoutMap in_map, const LayoutMap out_map, const RhsBroadcast rhs, int vector, uint32_t *flags_word) {
+  const uint32_t flags = formal_elementwise_groups<kLinear, kOp, kFormat>(
+      runtime_op, runtime_format, out_format, input_count, in0, in1, dst, in_map, out_map, rhs, vector,
+      static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x, static_cast<int64_t>(gridDim.x) * blockDim.x);
   merge_block_flags(flags_word, flags);
 }
 
@@ -728,11 +741,9 @@ formal_chain_kernel(const ElementwiseChain chain, int vector, uint32_t *flags_wo
 // The same fold for rank-4 NCx tensors [n, h, w, c] (every TargetCall-level reduce): coordinates are carried as loop
 // counters, so the only divisions are the three that split the output index.
 template <int kCombine, int kFormat>
-__global__ void __launch_bounds__(kThreads)
-formal_reduce_nhwc_kernel(const uint8_t *src, uint8_t *dst, const LayoutMap src_map, const LayoutMap dst_map,
-                          uint32_t reduced_mask, uint32_t *flags_word) {
+__device__ __forceinline__ uint32_t formal_reduce_nhwc_output(const uint8_t *src, uint8_t *dst, const LayoutMap &src_map, const LayoutMap &dst_map,
+                                                              uint32_t reduced_mask, int64_t out_index) {
   constexpr int format = kFormat, combine = kCombine;
-  const int64_t out_index = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   uint32_t block_flags_in = 0;
   if (out_index < dst_map.element_count) {
   const uint32_t out_c = static_cast<uint32_t>(dst_map.shape[3]), out_w = static_cast<uint32_t>(dst_map.shape[2]), out_h = static_cast<uint32_t>(dst_map.shape[1]);
@@ -782,7 +793,15 @@ formal_reduce_nhwc_kernel(const uint8_t *src, uint8_t *dst, const LayoutMap src_
   store_element_bits(dst, physical_index_nhwc(dst_map, n0, static_cast<int64_t>(h0) * out_w + w0, c0), format, accumulator);
   block_flags_in = flags;
   }
-  merge_block_flags(flags_word, block_flags_in);
+  return block_flags_in;
+}
+template <int kCombine, int kFormat>
+__global__ void __launch_bounds__(kThreads)
+formal_reduce_nhwc_kernel(const uint8_t *src, uint8_t *dst, const LayoutMap src_map, const LayoutMap dst_map,
+                          uint32_t reduced_mask, uint32_t *flags_word) {
+  const uint32_t flags = formal_reduce_nhwc_output<kCombine, kFormat>(src, dst, src_map, dst_map, reduced_mask,
+                                                                     static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x);
+  merge_block_flags(flags_word, flags);
 }
 
 // Formal reduction (lib/Wafer/Simulator/Reference/Numeric/FormalTensorNumeric.cpp:363-425 with the step of
@@ -829,6 +848,82 @@ formal_reduce_kernel(int op, int format, const uint8_t *src, uint8_t *dst, const
   block_flags_in = flags;
   }
   merge_block_flags(flags_word, block_flags_in);
+}
+
+// ------------------------------------------------------------------------------------------------ command runs
+// One launch for a run of formal commands of one Tile (FormalRun). A single block of kRunThreads threads executes the
+// commands in issue order with a block barrier after each, so a command reads what earlier commands of the run wrote
+// (same SM: its L1 sees its own stores). Elementwise commands and reductions go through the very device functions of
+// their own kernels; the GEMM is the formal chain of gemm_formal.cu written for one thread per output:
+//   acc = +0; for k ascending: acc = fma(widen(lhs), widen(rhs), acc); [acc = acc + psum;] dst = narrow(acc)
+// (lib/Wafer/Simulator/Reference/Numeric/FormalTensorNumeric.cpp:271-361), so every destination gets the bits the
+// command-by-command replay gives it.
+constexpr int kRunThreads = 1024;
+
+// Physical element index of (row, col) of a [rows, cols] matrix. Cx of rank 2 with a power-of-two channel block is
+// resolved with shifts; anything else takes the general map.
+__device__ __forceinline__ int64_t run_matrix_index(const LayoutMap &map, int64_t row, int64_t cols, int64_t col) {
+  if (map.layout == WB200_LAYOUT_TENSOR || map.layout == WB200_LAYOUT_NTENSOR) return row * cols + col;
+  if (map.layout != WB200_LAYOUT_CX || map.rank != 2 || (map.c_block & (map.c_block - 1)) != 0) return physical_index(map, row * cols + col);
+  const int64_t full_c = map.cx_blocks * map.c_block;
+  if (col < full_c) {
+    const int shift = __ffsll(map.c_block) - 1;
+    return (col >> shift) * (map.block_outer_elements * map.c_block) + row * map.c_block + (col & (map.c_block - 1));
+  }
+  return map.cx_blocks * map.block_outer_elements * map.c_block + row * map.c0 + (col - full_c);
+}
+
+__device__ __forceinline__ void run_gemm(const GemmFormalArgs &a) {
+  const int64_t outputs = static_cast<int64_t>(a.m) * a.n;
+  for (int64_t index = threadIdx.x; index < outputs; index += kRunThreads) {
+    const int64_t row = index / a.n, col = index - row * a.n;
+    float acc = 0.0f;
+    for (int k = 0; k < a.k; ++k) {
+      const int64_t lhs_at = a.lhs_transposed ? run_matrix_index(a.lhs_map, k, a.m, row) : run_matrix_index(a.lhs_map, row, a.k, k);
+      const int64_t rhs_at = a.rhs_transposed ? run_matrix_index(a.rhs_map, col, a.k, k) : run_matrix_index(a.rhs_map, k, a.n, col);
+      acc = __fmaf_rn(widen_bits(load_element_bits(a.lhs, lhs_at, a.in_format), a.in_format),
+                      widen_bits(load_element_bits(a.rhs, rhs_at, a.in_format), a.in_format), acc);
+    }
+    if (a.has_psum) acc = __fadd_rn(acc, __uint_as_float(load_element_bits(a.psum, run_matrix_index(a.psum_map, row, a.n, col), WB200_F32)));
+    store_element_bits(a.dst, run_matrix_index(a.dst_map, row, a.n, col), a.out_format, narrow_bits(acc, a.out_format));
+  }
+}
+
+__device__ __forceinline__ uint32_t run_reduce(const RunReduce &r) {
+  uint32_t flags = 0;
+  const bool nhwc = r.src_map.layout == WB200_LAYOUT_NCX && r.dst_map.layout == WB200_LAYOUT_NCX && r.src_map.rank == 4 && r.dst_map.rank == 4;
+  if (!nhwc) return flags;   // formal_run_admits lets nothing else in
+  for (int64_t out = threadIdx.x; out < r.dst_map.element_count; out += kRunThreads) {
+#define WB200_RUN_REDUCE(COMBINE)                                                                                                  \
+    if (r.format == WB200_F32) flags |= formal_reduce_nhwc_output<COMBINE, WB200_F32>(r.src, r.dst, r.src_map, r.dst_map, r.reduced_mask, out);   \
+    else if (r.format == WB200_BF16) flags |= formal_reduce_nhwc_output<COMBINE, WB200_BF16>(r.src, r.dst, r.src_map, r.dst_map, r.reduced_mask, out); \
+    else flags |= formal_reduce_nhwc_output<COMBINE, WB200_F16>(r.src, r.dst, r.src_map, r.dst_map, r.reduced_mask, out)
+    if (r.op == WB200_RED_SUM) { WB200_RUN_REDUCE(WB200_EW_ADD); }
+    else if (r.op == WB200_RED_MAX) { WB200_RUN_REDUCE(WB200_EW_MAX); }
+    else { WB200_RUN_REDUCE(WB200_EW_MIN); }
+#undef WB200_RUN_REDUCE
+  }
+  return flags;
+}
+
+__global__ void __launch_bounds__(kRunThreads) formal_run_kernel(const __grid_constant__ FormalRun run, uint32_t *flags_word) {
+  uint32_t flags = 0;
+#pragma unroll 1
+  for (int c = 0; c < run.count; ++c) {
+    const RunCommand &command = run.command[c];
+    if (command.kind == WB200_RUN_ELEMENTWISE) {
+      const RunElementwise &e = command.u.elementwise;
+      const int vector = ((reinterpret_cast<uintptr_t>(e.in0) | reinterpret_cast<uintptr_t>(e.in1) | reinterpret_cast<uintptr_t>(e.dst)) & 15) == 0;
+      flags |= formal_elementwise_groups<true, -1, 0>(e.op, e.in_format, e.out_format, e.input_count, e.in0, e.in1, e.dst, e.in_map, e.out_map,
+                                                      e.rhs, vector, threadIdx.x, kRunThreads);
+    } else if (command.kind == WB200_RUN_REDUCE) {
+      flags |= run_reduce(command.u.reduce);
+    } else {
+      run_gemm(command.u.gemm);
+    }
+    __syncthreads();   // the next command may read anything this one wrote
+  }
+  merge_block_flags(flags_word, flags);
 }
 
 // Plain pooling (lib/Wafer/Simulator/Kernel/TargetModelTensorNumeric.cpp:466-583): every output folds its window in
@@ -998,6 +1093,33 @@ wb200_status launch_elementwise_chain(const ElementwiseChain &chain, uint32_t *f
   if (chain.format == WB200_F32) formal_chain_kernel<WB200_F32><<<grid, kThreads, 0, stream>>>(chain, vector, flags_word);
   else if (chain.format == WB200_BF16) formal_chain_kernel<WB200_BF16><<<grid, kThreads, 0, stream>>>(chain, vector, flags_word);
   else formal_chain_kernel<WB200_F16><<<grid, kThreads, 0, stream>>>(chain, vector, flags_word);
+  WB200_CUDA_CHECK(cudaGetLastError());
+  return WB200_OK;
+}
+
+// Commands small enough for one thread block: one block is 1 / 148 of the machine, so a large command is faster in its
+// own kernel. Elementwise: linear 1-D vectors of at most 2^17 elements; reduce: NCx rank 4 with at most 2^18 inputs;
+// GEMM: one matrix of at most 2^20 multiply-adds.
+bool formal_run_admits(const RunCommand &command) {
+  auto linear = [](const LayoutMap &m) { return m.layout == WB200_LAYOUT_TENSOR || m.layout == WB200_LAYOUT_NTENSOR; };
+  if (command.kind == WB200_RUN_ELEMENTWISE) {
+    const RunElementwise &e = command.u.elementwise;
+    return linear(e.in_map) && linear(e.out_map) && e.out_map.element_count <= (1 << 17);
+  }
+  if (command.kind == WB200_RUN_REDUCE) {
+    const RunReduce &r = command.u.reduce;
+    return r.src_map.layout == WB200_LAYOUT_NCX && r.dst_map.layout == WB200_LAYOUT_NCX && r.src_map.rank == 4 && r.dst_map.rank == 4 &&
+           r.src_map.element_count <= (1 << 18);
+  }
+  const GemmFormalArgs &g = command.u.gemm;
+  return g.batch == 1 && static_cast<int64_t>(g.m) * g.n * g.k <= (1 << 20) && is_float_format(g.in_format) && is_float_format(g.out_format);
+}
+
+wb200_status launch_formal_run(const FormalRun &run, uint32_t *flags_word, cudaStream_t stream) {
+  if (run.count < 1 || run.count > kMaxRunCommands) return fail(WB200_ERR_INVALID_ARGUMENT, "malformed command run");
+  for (int c = 0; c < run.count; ++c)
+    if (!formal_run_admits(run.command[c])) return fail(WB200_ERR_INVALID_ARGUMENT, "command outside the domain of a command run");
+  formal_run_kernel<<<1, kRunThreads, 0, stream>>>(run, flags_word);
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }

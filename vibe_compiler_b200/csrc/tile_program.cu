@@ -641,8 +641,19 @@ struct PendingChain {
   int first_command = 0;
 };
 
+// Formal commands of one Tile (GEMMs, reductions and the elementwise commands between them) that are held back while
+// the following command may join them in one launch (FormalRun): the command run of an online-attention step - scores,
+// running maximum, probabilities, running sum, PV product - becomes one kernel instead of one per command.
+struct PendingRun {
+  FormalRun run;                  // run.count == 0 when nothing is pending
+  uint64_t first_args[20] = {0};  // the first command as issued: a run that stays one command long uses the command's own kernel
+  uint32_t first_operation = 0;
+  int first_command = 0;
+};
+
 struct TileState {
   PendingChain chain;
+  PendingRun run;
   std::vector<uint64_t> regs;
   int block = 0, previous = -1;
   size_t pc = 0;
@@ -961,8 +972,29 @@ wb200_status issue_elementwise(wb200_tile_program *program, wb200_spm_image *spm
   return st;
 }
 
-// Launches what the Tile holds back: one fused kernel for two or more commands, the ordinary kernel for one.
+wb200_status issue_run_command(wb200_tile_program *program, int tile_index, int command, uint32_t operation, const uint64_t *a, RunCommand *defer,
+                               bool *deferred);
+
+// Launches the Tile's pending command run: one kernel for two or more commands, the command's own kernel for one.
+wb200_status flush_run(wb200_tile_program *program, int tile_index) {
+  PendingRun &pending = program->state[tile_index].run;
+  if (pending.run.count == 0) return WB200_OK;
+  wb200_status st;
+  const int count = pending.run.count;
+  pending.run.count = 0;
+  if (count == 1) return issue_run_command(program, tile_index, pending.first_command, pending.first_operation, pending.first_args, nullptr, nullptr);
+  DeviceGuard guard(program->backend->device);
+  pending.run.count = count;
+  st = launch_formal_run(pending.run, program->numeric_words, program->spm[tile_index].work_stream());
+  pending.run.count = 0;
+  if (st == WB200_OK) { program->backend->launches += 1; program->stats.gpu_launches += 1; }
+  return st;
+}
+
+// Launches what the Tile holds back (a command run or an elementwise chain, never both): one fused kernel for two or
+// more commands, the ordinary kernel for one.
 wb200_status flush_chain(wb200_tile_program *program, int tile_index) {
+  if (wb200_status run_status = flush_run(program, tile_index)) return run_status;
   PendingChain &pending = program->state[tile_index].chain;
   if (pending.chain.steps == 0) return WB200_OK;
   wb200_spm_image *spm = &program->spm[tile_index];
@@ -1028,6 +1060,57 @@ wb200_status defer_elementwise(wb200_tile_program *program, int tile_index, int 
   return WB200_OK;
 }
 
+// One GEMM, reduction or elementwise command as issued. With `defer` nothing is launched: the command is validated and
+// described, and *deferred says whether it fits a command run. Without it the command's own kernel is launched.
+wb200_status issue_run_command(wb200_tile_program *program, int tile_index, int command, uint32_t operation, const uint64_t *a, RunCommand *defer,
+                               bool *deferred) {
+  wb200_spm_image *spm = program->execute ? &program->spm[tile_index] : nullptr;
+  wb200_spm_image probe_spm{nullptr, 0, program->spm_bytes, nullptr};
+  if (!program->execute) spm = &probe_spm;
+  const uint64_t before = program->execute ? program->backend->launches : 0;
+  wb200_status st;
+  if (command == kReduce) {
+    const uint32_t nhwc[4] = {static_cast<uint32_t>(a[3]), static_cast<uint32_t>(a[4]), static_cast<uint32_t>(a[5]), static_cast<uint32_t>(a[6])};
+    st = enqueue_image_reduce(spm, operation, a[0], a[1], static_cast<uint32_t>(a[2]), nhwc, static_cast<uint32_t>(a[7]), program->numeric_words,
+                              program->execute, defer, deferred);
+  } else if (command == kGemm || command == kGemmOriented) {
+    const uint32_t lhs_orientation = command == kGemmOriented ? static_cast<uint32_t>(a[11]) : WB200_NORMAL;
+    const uint32_t rhs_orientation = command == kGemmOriented ? static_cast<uint32_t>(a[12]) : WB200_NORMAL;
+    st = enqueue_image_gemm(spm, a[0], a[1], a[2], a[3], static_cast<uint32_t>(a[4]), static_cast<uint32_t>(a[5]), static_cast<uint32_t>(a[6]),
+                            static_cast<uint32_t>(a[7]), static_cast<uint32_t>(a[8]), static_cast<uint32_t>(a[9]), static_cast<uint32_t>(a[10]),
+                            lhs_orientation, rhs_orientation, program->gemm_policy, defer, deferred);
+  } else {
+    const bool unary = command == kElementwiseUnary, full = command == kElementwiseBinary;
+    const uint64_t rhs = unary ? 0 : a[1], destination = unary ? a[1] : a[2], count = unary ? a[2] : a[3], format = unary ? a[3] : a[4];
+    st = enqueue_image_elementwise(spm, operation, a[0], rhs, destination, static_cast<uint32_t>(count), static_cast<uint32_t>(format),
+                                   full ? static_cast<uint32_t>(a[5]) : 0, full ? static_cast<uint32_t>(a[6]) : 0, full ? static_cast<uint32_t>(a[7]) : 0,
+                                   program->numeric_words, program->execute, defer, deferred);
+  }
+  if (program->execute) program->stats.gpu_launches += program->backend->launches - before;
+  return st;
+}
+
+// Tries to add the command to the Tile's pending run. *joined is false when the command does not fit a run (too large,
+// tensor-core GEMM policy): the pending run has then been launched and the caller issues the command on its own.
+wb200_status join_run(wb200_tile_program *program, int tile_index, int command, uint32_t operation, const uint64_t *a, bool *joined) {
+  PendingRun &pending = program->state[tile_index].run;
+  *joined = false;
+  RunCommand described;
+  bool fits = false;
+  wb200_status st = issue_run_command(program, tile_index, command, operation, a, &described, &fits);
+  if (st != WB200_OK) return st;
+  if (!fits) return flush_chain(program, tile_index);
+  if (pending.run.count == kMaxRunCommands && (st = flush_run(program, tile_index)) != WB200_OK) return st;
+  if (pending.run.count == 0) {
+    pending.first_command = command;
+    pending.first_operation = operation;
+    for (int i = 0; i < 20; ++i) pending.first_args[i] = a[i];
+  }
+  pending.run.command[pending.run.count++] = described;
+  *joined = true;
+  return WB200_OK;
+}
+
 wb200_status execute_call(wb200_tile_program *program, int tile_index, const Inst &inst, bool *blocked, uint64_t *result) {
   TileState &tile = program->state[tile_index];
   uint64_t a[20] = {0};
@@ -1043,7 +1126,11 @@ wb200_status execute_call(wb200_tile_program *program, int tile_index, const Ins
   *blocked = false;
   *result = 0;
   const bool elementwise = inst.command == kElementwiseUnary || inst.command == kElementwiseBinary || inst.command == kElementwiseLogic;
-  if (!elementwise && (st = flush_chain(program, tile_index)) != WB200_OK) return st;   // held-back commands precede this one
+  const bool run_starter = inst.command == kGemm || inst.command == kGemmOriented || inst.command == kReduce;
+  const bool runs = program->execute && program->fuse_chains;
+  // Held-back commands precede this one, unless it may join them: a GEMM or a reduction joins (or opens) a command run,
+  // an elementwise command joins an open run or the elementwise chain.
+  if (!elementwise && !(run_starter && runs && tile.run.run.count > 0) && (st = flush_chain(program, tile_index)) != WB200_OK) return st;
   switch (inst.command) {
     case kNccJoin:
       if (a[0] == 0 || (a[0] & ~0xFull)) return program_error(program, tile_index, "NCC join mask is empty or outside the worker domain");
@@ -1178,6 +1265,10 @@ wb200_status execute_call(wb200_tile_program *program, int tile_index, const Ins
       program->stats.bytes_moved += count * (format_bits(static_cast<int>(format)) / 8) * (unary ? 2 : 3);
       if (!program->execute || !program->fuse_chains) return issue_elementwise(program, spm, inst.command, inst.operation, a, program->execute);
       if ((st = issue_elementwise(program, spm, inst.command, inst.operation, a, false)) != WB200_OK) return st;   // validation only
+      if (tile.run.run.count > 0) {
+        bool joined = false;
+        if ((st = join_run(program, tile_index, inst.command, inst.operation, a, &joined)) != WB200_OK || joined) return st;
+      }
       const uint32_t op = inst.operation;
       const bool arithmetic = op == WB200_EW_MAX || op == WB200_EW_MIN || op == WB200_EW_ADD || op == WB200_EW_SUB || op == WB200_EW_MUL;
       // same-index or immediate second operands only; relations, logic and the repeated-unit / grouped forms run unfused
@@ -1213,11 +1304,12 @@ wb200_status execute_call(wb200_tile_program *program, int tile_index, const Ins
       // (source, destination, dimension, n, h, w, c, format)
       const uint32_t nhwc[4] = {static_cast<uint32_t>(a[3]), static_cast<uint32_t>(a[4]), static_cast<uint32_t>(a[5]), static_cast<uint32_t>(a[6])};
       record(program, tile_index, inst.command, a, argc, inst.operation);
-      const uint64_t before = program->execute ? program->backend->launches : 0;
-      st = enqueue_image_reduce(spm, inst.operation, a[0], a[1], static_cast<uint32_t>(a[2]), nhwc, static_cast<uint32_t>(a[7]),
-                                program->numeric_words, program->execute);
-      if (program->execute) program->stats.gpu_launches += program->backend->launches - before;
-      return st;
+      if (runs) {
+        bool joined = false;
+        if ((st = join_run(program, tile_index, inst.command, inst.operation, a, &joined)) != WB200_OK || joined) return st;
+      }
+      return issue_run_command(program, tile_index, inst.command, inst.operation, a, nullptr, nullptr);
+      (void)nhwc;
     }
     case kConvert: {
       // (source, destination, count, zero point, rounding mode)
@@ -1238,12 +1330,11 @@ wb200_status execute_call(wb200_tile_program *program, int tile_index, const Ins
       program->stats.gemm_commands += 1;
       program->stats.gemm_fused_multiply_adds += a[4] * a[5] * a[6] * a[7];
       if (!program->execute) return WB200_OK;
-      const uint64_t before = program->backend->launches;
-      st = enqueue_image_gemm(spm, a[0], a[1], a[2], a[3], static_cast<uint32_t>(a[4]), static_cast<uint32_t>(a[5]), static_cast<uint32_t>(a[6]),
-                              static_cast<uint32_t>(a[7]), static_cast<uint32_t>(a[8]), static_cast<uint32_t>(a[9]), static_cast<uint32_t>(a[10]),
-                              lhs_orientation, rhs_orientation, program->gemm_policy);
-      program->stats.gpu_launches += program->backend->launches - before;
-      return st;
+      if (runs) {
+        bool joined = false;
+        if ((st = join_run(program, tile_index, inst.command, inst.operation, a, &joined)) != WB200_OK || joined) return st;
+      }
+      return issue_run_command(program, tile_index, inst.command, inst.operation, a, nullptr, nullptr);
     }
     default:
       return program_error(program, tile_index, "command outside the executed set");
