@@ -542,6 +542,7 @@ wb200_status enqueue_image_gemm(wb200_spm_image *image, uint64_t lhs, uint64_t r
     f.has_psum = g.has_psum;
     f.lhs = g.lhs; f.rhs = g.rhs; f.psum = g.psum; f.dst = g.dst;
     f.lhs_map = g.lhs_map; f.rhs_map = g.rhs_map; f.psum_map = g.psum_map; f.dst_map = g.dst_map;
+    command.variant = formal_gemm_variant(f);
     *defer = command;
     *deferred = formal_run_admits(command);
     return WB200_OK;

@@ -139,19 +139,21 @@ struct RunReduce {
 };
 struct RunCommand {
   int32_t kind;
+  int32_t variant = 0;   // GEMM: which instantiation of the tile function (gemm_formal_variant)
   union Payload {
     RunElementwise elementwise;
     RunReduce reduce;
     GemmFormalArgs gemm;
     __host__ __device__ Payload() {}
   } u;
-  __host__ __device__ RunCommand() : kind(0) {}
+  __host__ __device__ RunCommand() : kind(0), variant(0) {}
 };
 struct FormalRun {
   int32_t count = 0;
   RunCommand command[kMaxRunCommands];
 };
 bool formal_run_admits(const RunCommand &command);
+int formal_gemm_variant(const GemmFormalArgs &args);   // gemm_formal.cu
 wb200_status launch_formal_run(const FormalRun &run, uint32_t *flags_word, cudaStream_t stream);
 // Formal reduction: NaN-canonicalising, flag-raising fold in row-major input order (bit d of `reduced_mask` = dimension d reduced).
 wb200_status launch_reduce_formal(int op, int format, const uint8_t *src, uint8_t *dst, const LayoutMap &src_map, const LayoutMap &dst_map,

@@ -3,6 +3,7 @@
 // decode every operand to f32 (:137-155), apply one f32 operation (:230-299), encode with
 // round-to-nearest-even (:157-185); NaN inputs or results are reported, not produced. Arithmetic
 // uses the explicitly rounded intrinsics so the compiler cannot contract or reassociate.
+#include "gemm_formal.cuh"
 #include "kernels.h"
 #include "formal_functions_f32.cuh"
 
@@ -856,37 +857,60 @@ formal_reduce_kernel(int op, int format, const uint8_t *src, uint8_t *dst, const
 // (same SM: its L1 sees its own stores). Elementwise commands and reductions go through the very device functions of
 // their own kernels; the GEMM is the formal chain of gemm_formal.cu written for one thread per output:
 //   acc = +0; for k ascending: acc = fma(widen(lhs), widen(rhs), acc); [acc = acc + psum;] dst = narrow(acc)
-// (lib/Wafer/Simulator/Reference/Numeric/FormalTensorNumeric.cpp:271-361), so every destination gets the bits the
-// command-by-command replay gives it.
-constexpr int kRunThreads = 1024;
+// (lib/Wafer/Simulator/Reference/Numeric/FormalTensorNumeric.cpp:271-361) through the tile function of gemm_formal.cuh, so
+// every destination gets the bits the command-by-command replay gives it.
+constexpr int kRunThreads = 512;   // 128 registers per thread: the formal evaluators need them
 
-// Physical element index of (row, col) of a [rows, cols] matrix. Cx of rank 2 with a power-of-two channel block is
-// resolved with shifts; anything else takes the general map.
-__device__ __forceinline__ int64_t run_matrix_index(const LayoutMap &map, int64_t row, int64_t cols, int64_t col) {
-  if (map.layout == WB200_LAYOUT_TENSOR || map.layout == WB200_LAYOUT_NTENSOR) return row * cols + col;
-  if (map.layout != WB200_LAYOUT_CX || map.rank != 2 || (map.c_block & (map.c_block - 1)) != 0) return physical_index(map, row * cols + col);
-  const int64_t full_c = map.cx_blocks * map.c_block;
-  if (col < full_c) {
-    const int shift = __ffsll(map.c_block) - 1;
-    return (col >> shift) * (map.block_outer_elements * map.c_block) + row * map.c_block + (col & (map.c_block - 1));
+// The GEMM of a run: 64 x 64 output tiles, four at a time (one per group of 256 threads, each group with shared-memory
+// panels of its own), through the tile function of the command's own kernel, so every output sees the same k-ascending
+// chain. `variant` was chosen on the host (gemm_formal_variant).
+struct RunPanels {
+  float lhs[kRunThreads / 256][kPanelK][kBlockM + 4];
+  float rhs[kRunThreads / 256][kPanelK][kBlockN + 4];
+};
+__device__ __forceinline__ void run_gemm(const GemmFormalArgs &a, int variant, RunPanels &panels) {
+  const int group = threadIdx.x >> 8, tid = threadIdx.x & 255;
+  const int tiles_n = (a.n + kBlockN - 1) / kBlockN, tiles = ((a.m + kBlockM - 1) / kBlockM) * tiles_n;
+  for (int first = 0; first < tiles; first += kRunThreads / 256) {
+    const int tile = first + group;
+    const bool active = tile < tiles;
+    const int row0 = active ? (tile / tiles_n) * kBlockM : 0, col0 = active ? (tile % tiles_n) * kBlockN : 0;
+    if (variant == 3) gemm_formal_tile<true, true, true>(a, 0, row0, col0, tid, active, panels.lhs[group], panels.rhs[group]);
+    else if (variant == 2) gemm_formal_tile<true, true, false>(a, 0, row0, col0, tid, active, panels.lhs[group], panels.rhs[group]);
+    else gemm_formal_tile<false, false, false>(a, 0, row0, col0, tid, active, panels.lhs[group], panels.rhs[group]);
   }
-  return map.cx_blocks * map.block_outer_elements * map.c_block + row * map.c0 + (col - full_c);
 }
 
-__device__ __forceinline__ void run_gemm(const GemmFormalArgs &a) {
-  const int64_t outputs = static_cast<int64_t>(a.m) * a.n;
-  for (int64_t index = threadIdx.x; index < outputs; index += kRunThreads) {
-    const int64_t row = index / a.n, col = index - row * a.n;
-    float acc = 0.0f;
-    for (int k = 0; k < a.k; ++k) {
-      const int64_t lhs_at = a.lhs_transposed ? run_matrix_index(a.lhs_map, k, a.m, row) : run_matrix_index(a.lhs_map, row, a.k, k);
-      const int64_t rhs_at = a.rhs_transposed ? run_matrix_index(a.rhs_map, col, a.k, k) : run_matrix_index(a.rhs_map, k, a.n, col);
-      acc = __fmaf_rn(widen_bits(load_element_bits(a.lhs, lhs_at, a.in_format), a.in_format),
-                      widen_bits(load_element_bits(a.rhs, rhs_at, a.in_format), a.in_format), acc);
+// An elementwise command of a run. The arithmetic family on float operands takes the instantiation with the operation
+// and format fixed at compile time, as in the command's own kernel (a few dozen instructions per element instead of the
+// generic evaluator's decision tree); everything else takes the generic one.
+template <int kOp>
+__device__ __noinline__ uint32_t run_elementwise_op(const RunElementwise &e, int vector) {
+  if (e.in_format == WB200_F32)
+    return formal_elementwise_groups<true, kOp, WB200_F32>(e.op, e.in_format, e.out_format, e.input_count, e.in0, e.in1, e.dst, e.in_map, e.out_map,
+                                                           e.rhs, vector, threadIdx.x, kRunThreads);
+  if (e.in_format == WB200_BF16)
+    return formal_elementwise_groups<true, kOp, WB200_BF16>(e.op, e.in_format, e.out_format, e.input_count, e.in0, e.in1, e.dst, e.in_map, e.out_map,
+                                                            e.rhs, vector, threadIdx.x, kRunThreads);
+  return formal_elementwise_groups<true, kOp, WB200_F16>(e.op, e.in_format, e.out_format, e.input_count, e.in0, e.in1, e.dst, e.in_map, e.out_map,
+                                                         e.rhs, vector, threadIdx.x, kRunThreads);
+}
+__device__ __noinline__ uint32_t run_elementwise_generic(const RunElementwise &e, int vector) {
+  return formal_elementwise_groups<true, -1, 0>(e.op, e.in_format, e.out_format, e.input_count, e.in0, e.in1, e.dst, e.in_map, e.out_map, e.rhs,
+                                                vector, threadIdx.x, kRunThreads);
+}
+__device__ __forceinline__ uint32_t run_elementwise(const RunElementwise &e, int vector) {
+  if (is_float_format(e.in_format)) {
+    switch (e.op) {
+      case WB200_EW_MAX: return run_elementwise_op<WB200_EW_MAX>(e, vector);
+      case WB200_EW_MIN: return run_elementwise_op<WB200_EW_MIN>(e, vector);
+      case WB200_EW_ADD: return run_elementwise_op<WB200_EW_ADD>(e, vector);
+      case WB200_EW_SUB: return run_elementwise_op<WB200_EW_SUB>(e, vector);
+      case WB200_EW_MUL: return run_elementwise_op<WB200_EW_MUL>(e, vector);
+      default: break;
     }
-    if (a.has_psum) acc = __fadd_rn(acc, __uint_as_float(load_element_bits(a.psum, run_matrix_index(a.psum_map, row, a.n, col), WB200_F32)));
-    store_element_bits(a.dst, run_matrix_index(a.dst_map, row, a.n, col), a.out_format, narrow_bits(acc, a.out_format));
   }
+  return run_elementwise_generic(e, vector);
 }
 
 __device__ __forceinline__ uint32_t run_reduce(const RunReduce &r) {
@@ -907,6 +931,7 @@ __device__ __forceinline__ uint32_t run_reduce(const RunReduce &r) {
 }
 
 __global__ void __launch_bounds__(kRunThreads) formal_run_kernel(const __grid_constant__ FormalRun run, uint32_t *flags_word) {
+  __shared__ __align__(16) RunPanels panels;
   uint32_t flags = 0;
 #pragma unroll 1
   for (int c = 0; c < run.count; ++c) {
@@ -914,12 +939,11 @@ __global__ void __launch_bounds__(kRunThreads) formal_run_kernel(const __grid_co
     if (command.kind == WB200_RUN_ELEMENTWISE) {
       const RunElementwise &e = command.u.elementwise;
       const int vector = ((reinterpret_cast<uintptr_t>(e.in0) | reinterpret_cast<uintptr_t>(e.in1) | reinterpret_cast<uintptr_t>(e.dst)) & 15) == 0;
-      flags |= formal_elementwise_groups<true, -1, 0>(e.op, e.in_format, e.out_format, e.input_count, e.in0, e.in1, e.dst, e.in_map, e.out_map,
-                                                      e.rhs, vector, threadIdx.x, kRunThreads);
+      flags |= run_elementwise(e, vector);
     } else if (command.kind == WB200_RUN_REDUCE) {
       flags |= run_reduce(command.u.reduce);
     } else {
-      run_gemm(command.u.gemm);
+      run_gemm(command.u.gemm, command.variant, panels);
     }
     __syncthreads();   // the next command may read anything this one wrote
   }
