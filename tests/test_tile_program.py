@@ -505,7 +505,9 @@ def test_elementwise_chain_is_fused_and_matches_the_unfused_replay_and_the_cpu(b
 @pytest.mark.gpu
 def test_attention_step_run_is_one_launch_and_matches_the_unfused_replay_and_the_cpu(backend, monkeypatch):
     (want_out, want_m, want_l), want_flags, _ = _attention_cpu_replay(TileProgram([ATTENTION], spm_bytes=1 << 17))
+    monkeypatch.setenv("WB200_REPLAY_RUNS", "1")     # command runs are opt-in: read when the program is loaded
     fused = TileProgram([ATTENTION], backend, spm_bytes=1 << 17)
+    monkeypatch.delenv("WB200_REPLAY_RUNS")
     monkeypatch.setenv("WB200_REPLAY_FUSE", "0")
     unfused = TileProgram([ATTENTION], backend, spm_bytes=1 << 17)
     monkeypatch.delenv("WB200_REPLAY_FUSE")

@@ -589,6 +589,19 @@ formal_elementwise_groups(int runtime_op, int runtime_format, int out_format, in
   const int in_bytes = format_bits(in_format) / 8, out_bytes = format_bits(out_format) / 8;   // 0 for Bool
   const bool same_rhs = input_count > 1 && rhs.mode == WB200_RHS_SAME;
   const bool scalar_rhs = input_count > 1 && rhs.mode == WB200_RHS_SCALAR;   // decided once, not per element
+  if (kOp < 0 && mpfr_family) {
+    // The correctly rounded functions cost hundreds to thousands of instructions per element: one element per thread
+    // and step (first_group / group_stride are then the thread's index and the thread count), so that a short vector
+    // spreads over as many threads as it has elements. Unary, float in and out: no Bool packing to respect.
+    for (int64_t i = first_group; i < total; i += stride) {
+      const uint32_t a = kLinear ? load_element_bits(in0, i, in_format) : formal_load(in0, in_format, in_map, i);
+      uint32_t element_flags = 0;
+      const uint32_t value = formal_mpfr_scalar(op, in_format, a, &element_flags);
+      flags |= element_flags;
+      store_element_bits(dst, kLinear ? i : physical_index(out_map, i), out_format, value);
+    }
+    return flags;
+  }
   for (int64_t g = first_group; g < groups; g += stride) {
     const int64_t first = g * 8;
     const int count = total - first < 8 ? static_cast<int>(total - first) : 8;
@@ -852,17 +865,27 @@ formal_reduce_kernel(int op, int format, const uint8_t *src, uint8_t *dst, const
 }
 
 // ------------------------------------------------------------------------------------------------ command runs
-// One launch for a run of formal commands of one Tile (FormalRun). A single block of kRunThreads threads executes the
-// commands in issue order with a block barrier after each, so a command reads what earlier commands of the run wrote
-// (same SM: its L1 sees its own stores). Elementwise commands and reductions go through the very device functions of
-// their own kernels; the GEMM is the formal chain of gemm_formal.cu written for one thread per output:
+// One launch for a run of formal commands of one Tile (FormalRun). A cluster of kRunCtas thread blocks of kRunThreads
+// threads executes the commands in issue order with a cluster barrier (release / acquire at cluster scope) after each,
+// so a command reads what earlier commands of the run wrote, whichever block wrote it. A cluster is co-scheduled by the
+// hardware, so its blocks may wait for one another. Elementwise commands and reductions go through the very device
+// functions of their own kernels, spread over the cluster's threads; the GEMM is the formal chain of gemm_formal.cu written for one thread per output:
 //   acc = +0; for k ascending: acc = fma(widen(lhs), widen(rhs), acc); [acc = acc + psum;] dst = narrow(acc)
 // (lib/Wafer/Simulator/Reference/Numeric/FormalTensorNumeric.cpp:271-361) through the tile function of gemm_formal.cuh, so
 // every destination gets the bits the command-by-command replay gives it.
 constexpr int kRunThreads = 512;   // 128 registers per thread: the formal evaluators need them
+constexpr int kRunCtas = 8;        // one cluster (the portable maximum)
+__device__ __forceinline__ uint32_t run_cta_rank() {
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  return rank;
+}
+__device__ __forceinline__ void run_cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 
-// The GEMM of a run: 64 x 64 output tiles, four at a time (one per group of 256 threads, each group with shared-memory
-// panels of its own), through the tile function of the command's own kernel, so every output sees the same k-ascending
+// The GEMM of a run: 64 x 64 output tiles, sixteen at a time (one per group of 256 threads of the cluster, each group with
+// shared-memory panels of its own), through the tile function of the command's own kernel, so every output sees the same k-ascending
 // chain. `variant` was chosen on the host (gemm_formal_variant).
 struct RunPanels {
   float lhs[kRunThreads / 256][kPanelK][kBlockM + 4];
@@ -870,9 +893,10 @@ struct RunPanels {
 };
 __device__ __forceinline__ void run_gemm(const GemmFormalArgs &a, int variant, RunPanels &panels) {
   const int group = threadIdx.x >> 8, tid = threadIdx.x & 255;
+  const int cluster_group = static_cast<int>(run_cta_rank()) * (kRunThreads / 256) + group;
   const int tiles_n = (a.n + kBlockN - 1) / kBlockN, tiles = ((a.m + kBlockM - 1) / kBlockM) * tiles_n;
-  for (int first = 0; first < tiles; first += kRunThreads / 256) {
-    const int tile = first + group;
+  for (int first = 0; first < tiles; first += kRunCtas * (kRunThreads / 256)) {
+    const int tile = first + cluster_group;
     const bool active = tile < tiles;
     const int row0 = active ? (tile / tiles_n) * kBlockM : 0, col0 = active ? (tile % tiles_n) * kBlockN : 0;
     if (variant == 3) gemm_formal_tile<true, true, true>(a, 0, row0, col0, tid, active, panels.lhs[group], panels.rhs[group]);
@@ -888,16 +912,16 @@ template <int kOp>
 __device__ __noinline__ uint32_t run_elementwise_op(const RunElementwise &e, int vector) {
   if (e.in_format == WB200_F32)
     return formal_elementwise_groups<true, kOp, WB200_F32>(e.op, e.in_format, e.out_format, e.input_count, e.in0, e.in1, e.dst, e.in_map, e.out_map,
-                                                           e.rhs, vector, threadIdx.x, kRunThreads);
+                                                           e.rhs, vector, run_cta_rank() * kRunThreads + threadIdx.x, kRunCtas * kRunThreads);
   if (e.in_format == WB200_BF16)
     return formal_elementwise_groups<true, kOp, WB200_BF16>(e.op, e.in_format, e.out_format, e.input_count, e.in0, e.in1, e.dst, e.in_map, e.out_map,
-                                                            e.rhs, vector, threadIdx.x, kRunThreads);
+                                                            e.rhs, vector, run_cta_rank() * kRunThreads + threadIdx.x, kRunCtas * kRunThreads);
   return formal_elementwise_groups<true, kOp, WB200_F16>(e.op, e.in_format, e.out_format, e.input_count, e.in0, e.in1, e.dst, e.in_map, e.out_map,
-                                                         e.rhs, vector, threadIdx.x, kRunThreads);
+                                                         e.rhs, vector, run_cta_rank() * kRunThreads + threadIdx.x, kRunCtas * kRunThreads);
 }
 __device__ __noinline__ uint32_t run_elementwise_generic(const RunElementwise &e, int vector) {
   return formal_elementwise_groups<true, -1, 0>(e.op, e.in_format, e.out_format, e.input_count, e.in0, e.in1, e.dst, e.in_map, e.out_map, e.rhs,
-                                                vector, threadIdx.x, kRunThreads);
+                                                vector, run_cta_rank() * kRunThreads + threadIdx.x, kRunCtas * kRunThreads);
 }
 __device__ __forceinline__ uint32_t run_elementwise(const RunElementwise &e, int vector) {
   if (is_float_format(e.in_format)) {
@@ -917,7 +941,7 @@ __device__ __forceinline__ uint32_t run_reduce(const RunReduce &r) {
   uint32_t flags = 0;
   const bool nhwc = r.src_map.layout == WB200_LAYOUT_NCX && r.dst_map.layout == WB200_LAYOUT_NCX && r.src_map.rank == 4 && r.dst_map.rank == 4;
   if (!nhwc) return flags;   // formal_run_admits lets nothing else in
-  for (int64_t out = threadIdx.x; out < r.dst_map.element_count; out += kRunThreads) {
+  for (int64_t out = run_cta_rank() * kRunThreads + threadIdx.x; out < r.dst_map.element_count; out += kRunCtas * kRunThreads) {
 #define WB200_RUN_REDUCE(COMBINE)                                                                                                  \
     if (r.format == WB200_F32) flags |= formal_reduce_nhwc_output<COMBINE, WB200_F32>(r.src, r.dst, r.src_map, r.dst_map, r.reduced_mask, out);   \
     else if (r.format == WB200_BF16) flags |= formal_reduce_nhwc_output<COMBINE, WB200_BF16>(r.src, r.dst, r.src_map, r.dst_map, r.reduced_mask, out); \
@@ -930,12 +954,22 @@ __device__ __forceinline__ uint32_t run_reduce(const RunReduce &r) {
   return flags;
 }
 
-__global__ void __launch_bounds__(kRunThreads) formal_run_kernel(const __grid_constant__ FormalRun run, uint32_t *flags_word) {
+__global__ void __cluster_dims__(kRunCtas, 1, 1) __launch_bounds__(kRunThreads) formal_run_kernel(const __grid_constant__ FormalRun run, uint32_t *flags_word) {
   __shared__ __align__(16) RunPanels panels;
+  // The command being executed, copied from the parameter space: its fields are read inside the inner loops, and a
+  // dynamically indexed kernel parameter costs a constant-bank load per use.
+  __shared__ __align__(16) unsigned char command_storage[sizeof(RunCommand)];
+  const RunCommand &command = *reinterpret_cast<const RunCommand *>(command_storage);
+  static_assert(sizeof(RunCommand) % 4 == 0, "copied as 32-bit words");
   uint32_t flags = 0;
 #pragma unroll 1
   for (int c = 0; c < run.count; ++c) {
-    const RunCommand &command = run.command[c];
+    {
+      const uint32_t *from = reinterpret_cast<const uint32_t *>(&run.command[c]);
+      uint32_t *to = reinterpret_cast<uint32_t *>(command_storage);
+      for (int w = threadIdx.x; w < static_cast<int>(sizeof(RunCommand) / 4); w += kRunThreads) to[w] = from[w];
+    }
+    __syncthreads();
     if (command.kind == WB200_RUN_ELEMENTWISE) {
       const RunElementwise &e = command.u.elementwise;
       const int vector = ((reinterpret_cast<uintptr_t>(e.in0) | reinterpret_cast<uintptr_t>(e.in1) | reinterpret_cast<uintptr_t>(e.dst)) & 15) == 0;
@@ -945,7 +979,7 @@ __global__ void __launch_bounds__(kRunThreads) formal_run_kernel(const __grid_co
     } else {
       run_gemm(command.u.gemm, command.variant, panels);
     }
-    __syncthreads();   // the next command may read anything this one wrote
+    run_cluster_barrier();   // the next command may read anything this one wrote, in any block
   }
   merge_block_flags(flags_word, flags);
 }
@@ -1071,7 +1105,10 @@ wb200_status launch_elementwise_formal(int op, int in_format, int out_format, in
                                        uint8_t *dst, const LayoutMap &in_map, const LayoutMap &out_map, uint32_t *flags_word,
                                        cudaStream_t stream, RhsBroadcast rhs) {
   auto linear_layout = [](const LayoutMap &m) { return m.layout == WB200_LAYOUT_TENSOR || m.layout == WB200_LAYOUT_NTENSOR; };
-  const int64_t groups = (out_map.element_count + 7) / 8;
+  const bool function_family = op == WB200_EW_SQRT || op == WB200_EW_RSQRT || (op >= WB200_EW_LOG2 && op <= WB200_EW_EXP) ||
+                               (op >= WB200_EW_SIN && op <= WB200_EW_SIGMOID) || op == WB200_EW_SOFTPLUS;
+  // a thread takes eight consecutive elements, or one at a time for the correctly rounded functions
+  const int64_t groups = function_family ? out_map.element_count : (out_map.element_count + 7) / 8;
   int64_t blocks = (groups + kThreads - 1) / kThreads;
   blocks = blocks < 1 ? 1 : blocks > 148 * 32 ? 148 * 32 : blocks;
   const int grid = static_cast<int>(blocks);
@@ -1143,7 +1180,7 @@ wb200_status launch_formal_run(const FormalRun &run, uint32_t *flags_word, cudaS
   if (run.count < 1 || run.count > kMaxRunCommands) return fail(WB200_ERR_INVALID_ARGUMENT, "malformed command run");
   for (int c = 0; c < run.count; ++c)
     if (!formal_run_admits(run.command[c])) return fail(WB200_ERR_INVALID_ARGUMENT, "command outside the domain of a command run");
-  formal_run_kernel<<<1, kRunThreads, 0, stream>>>(run, flags_word);
+  formal_run_kernel<<<kRunCtas, kRunThreads, 0, stream>>>(run, flags_word);
   WB200_CUDA_CHECK(cudaGetLastError());
   return WB200_OK;
 }

@@ -694,6 +694,8 @@ struct wb200_tile_program {
   uint64_t next_event = 1;
   bool execute = false;
   bool fuse_chains = true;   // WB200_REPLAY_FUSE=0 in the environment issues every elementwise command as its own launch
+  bool fuse_runs = false;    // WB200_REPLAY_RUNS=1 issues runs of GEMM / reduce / elementwise commands as one launch each (measured
+                             // slower than one launch per command under the graph, so it is not the default)
   uint32_t gemm_policy = WB200_GEMM_FORMAL;
   wb200_program_stats stats{};
   std::vector<wb200_program_command> *trace = nullptr;
@@ -1127,7 +1129,7 @@ wb200_status execute_call(wb200_tile_program *program, int tile_index, const Ins
   *result = 0;
   const bool elementwise = inst.command == kElementwiseUnary || inst.command == kElementwiseBinary || inst.command == kElementwiseLogic;
   const bool run_starter = inst.command == kGemm || inst.command == kGemmOriented || inst.command == kReduce;
-  const bool runs = program->execute && program->fuse_chains;
+  const bool runs = program->execute && program->fuse_chains && program->fuse_runs;
   // Held-back commands precede this one, unless it may join them: a GEMM or a reduction joins (or opens) a command run,
   // an elementwise command joins an open run or the elementwise chain.
   if (!elementwise && !(run_starter && runs && tile.run.run.count > 0) && (st = flush_chain(program, tile_index)) != WB200_OK) return st;
@@ -1558,6 +1560,7 @@ wb200_status wb200_tile_program_load(wb200_backend *backend, const char *const *
   program->backend = backend;
   program->spm_bytes = spm_bytes ? spm_bytes : kDefaultSpmBytes;
   { const char *env = getenv("WB200_REPLAY_FUSE"); program->fuse_chains = !(env && env[0] == '0'); }
+  { const char *env = getenv("WB200_REPLAY_RUNS"); program->fuse_runs = env && env[0] == '1'; }
   program->tiles.resize(tile_count);
   std::vector<bool> seen(tile_count, false);
   for (uint32_t i = 0; i < tile_count; ++i) {
