@@ -480,6 +480,11 @@ typedef struct wb200_switch_sum_params {
   void *signals[WB200_MAX_EXCHANGE_RANKS];
   uint32_t *epoch;
   void *stream;
+  void *multicast_out;         /* optional: multicast address (same allocation rules) the sums are stored to instead of the
+                                  buffer itself */
+  const void *residual;        /* optional: this rank's device copy of a tensor of the same extent and format, identical on
+                                  every rank, added to the sums before the store: out = round(sum + residual). The decoder
+                                  layer's residual adds ride in the sum this way */
 } wb200_switch_sum_params;
 uint64_t wb200_switch_sum_signal_bytes(uint32_t world);
 wb200_status wb200_switch_sum(wb200_backend *backend, const wb200_switch_sum_params *params);

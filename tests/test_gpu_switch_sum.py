@@ -56,6 +56,23 @@ def _worker(rank, world, port, results):
                 gathered = [torch.empty_like(region) for _ in range(world)]
                 dist.all_gather(gathered, region.clone())
                 identical = identical and all(torch.equal(gathered[0], g) for g in gathered)
+        # sum + residual stored to another region: the residual is the same tensor on every rank
+        elements = 8 * 4099
+        region = buffer[4096:4096 + elements * 2].view(torch.bfloat16)
+        target = buffer[(24 << 20):(24 << 20) + elements * 2].view(torch.bfloat16)
+        region.copy_(_rank_values(rank, elements, torch.bfloat16, device))
+        residual = _rank_values(1000, elements, torch.bfloat16, device)
+        torch.cuda.synchronize()
+        dist.barrier()
+        sums(region, residual=residual, out=target)
+        torch.cuda.synchronize()
+        backend.poll()
+        dist.barrier()
+        total = sum(_rank_values(r, elements, torch.bfloat16, device).double() for r in range(world))
+        want = (total.to(torch.bfloat16).float() + residual.float()).to(torch.bfloat16)       # the sum is rounded, then the add
+        close = (target.double() - want.double()).abs().max() / want.double().abs().max()
+        report["residual_rel_err"] = float(close)
+        report["partials_kept"] = bool(torch.equal(region, _rank_values(rank, elements, torch.bfloat16, device)))
         report["max_rel_err"], report["identical"] = worst, identical
         # the decoder layer with the switch doing its sums against the same layer with the library all-reduce
         cfg = LayerConfig(d_model=1024, q_heads=8, kv_heads=4, head_dim=128, ffn=2048)
@@ -92,5 +109,6 @@ def test_switch_sum_matches_a_float64_sum_on_every_rank():
         pytest.skip("these GPUs offer no NVLink multicast")
     assert results["identical"]
     assert results["max_rel_err"] <= 2.0 ** -7        # one rounding to 16 bits of an f32 sum
+    assert results["residual_rel_err"] <= 2.0 ** -6 and results["partials_kept"]
     assert results["layer_used_switch"]
     assert results["layer_rel_err"] <= 1e-2

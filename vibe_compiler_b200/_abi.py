@@ -120,7 +120,7 @@ ALLREDUCE_FN = C.CFUNCTYPE(C.c_int32, C.c_void_p, C.c_void_p, C.c_uint64, C.c_ui
 class SwitchSumParams(C.Structure):
     _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("multicast", C.c_void_p), ("elements", C.c_uint64),
                 ("format", C.c_uint32), ("blocks", C.c_uint32), ("signals", C.c_void_p * 16), ("epoch", C.c_void_p),
-                ("stream", C.c_void_p)]
+                ("stream", C.c_void_p), ("multicast_out", C.c_void_p), ("residual", C.c_void_p)]
 
 
 class DecoderLayerParams(C.Structure):

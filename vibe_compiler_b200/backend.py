@@ -398,10 +398,13 @@ class B200TargetModelBackend:
         return int(self._lib.wb200_switch_sum_signal_bytes(world))
 
     def switch_sum(self, multicast_pointer: int, elements: int, dtype, *, rank: int, signal_pointers: Sequence[int],
-                   epoch: torch.Tensor, blocks: int = 0, stream: Optional[int] = None) -> None:
+                   epoch: torch.Tensor, blocks: int = 0, stream: Optional[int] = None, multicast_out: int = 0,
+                   residual: Optional[torch.Tensor] = None) -> None:
         """In-place sum over the ranks of the buffer at `multicast_pointer` (an NVLink multicast address of a symmetric
         allocation) by one kernel per GPU: the switch adds and broadcasts (wb200_switch_sum). `signal_pointers[r]` are
-        rank r's signal words as addressable from this GPU; `epoch` a zeroed int32[2] of this rank."""
+        rank r's signal words as addressable from this GPU; `epoch` a zeroed int32[2] of this rank. `multicast_out`: store
+        the sums there instead of in place; `residual`: this rank's copy of a tensor (identical on every rank) that is
+        added to the sums before the store."""
         if stream is None:
             stream = torch.cuda.current_stream().cuda_stream
         x = abi.SwitchSumParams()
@@ -410,6 +413,8 @@ class B200TargetModelBackend:
         for r, pointer in enumerate(signal_pointers):
             x.signals[r] = pointer
         x.epoch, x.stream = epoch.data_ptr(), stream
+        x.multicast_out = multicast_out or None
+        x.residual = residual.data_ptr() if residual is not None else None
         self._check(self._lib.wb200_switch_sum(self._handle, C.byref(x)))
 
     def attention_fd_merge(self, states, like_q, *, out=None, lse=None, zero_fully_masked: bool = False,

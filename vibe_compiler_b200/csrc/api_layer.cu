@@ -78,6 +78,9 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
       if (!switch_sum->signals[r]) return fail(WB200_ERR_INVALID_ARGUMENT, "switch_sum needs every rank's signal words");
   }
   const bool has_sum = p->allreduce || switch_sum;
+  // WB200_LAYER_FUSED_RESIDUAL=0 in the environment keeps the residual adds as kernels of their own beside the library's sum.
+  static const bool fuse_residual_enabled = []() { const char *env = getenv("WB200_LAYER_FUSED_RESIDUAL"); return !(env && env[0] == '0'); }();
+  const bool fused_residual = switch_sum && fuse_residual_enabled;
   const uint32_t parts = (p->micro_batches > 1 && has_sum) ? p->micro_batches : 1;
   if (parts > 1 && (p->batch % parts != 0 || ((static_cast<uint64_t>(p->batch / parts) * p->seq) % 8) != 0))
     return fail(WB200_ERR_INVALID_ARGUMENT, "micro_batches must divide the batch into parts of a multiple of 8 tokens");
@@ -138,6 +141,10 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
   };
   // The sum over shards of a part's partial output: ordered after the part's kernels by an event, enqueued on the
   // communication stream; `done` is recorded behind it for the kernels that consume the sum.
+  // With the library's own sum the residual add rides in the sum kernel: the owner of a slice adds its copy of the
+  // residual to the switch's sum and stores round(residual + sum) - phase 0: x1 = x + attention, into the x1 buffer;
+  // phase 1: x1 + FFN, in place - so the layer's residual add kernels (three passes over [tokens, d_model] each) are
+  // not launched. The arithmetic is that of the add kernel, bit for bit.
   auto reduce = [&](const Part &part, int phase) -> wb200_status {
     if (!has_sum) return WB200_OK;
     if (parts > 1) {
@@ -148,10 +155,16 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
     if (switch_sum) {
       // the library's own sum: the switch adds and broadcasts the part's region of the (symmetric) workspace
       uint8_t *multicast = static_cast<uint8_t *>(switch_sum->multicast) + (part.partial - static_cast<uint8_t *>(p->workspace));
+      uint8_t *multicast_out = multicast;
+      const void *residual = nullptr;
+      if (fused_residual) {
+        if (phase == 0) multicast_out = static_cast<uint8_t *>(switch_sum->multicast) + (part.x1 - static_cast<uint8_t *>(p->workspace));
+        residual = phase == 0 ? static_cast<const void *>(part.x) : static_cast<const void *>(part.x1);
+      }
       const int blocks = switch_sum->blocks ? static_cast<int>(switch_sum->blocks) : (p->reserved_sms ? static_cast<int>(p->reserved_sms) : 32);
       wb200_status s = launch_switch_sum(multicast, static_cast<uint64_t>(tokens) * d, p->format, static_cast<int>(switch_sum->rank),
                                          static_cast<int>(switch_sum->world), switch_sum->signals, switch_sum->epoch, blocks,
-                                         backend->d_status, comm_stream);
+                                         backend->d_status, comm_stream, multicast_out, residual);
       if (s != WB200_OK) return s;
       backend->launches += 1;
     } else if (p->allreduce(p->allreduce_user, part.partial, static_cast<uint64_t>(tokens) * d, p->format, comm_stream) != 0) {
@@ -192,8 +205,10 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
   auto ffn_phase = [&](const Part &part) -> wb200_status {
     wb200_status s;
     if ((s = await_sum(part, 0)) != WB200_OK) return s;
-    if ((s = launch_residual_add(fmt, part.x, part.partial, part.x1, static_cast<size_t>(tokens) * d, part.stream)) != WB200_OK) return s;
-    backend->launches += 1;
+    if (!fused_residual) {
+      if ((s = launch_residual_add(fmt, part.x, part.partial, part.x1, static_cast<size_t>(tokens) * d, part.stream)) != WB200_OK) return s;
+      backend->launches += 1;
+    }
     if ((s = launch_rmsnorm(fmt, part.x1, p->norm2, part.h, tokens, d, p->eps, part.stream)) != WB200_OK) return s;
     backend->launches += 1;
     if ((s = gemm(part.stream, part.h, p->wgu, part.act, tokens, 2 * static_cast<int>(p->ffn), d, WB200_EPI_SWIGLU)) != WB200_OK) return s;
@@ -203,6 +218,10 @@ wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_lay
   auto final_residual = [&](const Part &part) -> wb200_status {
     wb200_status s;
     if ((s = await_sum(part, 1)) != WB200_OK) return s;
+    if (fused_residual) {   // the sum kernel left x1 + FFN in the partial buffer
+      WB200_CUDA_CHECK(cudaMemcpyAsync(part.out, part.partial, static_cast<size_t>(tokens) * d * e, cudaMemcpyDeviceToDevice, part.stream));
+      return WB200_OK;
+    }
     if ((s = launch_residual_add(fmt, part.x1, part.partial, part.out, static_cast<size_t>(tokens) * d, part.stream)) != WB200_OK) return s;
     backend->launches += 1;
     return WB200_OK;

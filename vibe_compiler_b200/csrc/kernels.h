@@ -216,8 +216,11 @@ wb200_status launch_attention_fd_exchange(const AttentionArgs &args, uint32_t sp
 // (switch_sum.cu): in place, every rank ends with the same sums. `signals` holds every rank's 2 * world zero-initialised
 // signal words (peer-mapped), `epoch` this rank's pair of zero-initialised words.
 constexpr int kMaxSwitchRanks = 16;
+// `multicast_out` (null: in place) is the multicast address the sums are stored to; `residual` (null: none) is this rank's
+// copy of a tensor of the same extent that is added to the sums before the store (round(sum + residual), one rounding).
 wb200_status launch_switch_sum(void *multicast, uint64_t elements, int format, int rank, int world, void *const *signals,
-                               unsigned int *epoch, int blocks, int *device_status, cudaStream_t stream);
+                               unsigned int *epoch, int blocks, int *device_status, cudaStream_t stream, void *multicast_out = nullptr,
+                               const void *residual = nullptr);
 
 
 // ---- decoder-layer pieces (layer_ops.cu); device pointers, bf16 / f16 storage

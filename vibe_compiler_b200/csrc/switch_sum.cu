@@ -20,6 +20,8 @@
 // its buffer has landed. All waits are bounded (about a second); a wait that runs out sets the backend's status word
 // and the kernel carries on to its end, so a missing peer costs a second and an error, never a hung GPU.
 // One sequence of launches per signal area: sums that may run concurrently need areas of their own.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
@@ -41,6 +43,8 @@ constexpr int kSwitchSmemBytes = 120 * 1024;
 
 struct SwitchSumParams {
   uint8_t *multicast;                        // multicast address of the buffer
+  uint8_t *multicast_out;                    // multicast address the sums are stored to (the buffer itself: in place)
+  const uint8_t *residual;                   // optional: this rank's copy of a tensor added to the sums before the store
   uint64_t chunks;                           // 16-byte chunks in the buffer
   int format;
   int rank, world;
@@ -81,6 +85,29 @@ __device__ __forceinline__ uint4 switch_load_sum(const uint8_t *address) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(address) : "memory");
   return v;
 }
+// sums + residual, element by element: widened to f32, added, rounded once to the storage format (the arithmetic of the
+// layer's residual add kernel, so fusing the add into the sum changes no bit).
+template <int kFormat>
+__device__ __forceinline__ uint4 add_residual(const uint4 &sums, const uint4 &residual) {
+  const uint32_t a[4] = {sums.x, sums.y, sums.z, sums.w}, b[4] = {residual.x, residual.y, residual.z, residual.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if constexpr (kFormat == WB200_F32) {
+      o[i] = __float_as_uint(__uint_as_float(a[i]) + __uint_as_float(b[i]));
+    } else if constexpr (kFormat == WB200_BF16) {
+      const float lo = __uint_as_float(a[i] << 16) + __uint_as_float(b[i] << 16);
+      const float hi = __uint_as_float(a[i] & 0xffff0000u) + __uint_as_float(b[i] & 0xffff0000u);
+      const __nv_bfloat162 packed = __floats2bfloat162_rn(lo, hi);
+      o[i] = *reinterpret_cast<const uint32_t *>(&packed);
+    } else {
+      const float2 fa = __half22float2(*reinterpret_cast<const __half2 *>(&a[i])), fb = __half22float2(*reinterpret_cast<const __half2 *>(&b[i]));
+      const __half2 packed = __floats2half2_rn(fa.x + fb.x, fa.y + fb.y);
+      o[i] = *reinterpret_cast<const uint32_t *>(&packed);
+    }
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
 __device__ __forceinline__ void switch_store(uint8_t *address, const uint4 &v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(address), "r"(v.x), "r"(v.y), "r"(v.z),
                "r"(v.w) : "memory");
@@ -105,16 +132,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSwitchThreads) swit
   const uint64_t end = begin + per_rank < p.chunks ? begin + per_rank : p.chunks;
   const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kSwitchThreads;
   for (uint64_t base = begin + static_cast<uint64_t>(blockIdx.x) * kSwitchThreads + threadIdx.x; base < end; base += stride * kSwitchUnroll) {
-    uint4 sums[kSwitchUnroll];
+    uint4 sums[kSwitchUnroll], rest[kSwitchUnroll];
 #pragma unroll
-    for (int u = 0; u < kSwitchUnroll; ++u) {
+    for (int u = 0; u < kSwitchUnroll; ++u) {   // all requests of the round are in flight together, the residual's too
       const uint64_t chunk = base + u * stride;
-      if (chunk < end) sums[u] = switch_load_sum<kFormat>(p.multicast + chunk * 16);
+      if (chunk < end) {
+        sums[u] = switch_load_sum<kFormat>(p.multicast + chunk * 16);
+        if (p.residual) rest[u] = __ldcs(reinterpret_cast<const uint4 *>(p.residual + chunk * 16));
+      }
     }
 #pragma unroll
     for (int u = 0; u < kSwitchUnroll; ++u) {
       const uint64_t chunk = base + u * stride;
-      if (chunk < end) switch_store(p.multicast + chunk * 16, sums[u]);
+      if (chunk < end) {
+        if (p.residual) sums[u] = add_residual<kFormat>(sums[u], rest[u]);
+        switch_store(p.multicast_out + chunk * 16, sums[u]);
+      }
     }
   }
 
@@ -141,7 +174,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kSwitchThreads) swit
 }  // namespace
 
 wb200_status launch_switch_sum(void *multicast, uint64_t elements, int format, int rank, int world, void *const *signals,
-                               unsigned int *epoch, int blocks, int *device_status, cudaStream_t stream) {
+                               unsigned int *epoch, int blocks, int *device_status, cudaStream_t stream, void *multicast_out,
+                               const void *residual) {
   if (world < 2 || world > kMaxSwitchRanks || rank < 0 || rank >= world)
     return fail(WB200_ERR_INVALID_ARGUMENT, "the switch sum takes 2 to 16 ranks and a rank inside the world");
   const uint64_t bytes = elements * (format == WB200_F32 ? 4u : 2u);
@@ -150,7 +184,11 @@ wb200_status launch_switch_sum(void *multicast, uint64_t elements, int format, i
   if ((reinterpret_cast<uintptr_t>(multicast) & 15u) || (bytes & 15u) || bytes == 0)
     return fail(WB200_ERR_INVALID_ARGUMENT, "the switch sum takes a 16-byte aligned buffer whose size is a positive multiple of 16 bytes");
   SwitchSumParams p;
+  if ((reinterpret_cast<uintptr_t>(multicast_out) & 15u) || (reinterpret_cast<uintptr_t>(residual) & 15u))
+    return fail(WB200_ERR_INVALID_ARGUMENT, "the switch sum's output and residual must be 16-byte aligned");
   p.multicast = static_cast<uint8_t *>(multicast);
+  p.multicast_out = multicast_out ? static_cast<uint8_t *>(multicast_out) : p.multicast;
+  p.residual = static_cast<const uint8_t *>(residual);
   p.chunks = bytes / 16;
   p.format = format;
   p.rank = rank; p.world = world;
@@ -193,7 +231,7 @@ extern "C" wb200_status wb200_switch_sum(wb200_backend *backend, const wb200_swi
   const int blocks = x->blocks ? static_cast<int>(x->blocks) : 32;
   wb200_status st = launch_switch_sum(x->multicast, x->elements, static_cast<int>(x->format), static_cast<int>(x->rank),
                                       static_cast<int>(x->world), x->signals, x->epoch, blocks, backend->d_status,
-                                      static_cast<cudaStream_t>(x->stream));
+                                      static_cast<cudaStream_t>(x->stream), x->multicast_out, x->residual);
   if (st == WB200_OK) backend->launches += 1;
   return st;
 }

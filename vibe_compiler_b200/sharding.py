@@ -171,10 +171,13 @@ class SwitchSum:
                 return multicast + offset
         raise ValueError("the region does not lie in a buffer made by allocate()")
 
-    def __call__(self, region: torch.Tensor) -> torch.Tensor:
-        if not region.is_contiguous():
-            raise ValueError("the region must be contiguous")
+    def __call__(self, region: torch.Tensor, residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """region <- sum over the ranks of region (+ residual, this rank's copy of a tensor that is the same on every rank);
+        with `out` (inside a buffer made by allocate(), same extent) the result goes there and region keeps the partial sums."""
+        if not region.is_contiguous() or (residual is not None and not residual.is_contiguous()) or (out is not None and not out.is_contiguous()):
+            raise ValueError("the tensors must be contiguous")
         self.backend.switch_sum(self.multicast_of(region), region.numel(), region.dtype, rank=self.rank,
-                                signal_pointers=self.signal_pointers, epoch=self.epoch, blocks=self.blocks)
-        return region
+                                signal_pointers=self.signal_pointers, epoch=self.epoch, blocks=self.blocks,
+                                multicast_out=self.multicast_of(out) if out is not None else 0, residual=residual)
+        return region if out is None else out
 
