@@ -445,7 +445,8 @@ typedef struct wb200_decoder_layer_params {
                                   NVSwitch kernel (wb200_switch_sum, below) without leaving the call. `multicast` is the
                                   multicast address of `workspace`, which must then be a symmetric allocation bound to a
                                   multicast object; rank, world, signals and epoch as for wb200_switch_sum; blocks 0 means
-                                  reserved_sms; elements, format and stream are ignored */
+                                  reserved_sms; elements, format, stream, multicast_out and residual are ignored (the layer
+                                  sets them: its two residual adds are done by the sums, bit-identically) */
 } wb200_decoder_layer_params;
 uint64_t wb200_decoder_layer_workspace_bytes(const wb200_decoder_layer_params *params);
 wb200_status wb200_decoder_layer(wb200_backend *backend, const wb200_decoder_layer_params *params);
