@@ -307,7 +307,8 @@ def layer_extra(backend, args, torch, dist, rank, world, device, peak, failures)
         dist.all_reduce(both, op=dist.ReduceOp.MAX)
         breakdown = {"compute_only_ms": both[0].item(), "nccl_allreduce_128MiB_ms": both[1].item(),
                      "switch_sum_128MiB_ms": both[2].item() if sums is not None else None, "sums_per_step": 2,
-                     "exposed_ms": ms - both[0].item(), "micro_batches": parts or layer.default_micro_batches(LAYER["batch"]), "reserved_sms": reserved}
+                     "exposed_ms": ms - both[0].item(),
+                     "note": "compute_only_ms runs the layer with its sums left out and so with the two residual add kernels, which the timed step folds into its sums", "micro_batches": parts or layer.default_micro_batches(LAYER["batch"]), "reserved_sms": reserved}
         del message
     sum_kind = "one shard" if world == 1 else ("NVSwitch multimem kernel of the library" if layer.switch_sums(blocks=reserved) is not None else "NCCL all-reduce")
     return {"workload": f"decoder layer forward bf16 d4096 32/8 heads hd128 FFN14336, batch 8 x seq 2048, TP{world} (sum over shards after o-proj and down-proj: {sum_kind})",

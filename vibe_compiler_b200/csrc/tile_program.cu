@@ -1304,14 +1304,12 @@ wb200_status execute_call(wb200_tile_program *program, int tile_index, const Ins
                                      reinterpret_cast<unsigned long long *>(program->numeric_words + 2), &program->stats.gpu_launches);
     case kReduce: {
       // (source, destination, dimension, n, h, w, c, format)
-      const uint32_t nhwc[4] = {static_cast<uint32_t>(a[3]), static_cast<uint32_t>(a[4]), static_cast<uint32_t>(a[5]), static_cast<uint32_t>(a[6])};
       record(program, tile_index, inst.command, a, argc, inst.operation);
       if (runs) {
         bool joined = false;
         if ((st = join_run(program, tile_index, inst.command, inst.operation, a, &joined)) != WB200_OK || joined) return st;
       }
       return issue_run_command(program, tile_index, inst.command, inst.operation, a, nullptr, nullptr);
-      (void)nhwc;
     }
     case kConvert: {
       // (source, destination, count, zero point, rounding mode)
