@@ -339,7 +339,7 @@ def run_reference(args):
     seconds = sum(t_all) / len(t_all)
     value = flops / seconds / 1e12
     line = {"impl": "reference", "metric": "fa_prefill_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "weak",
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": seconds * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "FA prefill bf16 B4 H32 S4096 D128 causal", "sample": sample},
             "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
