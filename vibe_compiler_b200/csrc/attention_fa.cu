@@ -90,6 +90,10 @@ __device__ __forceinline__ void setmaxnreg_dec() {
 // 2^x on the FMA pipe for x <= 0: x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-3 polynomial (maximum
 // relative error 7.5e-5, far below the rounding of P to 16 bits), 2^n by adding n to the exponent field. x is clamped at
 // -126, so the result is never exactly zero: tiles that hold masked (-inf) scores use the hardware ex2 throughout.
+#ifndef WB200_FA_POLY_PERIOD
+#define WB200_FA_POLY_PERIOD 4
+#endif
+constexpr int kPolyPeriod = WB200_FA_POLY_PERIOD;   // one pair of exponentials in kPolyPeriod runs on the FMA pipe
 __device__ __forceinline__ float ex2_poly(float x) {
   x = fmaxf(x, -126.0f);
   const float shifted = x + 12582912.0f;                 // 1.5 * 2^23: the low mantissa bits now hold n
@@ -496,7 +500,7 @@ fa_umma_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant
           unpack_f32x2(x2, x0, x1);
           // Every fourth pair of exponentials runs on the FMA pipe: the special-function pipe (ex2 and the 16-bit
           // conversions) is the busiest unit of the softmax warps.
-          const bool poly = !kMasked && ((i >> 1) & 3) == 3;
+          const bool poly = !kMasked && ((i >> 1) % kPolyPeriod) == kPolyPeriod - 1;
           const float e0 = poly ? ex2_poly(x0) : ex2_approx(x0);
           const float e1 = poly ? ex2_poly(x1) : ex2_approx(x1);
           sum2[(i >> 1) & 3] = add_f32x2(sum2[(i >> 1) & 3], pack_f32x2(e0, e1));
