@@ -426,11 +426,26 @@ __device__ void fd_exchange_rows(const FdTailParams &x, const float *records, in
     const int row = first_row + base + warp;
     const bool active = warp < count;
     if (active) {
-      // fold this rank's splits (records of other CTAs: read past L1), four records in flight
+      // fold this rank's splits (records of other CTAs: read past L1), twelve records in flight: the fold is a chain
+      // of L2 round trips otherwise (a single resident wave of a long sequence has 37 splits per head)
       const float *rec = records + static_cast<size_t>(row) * splits * kRecord;
       float m = __ldcg(rec + kD), l = __ldcg(rec + kD + 1);
       float4 a = ldcg_quad(rec + 4 * lane);
       int s = 1;
+      constexpr int kBatch = 12;
+      for (; s + kBatch <= splits; s += kBatch) {
+        float mr[kBatch], lr[kBatch];
+        float4 ar[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+          const float *right = rec + static_cast<size_t>(s + u) * kRecord;
+          const float2 ml = __ldcg(reinterpret_cast<const float2 *>(right + kD));
+          mr[u] = ml.x; lr[u] = ml.y;
+          ar[u] = ldcg_quad(right + 4 * lane);
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) fd_merge_right(m, l, a, mr[u], lr[u], ar[u]);
+      }
       for (; s + 4 <= splits; s += 4) {
         float mr[4], lr[4];
         float4 ar[4];
@@ -491,7 +506,16 @@ __device__ void fd_exchange_rows(const FdTailParams &x, const float *records, in
       float m, l;
       float4 a;
       load_state(0, m, l, a);
-      for (int r = 1; r < x.world; ++r) {
+      int r = 1;
+      for (; r + 7 <= x.world; r += 7) {   // the states of seven more ranks in flight together (eight GPUs: one batch)
+        float mr[7], lr[7];
+        float4 ar[7];
+#pragma unroll
+        for (int u = 0; u < 7; ++u) load_state(r + u, mr[u], lr[u], ar[u]);
+#pragma unroll
+        for (int u = 0; u < 7; ++u) fd_merge_right(m, l, a, mr[u], lr[u], ar[u]);
+      }
+      for (; r < x.world; ++r) {
         float m_right, l_right;
         float4 a_right;
         load_state(r, m_right, l_right, a_right);
