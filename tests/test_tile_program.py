@@ -599,7 +599,7 @@ def test_one_plan_against_the_live_cpu_replay(backend):
 def test_graph_replay_is_reused_and_agrees_with_the_single_stream_order(backend):
     # The first run captures the invocation (one stream per Tile, Direct-DTE transfers as event edges) into a CUDA
     # graph; later runs relaunch it. Doubling arg0 doubles every product exactly, so the second run's output must be
-    # exactly twice the first one's; the tensor-core policy (single stream, no graph) must pass the similarity gate.
+    # exactly twice the first one's.
     plan = "tensor-candidate-38"
     inputs = expected_tools.program_inputs()
     program = TileProgram(FIXTURE["plans"][plan], backend)
@@ -611,6 +611,37 @@ def test_graph_replay_is_reused_and_agrees_with_the_single_stream_order(backend)
     assert stats2["commands"] == stats1["commands"] and stats2["gpu_launches"] == stats1["gpu_launches"]
     (again,), _ = program.run(inputs)
     assert np.array_equal(again, first)
+
+
+@pytest.mark.gpu
+def test_tensor_core_policy_replays_concurrently_and_matches_its_single_stream_order(backend, oracle):
+    # Under the tensor-core GEMM policy the Tiles run side by side too (one stream per Tile in a captured graph of its
+    # own, compact operands staged in areas private to each Tile). Same kernels, same per-Tile order: the bits must equal
+    # the single-stream replay's, the relaunch must equal the first run, and the output passes the reference's gate.
+    import os, subprocess, sys
+    plan = "tensor-winner"
+    inputs = expected_tools.program_inputs()
+    program = TileProgram(FIXTURE["plans"][plan], backend)
+    (first,), stats1 = program.run(inputs, abi.GEMM_TENSOR)
+    (second,), stats2 = program.run(inputs, abi.GEMM_TENSOR)
+    assert np.array_equal(first, second) and stats1["gpu_launches"] == stats2["gpu_launches"]
+    want = (_as_torch(inputs[1]).float()[0].cuda() @ _as_torch(inputs[0]).float()[0].cuda()).bfloat16().cpu()
+    helpers.reference_gate(oracle, "bf16", first.reshape(-1), helpers.bits(want).reshape(-1))
+    (formal,), _ = program.run(inputs, abi.GEMM_FORMAL)                 # the other policy's graph lives beside it
+    assert hashlib.sha256(formal.tobytes()).hexdigest() == EXPECTED["plans"][plan]["sha256"]
+    (third,), _ = program.run(inputs, abi.GEMM_TENSOR)
+    assert np.array_equal(first, third)
+    code = ("import sys, hashlib; sys.path.insert(0, %r);"
+            "from tests.test_tile_program import FIXTURE, expected_tools;"
+            "from vibe_compiler_b200 import _abi as abi;"
+            "from vibe_compiler_b200.backend import B200TargetModelBackend as B;"
+            "from vibe_compiler_b200.tile_program import TileProgram;"
+            "(out,), stats = TileProgram(FIXTURE['plans']['tensor-winner'], B(0)).run(expected_tools.program_inputs(), abi.GEMM_TENSOR);"
+            "print(hashlib.sha256(out.tobytes()).hexdigest())") % str(ROOT)
+    result = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, WB200_REPLAY_GRAPH="0"), capture_output=True, text=True, timeout=300)
+    assert result.returncode == 0, result.stderr[-2000:]
+    assert result.stdout.strip().splitlines()[-1] == hashlib.sha256(first.tobytes()).hexdigest()
+    program.close()
 
 
 @pytest.mark.gpu

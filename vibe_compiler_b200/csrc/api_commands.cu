@@ -19,8 +19,11 @@ struct DeviceGemm {
 
 // Runs one GEMM command whose operands already sit on the device. `scratch_slot` is the first of
 // three backend staging slots the tensor path may use for compact operands.
+// `private_staging` (three areas of `private_each` bytes) replaces the backend slots when given: commands of different
+// Tiles that run side by side on streams of their own must not share the compact operands.
 wb200_status run_device_gemm(wb200_backend *backend, const DeviceGemm &g, int policy, size_t scratch_slot,
-                             cudaStream_t stream, const char **implementation) {
+                             cudaStream_t stream, const char **implementation, uint8_t *private_staging = nullptr,
+                             size_t private_each = 0) {
   const bool tensor_domain = policy == WB200_GEMM_TENSOR && !g.has_psum &&
                              (g.in_format == WB200_BF16 || g.in_format == WB200_F16);
   if (tensor_domain) {
@@ -39,9 +42,15 @@ wb200_status run_device_gemm(wb200_backend *backend, const DeviceGemm &g, int po
                                                 (static_cast<size_t>(g.m) * g.n * out_bytes) % 16 == 0);
     void *c_lhs, *c_rhs, *c_dst;
     wb200_status st;
-    if ((st = backend->buffer(scratch_slot, lhs_count * in_bytes, &c_lhs)) != WB200_OK) return st;
-    if ((st = backend->buffer(scratch_slot + 1, rhs_count * in_bytes, &c_rhs)) != WB200_OK) return st;
-    if ((st = backend->buffer(scratch_slot + 2, dst_count * out_bytes, &c_dst)) != WB200_OK) return st;
+    if (private_staging) {
+      if (lhs_count * in_bytes > private_each || rhs_count * in_bytes > private_each || dst_count * out_bytes > private_each)
+        return fail(WB200_ERR_LIMIT, "GEMM operand larger than the image's private staging area");
+      c_lhs = private_staging; c_rhs = private_staging + private_each; c_dst = private_staging + 2 * private_each;
+    } else {
+      if ((st = backend->buffer(scratch_slot, lhs_count * in_bytes, &c_lhs)) != WB200_OK) return st;
+      if ((st = backend->buffer(scratch_slot + 1, rhs_count * in_bytes, &c_rhs)) != WB200_OK) return st;
+      if ((st = backend->buffer(scratch_slot + 2, dst_count * out_bytes, &c_dst)) != WB200_OK) return st;
+    }
     probe.a = c_lhs; probe.b = c_rhs; probe.out = c_dst;
     if (batch_aligned && gemm_umma_supports(probe)) {
       if ((st = launch_unpack(g.lhs, static_cast<uint8_t *>(c_lhs), g.lhs_map, 2, stream)) != WB200_OK) return st;
@@ -548,7 +557,8 @@ wb200_status enqueue_image_gemm(wb200_spm_image *image, uint64_t lhs, uint64_t r
     return WB200_OK;
   }
   if (defer && deferred) return WB200_OK;   // tensor-core policy: not part of a run, *deferred stays false
-  return run_device_gemm(backend, g, effective_policy, 4, image->work_stream(), &implementation);
+  return run_device_gemm(backend, g, effective_policy, 4, image->work_stream(), &implementation, image->gemm_staging,
+                         static_cast<size_t>(image->bytes));
 }
 
 

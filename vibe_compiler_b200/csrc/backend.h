@@ -97,6 +97,7 @@ struct wb200_spm_image {
   uint8_t *device;
   cudaStream_t stream = nullptr;     // null: the backend stream
   uint8_t *staging = nullptr;        // private scratch of `bytes` bytes for in-place gather / scatter (null: a backend slot)
+  uint8_t *gemm_staging = nullptr;   // private scratch of 3 * `bytes` bytes for the tensor-core GEMM's compact operands (null: backend slots)
   cudaStream_t work_stream() const { return stream ? stream : backend->stream; }
 };
 

@@ -472,6 +472,29 @@ bool gemm_umma_supports(const GemmUmmaArgs &a) {
   return true;
 }
 
+namespace {
+using GemmKernel = void (*)(const CUtensorMap, const CUtensorMap, const GemmUmmaParams);
+const GemmKernel kernels[8] = {
+    gemm_umma_kernel<false, false, false>, gemm_umma_kernel<false, false, true>, gemm_umma_kernel<false, true, false>,
+    gemm_umma_kernel<false, true, true>,   gemm_umma_kernel<true, false, false>, gemm_umma_kernel<true, false, true>,
+    gemm_umma_kernel<true, true, false>,   gemm_umma_kernel<true, true, true>};
+const GemmKernel pair_kernels[8] = {
+    gemm_umma_pair_kernel<false, false, false>, gemm_umma_pair_kernel<false, false, true>, gemm_umma_pair_kernel<false, true, false>,
+    gemm_umma_pair_kernel<false, true, true>,   gemm_umma_pair_kernel<true, false, false>, gemm_umma_pair_kernel<true, false, true>,
+    gemm_umma_pair_kernel<true, true, false>,   gemm_umma_pair_kernel<true, true, true>};
+}  // namespace
+
+wb200_status gemm_umma_prepare() {
+  static PerDeviceOnce attributes;
+  return attributes.run([]() -> wb200_status {
+    for (GemmKernel kernel : kernels)
+      WB200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes)));
+    for (GemmKernel kernel : pair_kernels)
+      WB200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPairSmemBytes)));
+    return WB200_OK;
+  });
+}
+
 wb200_status launch_gemm_umma(const GemmUmmaArgs &a, int sm_count, int *device_status,
                               cudaStream_t stream) {
   if (!gemm_umma_supports(a)) return fail(WB200_ERR_UNSUPPORTED, "GEMM outside the tcgen05 kernel's domain");
@@ -508,24 +531,8 @@ wb200_status launch_gemm_umma(const GemmUmmaArgs &a, int sm_count, int *device_s
   static const int group_override = []() { const char *env = getenv("WB200_GEMM_GROUP_M"); return env ? atoi(env) : 0; }();
   p.group_m = group_override > 0 ? group_override : kGroupM;
 
-  using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const GemmUmmaParams);
-  static const Kernel kernels[8] = {
-      gemm_umma_kernel<false, false, false>, gemm_umma_kernel<false, false, true>, gemm_umma_kernel<false, true, false>,
-      gemm_umma_kernel<false, true, true>,   gemm_umma_kernel<true, false, false>, gemm_umma_kernel<true, false, true>,
-      gemm_umma_kernel<true, true, false>,   gemm_umma_kernel<true, true, true>};
-  static const Kernel pair_kernels[8] = {
-      gemm_umma_pair_kernel<false, false, false>, gemm_umma_pair_kernel<false, false, true>, gemm_umma_pair_kernel<false, true, false>,
-      gemm_umma_pair_kernel<false, true, true>,   gemm_umma_pair_kernel<true, false, false>, gemm_umma_pair_kernel<true, false, true>,
-      gemm_umma_pair_kernel<true, true, false>,   gemm_umma_pair_kernel<true, true, true>};
-  static PerDeviceOnce attributes;
-  st = attributes.run([]() -> wb200_status {
-    for (Kernel kernel : kernels)
-      WB200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes)));
-    for (Kernel kernel : pair_kernels)
-      WB200_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPairSmemBytes)));
-    return WB200_OK;
-  });
-  if (st != WB200_OK) return st;
+  wb200_status st_attributes = gemm_umma_prepare();
+  if (st_attributes != WB200_OK) return st_attributes;
   const int variant = (p.a_mn_major ? 4 : 0) | (p.b_mn_major ? 2 : 0) | (p.bf16 ? 1 : 0);
   if (use_pairs) {
     int clusters = sm_count / 2;

@@ -63,6 +63,9 @@ struct GemmUmmaArgs {
   void *out;
 };
 bool gemm_umma_supports(const GemmUmmaArgs &args);
+// Sets the kernels' per-device launch attributes (also done lazily by the first launch): call before a stream capture that
+// will contain tensor-core GEMM launches.
+wb200_status gemm_umma_prepare();
 wb200_status launch_gemm_umma(const GemmUmmaArgs &args, int sm_count, int *device_status,
                               cudaStream_t stream);
 

@@ -684,8 +684,9 @@ struct wb200_tile_program {
   std::vector<cudaStream_t> tile_streams;
   std::vector<cudaEvent_t> edge_events;
   size_t edge_events_used = 0;
-  cudaGraphExec_t graph = nullptr;
-  wb200_program_stats graph_stats{};
+  cudaGraphExec_t graph[2] = {nullptr, nullptr};   // one captured invocation per GEMM policy
+  wb200_program_stats graph_stats[2] = {};
+  std::vector<uint8_t *> gemm_staging;              // per Tile: compact operands of the tensor-core GEMM path (3 x scratch-pad size)
 
   // per-run state
   std::vector<TileState> state;
@@ -1505,9 +1506,22 @@ namespace {
 wb200_status capture_invocation(wb200_tile_program *program) {
   wb200_backend *backend = program->backend;
   cudaStream_t origin = backend->stream;
+  const uint32_t policy = program->gemm_policy;
+  if (policy == WB200_GEMM_TENSOR) {
+    // Nothing may allocate or set launch attributes while the streams are being captured: the Tiles' private areas for
+    // the compact GEMM operands (the backend's slots would be shared by Tiles that now run side by side) and the
+    // kernels' attributes come first.
+    if (program->gemm_staging.empty()) {
+      program->gemm_staging.assign(program->spm.size(), nullptr);
+      for (size_t t = 0; t < program->spm.size(); ++t) WB200_CUDA_CHECK(cudaMalloc(&program->gemm_staging[t], 3 * program->spm_bytes));
+    }
+    wb200_status prepared = gemm_umma_prepare();
+    if (prepared != WB200_OK) return prepared;
+  }
   for (size_t t = 0; t < program->spm.size(); ++t) {
     program->spm[t].stream = program->tile_streams[t];
     program->spm[t].staging = program->spm[t].device + program->spm_bytes;
+    program->spm[t].gemm_staging = policy == WB200_GEMM_TENSOR ? program->gemm_staging[t] : nullptr;
   }
   program->edge_events_used = 0;
   cudaEvent_t fork;
@@ -1534,10 +1548,10 @@ wb200_status capture_invocation(wb200_tile_program *program) {
     cudaGetLastError();
     return st;
   }
-  err = cudaGraphInstantiate(&program->graph, graph, 0);
+  err = cudaGraphInstantiate(&program->graph[policy], graph, 0);
   cudaGraphDestroy(graph);
-  if (err != cudaSuccess) { program->graph = nullptr; return fail(WB200_ERR_CUDA, std::string("instantiating the invocation graph: ") + cudaGetErrorString(err)); }
-  program->graph_stats = program->stats;
+  if (err != cudaSuccess) { program->graph[policy] = nullptr; return fail(WB200_ERR_CUDA, std::string("instantiating the invocation graph: ") + cudaGetErrorString(err)); }
+  program->graph_stats[policy] = program->stats;
   return WB200_OK;
 }
 
@@ -1613,7 +1627,10 @@ void wb200_tile_program_destroy(wb200_tile_program *program) {
       if (image.device) cudaFree(image.device);
     if (program->begin) cudaEventDestroy(program->begin);
     if (program->end) cudaEventDestroy(program->end);
-    if (program->graph) cudaGraphExecDestroy(program->graph);
+    for (cudaGraphExec_t graph : program->graph)
+      if (graph) cudaGraphExecDestroy(graph);
+    for (uint8_t *staging : program->gemm_staging)
+      if (staging) cudaFree(staging);
     for (cudaStream_t tile_stream : program->tile_streams) cudaStreamDestroy(tile_stream);
     for (cudaEvent_t event : program->edge_events) cudaEventDestroy(event);
   }
@@ -1695,20 +1712,21 @@ wb200_status wb200_tile_program_run(wb200_tile_program *program, const void *con
   program->execute = true;
   program->gemm_policy = gemm_policy;
   program->trace = nullptr;
-  // The bit-exact policy replays concurrently: the tensor-core GEMM path stages operands in backend slots that the
-  // Tiles would share, so it keeps the single-stream order. WB200_REPLAY_GRAPH=0 forces the single stream.
+  // Both GEMM policies replay concurrently (one stream per Tile inside a captured graph, one graph per policy); the
+  // tensor-core path stages its compact operands in areas private to each Tile. WB200_REPLAY_GRAPH=0 forces the single
+  // stream, where the backend's shared slots serve.
   static const bool graph_enabled = [] { const char *env = getenv("WB200_REPLAY_GRAPH"); return !(env && env[0] == '0'); }();
-  const bool concurrent = graph_enabled && gemm_policy == WB200_GEMM_FORMAL && !program->tile_streams.empty();
-  if (concurrent && !program->graph && (st = capture_invocation(program)) != WB200_OK) return st;
+  const bool concurrent = graph_enabled && !program->tile_streams.empty();
+  if (concurrent && !program->graph[gemm_policy] && (st = capture_invocation(program)) != WB200_OK) return st;
   WB200_CUDA_CHECK(cudaMemsetAsync(program->numeric_words, 0, 8, stream));
   WB200_CUDA_CHECK(cudaMemsetAsync(program->numeric_words + 2, 0xff, 8, stream));
   WB200_CUDA_CHECK(cudaEventRecord(program->begin, stream));
   if (concurrent) {
-    WB200_CUDA_CHECK(cudaGraphLaunch(program->graph, stream));
-    program->stats = program->graph_stats;
+    WB200_CUDA_CHECK(cudaGraphLaunch(program->graph[gemm_policy], stream));
+    program->stats = program->graph_stats[gemm_policy];
     backend->launches += program->stats.gpu_launches;
   } else {
-    for (wb200_spm_image &image : program->spm) { image.stream = nullptr; image.staging = nullptr; }
+    for (wb200_spm_image &image : program->spm) { image.stream = nullptr; image.staging = nullptr; image.gemm_staging = nullptr; }
     st = run_all_tiles(program);
     if (st != WB200_OK) { cudaStreamSynchronize(stream); return st; }
   }

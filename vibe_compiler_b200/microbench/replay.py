@@ -21,6 +21,7 @@ from pathlib import Path
 
 import numpy as np
 
+from .. import _abi as abi
 from ..backend import B200TargetModelBackend
 from ..tile_program import TileProgram
 
@@ -29,6 +30,8 @@ def main(argv=None) -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--plan", default="", help="only the plans whose name contains this text")
     parser.add_argument("--runs", type=int, default=5)
+    parser.add_argument("--gemm-policy", choices=["formal", "tensor"], default="formal",
+                        help="bit-exact k-ascending FMA chains, or the tcgen05 kernel on unpacked operands (f32 accumulation, one rounding)")
     parser.add_argument("--module", default="", help="one Tile's .ll module instead of a fixture of plans")
     parser.add_argument("--spm-bytes", type=int, default=0, help="scratch-pad size for --module (default: the library's)")
     parser.add_argument("--fixture", default="",
@@ -39,6 +42,7 @@ def main(argv=None) -> int:
         parser.error("give --fixture or --module")
     backend = B200TargetModelBackend(0)
     rng = np.random.default_rng(20260803)
+    policy = abi.GEMM_TENSOR if args.gemm_policy == "tensor" else abi.GEMM_FORMAL
     if args.module:
         text = Path(args.module).read_text()
         program = TileProgram([text], backend, **({"spm_bytes": args.spm_bytes} if args.spm_bytes else {}))
@@ -60,9 +64,9 @@ def main(argv=None) -> int:
         inputs = [rng.integers(0x3c00, 0x4000, size=t.shape, dtype=np.uint16) for t in program.inputs]   # bf16 values in [0.0078, 2)
         times, stats = [], None
         for _ in range(max(2, args.runs)):
-            _, stats = program.run(inputs)
+            _, stats = program.run(inputs, policy)
             times.append(stats["device_ms"])
-        print(json.dumps({"plan": plan, "commands": stats["commands"], "gemm_commands": stats["gemm_commands"],
+        print(json.dumps({"plan": plan, "gemm_policy": args.gemm_policy, "commands": stats["commands"], "gemm_commands": stats["gemm_commands"],
                           "movement_commands": stats["movement_commands"], "gpu_launches": stats["gpu_launches"],
                           "device_ms_first": round(times[0], 3), "device_ms": round(statistics.median(times[1:]), 3)}), flush=True)
         program.close()
