@@ -644,6 +644,57 @@ def test_tensor_core_policy_replays_concurrently_and_matches_its_single_stream_o
     program.close()
 
 
+# Two Tiles, each one 256 x 256 x 256 bf16 GEMM without a partial sum (the form the tensor-core policy takes to the
+# tcgen05 kernel; every GEMM of the shipped plans carries a partial sum and stays on the bit-exact kernel under either
+# policy). The operands are copied flat into the scratch-pad, whose Cx reading permutes them: still a matrix product.
+def _two_tile_gemm_modules():
+    body = """
+  call void @wafer_tx81_rdma(i64 %0, i64 0, i32 131072, i32 131072, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 3, i32 0)
+  call void @wafer_tx81_rdma(i64 %1, i64 131072, i32 131072, i32 131072, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 3, i32 0)
+  call void @wafer_tx81_gemm(i64 0, i64 131072, i64 262144, i64 0, i32 256, i32 256, i32 256, i32 1, i32 3, i32 3, i32 13, i32 0)
+  call void @wafer_tx81_wdma(i64 262144, i64 %2, i32 131072, i32 131072, i32 0, i32 0, i32 0, i32 1, i32 1, i32 1, i32 3, i32 0)
+  ret void
+"""
+    def rows(first_input, output):
+        matrix = '!"", !"bf16", !"tensor", i64 131072, i64 65536'
+        return [f'!{{i64 0, !"external-input", i64 {first_input}, {matrix}, !"read-only", i64 256, i64 256, i64 0}}',
+                f'!{{i64 1, !"external-input", i64 {first_input + 1}, {matrix}, !"read-only", i64 256, i64 256, i64 0}}',
+                f'!{{i64 2, !"external-output", i64 {output}, {matrix}, !"write-only", i64 256, i64 256, i64 0}}']
+    return [_module(body, arguments="i64 %0, i64 %1, i64 %2", rows=rows(0, 0), tile=0),
+            _module(body, arguments="i64 %0, i64 %1, i64 %2", rows=rows(2, 1), tile=1)]
+
+
+def _two_tile_gemm_inputs():
+    rng = np.random.default_rng(5)
+    return [(rng.uniform(-1, 1, (256, 256)).astype(np.float32).view(np.uint32) >> 16).astype(np.uint16) for _ in range(4)]
+
+
+@pytest.mark.gpu
+def test_tensor_core_gemms_of_two_tiles_run_side_by_side(backend):
+    import os, subprocess, sys
+    program = TileProgram(_two_tile_gemm_modules(), backend)
+    inputs = _two_tile_gemm_inputs()
+    formal, stats_formal = program.run(inputs, abi.GEMM_FORMAL)
+    first, stats1 = program.run(inputs, abi.GEMM_TENSOR)        # captures the tensor-policy graph
+    second, stats2 = program.run(inputs, abi.GEMM_TENSOR)       # relaunches it
+    assert stats_formal["gpu_launches"] == 8 and stats1["gpu_launches"] == stats2["gpu_launches"] == 14   # + 2 unpacks and a pack per GEMM
+    for tile in range(2):
+        assert np.array_equal(first[tile], second[tile])
+        want, got = _as_torch(formal[tile]).float(), _as_torch(first[tile]).float()
+        assert float((got - want).abs().max() / want.abs().max()) <= 1e-2        # f32 accumulation, one rounding, another order
+    code = ("import sys, hashlib; sys.path.insert(0, %r);"
+            "from tests.test_tile_program import _two_tile_gemm_modules, _two_tile_gemm_inputs;"
+            "from vibe_compiler_b200 import _abi as abi;"
+            "from vibe_compiler_b200.backend import B200TargetModelBackend as B;"
+            "from vibe_compiler_b200.tile_program import TileProgram;"
+            "outs, stats = TileProgram(_two_tile_gemm_modules(), B(0)).run(_two_tile_gemm_inputs(), abi.GEMM_TENSOR);"
+            "print(hashlib.sha256(b''.join(o.tobytes() for o in outs)).hexdigest())") % str(ROOT)
+    result = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, WB200_REPLAY_GRAPH="0"), capture_output=True, text=True, timeout=300)
+    assert result.returncode == 0, result.stderr[-2000:]
+    assert result.stdout.strip().splitlines()[-1] == hashlib.sha256(b"".join(o.tobytes() for o in first)).hexdigest()
+    program.close()
+
+
 @pytest.mark.gpu
 def test_single_stream_replay_matches_the_graph_replay():
     import os, subprocess, sys
